@@ -1,0 +1,456 @@
+// Implementation of include/ainfer_cuda.h over the CUDA runtime: one stream as
+// the execution queue, CUDA graphs as recorded command lists. There is no CPU
+// fallback: without a usable GPU ainfer_device_open fails.
+#include "../../../include/ainfer_cuda.h"
+
+#include <cuda_runtime.h>
+#include <time.h>
+
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "../kernels/registry.h"
+
+namespace ainfer {
+
+static std::vector<KernelDesc> &registry() {
+  static std::vector<KernelDesc> r;
+  return r;
+}
+void register_kernel(const KernelDesc &d) { registry().push_back(d); }
+int kernel_count() { return (int)registry().size(); }
+const KernelDesc *kernel_at(int i) {
+  return i >= 0 && i < kernel_count() ? &registry()[i] : nullptr;
+}
+const KernelDesc *kernel_find(const char *name) {
+  for (auto &d : registry())
+    if (std::strcmp(d.name, name) == 0) return &d;
+  return nullptr;
+}
+
+}  // namespace ainfer
+
+using namespace ainfer;
+
+struct ainfer_device_s {
+  int ordinal = 0;
+  cudaStream_t stream = nullptr;
+  std::string err;
+  uint64_t launches = 0;
+  void *flush_buf = nullptr;
+  size_t flush_bytes = 0;
+  int sm_count = 0;
+};
+struct ainfer_kernel_s {
+  ainfer_device_t dev;
+  const KernelDesc *desc;
+  std::vector<unsigned char> args;
+  std::vector<bool> set;
+};
+struct ainfer_list_s {
+  ainfer_device_t dev;
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  cudaGraphNode_t last = nullptr;
+  bool has_last = false;
+  bool closed = false;
+  uint32_t launches = 0;
+};
+struct ainfer_event_s {
+  ainfer_device_t dev;
+  cudaEvent_t ev;
+};
+
+static thread_local std::string g_open_err;
+
+static int fail(ainfer_device_t dev, int code, const std::string &msg) {
+  if (dev) dev->err = msg;
+  else g_open_err = msg;
+  return code;
+}
+#define CU(dev, expr)                                                                         \
+  do {                                                                                        \
+    cudaError_t _e = (expr);                                                                  \
+    if (_e != cudaSuccess) {                                                                  \
+      char _b[512];                                                                           \
+      std::snprintf(_b, sizeof _b, "CUDA error %d (%s) at %s:%d (%s)", (int)_e,               \
+                    cudaGetErrorString(_e), __FILE__, __LINE__, #expr);                       \
+      return fail(dev, _e == cudaErrorMemoryAllocation ? AINFER_ERR_OOM : AINFER_ERR_DEVICE,  \
+                  _b);                                                                        \
+    }                                                                                         \
+  } while (0)
+
+extern "C" {
+
+int ainfer_device_open(int ordinal, ainfer_device_t *out) {
+  if (!out) return fail(nullptr, AINFER_ERR_INVALID, "null out pointer");
+  *out = nullptr;
+  int n = 0;
+  cudaError_t e = cudaGetDeviceCount(&n);
+  if (e != cudaSuccess || n == 0) {
+    cudaGetLastError();
+    return fail(nullptr, AINFER_ERR_NO_DEVICE,
+                std::string("no CUDA device available (") +
+                    (e != cudaSuccess ? cudaGetErrorString(e) : "device count is 0") +
+                    "); this library has no CPU fallback");
+  }
+  if (ordinal < 0 || ordinal >= n) return fail(nullptr, AINFER_ERR_INVALID, "bad device ordinal");
+  ainfer_device_t d = new ainfer_device_s;
+  d->ordinal = ordinal;
+  CU(nullptr, cudaSetDevice(ordinal));
+  cudaDeviceProp pr;
+  CU(nullptr, cudaGetDeviceProperties(&pr, ordinal));
+  d->sm_count = pr.multiProcessorCount;
+  if (pr.major < 10) {
+    delete d;
+    return fail(nullptr, AINFER_ERR_NO_DEVICE,
+                "device is not sm_100 class: kernels are built for sm_100a only");
+  }
+  CU(nullptr, cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking));
+  *out = d;
+  return AINFER_OK;
+}
+
+int ainfer_device_close(ainfer_device_t dev) {
+  if (!dev) return AINFER_ERR_INVALID;
+  cudaSetDevice(dev->ordinal);
+  cudaStreamSynchronize(dev->stream);
+  if (dev->flush_buf) cudaFree(dev->flush_buf);
+  cudaStreamDestroy(dev->stream);
+  delete dev;
+  return AINFER_OK;
+}
+
+int ainfer_device_get_info(ainfer_device_t dev, ainfer_device_info *info) {
+  if (!dev || !info) return AINFER_ERR_INVALID;
+  cudaDeviceProp pr;
+  CU(dev, cudaGetDeviceProperties(&pr, dev->ordinal));
+  std::memset(info, 0, sizeof *info);
+  std::snprintf(info->name, sizeof info->name, "%s", pr.name);
+  info->sm_count = pr.multiProcessorCount;
+  info->cc_major = pr.major;
+  info->cc_minor = pr.minor;
+  info->l2_bytes_mb = pr.l2CacheSize >> 20;
+  size_t fr = 0, tot = 0;
+  CU(dev, cudaSetDevice(dev->ordinal));
+  CU(dev, cudaMemGetInfo(&fr, &tot));
+  info->total_mem = tot;
+  info->free_mem = fr;
+  return AINFER_OK;
+}
+
+const char *ainfer_last_error(ainfer_device_t dev) {
+  return dev ? dev->err.c_str() : g_open_err.c_str();
+}
+
+int ainfer_mem_alloc(ainfer_device_t dev, size_t bytes, size_t align, void **out) {
+  if (!dev || !out) return AINFER_ERR_INVALID;
+  if (align > 4096 || (align & (align - 1))) return fail(dev, AINFER_ERR_INVALID, "bad alignment");
+  CU(dev, cudaSetDevice(dev->ordinal));
+  CU(dev, cudaMalloc(out, bytes ? bytes : 1));  // cudaMalloc returns >= 256-byte aligned blocks
+  if (align > 256 && ((uintptr_t)*out & (align - 1))) {
+    cudaFree(*out);
+    *out = nullptr;
+    return fail(dev, AINFER_ERR_INVALID, "allocator returned a block below the asked alignment");
+  }
+  return AINFER_OK;
+}
+int ainfer_mem_free(ainfer_device_t dev, void *ptr) {
+  if (!dev) return AINFER_ERR_INVALID;
+  CU(dev, cudaFree(ptr));
+  return AINFER_OK;
+}
+int ainfer_memcpy_h2d(ainfer_device_t dev, void *dst, const void *src, size_t bytes) {
+  if (!dev) return AINFER_ERR_INVALID;
+  CU(dev, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, dev->stream));
+  CU(dev, cudaStreamSynchronize(dev->stream));
+  return AINFER_OK;
+}
+int ainfer_memcpy_d2h(ainfer_device_t dev, void *dst, const void *src, size_t bytes) {
+  if (!dev) return AINFER_ERR_INVALID;
+  CU(dev, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, dev->stream));
+  CU(dev, cudaStreamSynchronize(dev->stream));
+  return AINFER_OK;
+}
+int ainfer_memcpy_d2d(ainfer_device_t dev, void *dst, const void *src, size_t bytes) {
+  if (!dev) return AINFER_ERR_INVALID;
+  CU(dev, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, dev->stream));
+  CU(dev, cudaStreamSynchronize(dev->stream));
+  return AINFER_OK;
+}
+int ainfer_mem_fill(ainfer_device_t dev, void *dst, int byte_value, size_t bytes) {
+  if (!dev) return AINFER_ERR_INVALID;
+  CU(dev, cudaMemsetAsync(dst, byte_value, bytes, dev->stream));
+  CU(dev, cudaStreamSynchronize(dev->stream));
+  return AINFER_OK;
+}
+int ainfer_host_alloc(ainfer_device_t dev, size_t bytes, void **out) {
+  if (!dev || !out) return AINFER_ERR_INVALID;
+  CU(dev, cudaMallocHost(out, bytes ? bytes : 1));
+  return AINFER_OK;
+}
+int ainfer_host_free(ainfer_device_t dev, void *ptr) {
+  if (!dev) return AINFER_ERR_INVALID;
+  CU(dev, cudaFreeHost(ptr));
+  return AINFER_OK;
+}
+int ainfer_memcpy_h2d_async(ainfer_device_t dev, void *dst, const void *src, size_t bytes) {
+  if (!dev) return AINFER_ERR_INVALID;
+  CU(dev, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, dev->stream));
+  return AINFER_OK;
+}
+int ainfer_memcpy_d2h_async(ainfer_device_t dev, void *dst, const void *src, size_t bytes) {
+  if (!dev) return AINFER_ERR_INVALID;
+  CU(dev, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, dev->stream));
+  return AINFER_OK;
+}
+
+int ainfer_kernel_count(void) { return kernel_count(); }
+const char *ainfer_kernel_name(int index) {
+  const KernelDesc *d = kernel_at(index);
+  return d ? d->name : nullptr;
+}
+int ainfer_kernel_get(ainfer_device_t dev, const char *name, ainfer_kernel_t *out) {
+  if (!dev || !name || !out) return AINFER_ERR_INVALID;
+  const KernelDesc *d = kernel_find(name);
+  if (!d) return fail(dev, AINFER_ERR_NOT_FOUND, std::string("entry ") + name + " not found");
+  ainfer_kernel_t k = new ainfer_kernel_s;
+  k->dev = dev;
+  k->desc = d;
+  k->args.assign(d->args_size, 0);
+  k->set.assign(d->nfields, false);
+  *out = k;
+  return AINFER_OK;
+}
+int ainfer_kernel_release(ainfer_kernel_t k) {
+  if (!k) return AINFER_ERR_INVALID;
+  delete k;
+  return AINFER_OK;
+}
+int ainfer_kernel_query(ainfer_kernel_t k, int *arg_count, int *group_threads, int *items) {
+  if (!k) return AINFER_ERR_INVALID;
+  if (arg_count) *arg_count = k->desc->nfields;
+  if (group_threads) *group_threads = k->desc->threads;
+  if (items) *items = k->desc->items_per_group;
+  return AINFER_OK;
+}
+int ainfer_kernel_arg_size(ainfer_kernel_t k, uint32_t index, size_t *size) {
+  if (!k || !size || index >= (uint32_t)k->desc->nfields) return AINFER_ERR_INVALID;
+  *size = k->desc->fields[index].size;
+  return AINFER_OK;
+}
+int ainfer_kernel_set_arg(ainfer_kernel_t k, uint32_t index, size_t size, const void *value) {
+  if (!k) return AINFER_ERR_INVALID;
+  if (index >= (uint32_t)k->desc->nfields)
+    return fail(k->dev, AINFER_ERR_INVALID, std::string("setArg index out of range for ") + k->desc->name);
+  const ArgField &f = k->desc->fields[index];
+  if (size != f.size || !value) {
+    char b[160];
+    std::snprintf(b, sizeof b, "setArg %u of %s: size %zu, expected %u", index, k->desc->name, size,
+                  f.size);
+    return fail(k->dev, AINFER_ERR_INVALID, b);
+  }
+  std::memcpy(k->args.data() + f.offset, value, size);
+  k->set[index] = true;
+  return AINFER_OK;
+}
+
+static int check_launch(ainfer_kernel_t k, uint32_t groups, uint32_t *smem) {
+  for (int i = 0; i < k->desc->nfields; ++i)
+    if (!k->set[i]) {
+      char b[160];
+      std::snprintf(b, sizeof b, "launch of %s with argument %d never set", k->desc->name, i);
+      return fail(k->dev, AINFER_ERR_UNSET_ARG, b);
+    }
+  if (groups == 0) return fail(k->dev, AINFER_ERR_INVALID, "group count 0");
+  *smem = k->desc->smem_fn ? k->desc->smem_fn(k->args.data()) : k->desc->smem_bytes;
+  if (*smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(k->desc->fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)*smem);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return fail(k->dev, AINFER_ERR_INVALID, std::string("shared memory request too large for ") + k->desc->name);
+    }
+  }
+  return AINFER_OK;
+}
+
+int ainfer_kernel_launch(ainfer_device_t dev, ainfer_kernel_t k, uint32_t groups) {
+  if (!dev || !k) return AINFER_ERR_INVALID;
+  uint32_t smem = 0;
+  int r = check_launch(k, groups, &smem);
+  if (r) return r;
+  void *params[1] = {k->args.data()};
+  CU(dev, cudaLaunchKernel(k->desc->fn, dim3(groups), dim3(k->desc->threads), params, smem, dev->stream));
+  dev->launches += 1;
+  return AINFER_OK;
+}
+
+int ainfer_list_create(ainfer_device_t dev, ainfer_list_t *out) {
+  if (!dev || !out) return AINFER_ERR_INVALID;
+  ainfer_list_t l = new ainfer_list_s;
+  l->dev = dev;
+  cudaError_t e = cudaGraphCreate(&l->graph, 0);
+  if (e != cudaSuccess) {
+    delete l;
+    return fail(dev, AINFER_ERR_DEVICE, std::string("list create failed: ") + cudaGetErrorString(e));
+  }
+  *out = l;
+  return AINFER_OK;
+}
+static const cudaGraphNode_t *deps(ainfer_list_t l) { return l->has_last ? &l->last : nullptr; }
+
+int ainfer_list_append_launch(ainfer_list_t l, ainfer_kernel_t k, uint32_t groups) {
+  if (!l || !k) return AINFER_ERR_INVALID;
+  if (l->closed) return fail(l->dev, AINFER_ERR_INVALID, "append to a closed list");
+  uint32_t smem = 0;
+  int r = check_launch(k, groups, &smem);
+  if (r) return r;
+  void *params[1] = {k->args.data()};
+  cudaKernelNodeParams np;
+  std::memset(&np, 0, sizeof np);
+  np.func = const_cast<void *>(k->desc->fn);
+  np.gridDim = dim3(groups);
+  np.blockDim = dim3(k->desc->threads);
+  np.sharedMemBytes = smem;
+  np.kernelParams = params;
+  cudaGraphNode_t node;
+  CU(l->dev, cudaGraphAddKernelNode(&node, l->graph, deps(l), l->has_last ? 1 : 0, &np));
+  l->last = node;
+  l->has_last = true;
+  l->launches += 1;
+  return AINFER_OK;
+}
+int ainfer_list_append_memcpy(ainfer_list_t l, void *dst, const void *src, size_t bytes) {
+  if (!l) return AINFER_ERR_INVALID;
+  if (l->closed) return fail(l->dev, AINFER_ERR_INVALID, "append to a closed list");
+  cudaGraphNode_t node;
+  CU(l->dev, cudaGraphAddMemcpyNode1D(&node, l->graph, deps(l), l->has_last ? 1 : 0, dst, src, bytes,
+                                      cudaMemcpyDeviceToDevice));
+  l->last = node;
+  l->has_last = true;
+  return AINFER_OK;
+}
+int ainfer_list_append_fill(ainfer_list_t l, void *dst, int byte_value, size_t bytes) {
+  if (!l) return AINFER_ERR_INVALID;
+  if (l->closed) return fail(l->dev, AINFER_ERR_INVALID, "append to a closed list");
+  cudaMemsetParams mp;
+  std::memset(&mp, 0, sizeof mp);
+  mp.dst = dst;
+  mp.value = (unsigned)byte_value & 0xFF;
+  mp.elementSize = 1;
+  mp.width = bytes;
+  mp.height = 1;
+  mp.pitch = bytes;
+  cudaGraphNode_t node;
+  CU(l->dev, cudaGraphAddMemsetNode(&node, l->graph, deps(l), l->has_last ? 1 : 0, &mp));
+  l->last = node;
+  l->has_last = true;
+  return AINFER_OK;
+}
+int ainfer_list_close(ainfer_list_t l) {
+  if (!l) return AINFER_ERR_INVALID;
+  if (l->closed) return fail(l->dev, AINFER_ERR_INVALID, "list already closed");
+  CU(l->dev, cudaGraphInstantiate(&l->exec, l->graph, 0));
+  l->closed = true;
+  return AINFER_OK;
+}
+int ainfer_list_launch_count(ainfer_list_t l, uint32_t *launches) {
+  if (!l || !launches) return AINFER_ERR_INVALID;
+  *launches = l->launches;
+  return AINFER_OK;
+}
+int ainfer_list_destroy(ainfer_list_t l) {
+  if (!l) return AINFER_ERR_INVALID;
+  if (l->exec) cudaGraphExecDestroy(l->exec);
+  if (l->graph) cudaGraphDestroy(l->graph);
+  delete l;
+  return AINFER_OK;
+}
+int ainfer_list_execute(ainfer_list_t l) {
+  if (!l) return AINFER_ERR_INVALID;
+  if (!l->closed) return fail(l->dev, AINFER_ERR_INVALID, "execute of a list that is not closed");
+  CU(l->dev, cudaGraphLaunch(l->exec, l->dev->stream));
+  l->dev->launches += l->launches;
+  return AINFER_OK;
+}
+
+int ainfer_sync(ainfer_device_t dev, uint64_t timeout_ns) {
+  if (!dev) return AINFER_ERR_INVALID;
+  if (timeout_ns == UINT64_MAX) {
+    CU(dev, cudaStreamSynchronize(dev->stream));
+    return AINFER_OK;
+  }
+  struct timespec t0, t;
+  clock_gettime(CLOCK_MONOTONIC, &t0);
+  for (;;) {
+    cudaError_t e = cudaStreamQuery(dev->stream);
+    if (e == cudaSuccess) return AINFER_OK;
+    if (e != cudaErrorNotReady) CU(dev, e);
+    clock_gettime(CLOCK_MONOTONIC, &t);
+    uint64_t el = (uint64_t)(t.tv_sec - t0.tv_sec) * 1000000000ull + (uint64_t)(t.tv_nsec - t0.tv_nsec);
+    if (el >= timeout_ns) return fail(dev, AINFER_ERR_TIMEOUT, "sync timed out");
+    struct timespec nap = {0, 20000};
+    nanosleep(&nap, nullptr);
+  }
+}
+
+int ainfer_control_write(ainfer_device_t dev, void *dctrl, const ainfer_control *c) {
+  return ainfer_memcpy_h2d(dev, dctrl, c, sizeof *c);
+}
+int ainfer_control_write_async(ainfer_device_t dev, void *dctrl, const ainfer_control *c) {
+  return ainfer_memcpy_h2d_async(dev, dctrl, c, sizeof *c);
+}
+
+int ainfer_event_create(ainfer_device_t dev, ainfer_event_t *out) {
+  if (!dev || !out) return AINFER_ERR_INVALID;
+  ainfer_event_t e = new ainfer_event_s;
+  e->dev = dev;
+  cudaError_t r = cudaEventCreate(&e->ev);
+  if (r != cudaSuccess) {
+    delete e;
+    return fail(dev, AINFER_ERR_DEVICE, cudaGetErrorString(r));
+  }
+  *out = e;
+  return AINFER_OK;
+}
+int ainfer_event_record(ainfer_event_t ev) {
+  if (!ev) return AINFER_ERR_INVALID;
+  CU(ev->dev, cudaEventRecord(ev->ev, ev->dev->stream));
+  return AINFER_OK;
+}
+int ainfer_event_elapsed_ms(ainfer_event_t start, ainfer_event_t stop, float *ms) {
+  if (!start || !stop || !ms) return AINFER_ERR_INVALID;
+  CU(stop->dev, cudaEventSynchronize(stop->ev));
+  CU(stop->dev, cudaEventElapsedTime(ms, start->ev, stop->ev));
+  return AINFER_OK;
+}
+int ainfer_event_destroy(ainfer_event_t ev) {
+  if (!ev) return AINFER_ERR_INVALID;
+  cudaEventDestroy(ev->ev);
+  delete ev;
+  return AINFER_OK;
+}
+int ainfer_launch_counter(ainfer_device_t dev, uint64_t *launches) {
+  if (!dev || !launches) return AINFER_ERR_INVALID;
+  *launches = dev->launches;
+  return AINFER_OK;
+}
+int ainfer_flush_l2(ainfer_device_t dev) {
+  if (!dev) return AINFER_ERR_INVALID;
+  if (!dev->flush_buf) {
+    dev->flush_bytes = (size_t)256 << 20;
+    CU(dev, cudaMalloc(&dev->flush_buf, dev->flush_bytes));
+  }
+  CU(dev, cudaMemsetAsync(dev->flush_buf, 0, dev->flush_bytes, dev->stream));
+  return AINFER_OK;
+}
+int ainfer_device_stream(ainfer_device_t dev, void **stream) {
+  if (!dev || !stream) return AINFER_ERR_INVALID;
+  *stream = (void *)dev->stream;
+  return AINFER_OK;
+}
+
+}  // extern "C"

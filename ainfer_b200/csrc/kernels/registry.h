@@ -1,0 +1,48 @@
+// Kernel registry: every device kernel is a __global__ function taking one
+// POD argument struct by value. The registry records the struct's member
+// offsets so that arguments can be set by index in member order, the
+// convention of the reference's raw Level Zero loop
+// (tools/decode/decode_l0.cpp:474-480: zeKernelSetArgumentValue by index).
+#pragma once
+#include <cstddef>
+#include <cstdint>
+
+namespace ainfer {
+
+struct ArgField {
+  uint32_t offset, size;
+};
+
+struct KernelDesc {
+  const char *name;
+  const void *fn;
+  uint32_t args_size;
+  const ArgField *fields;
+  int nfields;
+  int threads;          // threads per group (fixed)
+  int items_per_group;  // work items one group covers; 0 = strides over any group count
+  uint32_t smem_bytes;  // fixed dynamic shared memory (0 if none / static only)
+  // optional: dynamic shared memory as a function of the argument bytes
+  uint32_t (*smem_fn)(const void *args);
+};
+
+void register_kernel(const KernelDesc &d);
+int kernel_count();
+const KernelDesc *kernel_at(int i);
+const KernelDesc *kernel_find(const char *name);
+
+struct Registrar {
+  explicit Registrar(const KernelDesc &d) { register_kernel(d); }
+};
+
+}  // namespace ainfer
+
+#define AINFER_ARG(T, f) \
+  { (uint32_t)offsetof(T, f), (uint32_t)sizeof(((T *)0)->f) }
+
+// AINFER_REGISTER(Name, ArgsStruct, threads, items_per_group, smem_bytes, smem_fn, fields...)
+#define AINFER_REGISTER(NAME, T, THREADS, ITEMS, SMEM, SMEMFN, ...)                          \
+  static const ::ainfer::ArgField NAME##_fields[] = {__VA_ARGS__};                           \
+  static ::ainfer::Registrar NAME##_registrar(::ainfer::KernelDesc{                          \
+      #NAME, (const void *)NAME, (uint32_t)sizeof(T), NAME##_fields,                         \
+      (int)(sizeof(NAME##_fields) / sizeof(NAME##_fields[0])), THREADS, ITEMS, SMEM, SMEMFN})
