@@ -4,31 +4,10 @@
 // the recorded layer lists (tools/decode/decode_l0.cpp:611-621,630-638,663):
 // ResAddF, SsmConv, BetaG. One launch covers several matrices that share the
 // same quantised activation (e.g. in_proj_qkv, in_proj_z, in_proj_b, in_proj_a).
+#include "../common/tables.h"
 #include "gemv_core.cuh"
 
 namespace ainfer {
-
-enum GemvEpilogue {
-  EPI_STORE = 0,     // Y[m][n] = acc
-  EPI_RESADD = 1,    // Y[m][n] = e0[m][n] + acc                     (ResAddF, kernels.cpp:646-652)
-  EPI_CONV_SILU = 2, // depthwise conv k=4 + SiLU + history shift     (SsmConv, kernels.cpp:322-338)
-  EPI_BETA = 3,      // Y[n] = sigmoid(acc)                           (BetaG, kernels.cpp:612)
-  EPI_GDECAY = 4     // Y[n] = -exp(A_log[n]) * softplus(acc + dt[n]) (BetaG, kernels.cpp:613-615)
-};
-
-// One entry of the device-resident matrix table of a launch.
-struct GemvMat {
-  const uint8_t *P;    // packed nibbles [N][K/2]
-  const uint16_t *S;   // bf16 scales [N][K/128]
-  float *Y;            // output
-  const float *e0;     // EPI_RESADD: residual; CONV: weights [N][4]; GDECAY: A_log
-  float *e1;           // CONV: history [N][3] (updated in place)
-  const float *e2;     // GDECAY: dt_bias
-  int32_t row_start;   // first global row of this matrix in the launch
-  int32_t N;
-  int32_t epi;
-  int32_t ldy;         // row stride of Y / e0 between batch entries (elements)
-};
 
 struct Int4GemvA8Args {
   const GemvMat *mats;

@@ -3,17 +3,10 @@
 // quantise, down GEMV, ResAddF: tools/decode/decode_l0.cpp:666-674); each
 // expert here is that same MLP, the routing around it has no reference
 // counterpart and follows the arithmetic stated with each kernel.
+#include "../common/tables.h"
 #include "gemv_core.cuh"
 
 namespace ainfer {
-
-// Device-resident pointers of one expert's three matrices. A layer's table has
-// n_experts entries followed by the shared expert.
-struct ExpertW {
-  const uint8_t *gP; const uint16_t *gS;   // gate_proj [I][H]
-  const uint8_t *uP; const uint16_t *uS;   // up_proj   [I][H]
-  const uint8_t *dP; const uint16_t *dS;   // down_proj [H][I]
-};
 
 // ----------------------------------------------------------- RouterTopK ---
 // logits[e] = sum_k bf16(Wr[e][k]) * hn[k]: 32 lanes, lane l takes k =
@@ -251,8 +244,10 @@ __global__ void __launch_bounds__(256) ExpertDownCombine(const ExpertDownCombine
   }
 }
 static uint32_t down_smem_fn(const void *args) {
+  // sized for the template's pass count (6 or 12): passes beyond the active
+  // slots are masked but still index the staged arrays
   const ExpertDownCombineArgs *a = (const ExpertDownCombineArgs *)args;
-  return staged_act_bytes(a->I, a->slots);
+  return staged_act_bytes(a->I, a->slots <= 6 ? 6 : 12);
 }
 #define F(f) AINFER_ARG(ExpertDownCombineArgs, f)
 AINFER_REGISTER(ExpertDownCombine, ExpertDownCombineArgs, 256, 0, 0, down_smem_fn, F(Experts),

@@ -1,0 +1,522 @@
+#include "executor.h"
+
+#include <time.h>
+
+#include <algorithm>
+#include <cstring>
+
+#include "../common/tables.h"
+
+namespace ainfer {
+
+namespace {
+
+// ---- recording helpers ----------------------------------------------------
+struct Recorder {
+  Session *s;
+  ainfer_list_t list;
+  int status = 0;
+
+  ainfer_kernel_t kernel(const char *name) {
+    auto it = s->kernels.find(name);
+    if (it != s->kernels.end()) return it->second;
+    ainfer_kernel_t k = nullptr;
+    if (ainfer_kernel_get(s->dev, name, &k) != AINFER_OK) {
+      s->err = std::string("entry ") + name + " not found";
+      status = 1;
+      return nullptr;
+    }
+    s->kernels[name] = k;
+    return k;
+  }
+  template <typename T>
+  void set(ainfer_kernel_t k, uint32_t &idx, const T &v) {
+    if (status) return;
+    if (ainfer_kernel_set_arg(k, idx, sizeof(T), &v) != AINFER_OK) {
+      s->err = ainfer_last_error(s->dev);
+      status = 1;
+    }
+    ++idx;
+  }
+  // Appends one launch; arguments are set by index in the order given, which is
+  // the member order of the kernel's argument struct.
+  template <typename... A>
+  void launch(const char *name, uint32_t groups, const A &...args) {
+    if (status) return;
+    ainfer_kernel_t k = kernel(name);
+    if (!k) return;
+    uint32_t idx = 0;
+    (set(k, idx, args), ...);
+    if (status) return;
+    if (ainfer_list_append_launch(list, k, groups ? groups : 1) != AINFER_OK) {
+      s->err = std::string("append failed: ") + ainfer_last_error(s->dev);
+      status = 1;
+    }
+    s->launches_per_token += 1;
+  }
+  void copy(void *dst, const void *src, size_t bytes) {
+    if (status) return;
+    if (ainfer_list_append_memcpy(list, dst, src, bytes) != AINFER_OK) {
+      s->err = std::string("append failed: ") + ainfer_last_error(s->dev);
+      status = 1;
+    }
+  }
+};
+
+int gemv_rows_per_group(int K) {
+  int cpr = K / 32, lpr = std::min(cpr, 32), rpw = 32 / lpr;
+  int rt = K <= 1024 ? 4 : (K == 2048 ? 2 : 1);
+  return 8 * rt * rpw;
+}
+
+struct MatSpec {
+  DeviceTensor t;
+  float *Y;
+  int epi;
+  const float *e0;
+  float *e1;
+  const float *e2;
+};
+
+// Adds a matrix table for one GEMV launch to the session's table arena and
+// appends the launch.
+void record_gemv(Recorder &r, const std::vector<MatSpec> &mats, int K, const int8_t *XQ,
+                 const float *SQ) {
+  Session *s = r.s;
+  if (r.status) return;
+  std::vector<GemvMat> tab(mats.size());
+  int row = 0;
+  for (size_t i = 0; i < mats.size(); ++i) {
+    const MatSpec &m = mats[i];
+    if (!m.t.entry) { s->err = "missing tensor for GEMV"; r.status = 1; return; }
+    if ((int)m.t.entry->shape[1] != K || m.t.entry->storage != DT_INT4_SYM_G128) {
+      s->err = "unexpected shape/storage of " + m.t.entry->name;
+      r.status = 2;
+      return;
+    }
+    GemvMat &g = tab[i];
+    g.P = (const uint8_t *)m.t.data;
+    g.S = (const uint16_t *)m.t.scales;
+    g.Y = m.Y; g.e0 = m.e0; g.e1 = m.e1; g.e2 = m.e2;
+    g.row_start = row;
+    g.N = (int)m.t.entry->shape[0];
+    g.epi = m.epi;
+    g.ldy = g.N;
+    row += g.N;
+  }
+  size_t bytes = tab.size() * sizeof(GemvMat);
+  size_t off = s->gemv_tables_host.size();
+  if (off + bytes > s->gemv_tables_cap) { s->err = "internal: GEMV table arena too small"; r.status = 3; return; }
+  s->gemv_tables_host.resize(off + bytes);
+  std::memcpy(s->gemv_tables_host.data() + off, tab.data(), bytes);
+  const GemvMat *dtab = (const GemvMat *)((char *)s->gemv_tables + off);
+  int rpg = gemv_rows_per_group(K);
+  uint32_t groups = (uint32_t)std::min((row + rpg - 1) / rpg, s->sm_count * 8);
+  r.launch("Int4GemvA8", groups, dtab, (int32_t)mats.size(), (int32_t)row, XQ, SQ, (int32_t)K,
+           (int32_t)1);
+}
+
+template <typename T>
+int salloc(Session *s, size_t count, T **out, bool zero = true) {
+  void *p = nullptr;
+  size_t bytes = std::max<size_t>(count * sizeof(T), 16);
+  if (ainfer_mem_alloc(s->dev, bytes, 256, &p) != AINFER_OK) {
+    s->err = std::string("alloc ") + std::to_string(bytes) + " failed: " + ainfer_last_error(s->dev);
+    return 1;
+  }
+  s->owned.push_back(p);
+  if (zero && ainfer_mem_fill(s->dev, p, 0, bytes) != AINFER_OK) { s->err = ainfer_last_error(s->dev); return 1; }
+  *out = (T *)p;
+  return 0;
+}
+
+// ---- layer templates ------------------------------------------------------
+// MoE block shared by both layer kinds (replaces the dense MLP of
+// tools/decode/decode_l0.cpp:664-674).
+void record_moe(Recorder &r, int L, const std::string &p, const float *post_norm_w) {
+  Session *s = r.s;
+  const ModelConfig &c = s->m->cfg;
+  const int H = c.hidden, E = c.experts, k = c.top_k, I = c.expert_inter;
+  const int slots = k + (c.shared_experts ? 1 : 0);
+  const float eps = (float)c.rms_eps;
+  r.launch("RmsNormQuant", 1, (const float *)s->Tmp, (const float *)nullptr, (float *)nullptr,
+           post_norm_w, s->Hn, s->Q8, s->SQ, (int32_t)H, eps);
+  DeviceTensor router = s->m->tensor(p + "mlp.gate.weight");
+  DeviceTensor sgate = s->m->tensor(p + "mlp.shared_expert_gate.weight");
+  if (!router.entry || (c.shared_experts && !sgate.entry)) {
+    s->err = "missing " + p + "mlp.gate.weight / shared_expert_gate.weight";
+    r.status = 1;
+    return;
+  }
+  r.launch("RouterTopK", (uint32_t)((E + 1 + 7) / 8), (const uint16_t *)router.data,
+           (const uint16_t *)(c.shared_experts ? sgate.data : nullptr), (const float *)s->Hn,
+           s->RLogits, s->Counter, s->SelIdx, s->SelW, s->NearGap, (int32_t)E, (int32_t)H, (int32_t)k);
+  const ExpertW *tab = (const ExpertW *)s->m->expert_tables + (size_t)L * (E + 1);
+  int rpg_up = 8 * (32 / std::min(H / 32, 32));
+  uint32_t g_up = (uint32_t)std::min((slots * I + rpg_up - 1) / rpg_up, s->sm_count * 8);
+  r.launch("ExpertGateUp", g_up, tab, (const int32_t *)s->SelIdx, (const int8_t *)s->Q8,
+           (const float *)s->SQ, s->Act, (int32_t)slots, (int32_t)I, (int32_t)H, (int32_t)0);
+  int rpg_dn = 8 * (32 / std::min(I / 32, 32));
+  uint32_t g_dn = (uint32_t)std::min((H + rpg_dn - 1) / rpg_dn, s->sm_count * 8);
+  r.launch("ExpertDownCombine", g_dn, tab, (const int32_t *)s->SelIdx, (const float *)s->SelW,
+           (const float *)s->Act, (const float *)s->Tmp, s->X, (float *)nullptr, (int32_t)slots,
+           (int32_t)I, (int32_t)H);
+  if (s->flags & SESSION_DIAG) {
+    if (L < c.layers) {
+      r.copy(s->layer_out + (size_t)L * H, s->X, (size_t)H * 4);
+      r.copy(s->routed + (size_t)L * (k + 1), s->SelIdx, (size_t)(k + 1) * 4);
+      r.copy(s->near_gap + L, s->NearGap, 4);
+    }
+  }
+}
+
+// Gated DeltaNet layer (tools/decode/decode_l0.cpp:560-561,610-663).
+void record_linear_layer(Recorder &r, int L) {
+  Session *s = r.s;
+  DeviceModel *m = s->m;
+  const ModelConfig &c = m->cfg;
+  const int H = c.hidden, nK = c.lin_k_heads, nV = c.lin_v_heads, C = c.conv_dim(), VD = c.value_dim();
+  const int slot = m->slot[L];
+  const std::string p = layer_prefix(L);
+  const float eps = (float)c.rms_eps;
+  r.launch("RmsNormQuant", 1, (const float *)s->X, (const float *)nullptr, (float *)nullptr,
+           (const float *)(m->in_norm + (size_t)L * H), (float *)nullptr, s->Q8, s->SQ, (int32_t)H, eps);
+  record_gemv(r,
+              {{m->tensor(p + "linear_attn.in_proj_qkv.weight"), s->Mx, EPI_CONV_SILU,
+                m->conv_w + (size_t)slot * C * 4, s->conv + (size_t)slot * C * 3, nullptr},
+               {m->tensor(p + "linear_attn.in_proj_z.weight"), s->Z, EPI_STORE, nullptr, nullptr, nullptr},
+               {m->tensor(p + "linear_attn.in_proj_b.weight"), s->Bt, EPI_BETA, nullptr, nullptr, nullptr},
+               {m->tensor(p + "linear_attn.in_proj_a.weight"), s->Gt, EPI_GDECAY,
+                m->a_log + (size_t)slot * nV, nullptr, m->dt_bias + (size_t)slot * nV}},
+              H, s->Q8, s->SQ);
+  r.launch("DeltaNetStep", (uint32_t)(nV * 4), s->O, (const float *)s->Mx,
+           s->S + (size_t)slot * nV * 128 * 128, (const float *)s->Bt, (const float *)s->Gt,
+           (int32_t)nK, (int32_t)nV);
+  r.launch("GatedNormQuant", (uint32_t)((nV + 3) / 4), (const float *)s->O, (const float *)s->Z,
+           (const float *)(m->lin_norm + (size_t)slot * c.lin_head_dim), s->Q8, s->SQ,
+           (float *)nullptr, (int32_t)nV, eps);
+  record_gemv(r, {{m->tensor(p + "linear_attn.out_proj.weight"), s->Tmp, EPI_RESADD, s->X, nullptr, nullptr}},
+              VD, s->Q8, s->SQ);
+  record_moe(r, L, p, m->post_norm + (size_t)L * H);
+}
+
+// Gated GQA attention layer (tools/decode/decode_l0.cpp:560-608,663). kv_slot
+// selects the cache; in_x is the residual input (X for trunk layers).
+void record_attn_layer(Recorder &r, int L, const std::string &p) {
+  Session *s = r.s;
+  DeviceModel *m = s->m;
+  const ModelConfig &c = m->cfg;
+  const int H = c.hidden, nQ = c.q_heads, nKV = c.kv_heads, D = c.head_dim;
+  const int slot = m->slot[L];
+  const float eps = (float)c.rms_eps;
+  r.launch("RmsNormQuant", 1, (const float *)s->X, (const float *)nullptr, (float *)nullptr,
+           (const float *)(m->in_norm + (size_t)L * H), (float *)nullptr, s->Q8, s->SQ, (int32_t)H, eps);
+  record_gemv(r,
+              {{m->tensor(p + "self_attn.q_proj.weight"), s->Q16, EPI_STORE, nullptr, nullptr, nullptr},
+               {m->tensor(p + "self_attn.k_proj.weight"), s->K16, EPI_STORE, nullptr, nullptr, nullptr},
+               {m->tensor(p + "self_attn.v_proj.weight"), s->V16, EPI_STORE, nullptr, nullptr, nullptr}},
+              H, s->Q8, s->SQ);
+  size_t kv_off = (size_t)slot * s->max_ctx * nKV;
+  int8_t *Kc = s->Kc + kv_off * D, *Vc = s->Vc + kv_off * D;
+  uint16_t *Ks = s->Ks + kv_off, *Vs = s->Vs + kv_off;
+  r.launch("AttnPrep", (uint32_t)((nQ + 2 * nKV + 7) / 8), (const float *)s->Q16, (const float *)s->K16,
+           (const float *)s->V16, (const float *)(m->q_norm + (size_t)slot * D),
+           (const float *)(m->k_norm + (size_t)slot * D), (const float *)m->rope_cos,
+           (const float *)m->rope_sin, (const int32_t *)s->ctrl, s->Qn, Kc, Vc, Ks, Vs, (int32_t)nQ,
+           (int32_t)nKV, (int32_t)c.rotary_dim, (int32_t)s->max_ctx, eps);
+  uint32_t g_split = (uint32_t)std::min(s->max_chunks * nKV, s->sm_count * 8);
+  r.launch("AttnSplit", g_split, (const float *)s->Qn, (const int8_t *)Kc, (const int8_t *)Vc,
+           (const uint16_t *)Ks, (const uint16_t *)Vs, (const int32_t *)s->ctrl, s->Pm, s->Pse, s->Pacc,
+           (int32_t)nQ, (int32_t)nKV, (int32_t)s->max_ctx, (int32_t)s->max_chunks);
+  r.launch("AttnCombine", (uint32_t)nQ, (const float *)s->Pm, (const float *)s->Pse,
+           (const float *)s->Pacc, (const float *)s->Q16, (const int32_t *)s->ctrl, s->Q8, s->SQ,
+           (float *)nullptr, (int32_t)nQ, (int32_t)s->max_ctx, (int32_t)s->max_chunks);
+  record_gemv(r, {{m->tensor(p + "self_attn.o_proj.weight"), s->Tmp, EPI_RESADD, s->X, nullptr, nullptr}},
+              nQ * D, s->Q8, s->SQ);
+  record_moe(r, L, p, m->post_norm + (size_t)L * H);
+}
+
+void record_layer(Recorder &r, int L) {
+  if (r.s->m->cfg.layer_types[L] == 'A') record_attn_layer(r, L, layer_prefix(L));
+  else record_linear_layer(r, L);
+}
+
+void record_embed(Recorder &r) {
+  Session *s = r.s;
+  DeviceTensor emb = s->m->tensor("model.language_model.embed_tokens.weight");
+  if (!emb.entry) { s->err = "missing model.language_model.embed_tokens.weight"; r.status = 1; return; }
+  r.launch("EmbedRow", 1, s->X, (const uint16_t *)emb.data, (const int32_t *)s->ctrl,
+           (int32_t)s->m->cfg.hidden, (int32_t)s->m->cfg.vocab, (int32_t)4);
+}
+
+// Tail: final norm + lm_head + argmax (tools/decode/decode_l0.cpp:679-699).
+void record_tail(Recorder &r, bool advance) {
+  Session *s = r.s;
+  DeviceModel *m = s->m;
+  const ModelConfig &c = m->cfg;
+  r.launch("RmsNormQuant", 1, (const float *)s->X, (const float *)nullptr, (float *)nullptr,
+           (const float *)m->final_norm, (float *)nullptr, s->Q8, s->SQ, (int32_t)c.hidden,
+           (float)c.rms_eps);
+  record_gemv(r, {{m->tensor("lm_head.weight"), s->Logits, EPI_STORE, nullptr, nullptr, nullptr}},
+              c.hidden, s->Q8, s->SQ);
+  r.launch("ArgmaxStage1", (uint32_t)s->argmax_parts, (const float *)s->Logits, s->PV, s->PI,
+           (int32_t)c.vocab);
+  r.launch("ArgmaxStage2", 1, (const float *)s->PV, (const int32_t *)s->PI, s->out_tok, s->ctrl,
+           s->history, (int32_t)s->argmax_parts, (int32_t)(advance ? 1 : 0), (int32_t)s->max_ctx);
+}
+
+int close_list(Session *s, ainfer_list_t l) {
+  if (ainfer_list_close(l) != AINFER_OK) { s->err = std::string("list close failed: ") + ainfer_last_error(s->dev); return 1; }
+  return 0;
+}
+
+}  // namespace
+
+int session_reset(Session *s) {
+  const ModelConfig &c = s->m->cfg;
+  size_t n_kv = (size_t)(c.n_attn() + c.mtp_layers) * s->max_ctx * c.kv_heads;
+  int r = 0;
+  r |= ainfer_mem_fill(s->dev, s->conv, 0, std::max<size_t>((size_t)c.n_lin() * c.conv_dim() * 3 * 4, 16));
+  r |= ainfer_mem_fill(s->dev, s->S, 0, std::max<size_t>((size_t)c.n_lin() * c.lin_v_heads * 128 * 128 * 4, 16));
+  r |= ainfer_mem_fill(s->dev, s->Kc, 0, std::max<size_t>(n_kv * c.head_dim, 16));
+  r |= ainfer_mem_fill(s->dev, s->Vc, 0, std::max<size_t>(n_kv * c.head_dim, 16));
+  r |= ainfer_mem_fill(s->dev, s->Ks, 0, std::max<size_t>(n_kv * 2, 16));
+  r |= ainfer_mem_fill(s->dev, s->Vs, 0, std::max<size_t>(n_kv * 2, 16));
+  if (r) { s->err = ainfer_last_error(s->dev); return 1; }
+  return 0;
+}
+
+int session_create(DeviceModel *m, int max_ctx, int flags, Session **out, std::string &err) {
+  *out = nullptr;
+  if (max_ctx < 1) { err = "max_ctx must be positive"; return 2; }
+  Session *s = new Session;
+  s->m = m;
+  s->dev = m->dev;
+  s->max_ctx = max_ctx;
+  s->flags = flags;
+  auto fail = [&](int code) { err = s->err; session_destroy(s); return code; };
+  ainfer_device_info info;
+  if (ainfer_device_get_info(s->dev, &info) != AINFER_OK) { s->err = ainfer_last_error(s->dev); return fail(1); }
+  s->sm_count = info.sm_count;
+  const ModelConfig &c = m->cfg;
+  const int H = c.hidden, D = c.head_dim, nQ = c.q_heads, nKV = c.kv_heads, nV = c.lin_v_heads;
+  const int C = std::max(c.conv_dim(), 1), VD = std::max(c.value_dim(), 1);
+  const int n_kv_layers = c.n_attn() + c.mtp_layers;
+  s->max_chunks = (max_ctx + 63) / 64;
+  s->argmax_parts = std::min(s->sm_count * 2, std::max(1, (c.vocab + 255) / 256));
+  if (model_ensure_rope(m, max_ctx, s->err)) return fail(1);
+  int r = 0;
+  size_t n_kv = (size_t)n_kv_layers * max_ctx * nKV;
+  r |= salloc(s, (size_t)c.n_lin() * C * 3, &s->conv);
+  r |= salloc(s, (size_t)c.n_lin() * nV * 128 * 128, &s->S);
+  r |= salloc(s, n_kv * D, &s->Kc);
+  r |= salloc(s, n_kv * D, &s->Vc);
+  r |= salloc(s, n_kv, &s->Ks);
+  r |= salloc(s, n_kv, &s->Vs);
+  r |= salloc(s, 4, &s->ctrl);
+  r |= salloc(s, (size_t)max_ctx, &s->ids);
+  r |= salloc(s, (size_t)max_ctx, &s->history);
+  r |= salloc(s, 1, &s->out_tok);
+  r |= salloc(s, (size_t)H, &s->X);
+  r |= salloc(s, (size_t)H, &s->Tmp);
+  r |= salloc(s, (size_t)H, &s->Hn);
+  r |= salloc(s, (size_t)H, &s->Mix);
+  int maxK = std::max(std::max(2 * H, VD), nQ * D);
+  r |= salloc(s, (size_t)maxK, &s->Q8);
+  r |= salloc(s, (size_t)maxK / 128, &s->SQ);
+  r |= salloc(s, (size_t)C, &s->Mx);
+  r |= salloc(s, (size_t)VD, &s->Z);
+  r |= salloc(s, (size_t)std::max(nV, 1), &s->Bt);
+  r |= salloc(s, (size_t)std::max(nV, 1), &s->Gt);
+  r |= salloc(s, (size_t)VD, &s->O);
+  r |= salloc(s, (size_t)nQ * 2 * D, &s->Q16);
+  r |= salloc(s, (size_t)nKV * D, &s->K16);
+  r |= salloc(s, (size_t)nKV * D, &s->V16);
+  r |= salloc(s, (size_t)nQ * D, &s->Qn);
+  r |= salloc(s, (size_t)nQ * s->max_chunks, &s->Pm);
+  r |= salloc(s, (size_t)nQ * s->max_chunks, &s->Pse);
+  r |= salloc(s, (size_t)nQ * s->max_chunks * D, &s->Pacc);
+  r |= salloc(s, (size_t)c.experts + 1, &s->RLogits);
+  r |= salloc(s, 1, &s->Counter);
+  r |= salloc(s, (size_t)c.top_k + 1, &s->SelIdx);
+  r |= salloc(s, (size_t)c.top_k + 1, &s->SelW);
+  r |= salloc(s, 1, &s->NearGap);
+  r |= salloc(s, (size_t)(c.top_k + 1) * c.expert_inter, &s->Act);
+  r |= salloc(s, (size_t)c.vocab, &s->Logits);
+  r |= salloc(s, (size_t)s->argmax_parts, &s->PV);
+  r |= salloc(s, (size_t)s->argmax_parts, &s->PI);
+  if (flags & SESSION_DIAG) {
+    r |= salloc(s, (size_t)c.layers * H, &s->layer_out);
+    r |= salloc(s, (size_t)c.layers * (c.top_k + 1), &s->routed);
+    r |= salloc(s, (size_t)c.layers, &s->near_gap);
+  }
+  s->gemv_tables_cap = (size_t)(c.layers + 2) * 8 * sizeof(GemvMat) * 2 + 4096;
+  {
+    unsigned char *p = nullptr;
+    r |= salloc(s, s->gemv_tables_cap, &p);
+    s->gemv_tables = p;
+  }
+  if (r) return fail(1);
+  void *hp = nullptr;
+  if (ainfer_host_alloc(s->dev, (size_t)max_ctx * 4 + 64, &hp) != AINFER_OK) { s->err = ainfer_last_error(s->dev); return fail(1); }
+  s->host_tok = (int32_t *)hp;
+
+  // ---- record ----
+  Recorder rec{s, nullptr};
+  auto new_list = [&](ainfer_list_t *l) {
+    if (ainfer_list_create(s->dev, l) != AINFER_OK) { s->err = "list create failed"; rec.status = 1; }
+    rec.list = *l;
+  };
+  if (flags & SESSION_PER_LAYER_LISTS) {
+    new_list(&s->embed_list);
+    record_embed(rec);
+    if (!rec.status) rec.status = close_list(s, s->embed_list);
+    for (int L = 0; L < c.layers && !rec.status; ++L) {
+      ainfer_list_t l = nullptr;
+      new_list(&l);
+      s->layer_lists.push_back(l);
+      record_layer(rec, L);
+      if (!rec.status) rec.status = close_list(s, l);
+    }
+    if (!rec.status) {
+      new_list(&s->tail_list);
+      record_tail(rec, true);
+      if (!rec.status) rec.status = close_list(s, s->tail_list);
+    }
+    if (!rec.status) {
+      new_list(&s->advance_list);
+      rec.launch("ControlAdvance", 1, s->ctrl, (const int32_t *)s->ids, (int32_t)max_ctx);
+      if (!rec.status) rec.status = close_list(s, s->advance_list);
+    }
+  } else {
+    new_list(&s->gen_list);
+    s->launches_per_token = 0;
+    record_embed(rec);
+    for (int L = 0; L < c.layers && !rec.status; ++L) record_layer(rec, L);
+    record_tail(rec, true);
+    uint64_t per_token = s->launches_per_token;
+    if (!rec.status) rec.status = close_list(s, s->gen_list);
+    if (!rec.status) {
+      new_list(&s->body_list);
+      record_embed(rec);
+      for (int L = 0; L < c.layers && !rec.status; ++L) record_layer(rec, L);
+      rec.launch("ControlAdvance", 1, s->ctrl, (const int32_t *)s->ids, (int32_t)max_ctx);
+      if (!rec.status) rec.status = close_list(s, s->body_list);
+    }
+    s->launches_per_token = per_token;
+  }
+  if (rec.status) return fail(rec.status);
+  if (!s->gemv_tables_host.empty() &&
+      ainfer_memcpy_h2d(s->dev, s->gemv_tables, s->gemv_tables_host.data(), s->gemv_tables_host.size()) != AINFER_OK) {
+    s->err = ainfer_last_error(s->dev);
+    return fail(1);
+  }
+  *out = s;
+  return 0;
+}
+
+void session_destroy(Session *s) {
+  if (!s) return;
+  ainfer_sync(s->dev, UINT64_MAX);
+  for (auto l : s->layer_lists) ainfer_list_destroy(l);
+  for (ainfer_list_t l : {s->gen_list, s->body_list, s->embed_list, s->tail_list, s->advance_list})
+    if (l) ainfer_list_destroy(l);
+  for (auto &kv : s->kernels) ainfer_kernel_release(kv.second);
+  for (void *p : s->owned) ainfer_mem_free(s->dev, p);
+  if (s->host_tok) ainfer_host_free(s->dev, s->host_tok);
+  delete s;
+}
+
+#define S_CHECK(expr)                                                        \
+  do {                                                                       \
+    if ((expr) != AINFER_OK) {                                               \
+      s->err = std::string("device error: ") + ainfer_last_error(s->dev);    \
+      return 1;                                                              \
+    }                                                                        \
+  } while (0)
+
+// Executes one token's lists. with_tail: run final norm + lm_head + argmax
+// (and advance the control block); otherwise advance to the next prompt id.
+static double now_ns() {
+  struct timespec t;
+  clock_gettime(CLOCK_MONOTONIC, &t);
+  return (double)t.tv_sec * 1e9 + (double)t.tv_nsec;
+}
+
+static int exec_fenced(Session *s, ainfer_list_t l, const char *label) {
+  double t0 = s->profile ? now_ns() : 0;
+  S_CHECK(ainfer_list_execute(l));
+  S_CHECK(ainfer_sync(s->dev, UINT64_MAX));
+  if (s->profile) s->buckets[label].push_back(now_ns() - t0);
+  return 0;
+}
+
+static int run_token(Session *s, bool with_tail) {
+  if (s->flags & SESSION_PER_LAYER_LISTS) {
+    // the reference's execution model: execute + fence per list (decode_l0.cpp:714-721)
+    int r = exec_fenced(s, s->embed_list, "embed");
+    for (size_t L = 0; L < s->layer_lists.size() && !r; ++L)
+      r = exec_fenced(s, s->layer_lists[L], s->m->cfg.layer_types[L] == 'A' ? "attn_layer" : "linear_layer");
+    if (!r) r = exec_fenced(s, with_tail ? s->tail_list : s->advance_list, with_tail ? "tail" : "control");
+    return r;
+  }
+  S_CHECK(ainfer_list_execute(with_tail ? s->gen_list : s->body_list));
+  return 0;
+}
+
+int session_step(Session *s, int token, int pos, int *out_token) {
+  if (pos < 0 || pos >= s->max_ctx) {
+    s->err = "context overflow: pos " + std::to_string(pos) + " >= MAXCTX " + std::to_string(s->max_ctx);
+    return 3;
+  }
+  ainfer_control c{token, pos, pos + 1, -1};
+  S_CHECK(ainfer_control_write(s->dev, s->ctrl, &c));
+  int r = run_token(s, true);
+  if (r) return r;
+  S_CHECK(ainfer_memcpy_d2h(s->dev, s->host_tok, s->out_tok, 4));
+  if (out_token) *out_token = s->host_tok[0];
+  return 0;
+}
+
+int session_generate(Session *s, const int *prompt, int P, int G, int start_pos, int *out_tokens,
+                     float *gen_elapsed_ms) {
+  if (P < 1 || G < 0) { s->err = "usage: need at least one prompt id"; return 2; }
+  if (start_pos < 0 || start_pos + P + G - 1 > s->max_ctx) {
+    s->err = "context overflow: pos " + std::to_string(start_pos + P + G - 1) + " >= MAXCTX " +
+             std::to_string(s->max_ctx);
+    return 3;
+  }
+  S_CHECK(ainfer_memcpy_h2d(s->dev, s->ids + start_pos, prompt, (size_t)P * 4));
+  ainfer_control c{prompt[0], start_pos, start_pos + 1, -1};
+  S_CHECK(ainfer_control_write(s->dev, s->ctrl, &c));
+  for (int i = 0; i < P - 1; ++i) {
+    int r = run_token(s, false);
+    if (r) return r;
+  }
+  ainfer_event_t e0 = nullptr, e1 = nullptr;
+  if (gen_elapsed_ms) {
+    S_CHECK(ainfer_event_create(s->dev, &e0));
+    S_CHECK(ainfer_event_create(s->dev, &e1));
+    S_CHECK(ainfer_event_record(e0));
+  }
+  for (int g = 0; g < G; ++g) {
+    int r = run_token(s, true);
+    if (r) return r;
+  }
+  if (gen_elapsed_ms) {
+    S_CHECK(ainfer_event_record(e1));
+    S_CHECK(ainfer_event_elapsed_ms(e0, e1, gen_elapsed_ms));
+    ainfer_event_destroy(e0);
+    ainfer_event_destroy(e1);
+  }
+  if (G > 0) {
+    // tokens were logged on the device at the position of the input that produced them
+    S_CHECK(ainfer_memcpy_d2h(s->dev, s->host_tok, s->history + (start_pos + P - 1), (size_t)G * 4));
+    for (int g = 0; g < G; ++g) out_tokens[g] = s->host_tok[g];
+  } else {
+    S_CHECK(ainfer_sync(s->dev, UINT64_MAX));
+  }
+  return 0;
+}
+
+}  // namespace ainfer

@@ -1,0 +1,189 @@
+// extern "C" face of the decode runtime (include/ainfer_runtime.h).
+#include <cstring>
+#include <string>
+
+#include "../../../include/ainfer_runtime.h"
+#include "executor.h"
+#include "host_sampler.h"
+#include "model.h"
+
+using namespace ainfer;
+
+struct ainfer_model_s { DeviceModel *m; std::string cfg_json; };
+struct ainfer_session_s { Session *s; };
+
+static thread_local std::string g_err;
+static int set_err(int code, const std::string &e) {
+  if (code) g_err = e;
+  return code;
+}
+
+extern "C" {
+
+const char *ainfer_rt_last_error(void) { return g_err.c_str(); }
+
+int ainfer_binfer_validate(const char *path, int level) {
+  Container c;
+  std::string err;
+  int r = container_open(path, level, c, err);
+  if (r == 0) {
+    ModelConfig cfg;
+    if (!c.arch_json.empty() && c.arch_json.find("\"text_layers\"") != std::string::npos &&
+        !ModelConfig::from_json(c.arch_json, cfg, err))
+      r = 2;
+  }
+  return set_err(r, err);
+}
+
+int ainfer_synth_write(const char *path, const char *preset, uint64_t seed) {
+  ModelConfig cfg;
+  if (!preset || !preset_config(preset, cfg)) return set_err(2, std::string("unknown synthetic preset: ") + (preset ? preset : "(null)"));
+  std::string err;
+  int r = synth_write_file(path, cfg, seed, err);
+  return set_err(r, err);
+}
+
+const char *ainfer_preset_config_json(const char *preset) {
+  static thread_local std::string js;
+  ModelConfig cfg;
+  if (!preset || !preset_config(preset, cfg)) return nullptr;
+  js = cfg.to_json();
+  return js.c_str();
+}
+
+int ainfer_model_open(ainfer_device_t dev, const char *spec, int validate_level, ainfer_model_t *out) {
+  if (!dev || !spec || !out) return set_err(2, "usage: null argument");
+  *out = nullptr;
+  DeviceModel *m = nullptr;
+  std::string err;
+  int r = model_open(dev, spec, validate_level, &m, err);
+  if (r) return set_err(r, err);
+  ainfer_model_t h = new ainfer_model_s{m, m->cfg.to_json()};
+  *out = h;
+  return 0;
+}
+int ainfer_model_close(ainfer_model_t m) {
+  if (!m) return 2;
+  model_close(m->m);
+  delete m;
+  return 0;
+}
+const char *ainfer_model_config_json(ainfer_model_t m) { return m ? m->cfg_json.c_str() : nullptr; }
+int ainfer_model_tensor_count(ainfer_model_t m) { return m ? (int)m->m->dir.entries.size() : -1; }
+
+static void fill_info(const DeviceModel *dm, const TensorEntry &e, ainfer_tensor_info *info) {
+  std::memset(info, 0, sizeof *info);
+  std::snprintf(info->name, sizeof info->name, "%s", e.name.c_str());
+  info->storage = e.storage;
+  info->ndim = e.ndim;
+  for (int i = 0; i < 8; ++i) info->shape[i] = e.shape[i];
+  DeviceTensor t = dm->tensor(e.name);
+  info->data = t.data;
+  info->data_bytes = e.d_bytes;
+  info->scales = t.scales;
+  info->scale_bytes = e.sc_bytes;
+}
+int ainfer_model_tensor_at(ainfer_model_t m, int index, ainfer_tensor_info *info) {
+  if (!m || !info || index < 0 || index >= (int)m->m->dir.entries.size()) return set_err(2, "bad tensor index");
+  fill_info(m->m, m->m->dir.entries[(size_t)index], info);
+  return 0;
+}
+int ainfer_model_tensor(ainfer_model_t m, const char *name, ainfer_tensor_info *info) {
+  if (!m || !name || !info) return set_err(2, "usage: null argument");
+  const TensorEntry *e = m->m->dir.find(name);
+  if (!e) return set_err(1, std::string("missing ") + name);
+  fill_info(m->m, *e, info);
+  return 0;
+}
+int ainfer_model_bytes(ainfer_model_t m, uint64_t *payload_bytes, uint64_t *scale_bytes) {
+  if (!m) return 2;
+  if (payload_bytes) *payload_bytes = m->m->pay_bytes;
+  if (scale_bytes) *scale_bytes = m->m->sc_bytes;
+  return 0;
+}
+
+int ainfer_session_create(ainfer_model_t m, int max_ctx, int flags, ainfer_session_t *out) {
+  if (!m || !out) return set_err(2, "usage: null argument");
+  *out = nullptr;
+  Session *s = nullptr;
+  std::string err;
+  int r = session_create(m->m, max_ctx, flags, &s, err);
+  if (r) return set_err(r, err);
+  *out = new ainfer_session_s{s};
+  return 0;
+}
+int ainfer_session_destroy(ainfer_session_t s) {
+  if (!s) return 2;
+  session_destroy(s->s);
+  delete s;
+  return 0;
+}
+int ainfer_session_reset(ainfer_session_t s) {
+  if (!s) return 2;
+  int r = session_reset(s->s);
+  return set_err(r, s->s->err);
+}
+int ainfer_session_buffer(ainfer_session_t h, const char *which, void **dptr, uint64_t *bytes) {
+  if (!h || !which || !dptr || !bytes) return set_err(2, "usage: null argument");
+  Session *s = h->s;
+  const ModelConfig &c = s->m->cfg;
+  std::string w = which;
+  size_t n_kv = (size_t)(c.n_attn() + c.mtp_layers) * s->max_ctx * c.kv_heads;
+  if (w == "conv") { *dptr = s->conv; *bytes = (uint64_t)c.n_lin() * c.conv_dim() * 3 * 4; }
+  else if (w == "S") { *dptr = s->S; *bytes = (uint64_t)c.n_lin() * c.lin_v_heads * 128 * 128 * 4; }
+  else if (w == "Kc") { *dptr = s->Kc; *bytes = n_kv * c.head_dim; }
+  else if (w == "Vc") { *dptr = s->Vc; *bytes = n_kv * c.head_dim; }
+  else if (w == "Ks") { *dptr = s->Ks; *bytes = n_kv * 2; }
+  else if (w == "Vs") { *dptr = s->Vs; *bytes = n_kv * 2; }
+  else if (w == "logits") { *dptr = s->Logits; *bytes = (uint64_t)c.vocab * 4; }
+  else if (w == "x") { *dptr = s->X; *bytes = (uint64_t)c.hidden * 4; }
+  else if (w == "ctrl") { *dptr = s->ctrl; *bytes = 16; }
+  else if (w == "history") { *dptr = s->history; *bytes = (uint64_t)s->max_ctx * 4; }
+  else if (w == "layer_out") { *dptr = s->layer_out; *bytes = s->layer_out ? (uint64_t)c.layers * c.hidden * 4 : 0; }
+  else if (w == "routed") { *dptr = s->routed; *bytes = s->routed ? (uint64_t)c.layers * (c.top_k + 1) * 4 : 0; }
+  else if (w == "near_gap") { *dptr = s->near_gap; *bytes = s->near_gap ? (uint64_t)c.layers * 4 : 0; }
+  else return set_err(2, "unknown session buffer: " + w);
+  return 0;
+}
+int ainfer_session_step(ainfer_session_t s, int token, int pos, int *out_token) {
+  if (!s) return 2;
+  int r = session_step(s->s, token, pos, out_token);
+  return set_err(r, s->s->err);
+}
+int ainfer_session_generate(ainfer_session_t s, const int *prompt, int P, int G, int start_pos,
+                            int *out_tokens, float *gen_ms) {
+  if (!s || !prompt) return set_err(2, "usage: null argument");
+  int r = session_generate(s->s, prompt, P, G, start_pos, out_tokens, gen_ms);
+  return set_err(r, s->s->err);
+}
+int ainfer_session_logits(ainfer_session_t s, float *host_out) {
+  if (!s || !host_out) return 2;
+  if (ainfer_memcpy_d2h(s->s->dev, host_out, s->s->Logits, (size_t)s->s->m->cfg.vocab * 4) != AINFER_OK)
+    return set_err(1, ainfer_last_error(s->s->dev));
+  return 0;
+}
+int ainfer_session_launches_per_token(ainfer_session_t s, uint64_t *launches) {
+  if (!s || !launches) return 2;
+  *launches = s->s->launches_per_token;
+  return 0;
+}
+
+int ainfer_apply_rep_penalty(float *logits, int V, const int *seen, int nseen, float penalty) {
+  if (!logits || V <= 0) return 2;
+  std::vector<float> l(logits, logits + V);
+  apply_rep_penalty(l, seen, nseen, penalty);
+  std::memcpy(logits, l.data(), (size_t)V * 4);
+  return 0;
+}
+int ainfer_sample_token(const float *logits, int V, const ainfer_sample_params *p, uint64_t *rng,
+                        float *probs_out) {
+  if (!logits || !p || !rng || V <= 0) return -1;
+  SampleParams sp;
+  sp.temp = p->temp; sp.top_k = p->top_k; sp.top_p = p->top_p; sp.rep_penalty = p->rep_penalty; sp.seed = p->seed;
+  std::vector<float> probs;
+  int r = sample_token(logits, V, sp, *rng, probs_out ? &probs : nullptr);
+  if (probs_out) std::memcpy(probs_out, probs.data(), (size_t)V * 4);
+  return r;
+}
+
+}  // extern "C"

@@ -1,0 +1,106 @@
+/* ainfer_runtime.h — C ABI of the decode runtime (model-loader, block-executor,
+ * token loop, host sampler) that sits on top of ainfer_cuda.h.
+ *
+ * The reference has no in-process API: its callers drive the decode_l0 binary
+ * through argv, stdout lines and a JSON report (tools/http/ainfer_http.py:36,
+ * 54-72; tools/e2e/run_e2e.py:30-37). The ainfer_decode executable keeps that
+ * process contract; these entry points expose the same loader / executor /
+ * token-loop stages in-process so that tests and benchmarks can drive them
+ * with plain pointers. Each entry point names the stage of
+ * tools/decode/decode_l0.cpp it corresponds to.
+ *
+ * All calls return 0 on success, otherwise the reference's exit codes:
+ * 1 device/API error or missing tensor, 2 usage or bad container, 3 context
+ * overflow / internal. ainfer_rt_last_error() gives the message.
+ */
+#ifndef AINFER_RUNTIME_H
+#define AINFER_RUNTIME_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#include "ainfer_cuda.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct ainfer_model_s *ainfer_model_t;
+typedef struct ainfer_session_s *ainfer_session_t;
+
+const char *ainfer_rt_last_error(void);
+
+/* ---- container (host only, no GPU) ---- */
+/* Validation levels: 0 header + directory + span checks (the loader's checks,
+ * decode_l0.cpp:127-189), 1 + section CRCs / quant params / overlap, 2 + payload
+ * CRCs and trailing SHA-256 (docs/binfer_spec.md section 11). */
+int ainfer_binfer_validate(const char *path, int level);
+/* Writes a synthetic model of a named shape ("tiny", "mini", "mini-mtp",
+ * "small", "full") on the host. Counterpart of tools/binfer.py cmd_quantize
+ * (:155-353) with seeded N(0, 0.02) weights in place of a checkpoint. */
+int ainfer_synth_write(const char *path, const char *preset, uint64_t seed);
+/* Architecture JSON of a preset (pointer valid until the next call). */
+const char *ainfer_preset_config_json(const char *preset);
+
+/* ---- model-loader (decode_l0.cpp:127-374) ---- */
+/* spec: path of a .binfer file, or "synth:<preset>[:seed=N]" to fill the same
+ * tensors directly in device memory. */
+int ainfer_model_open(ainfer_device_t dev, const char *spec, int validate_level, ainfer_model_t *out);
+int ainfer_model_close(ainfer_model_t m);
+const char *ainfer_model_config_json(ainfer_model_t m);
+int ainfer_model_tensor_count(ainfer_model_t m);
+typedef struct ainfer_tensor_info {
+  char name[64];
+  int32_t storage, ndim;
+  uint64_t shape[8];
+  void *data;        /* device address */
+  uint64_t data_bytes;
+  void *scales;      /* device address or NULL */
+  uint64_t scale_bytes;
+} ainfer_tensor_info;
+int ainfer_model_tensor_at(ainfer_model_t m, int index, ainfer_tensor_info *info);
+int ainfer_model_tensor(ainfer_model_t m, const char *name, ainfer_tensor_info *info);
+/* Total payload + scale bytes resident on the device. */
+int ainfer_model_bytes(ainfer_model_t m, uint64_t *payload_bytes, uint64_t *scale_bytes);
+
+/* ---- block-executor + token loop (decode_l0.cpp:270-295,544-825) ---- */
+enum {
+  AINFER_SESSION_DIAG = 1,            /* per-layer residual dump (AINFER_DUMP0), routed experts, near-tie gaps */
+  AINFER_SESSION_PER_LAYER_LISTS = 2  /* one list per layer, fenced one by one, as the reference executes */
+};
+int ainfer_session_create(ainfer_model_t m, int max_ctx, int flags, ainfer_session_t *out);
+int ainfer_session_destroy(ainfer_session_t s);
+int ainfer_session_reset(ainfer_session_t s);
+/* Device buffers of the session, for state upload/download by tests:
+ * "conv", "S", "Kc", "Vc", "Ks", "Vs", "logits", "x", "ctrl", "layer_out",
+ * "routed", "near_gap", "history". */
+int ainfer_session_buffer(ainfer_session_t s, const char *which, void **dptr, uint64_t *bytes);
+/* One token at a position; returns the greedy token (4-byte readback). */
+int ainfer_session_step(ainfer_session_t s, int token, int pos, int *out_token);
+/* P prompt ids from start_pos, then G greedy tokens; device-advanced control
+ * block, one readback at the end. gen_ms (optional): device time of the G steps. */
+int ainfer_session_generate(ainfer_session_t s, const int *prompt, int P, int G, int start_pos,
+                            int *out_tokens, float *gen_ms);
+/* Copies the last step's logits to the host (V floats). */
+int ainfer_session_logits(ainfer_session_t s, float *host_out);
+int ainfer_session_launches_per_token(ainfer_session_t s, uint64_t *launches);
+
+/* ---- sampler (tools/sample/sampler.h:16-62) ---- */
+typedef struct ainfer_sample_params {
+  float temp;
+  int32_t top_k;
+  float top_p;
+  float rep_penalty;
+  uint64_t seed;
+} ainfer_sample_params;
+/* In-place repetition penalty over V logits. */
+int ainfer_apply_rep_penalty(float *logits, int V, const int *seen, int nseen, float penalty);
+/* Returns the selected id; rng is the caller's xorshift64* state; probs_out
+ * (optional, V floats) receives the final distribution. */
+int ainfer_sample_token(const float *logits, int V, const ainfer_sample_params *p, uint64_t *rng,
+                        float *probs_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AINFER_RUNTIME_H */

@@ -315,7 +315,7 @@ static void moe_block(const Model &M, const std::string &pfx, const float *hn, c
   parallel_for((int64_t)(slots), [&](int64_t s_) {
     int s = (int)s_;
     std::string ep = s < k ? pfx + "mlp.experts." + std::to_string(idx[s]) + "."
-                           : pfx + "mlp.shared_expert.";
+                           : pfx + "mlp.shared.";
     const Tensor &wg = M.get(ep + "gate_proj.weight"), &wu = M.get(ep + "up_proj.weight"),
                  &wd = M.get(ep + "down_proj.weight");
     std::vector<float> g(I), u(I);
