@@ -170,6 +170,7 @@ __device__ __forceinline__ void gateup_body(const ExpertGateUpArgs &a) {
 }
 __global__ void __launch_bounds__(256) ExpertGateUp(const ExpertGateUpArgs a) {
   switch (a.H) {
+    case 256: gateup_body<256>(a); break;
     case 512: gateup_body<512>(a); break;
     case 1024: gateup_body<1024>(a); break;
     case 2048: gateup_body<2048>(a); break;

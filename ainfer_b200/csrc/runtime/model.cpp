@@ -91,7 +91,7 @@ bool ModelConfig::check(std::string &err) const {
   if (layers <= 0 || (int)layer_types.size() != layers) return bad("layer_types/text_layers mismatch");
   for (char c : layer_types)
     if (c != 'L' && c != 'A') return bad("layer_types may hold only L and A");
-  if (!pow2_between(hidden, 256, 8192)) return bad("hidden must be a power of two in [256, 8192]");
+  if (!pow2_between(hidden, 256, 4096)) return bad("hidden must be a power of two in [256, 4096]");
   if (vocab <= 0) return bad("vocab");
   if (head_dim != 256) return bad("head_dim must be 256");
   if (rotary_dim != 64) return bad("rotary_dim must be 64");

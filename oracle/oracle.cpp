@@ -118,27 +118,139 @@ static uint32_t crc32_bytes(const uint8_t *p, size_t n, uint32_t crc = 0) {
   return ~crc;
 }
 
+// How a tensor of a lazily generated synthetic model is filled: N(0, std^2)
+// draws from (seed, FNV-1a(name), index), or a constant when std == 0.
+struct SynthRule {
+  float std_ = 0.02f, constant = 0.0f;
+};
+
 struct Model {
   Cfg cfg;
   std::string arch_json;
-  std::map<std::string, Tensor> tensors;
+  mutable std::map<std::string, Tensor> tensors;
   const uint8_t *map = nullptr;
   size_t map_bytes = 0;
   int fd = -1;
+  // lazily generated synthetic model: values are produced on first use by the
+  // oracle's own generator and quantiser, so that no product code is involved
+  bool lazy = false;
+  uint64_t seed = 0;
+  std::map<std::string, SynthRule> rules;
+  mutable std::map<std::string, std::pair<std::vector<uint8_t>, std::vector<uint16_t>>> store;
+  mutable std::mutex mu;
   ~Model() {
     if (map) munmap((void *)map, map_bytes);
     if (fd >= 0) close(fd);
   }
+  void materialise(const std::string &n, Tensor &t) const {
+    const SynthRule &r = rules.at(n);
+    uint64_t stream = fnv1a64(n.c_str());
+    size_t numel = t.numel();
+    auto &slot = store[n];
+    if (t.storage == ST_INT4) {
+      size_t ng = (numel + 127) / 128;
+      slot.first.resize(ng * 64);
+      slot.second.resize(ng);
+      uint8_t *pk = slot.first.data();
+      uint16_t *sc = slot.second.data();
+      const uint64_t sd = seed;
+      const float sdv = r.std_;
+      parallel_for((int64_t)ng, [&](int64_t g) {
+        float v[128];
+        for (int j = 0; j < 128; ++j) {
+          size_t i = (size_t)g * 128 + j;
+          v[j] = i < numel ? sdv * normal_from_u32(draw_u32(sd, stream, i)) : 0.0f;
+        }
+        quantize_int4_g128(v, 128, pk + (size_t)g * 64, sc + g);
+      });
+      t.scales = slot.second.data();
+      t.scale_bytes = ng * 2;
+    } else {
+      slot.first.resize(numel * 2);
+      uint16_t *o = (uint16_t *)slot.first.data();
+      const SynthRule rr = r;
+      const uint64_t sd = seed;
+      parallel_for((int64_t)numel, [&](int64_t i) {
+        o[i] = f32_to_bf16(rr.std_ == 0.0f ? rr.constant
+                                           : rr.std_ * normal_from_u32(draw_u32(sd, stream, (uint64_t)i)));
+      });
+    }
+    t.data = slot.first.data();
+    t.data_bytes = slot.first.size();
+  }
   const Tensor &get(const std::string &n) const {
+    std::lock_guard<std::mutex> lk(mu);
     auto it = tensors.find(n);
     if (it == tensors.end()) {
       std::fprintf(stderr, "oracle: missing %s\n", n.c_str());
       std::abort();
     }
+    if (lazy && !it->second.data) materialise(n, it->second);
     return it->second;
   }
   bool has(const std::string &n) const { return tensors.count(n) != 0; }
 };
+
+// Tensor list of a synthetic model of the given shape (names as the container
+// convention of the runtime: HF-style names under model.language_model.*, the
+// shared expert abbreviated to mlp.shared.* to fit the 63-byte name field).
+static void synth_plan(Model &M) {
+  const Cfg &c = M.cfg;
+  auto add = [&](const std::string &name, std::vector<uint64_t> shape, bool int4, SynthRule r) {
+    Tensor t;
+    t.storage = int4 ? ST_INT4 : ST_BF16;
+    t.ndim = (int)shape.size();
+    for (size_t i = 0; i < shape.size(); ++i) t.shape[i] = shape[i];
+    M.tensors[name] = t;
+    M.rules[name] = r;
+  };
+  const uint64_t H = c.hidden, V = c.vocab, I = c.expert_inter, D = c.head_dim;
+  SynthRule w{0.02f, 0.0f}, zero{0.0f, 0.0f}, one{0.0f, 1.0f};
+  auto layer = [&](const std::string &p, bool attn) {
+    add(p + "input_layernorm.weight", {H}, false, zero);
+    add(p + "post_attention_layernorm.weight", {H}, false, zero);
+    if (attn) {
+      add(p + "self_attn.q_proj.weight", {(uint64_t)c.q_heads * 2 * D, H}, true, w);
+      add(p + "self_attn.k_proj.weight", {(uint64_t)c.kv_heads * D, H}, true, w);
+      add(p + "self_attn.v_proj.weight", {(uint64_t)c.kv_heads * D, H}, true, w);
+      add(p + "self_attn.o_proj.weight", {H, (uint64_t)c.q_heads * D}, true, w);
+      add(p + "self_attn.q_norm.weight", {D}, false, zero);
+      add(p + "self_attn.k_norm.weight", {D}, false, zero);
+    } else {
+      const uint64_t C = c.conv_dim(), VD = c.value_dim(), NV = c.lin_v_heads;
+      add(p + "linear_attn.in_proj_qkv.weight", {C, H}, true, w);
+      add(p + "linear_attn.in_proj_z.weight", {VD, H}, true, w);
+      add(p + "linear_attn.in_proj_b.weight", {NV, H}, true, w);
+      add(p + "linear_attn.in_proj_a.weight", {NV, H}, true, w);
+      add(p + "linear_attn.conv1d.weight", {C, 1, 4}, false, SynthRule{0.5f, 0.0f});
+      add(p + "linear_attn.A_log", {NV}, false, SynthRule{0.05f, 0.0f});
+      add(p + "linear_attn.dt_bias", {NV}, false, SynthRule{0.05f, 0.0f});
+      add(p + "linear_attn.norm.weight", {(uint64_t)c.lin_head_dim}, false, one);
+      add(p + "linear_attn.out_proj.weight", {H, VD}, true, w);
+    }
+    add(p + "mlp.gate.weight", {(uint64_t)c.experts, H}, false, w);
+    for (int e = 0; e <= c.experts; ++e) {
+      if (e == c.experts && !c.shared_experts) break;
+      std::string ep = e < c.experts ? p + "mlp.experts." + std::to_string(e) + "." : p + "mlp.shared.";
+      add(ep + "gate_proj.weight", {I, H}, true, w);
+      add(ep + "up_proj.weight", {I, H}, true, w);
+      add(ep + "down_proj.weight", {H, I}, true, w);
+    }
+    if (c.shared_experts) add(p + "mlp.shared_expert_gate.weight", {1, H}, false, w);
+  };
+  add("lm_head.weight", {V, H}, true, w);
+  add("model.language_model.embed_tokens.weight", {V, H}, false, w);
+  for (int L = 0; L < c.layers; ++L)
+    layer("model.language_model.layers." + std::to_string(L) + ".", c.layer_types[L] == 'A');
+  add("model.language_model.norm.weight", {H}, false, zero);
+  if (c.mtp_layers) {
+    add("mtp.fc.weight", {H, 2 * H}, true, w);
+    layer("mtp.layers.0.", true);
+    add("mtp.norm.weight", {H}, false, zero);
+    add("mtp.pre_fc_norm_embedding.weight", {H}, false, zero);
+    add("mtp.pre_fc_norm_hidden.weight", {H}, false, zero);
+  }
+}
 
 template <typename T>
 static T rd(const uint8_t *p) {
@@ -536,6 +648,16 @@ void orc_model_add_tensor(void *model, const char *name, int storage, int ndim,
   t.scales = (const uint16_t *)scales; t.scale_bytes = scale_bytes;
   ((Model *)model)->tensors[name] = t;
 }
+// Lazily generated synthetic model of the shape given by arch_json.
+void *orc_model_synth(const char *arch_json, uint64_t seed) {
+  Model *m = new Model;
+  m->arch_json = arch_json;
+  m->cfg = parse_cfg(m->arch_json);
+  m->lazy = true;
+  m->seed = seed;
+  synth_plan(*m);
+  return m;
+}
 void orc_model_close(void *model) { delete (Model *)model; }
 const char *orc_model_arch_json(void *model) { return ((Model *)model)->arch_json.c_str(); }
 int orc_model_tensor_count(void *model) { return (int)((Model *)model)->tensors.size(); }
@@ -543,9 +665,8 @@ int orc_model_tensor_info(void *model, const char *name, int *storage, int *ndim
                           const void **data, uint64_t *data_bytes, const void **scales,
                           uint64_t *scale_bytes) {
   Model *m = (Model *)model;
-  auto it = m->tensors.find(name);
-  if (it == m->tensors.end()) return -1;
-  const Tensor &t = it->second;
+  if (!m->has(name)) return -1;
+  const Tensor &t = m->get(name);
   *storage = t.storage; *ndim = t.ndim;
   for (int i = 0; i < 8; ++i) shape[i] = t.shape[i];
   *data = t.data; *data_bytes = t.data_bytes; *scales = t.scales; *scale_bytes = t.scale_bytes;

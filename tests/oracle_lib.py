@@ -41,6 +41,7 @@ def lib():
     sig = {
         "orc_model_open": (vp, [C.c_char_p, i, C.c_char_p, i]),
         "orc_model_new": (vp, [C.c_char_p]),
+        "orc_model_synth": (vp, [C.c_char_p, u64]),
         "orc_model_add_tensor": (None, [vp, C.c_char_p, i, i, C.POINTER(u64), vp, u64, vp, u64]),
         "orc_model_close": (None, [vp]),
         "orc_model_arch_json": (C.c_char_p, [vp]),
@@ -146,10 +147,12 @@ def synth_normal(name, seed, count, std, first=0):
 
 
 class Model:
-    def __init__(self, path=None, arch_json=None, check_crc=True):
+    def __init__(self, path=None, arch_json=None, check_crc=True, synth_seed=None):
         L = lib()
         self._keep = []
-        if path is not None:
+        if synth_seed is not None:
+            self.h = L.orc_model_synth(arch_json.encode(), synth_seed)
+        elif path is not None:
             err = C.create_string_buffer(512)
             self.h = L.orc_model_open(os.fsencode(path), int(check_crc), err, 512)
             if not self.h:

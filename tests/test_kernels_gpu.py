@@ -266,7 +266,7 @@ def test_attention_decode_int8kv(dev, nQ, nKV, T):
     assert np.array_equal(dev.download(dSQ, nQ * 2, np.float32), sq)
 
 
-@pytest.mark.parametrize("E,k,H,I", [(64, 4, 1024, 256), (512, 10, 2048, 512)])
+@pytest.mark.parametrize("E,k,H,I", [(32, 2, 256, 128), (64, 4, 1024, 256), (512, 10, 2048, 512)])
 def test_moe_block(dev, E, k, H, I):
     """RouterTopK + ExpertGateUp + ExpertDownCombine vs the oracle's MoE arithmetic."""
     L = O.lib()
