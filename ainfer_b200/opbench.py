@@ -1,0 +1,108 @@
+"""Operator and short-decode microbenchmarks of the B200 decode path.
+
+  python -m ainfer_b200.opbench gemv [--m 1] [--n 151936] [--k 2048] [--reps 20] [--sweep]
+      INT4 g128 GEMV (Int4GemvA8) on seeded device-generated weights: ms and GB/s
+      of algorithmic bytes per launch, cold L2 (a >126 MB buffer is rewritten
+      between launches). --sweep runs the operator sweep shapes
+      M in {1,2,4,8} x (N,K) in {(512,2048),(4096,2048),(8192,2048),(151936,2048),(2048,512)}.
+  python -m ainfer_b200.opbench decode [--model small] [--prompt 4] [--steps 8]
+      A short greedy decode of a synthetic model preset through the runtime
+      (small enough to sit under a profiler).
+
+Prints one JSON object per line. Timing uses device timestamps on the
+execution queue.
+"""
+import argparse
+import json
+import sys
+
+import numpy as np
+
+from . import cuda_abi, runtime, synth_key
+
+GEMV_MAT = np.dtype([("P", "<u8"), ("S", "<u8"), ("Y", "<u8"), ("e0", "<u8"), ("e1", "<u8"), ("e2", "<u8"),
+                     ("row_start", "<i4"), ("N", "<i4"), ("epi", "<i4"), ("ldy", "<i4")])
+KERNEL_BY_M = {1: "Int4GemvA8", 2: "Int4GemvA8M2", 4: "Int4GemvA8M4", 8: "Int4GemvA8M8"}
+
+
+def gemv_bytes(N, K, M):
+    """Algorithmic bytes of one launch: packed nibbles + bf16 scales, INT8 activations + fp32 group
+    scales, fp32 outputs."""
+    return N * K * 0.515625 + M * (K + (K // 128) * 4) + M * N * 4
+
+
+def rows_per_group(K):
+    rt = 4 if K <= 1024 else (2 if K == 2048 else 1)
+    return 8 * rt * (32 // min(K // 32, 32))
+
+
+def gemv_once(dev, N, K, M=1, reps=20, flush=True):
+    dP, dS, dY = dev.alloc(N * K // 2), dev.alloc(N * K // 128 * 2), dev.zeros(M * N * 4)
+    k = dev.kernel("SynthInt4")
+    k.set_arg(0, dP); k.set_arg(1, dS); k.set_arg(2, synth_key(0, f"opbench.{N}.{K}"), "u64")
+    k.set_arg(3, N * K // 128, "u64"); k.set_arg(4, 0.02)
+    k.launch(dev.info().sm_count * 8)
+    rng = np.random.default_rng(0)
+    xq = dev.upload(rng.integers(-127, 128, (M, K), dtype=np.int8))
+    sq = dev.upload(np.full((M, K // 128), 0.01, np.float32))
+    tab = np.zeros(1, GEMV_MAT)
+    tab[0]["P"], tab[0]["S"], tab[0]["Y"], tab[0]["N"], tab[0]["ldy"] = dP, dS, dY, N, N
+    g = dev.kernel(KERNEL_BY_M[M])
+    groups = max(1, min((N + rows_per_group(K) - 1) // rows_per_group(K), dev.info().sm_count * 8))
+    g.set_args(dev.upload(tab.view(np.uint8)), 1, N, xq, sq, K, M)
+    e0, e1 = dev.event(), dev.event()
+    for _ in range(3):
+        g.launch(groups)
+    total = 0.0
+    for _ in range(reps):
+        if flush:
+            dev.flush_l2()
+        e0.record(); g.launch(groups); e1.record()
+        total += e0.elapsed_ms(e1)
+    dev.sync()
+    for p in (dP, dS, dY):
+        dev.free(p)
+    ms = total / reps
+    b = gemv_bytes(N, K, M)
+    return {"op": "int4_gemv_a8", "M": M, "N": N, "K": K, "ms": ms, "gbs": b / ms / 1e6, "bytes": b,
+            "groups": groups, "flops": 2.0 * M * N * K, "tflops": 2.0 * M * N * K / ms / 1e9}
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser()
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    g = sub.add_parser("gemv")
+    g.add_argument("--m", type=int, default=1)
+    g.add_argument("--n", type=int, default=151936)
+    g.add_argument("--k", type=int, default=2048)
+    g.add_argument("--reps", type=int, default=20)
+    g.add_argument("--sweep", action="store_true")
+    g.add_argument("--no-flush", action="store_true")
+    d = sub.add_parser("decode")
+    d.add_argument("--model", default="small")
+    d.add_argument("--prompt", type=int, default=4)
+    d.add_argument("--steps", type=int, default=8)
+    d.add_argument("--per-layer", action="store_true")
+    args = ap.parse_args(argv)
+    dev = cuda_abi.Device(0)
+    if args.cmd == "gemv":
+        shapes = ([(m, n, k) for (n, k) in [(512, 2048), (4096, 2048), (8192, 2048), (151936, 2048), (2048, 512)]
+                   for m in (1, 2, 4, 8)] if args.sweep else [(args.m, args.n, args.k)])
+        for (m, n, k) in shapes:
+            print(json.dumps(gemv_once(dev, n, k, m, args.reps, not args.no_flush)), flush=True)
+    else:
+        model = runtime.Model(dev, f"synth:{args.model}:seed=0")
+        sess = runtime.Session(model, args.prompt + args.steps + 8,
+                               runtime.Session.PER_LAYER_LISTS if args.per_layer else 0)
+        prompt = (np.arange(args.prompt, dtype=np.int32) * 7919 + 13) % model.config["vocab"]
+        toks, ms = sess.generate(prompt, args.steps, timed=True)
+        print(json.dumps({"op": "decode", "model": args.model, "prompt": args.prompt, "steps": args.steps,
+                          "ms_per_token": ms / args.steps, "launches_per_token": sess.launches_per_token(),
+                          "tokens": [int(t) for t in toks]}), flush=True)
+        sess.close(); model.close()
+    dev.close()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
