@@ -274,6 +274,36 @@ static int check_launch(ainfer_kernel_t k, uint32_t groups, uint32_t *smem) {
       return fail(k->dev, AINFER_ERR_INVALID, std::string("shared memory request too large for ") + k->desc->name);
     }
   }
+  if (k->desc->cooperative) {
+    // blocks of such a kernel wait on each other: every group must be resident at once
+    int per_sm = 0;
+    cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k->desc->fn, k->desc->threads, *smem);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return fail(k->dev, AINFER_ERR_DEVICE, std::string("occupancy query failed for ") + k->desc->name);
+    }
+    if ((long)groups > (long)per_sm * k->dev->sm_count) {
+      char b[200];
+      std::snprintf(b, sizeof b, "%s: %u groups cannot be co-resident (at most %d x %d)", k->desc->name,
+                    groups, per_sm, k->dev->sm_count);
+      return fail(k->dev, AINFER_ERR_INVALID, b);
+    }
+  }
+  return AINFER_OK;
+}
+
+int ainfer_kernel_max_groups(ainfer_kernel_t k, uint32_t *groups) {
+  if (!k || !groups) return AINFER_ERR_INVALID;
+  uint32_t smem = k->desc->smem_fn ? k->desc->smem_fn(k->args.data()) : k->desc->smem_bytes;
+  if (smem > 48 * 1024) {
+    if (cudaFuncSetAttribute(k->desc->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+      cudaGetLastError();
+      return fail(k->dev, AINFER_ERR_INVALID, std::string("shared memory request too large for ") + k->desc->name);
+    }
+  }
+  int per_sm = 0;
+  CU(k->dev, cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k->desc->fn, k->desc->threads, smem));
+  *groups = (uint32_t)per_sm * (uint32_t)k->dev->sm_count;
   return AINFER_OK;
 }
 
@@ -283,7 +313,10 @@ int ainfer_kernel_launch(ainfer_device_t dev, ainfer_kernel_t k, uint32_t groups
   int r = check_launch(k, groups, &smem);
   if (r) return r;
   void *params[1] = {k->args.data()};
-  CU(dev, cudaLaunchKernel(k->desc->fn, dim3(groups), dim3(k->desc->threads), params, smem, dev->stream));
+  if (k->desc->cooperative)
+    CU(dev, cudaLaunchCooperativeKernel(k->desc->fn, dim3(groups), dim3(k->desc->threads), params, smem, dev->stream));
+  else
+    CU(dev, cudaLaunchKernel(k->desc->fn, dim3(groups), dim3(k->desc->threads), params, smem, dev->stream));
   dev->launches += 1;
   return AINFER_OK;
 }
@@ -318,6 +351,12 @@ int ainfer_list_append_launch(ainfer_list_t l, ainfer_kernel_t k, uint32_t group
   np.kernelParams = params;
   cudaGraphNode_t node;
   CU(l->dev, cudaGraphAddKernelNode(&node, l->graph, deps(l), l->has_last ? 1 : 0, &np));
+  if (k->desc->cooperative) {
+    cudaKernelNodeAttrValue v;
+    std::memset(&v, 0, sizeof v);
+    v.cooperative = 1;
+    CU(l->dev, cudaGraphKernelNodeSetAttribute(node, cudaKernelNodeAttributeCooperative, &v));
+  }
   l->last = node;
   l->has_last = true;
   l->launches += 1;

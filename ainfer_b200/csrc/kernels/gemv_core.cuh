@@ -157,9 +157,9 @@ __device__ __forceinline__ void warp_rows_dot_paired(const LaneRows<RT> &rows, c
 // Quantises M fp32 vectors of K elements (per-128 activation quantiser,
 // tools/cmdlist/kernels.cpp:551-579) straight into the staged shared-memory
 // form. One warp per group; same smem layout as stage_act.
-__device__ __forceinline__ StagedAct stage_act_from_f32(unsigned char *smem,
-                                                        const float *__restrict__ x, int K, int M,
-                                                        long x_stride) {
+template <bool kGlobalSrc = true>
+__device__ __forceinline__ StagedAct stage_act_from_f32(unsigned char *smem, const float *x, int K,
+                                                        int M, long x_stride) {
   uint32_t *xw = reinterpret_cast<uint32_t *>(smem);
   const int G = K / 128;
   int *gs = reinterpret_cast<int *>(smem + (size_t)M * K);
@@ -167,7 +167,8 @@ __device__ __forceinline__ StagedAct stage_act_from_f32(unsigned char *smem,
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
   for (int i = warp; i < M * G; i += warps) {
     int m = i / G, g = i % G;
-    float4 v = *reinterpret_cast<const float4 *>(x + m * x_stride + (long)g * 128 + lane * 4);
+    const float4 *src = reinterpret_cast<const float4 *>(x + m * x_stride + (long)g * 128 + lane * 4);
+    float4 v = kGlobalSrc ? __ldcg(src) : *src;  // shared-memory sources take the plain load
     float mx = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
     mx = warp_max(mx);
     float s = mx / 127.0f;
@@ -205,11 +206,11 @@ __device__ __forceinline__ StagedAct stage_act(unsigned char *smem, const int8_t
   float *sqs = reinterpret_cast<float *>(smem + (size_t)M * K + (size_t)M * G * 4);
   for (int i = threadIdx.x; i < M * (K / 8); i += blockDim.x) {
     int m = i / (K / 8), j = i % (K / 8);
-    uint2 v = *reinterpret_cast<const uint2 *>(xq + m * xq_stride + (long)j * 8);
+    uint2 v = __ldcg(reinterpret_cast<const uint2 *>(xq + m * xq_stride + (long)j * 8));
     xw[2 * i] = __byte_perm(v.x, v.y, 0x6420);
     xw[2 * i + 1] = __byte_perm(v.x, v.y, 0x7531);
   }
-  for (int i = threadIdx.x; i < M * G; i += blockDim.x) sqs[i] = sq[(i / G) * sq_stride + (i % G)];
+  for (int i = threadIdx.x; i < M * G; i += blockDim.x) sqs[i] = __ldcg(sq + (i / G) * sq_stride + (i % G));
   __syncthreads();
   for (int i = threadIdx.x; i < M * G; i += blockDim.x) {
     int s = 0;

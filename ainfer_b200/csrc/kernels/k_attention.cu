@@ -1,276 +1,24 @@
-// Gated GQA decode attention over an INT8 KV cache, split over the sequence.
-//   AttnPrep    = SplitQK + BatchNorm(q,k) + RopeApply + KvAppend of the
-//                 reference (tools/cmdlist/kernels.cpp:429-462,656-684; recorded
-//                 at tools/decode/decode_l0.cpp:567-597), with the BF16 append
-//                 replaced by the per-token-per-head INT8 quantiser.
-//   AttnSplit   = the score/softmax/weighted-V body of AttnCore
-//                 (kernels.cpp:210-304) for one 64-token chunk of one KV head,
-//                 all query heads of the group sharing each K/V row read.
-//   AttnCombine = merges the chunk partials in ascending order, applies the
-//                 sigmoid output gate (kernels.cpp:291-302) and the activation
-//                 quantiser that feeds o_proj.
-// The reference runs one work-item per query head and re-reads K/V per head;
-// here a K/V row is read once per KV head and the sequence is spread over SMs.
-#include "common.cuh"
+// Kernel entries of the gated GQA decode attention; bodies in attention_core.cuh
+// (shared with the persistent decode kernel).
+#include "attention_core.cuh"
 
 namespace ainfer {
 
-constexpr int kAttnChunk = 64;  // tokens per split (fixed: part of the arithmetic contract)
-constexpr int kHeadDim = 256;
+__global__ void __launch_bounds__(256) AttnPrep(const AttnPrepArgs a) { attn_prep_body(a, blockIdx.x, gridDim.x); }
+__global__ void __launch_bounds__(256) AttnSplit(const AttnSplitArgs a) { attn_split_dispatch(a, blockIdx.x, gridDim.x); }
+__global__ void __launch_bounds__(256) AttnCombine(const AttnCombineArgs a) { attn_combine_body(a, blockIdx.x, gridDim.x); }
 
-// ------------------------------------------------------------- AttnPrep ---
-struct AttnPrepArgs {
-  const float *Q16;     // [nQ][2*D]: per head content D | gate D
-  const float *K16;     // [nKV][D]
-  const float *V16;     // [nKV][D]
-  const float *QNW;     // [D] q_norm weight
-  const float *KNW;     // [D] k_norm weight
-  const float *Cos;     // [max_ctx][rot]
-  const float *Sin;
-  const int32_t *Ctrl;  // position = Ctrl[1]
-  float *Qn;            // out [nQ][D]
-  int8_t *Kc;           // [max_ctx][nKV][D]
-  int8_t *Vc;
-  uint16_t *Ks;         // fp16 scales [max_ctx][nKV]
-  uint16_t *Vs;
-  int32_t nQ, nKV, rot, max_ctx;
-  float eps;
-};
-
-// quantise one 256-wide row held as x[i] = row[lane + 32*i]
-__device__ __forceinline__ void kv_quant_store(const float (&x)[8], int lane, int8_t *dst,
-                                               uint16_t *sdst) {
-  float m = 0.0f;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(x[i]));
-  m = warp_max(m);
-  float s = m / 127.0f;
-  if (s == 0.0f) s = 1.0f;
-  uint16_t h = f32_to_f16(s);
-  float sf = f16_to_f32(h);
-  if (sf == 0.0f) { sf = 1.0f; h = 0x3C00u; }
-  if (lane == 0) *sdst = h;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) dst[lane + 32 * i] = (int8_t)quant_round(x[i], sf);
-}
-
-__global__ void __launch_bounds__(256) AttnPrep(const AttnPrepArgs a) {
-  constexpr int D = kHeadDim;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int rows = a.nQ + 2 * a.nKV;
-  int pos = a.Ctrl[CTRL_POS];
-  int p = pos < a.max_ctx ? pos : a.max_ctx - 1;  // clamp, kernels.cpp:456
-  for (int r = blockIdx.x * 8 + warp; r < rows; r += gridDim.x * 8) {
-    float x[8];
-    if (r >= a.nQ + a.nKV) {  // V row: quantise only
-      int h = r - a.nQ - a.nKV;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) x[i] = a.V16[(size_t)h * D + lane + 32 * i];
-      kv_quant_store(x, lane, a.Vc + ((size_t)p * a.nKV + h) * D, a.Vs + (size_t)p * a.nKV + h);
-      continue;
-    }
-    const bool isq = r < a.nQ;
-    const int h = isq ? r : r - a.nQ;
-    const float *src = isq ? a.Q16 + (size_t)h * 2 * D : a.K16 + (size_t)h * D;
-    const float *w = isq ? a.QNW : a.KNW;
-    double ss = 0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      x[i] = src[lane + 32 * i];
-      double d = (double)x[i];
-      ss = ss + d * d;
-    }
-    ss = warp_tree_sum(ss);
-    float inv = 1.0f / sqrtf((float)(ss / (double)D) + a.eps);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) x[i] = (x[i] * inv) * (1.0f + w[lane + 32 * i]);
-    // NeoX half rotation on the leading rot dims: pairs (d, d + rot/2). With
-    // rot = 64 both members of a pair sit in the same lane (i = 0 and 1).
-    const int half = a.rot / 2;
-    if (half == 32) {
-      float c = a.Cos[(size_t)pos * a.rot + lane], s = a.Sin[(size_t)pos * a.rot + lane];
-      float x0 = x[0], x1 = x[1];
-      x[0] = x0 * c - x1 * s;
-      x[1] = x0 * s + x1 * c;
-    }
-    if (isq) {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) a.Qn[(size_t)h * D + lane + 32 * i] = x[i];
-    } else {
-      kv_quant_store(x, lane, a.Kc + ((size_t)p * a.nKV + h) * D, a.Ks + (size_t)p * a.nKV + h);
-    }
-  }
-}
 #define F(f) AINFER_ARG(AttnPrepArgs, f)
 AINFER_REGISTER(AttnPrep, AttnPrepArgs, 256, 8, 0, nullptr, F(Q16), F(K16), F(V16), F(QNW), F(KNW),
                 F(Cos), F(Sin), F(Ctrl), F(Qn), F(Kc), F(Vc), F(Ks), F(Vs), F(nQ), F(nKV), F(rot),
                 F(max_ctx), F(eps));
 #undef F
 
-// ------------------------------------------------------------ AttnSplit ---
-struct AttnSplitArgs {
-  const float *Qn;      // [nQ][D]
-  const int8_t *Kc;     // [max_ctx][nKV][D]
-  const int8_t *Vc;
-  const uint16_t *Ks;   // [max_ctx][nKV]
-  const uint16_t *Vs;
-  const int32_t *Ctrl;  // T = Ctrl[2] (active_length)
-  float *Pm;            // [nQ][max_chunks]   chunk max
-  float *Pse;           // [nQ][max_chunks]   chunk sum of exp
-  float *Pacc;          // [nQ][max_chunks][D] chunk weighted V
-  int32_t nQ, nKV, max_ctx, max_chunks;
-};
-
-template <int GQ>  // query heads per KV head
-__device__ __forceinline__ void attn_split_body(const AttnSplitArgs &a) {
-  constexpr int D = kHeadDim, C = kAttnChunk;
-  __shared__ float sc[GQ][C];   // scores, then p = w * v_scale
-  __shared__ float hmax[GQ], hse[GQ];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
-  int T = a.Ctrl[CTRL_LEN];
-  if (T > a.max_ctx) T = a.max_ctx;  // clamp, kernels.cpp:227-228
-  const int nch = (T + C - 1) / C;
-  const float scale = 1.0f / sqrtf((float)D);
-  for (int item = blockIdx.x; item < nch * a.nKV; item += gridDim.x) {
-    const int c = item / a.nKV, kv = item % a.nKV;
-    const int t0 = c * C, t1 = min(T, t0 + C), nt = t1 - t0;
-    // q rows of this group: lane holds dims 8*lane .. 8*lane+7 of each head
-    float q[GQ][8];
-#pragma unroll
-    for (int g = 0; g < GQ; ++g) {
-      const float4 *qp = reinterpret_cast<const float4 *>(a.Qn + (size_t)(kv * GQ + g) * D + lane * 8);
-      float4 v0 = qp[0], v1 = qp[1];
-      q[g][0] = v0.x; q[g][1] = v0.y; q[g][2] = v0.z; q[g][3] = v0.w;
-      q[g][4] = v1.x; q[g][5] = v1.y; q[g][6] = v1.z; q[g][7] = v1.w;
-    }
-    // phase 1: scores. warp w takes tokens t0+w, t0+w+8, ...
-    for (int tt = warp; tt < nt; tt += 8) {
-      const int t = t0 + tt;
-      uint2 kw = ldg_stream8(a.Kc + ((size_t)t * a.nKV + kv) * D + lane * 8);
-      float ks = f16_to_f32(a.Ks[(size_t)t * a.nKV + kv]);
-      float kf[8];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        kf[j] = (float)(int)(int8_t)((kw.x >> (8 * j)) & 0xFF);
-        kf[4 + j] = (float)(int)(int8_t)((kw.y >> (8 * j)) & 0xFF);
-      }
-#pragma unroll
-      for (int g = 0; g < GQ; ++g) {
-        float acc = 0.0f;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc = fmaf(q[g][j], kf[j], acc);
-        acc = warp_tree_sum(acc);
-        if (lane == 0) sc[g][tt] = (acc * ks) * scale;
-      }
-    }
-    __syncthreads();
-    // phase 2: per head max, weights, sum of exp (ascending t)
-    if (tid < GQ) {
-      float mx = -INFINITY;
-      for (int tt = 0; tt < nt; ++tt) mx = fmaxf(mx, sc[tid][tt]);
-      hmax[tid] = mx;
-    }
-    __syncthreads();
-    for (int i = tid; i < GQ * nt; i += 256) {
-      int g = i / nt, tt = i % nt;
-      sc[g][tt] = det_expf(sc[g][tt] - hmax[g]);
-    }
-    __syncthreads();
-    if (tid < GQ) {
-      float se = 0.0f;
-      for (int tt = 0; tt < nt; ++tt) se = se + sc[tid][tt];
-      hse[tid] = se;
-    }
-    __syncthreads();
-    for (int i = tid; i < GQ * nt; i += 256) {
-      int g = i / nt, tt = i % nt;
-      sc[g][tt] = sc[g][tt] * f16_to_f32(a.Vs[(size_t)(t0 + tt) * a.nKV + kv]);
-    }
-    __syncthreads();
-    // phase 3: thread d accumulates dim d for all heads of the group, ascending t
-    float acc[GQ];
-#pragma unroll
-    for (int g = 0; g < GQ; ++g) acc[g] = 0.0f;
-    const int8_t *vp = a.Vc + ((size_t)t0 * a.nKV + kv) * D + tid;
-    for (int tt = 0; tt < nt; ++tt) {
-      float v = (float)(int)vp[(size_t)tt * a.nKV * D];
-#pragma unroll
-      for (int g = 0; g < GQ; ++g) acc[g] = fmaf(sc[g][tt], v, acc[g]);
-    }
-#pragma unroll
-    for (int g = 0; g < GQ; ++g) {
-      size_t slot = (size_t)(kv * GQ + g) * a.max_chunks + c;
-      a.Pacc[slot * D + tid] = acc[g];
-      if (tid == 0) {
-        a.Pm[slot] = hmax[g];
-        a.Pse[slot] = hse[g];
-      }
-    }
-    __syncthreads();
-  }
-}
-
-__global__ void __launch_bounds__(256) AttnSplit(const AttnSplitArgs a) {
-  switch (a.nQ / a.nKV) {
-    case 1: attn_split_body<1>(a); break;
-    case 2: attn_split_body<2>(a); break;
-    case 4: attn_split_body<4>(a); break;
-    case 6: attn_split_body<6>(a); break;
-    case 8: attn_split_body<8>(a); break;
-    default: break;  // rejected on the host
-  }
-}
 #define F(f) AINFER_ARG(AttnSplitArgs, f)
 AINFER_REGISTER(AttnSplit, AttnSplitArgs, 256, 1, 0, nullptr, F(Qn), F(Kc), F(Vc), F(Ks), F(Vs),
                 F(Ctrl), F(Pm), F(Pse), F(Pacc), F(nQ), F(nKV), F(max_ctx), F(max_chunks));
 #undef F
 
-// ---------------------------------------------------------- AttnCombine ---
-struct AttnCombineArgs {
-  const float *Pm, *Pse, *Pacc;
-  const float *Q16;     // gate = Q16[h][D + d]
-  const int32_t *Ctrl;
-  int8_t *Q8;           // [nQ*D] quantised gated output
-  float *SQ;            // [nQ*D/128]
-  float *Att;           // optional fp32 copy
-  int32_t nQ, max_ctx, max_chunks;
-};
-__global__ void __launch_bounds__(256) AttnCombine(const AttnCombineArgs a) {
-  constexpr int D = kHeadDim, C = kAttnChunk;
-  __shared__ float wmax[8];
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  int T = a.Ctrl[CTRL_LEN];
-  if (T > a.max_ctx) T = a.max_ctx;
-  const int nch = (T + C - 1) / C;
-  for (int h = blockIdx.x; h < a.nQ; h += gridDim.x) {
-    const float *pm = a.Pm + (size_t)h * a.max_chunks;
-    const float *pse = a.Pse + (size_t)h * a.max_chunks;
-    const float *pacc = a.Pacc + (size_t)h * a.max_chunks * D;
-    float M = -INFINITY;
-    for (int c = 0; c < nch; ++c) M = fmaxf(M, pm[c]);
-    float se = 0.0f, acc = 0.0f;
-    for (int c = 0; c < nch; ++c) {
-      float f = det_expf(pm[c] - M);
-      se = fmaf(pse[c], f, se);
-      acc = fmaf(pacc[(size_t)c * D + tid], f, acc);
-    }
-    float o = acc / se;
-    float gate = a.Q16[(size_t)h * 2 * D + D + tid];
-    float y = o / (1.0f + det_expf(-gate));
-    if (a.Att) a.Att[(size_t)h * D + tid] = y;
-    // activation quantiser: groups of 128 = 4 warps
-    float m = warp_max(fabsf(y));
-    if (lane == 0) wmax[warp] = m;
-    __syncthreads();
-    int g0 = (warp >> 2) * 4;
-    m = fmaxf(fmaxf(wmax[g0], wmax[g0 + 1]), fmaxf(wmax[g0 + 2], wmax[g0 + 3]));
-    float s = m / 127.0f;
-    if (s == 0.0f) s = 1.0f;
-    if ((tid & 127) == 0) a.SQ[(size_t)h * 2 + (tid >> 7)] = s;
-    a.Q8[(size_t)h * D + tid] = (int8_t)quant_round(y, s);
-    __syncthreads();
-  }
-}
 #define F(f) AINFER_ARG(AttnCombineArgs, f)
 AINFER_REGISTER(AttnCombine, AttnCombineArgs, 256, 1, 0, nullptr, F(Pm), F(Pse), F(Pacc), F(Q16),
                 F(Ctrl), F(Q8), F(SQ), F(Att), F(nQ), F(max_ctx), F(max_chunks));

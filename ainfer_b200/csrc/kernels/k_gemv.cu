@@ -1,126 +1,24 @@
-// Int4GemvA8: the weight-streaming GEMV of the decode loop (batch <= 8).
-// Replaces the reference's Int4Gemv (tools/cmdlist/kernels.cpp:148-193) and,
-// through per-matrix epilogues, the single-purpose kernels that follow it in
-// the recorded layer lists (tools/decode/decode_l0.cpp:611-621,630-638,663):
-// ResAddF, SsmConv, BetaG. One launch covers several matrices that share the
-// same quantised activation (e.g. in_proj_qkv, in_proj_z, in_proj_b, in_proj_a).
-#include "../common/tables.h"
-#include "gemv_core.cuh"
+// Kernel entries of the INT4 x INT8 GEMV; row code in gemv_stage.cuh (shared
+// with the persistent decode kernel).
+#include "gemv_stage.cuh"
 
 namespace ainfer {
-
-struct Int4GemvA8Args {
-  const GemvMat *mats;
-  int32_t nmats;
-  int32_t total_rows;
-  const int8_t *XQ;   // [M][K] natural order
-  const float *SQ;    // [M][K/128]
-  int32_t K;
-  int32_t M;
-};
-
-__device__ __forceinline__ void gemv_epilogue(const GemvMat &mt, int n, int m, float acc) {
-  switch (mt.epi) {
-    case EPI_STORE:
-      mt.Y[(size_t)m * mt.ldy + n] = acc;
-      break;
-    case EPI_RESADD:
-      mt.Y[(size_t)m * mt.ldy + n] = mt.e0[(size_t)m * mt.ldy + n] + acc;
-      break;
-    case EPI_CONV_SILU: {
-      float *cs = mt.e1 + (size_t)n * 3;
-      const float *cw = mt.e0 + (size_t)n * 4;
-      float h0 = cs[0], h1 = cs[1], h2 = cs[2];
-      float a = h0 * cw[0];
-      a = a + h1 * cw[1];
-      a = a + h2 * cw[2];
-      a = a + acc * cw[3];
-      mt.Y[n] = a / (1.0f + det_expf(-a));
-      cs[0] = h1;
-      cs[1] = h2;
-      cs[2] = acc;
-      break;
-    }
-    case EPI_BETA:
-      mt.Y[n] = 1.0f / (1.0f + det_expf(-acc));
-      break;
-    case EPI_GDECAY: {
-      float sa = acc + mt.e2[n];
-      float soft = sa > 20.0f ? sa : det_logf(1.0f + det_expf(sa));
-      mt.Y[n] = (-det_expf(mt.e0[n])) * soft;
-      break;
-    }
-  }
-}
-
-template <int K, int M, int RT>
-__device__ __forceinline__ void gemv_body(const Int4GemvA8Args &a, unsigned char *smem,
-                                          const GemvMat *smats) {
-  using Gm = RowGeom<K>;
-  StagedAct act = stage_act(smem, a.XQ, a.SQ, K, M, K, K / 128);  // syncs inside
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int warps = blockDim.x >> 5;
-  constexpr int ROWS_PER_WARP = RT * Gm::RPW;
-  const long tile_rows = (long)warps * ROWS_PER_WARP;
-  for (long base = (long)blockIdx.x * tile_rows; base < a.total_rows;
-       base += (long)gridDim.x * tile_rows) {
-    long row0 = base + (long)warp * ROWS_PER_WARP;
-    if (row0 >= a.total_rows) continue;
-    // Per-lane row -> matrix lookup (rows are global over the table, nmats <= 8;
-    // lanes of one warp may fall into different matrices).
-    float acc[RT][M];
-    LaneRows<RT> rows;
-    int mi[RT];
-    long lrow[RT];
-#pragma unroll
-    for (int p = 0; p < RT; ++p) {
-      long r = row0 + (long)p * Gm::RPW + lane / Gm::LPR;
-      int idx = 0;
-      for (int i = 1; i < a.nmats; ++i)
-        if (r >= smats[i].row_start) idx = i;
-      mi[p] = idx;
-      lrow[p] = r - smats[idx].row_start;
-      rows.ok[p] = r < a.total_rows;
-      long lr = rows.ok[p] ? lrow[p] : 0;
-      rows.P[p] = smats[idx].P + lr * (K / 2);
-      rows.S[p] = smats[idx].S + lr * Gm::G;
-    }
-    warp_rows_dot<K, M, RT>(rows, act, acc);
-#pragma unroll
-    for (int p = 0; p < RT; ++p) {
-      long r = row0 + (long)p * Gm::RPW + lane / Gm::LPR;
-      if (r < a.total_rows && (lane % Gm::LPR) == 0) {
-        const GemvMat &mt = smats[mi[p]];
-#pragma unroll
-        for (int m = 0; m < M; ++m) gemv_epilogue(mt, (int)lrow[p], m, acc[p][m]);
-      }
-    }
-  }
-}
 
 extern __shared__ __align__(16) unsigned char gemv_smem[];
 
 template <int M>
-__device__ __forceinline__ void gemv_dispatch_k(const Int4GemvA8Args &a) {
+__device__ __forceinline__ void gemv_kernel(const Int4GemvA8Args &a) {
   __shared__ GemvMat smats[8];
   if (threadIdx.x < a.nmats) smats[threadIdx.x] = a.mats[threadIdx.x];  // synced by stage_act
-  switch (a.K) {
-    case 128: gemv_body<128, M, 4>(a, gemv_smem, smats); break;
-    case 256: gemv_body<256, M, 4>(a, gemv_smem, smats); break;
-    case 512: gemv_body<512, M, 4>(a, gemv_smem, smats); break;
-    case 1024: gemv_body<1024, M, 4>(a, gemv_smem, smats); break;
-    case 2048: gemv_body<2048, M, 2>(a, gemv_smem, smats); break;
-    case 4096: gemv_body<4096, M, 1>(a, gemv_smem, smats); break;
-    case 8192: gemv_body<8192, M, 1>(a, gemv_smem, smats); break;
-    default: break;  // rejected on the host before launch
-  }
+  StagedAct act = stage_act(gemv_smem, a.XQ, a.SQ, a.K, M, a.K, a.K / 128);
+  gemv_dispatch_k<M>(a, act, smats, blockIdx.x, gridDim.x);
 }
 
 // One entry point per batch width so that register allocation follows M.
-__global__ void __launch_bounds__(256) Int4GemvA8(const Int4GemvA8Args a) { gemv_dispatch_k<1>(a); }
-__global__ void __launch_bounds__(256) Int4GemvA8M2(const Int4GemvA8Args a) { gemv_dispatch_k<2>(a); }
-__global__ void __launch_bounds__(256) Int4GemvA8M4(const Int4GemvA8Args a) { gemv_dispatch_k<4>(a); }
-__global__ void __launch_bounds__(256) Int4GemvA8M8(const Int4GemvA8Args a) { gemv_dispatch_k<8>(a); }
+__global__ void __launch_bounds__(256) Int4GemvA8(const Int4GemvA8Args a) { gemv_kernel<1>(a); }
+__global__ void __launch_bounds__(256) Int4GemvA8M2(const Int4GemvA8Args a) { gemv_kernel<2>(a); }
+__global__ void __launch_bounds__(256) Int4GemvA8M4(const Int4GemvA8Args a) { gemv_kernel<4>(a); }
+__global__ void __launch_bounds__(256) Int4GemvA8M8(const Int4GemvA8Args a) { gemv_kernel<8>(a); }
 
 static uint32_t gemv_smem_fn(const void *args) {
   const Int4GemvA8Args *a = (const Int4GemvA8Args *)args;

@@ -1,0 +1,247 @@
+// Mixture-of-experts block of the decode loop: RouterTopK, ExpertGateUp,
+// ExpertDownCombine. The reference's MLP is dense (gate/up GEMV, SiluMul,
+// quantise, down GEMV, ResAddF: tools/decode/decode_l0.cpp:666-674); each
+// expert here is that same MLP, the routing around it has no reference
+// counterpart and follows the arithmetic stated with each kernel.
+#pragma once
+#include "../common/tables.h"
+#include "gemv_core.cuh"
+
+namespace ainfer {
+
+// ----------------------------------------------------------- RouterTopK ---
+// logits[e] = sum_k bf16(Wr[e][k]) * hn[k]: 32 lanes, lane l takes k =
+// (i*32+l)*8+j, fma chain in (i, j) order, then the lane tree. The last block
+// to finish runs softmax over all experts (max-subtracted, sum over 32 strided
+// lanes + tree), top-k by (probability desc, index asc), renormalises the k
+// weights in rank order, and evaluates the shared-expert gate sigmoid.
+struct RouterTopKArgs {
+  const uint16_t *Wr;    // [E][H] bf16 router
+  const uint16_t *Wsg;   // [H] bf16 shared-expert gate row (null: no shared expert)
+  const float *Hn;       // [H] normalised activations (fp32)
+  float *Logits;         // [E+1] scratch
+  uint32_t *Counter;     // zero-initialised arrival counter, left at zero
+  int32_t *SelIdx;       // [k+1]: routed expert ids in rank order, then E (shared slot)
+  float *SelW;           // [k+1]: renormalised weights, then sigmoid(shared gate)
+  float *NearGap;        // [1] relative gap between the k-th and (k+1)-th probability
+  int32_t E, H, k;
+};
+// Router logits: one warp per row (experts, then the shared-expert gate row).
+__device__ __forceinline__ void router_logits_rows(const RouterTopKArgs &a, int blk, int nblk) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rows = a.E + (a.Wsg ? 1 : 0);
+  for (int e = blk * 8 + warp; e < rows; e += nblk * 8) {
+    const uint16_t *w = e < a.E ? a.Wr + (size_t)e * a.H : a.Wsg;
+    float acc = 0.0f;
+    for (int i = 0; i < a.H / 256; ++i) {
+      int k0 = (i * 32 + lane) * 8;
+      uint4 wv = *reinterpret_cast<const uint4 *>(w + k0);
+      float4 x0 = __ldcg(reinterpret_cast<const float4 *>(a.Hn + k0));
+      float4 x1 = __ldcg(reinterpret_cast<const float4 *>(a.Hn + k0 + 4));
+      acc = fmaf(u2f(wv.x << 16), x0.x, acc);
+      acc = fmaf(u2f(wv.x & 0xFFFF0000u), x0.y, acc);
+      acc = fmaf(u2f(wv.y << 16), x0.z, acc);
+      acc = fmaf(u2f(wv.y & 0xFFFF0000u), x0.w, acc);
+      acc = fmaf(u2f(wv.z << 16), x1.x, acc);
+      acc = fmaf(u2f(wv.z & 0xFFFF0000u), x1.y, acc);
+      acc = fmaf(u2f(wv.w << 16), x1.z, acc);
+      acc = fmaf(u2f(wv.w & 0xFFFF0000u), x1.w, acc);
+    }
+    acc = warp_tree_sum(acc);
+    if (lane == 0) a.Logits[e] = acc;
+  }
+}
+
+// Selection by one warp: softmax over E logits, top-k by (probability desc,
+// index asc), renormalised weights, shared-expert gate. NI = ceil(E/32) values
+// per lane. Outputs may live in shared or global memory.
+template <int NI>
+__device__ __forceinline__ void router_select_warp(const float *lg, int E, int k, bool has_shared,
+                                                   int32_t *sel_idx, float *sel_w, float *near_gap) {
+  const int lane = threadIdx.x & 31;
+  float p[NI];
+  bool used[NI];
+  float m = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < NI; ++i) {
+    int e = lane + 32 * i;
+    p[i] = e < E ? __ldcg(lg + e) : -INFINITY;
+    used[i] = e >= E;
+    m = fmaxf(m, p[i]);
+  }
+  m = warp_max(m);
+  float sum = 0.0f;
+#pragma unroll
+  for (int i = 0; i < NI; ++i) {
+    int e = lane + 32 * i;
+    if (e < E) {
+      p[i] = det_expf(p[i] - m);
+      sum = sum + p[i];
+    }
+  }
+  sum = warp_tree_sum(sum);
+#pragma unroll
+  for (int i = 0; i < NI; ++i)
+    if (lane + 32 * i < E) p[i] = p[i] / sum;
+  float s = 0.0f, lastp = 0.0f;
+  float wsel = 0.0f;  // lane j keeps the weight of rank j (k <= 32)
+  for (int j = 0; j <= k && j < E; ++j) {
+    float bv = -1.0f;
+    int bi = 0x7FFFFFFF;
+#pragma unroll
+    for (int i = 0; i < NI; ++i)
+      if (!used[i] && p[i] > bv) { bv = p[i]; bi = lane + 32 * i; }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      float ov = __shfl_xor_sync(kFull, bv, off);
+      int oi = __shfl_xor_sync(kFull, bi, off);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (j == k) {
+      if (lane == 0) *near_gap = lastp > 0.0f ? (lastp - bv) / lastp : 0.0f;
+      break;
+    }
+    if ((bi & 31) == lane) {
+#pragma unroll
+      for (int i = 0; i < NI; ++i)
+        if (i == (bi >> 5)) used[i] = true;
+    }
+    if (lane == j) wsel = bv;
+    if (lane == 0) sel_idx[j] = bi;
+    s = s + bv;
+    lastp = bv;
+  }
+  if (k >= E && lane == 0) *near_gap = 1.0f;
+  if (lane < k) sel_w[lane] = wsel / s;
+  if (lane == 0) {
+    sel_idx[k] = E;
+    sel_w[k] = has_shared ? 1.0f / (1.0f + det_expf(-__ldcg(lg + E))) : 0.0f;
+  }
+}
+__device__ __forceinline__ void router_select(const float *lg, int E, int k, bool has_shared,
+                                              int32_t *sel_idx, float *sel_w, float *near_gap) {
+  if (E <= 64) router_select_warp<2>(lg, E, k, has_shared, sel_idx, sel_w, near_gap);
+  else if (E <= 512) router_select_warp<16>(lg, E, k, has_shared, sel_idx, sel_w, near_gap);
+  else router_select_warp<32>(lg, E, k, has_shared, sel_idx, sel_w, near_gap);
+}
+
+
+
+
+// --------------------------------------------------------- ExpertGateUp ---
+// For every active slot s (routed experts in rank order, then the shared
+// expert) and every intermediate row n: g = gate_e[n].h, u = up_e[n].h (W4A8
+// GEMV), Act[s][n] = (g / (1 + exp(-g))) * u  (SiluMul, kernels.cpp:29-37).
+struct ExpertGateUpArgs {
+  const ExpertW *Experts;  // [E+1]
+  const int32_t *SelIdx;   // [slots]
+  const int8_t *XQ;        // [H] quantised hidden
+  const float *SQ;         // [H/128]
+  float *Act;              // [slots][I]
+  int32_t slots, I, H;
+  int32_t slot_begin;      // first slot this launch handles (expert-parallel ranks)
+};
+// act: the staged quantised hidden vector; blk/nblk: this block's share of the rows.
+template <int K>
+__device__ __forceinline__ void gateup_rows(const ExpertGateUpArgs &a, const StagedAct &act, int blk,
+                                            int nblk) {
+  using Gm = RowGeom<K>;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  const long total = (long)a.slots * a.I;
+  const long tile = (long)warps * Gm::RPW;
+  for (long base = (long)blk * tile; base < total; base += (long)nblk * tile) {
+    long r = base + (long)warp * Gm::RPW + lane / Gm::LPR;
+    if (base + (long)warp * Gm::RPW >= total) continue;
+    bool ok = r < total;
+    int s = ok ? (int)(r / a.I) : 0, n = ok ? (int)(r % a.I) : 0;
+    const ExpertW &ew = a.Experts[a.SelIdx[a.slot_begin + s]];
+    LaneRows<2> rows;
+    rows.ok[0] = rows.ok[1] = ok;
+    rows.P[0] = ew.gP + (long)n * (K / 2);
+    rows.S[0] = ew.gS + (long)n * Gm::G;
+    rows.P[1] = ew.uP + (long)n * (K / 2);
+    rows.S[1] = ew.uS + (long)n * Gm::G;
+    float acc[2][1];
+    warp_rows_dot<K, 1, 2>(rows, act, acc);
+    if (ok && (lane % Gm::LPR) == 0) {
+      float g = acc[0][0], u = acc[1][0];
+      a.Act[(size_t)(a.slot_begin + s) * a.I + n] = (g / (1.0f + det_expf(-g))) * u;
+    }
+  }
+}
+__device__ __forceinline__ void gateup_dispatch(const ExpertGateUpArgs &a, const StagedAct &act, int blk,
+                                                int nblk) {
+  switch (a.H) {
+    case 256: gateup_rows<256>(a, act, blk, nblk); break;
+    case 512: gateup_rows<512>(a, act, blk, nblk); break;
+    case 1024: gateup_rows<1024>(a, act, blk, nblk); break;
+    case 2048: gateup_rows<2048>(a, act, blk, nblk); break;
+    case 4096: gateup_rows<4096>(a, act, blk, nblk); break;
+    default: break;
+  }
+}
+
+
+// ---------------------------------------------------- ExpertDownCombine ---
+// Quantises each slot's activation (per-128 quantiser), y_s[n] = down_e[n].act_s,
+// then out[n] = Res[n] + (sum_s w_s * y_s[n] in rank order, + sg * y_shared[n]),
+// products and sums unfused. (Down GEMV + ResAddF, decode_l0.cpp:672-674.)
+struct ExpertDownCombineArgs {
+  const ExpertW *Experts;
+  const int32_t *SelIdx;  // [slots]
+  const float *SelW;      // [slots] (last = shared-expert gate when has_shared)
+  const float *Act;       // [slots][I]
+  const float *Res;       // [H] residual input
+  float *X;               // [H] output residual stream
+  float *Moe;             // optional [H]: the MoE output before the residual add
+  int32_t slots, I, H;
+};
+template <int K, int RT>
+__device__ __forceinline__ void down_rows(const ExpertDownCombineArgs &a, const StagedAct &act, int blk,
+                                          int nblk) {
+  using Gm = RowGeom<K>;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  const long tile = (long)warps * Gm::RPW;
+  for (long base = (long)blk * tile; base < a.H; base += (long)nblk * tile) {
+    if (base + (long)warp * Gm::RPW >= a.H) continue;
+    long n = base + (long)warp * Gm::RPW + lane / Gm::LPR;
+    bool ok = n < a.H;
+    LaneRows<RT> rows;
+#pragma unroll
+    for (int p = 0; p < RT; ++p) {
+      rows.ok[p] = ok && p < a.slots;
+      const ExpertW &ew = a.Experts[a.SelIdx[p < a.slots ? p : 0]];
+      rows.P[p] = ew.dP + (ok ? n : 0) * (K / 2);
+      rows.S[p] = ew.dS + (ok ? n : 0) * Gm::G;
+    }
+    float y[RT];
+    warp_rows_dot_paired<K, RT>(rows, act, y);
+    if (ok && (lane % Gm::LPR) == 0) {
+      float acc = 0.0f;
+#pragma unroll
+      for (int p = 0; p < RT; ++p)
+        if (p < a.slots) acc = acc + a.SelW[p] * y[p];
+      if (a.Moe) a.Moe[n] = acc;
+      a.X[n] = __ldcg(a.Res + n) + acc;
+    }
+  }
+}
+template <int K>
+__device__ __forceinline__ void down_dispatch_k(const ExpertDownCombineArgs &a, const StagedAct &act,
+                                                int blk, int nblk) {
+  if (a.slots <= 6) down_rows<K, 6>(a, act, blk, nblk);
+  else down_rows<K, 12>(a, act, blk, nblk);
+}
+__device__ __forceinline__ void down_dispatch(const ExpertDownCombineArgs &a, const StagedAct &act, int blk,
+                                              int nblk) {
+  switch (a.I) {
+    case 128: down_dispatch_k<128>(a, act, blk, nblk); break;
+    case 256: down_dispatch_k<256>(a, act, blk, nblk); break;
+    case 512: down_dispatch_k<512>(a, act, blk, nblk); break;
+    case 1024: down_dispatch_k<1024>(a, act, blk, nblk); break;
+    default: break;
+  }
+}
+
+
+}  // namespace ainfer

@@ -24,6 +24,9 @@ struct KernelDesc {
   uint32_t smem_bytes;  // fixed dynamic shared memory (0 if none / static only)
   // optional: dynamic shared memory as a function of the argument bytes
   uint32_t (*smem_fn)(const void *args);
+  // 1: blocks synchronise with each other, so the launch must be cooperative
+  // (all groups co-resident) and the group count may not exceed what fits
+  int cooperative;
 };
 
 void register_kernel(const KernelDesc &d);
@@ -45,4 +48,10 @@ struct Registrar {
   static const ::ainfer::ArgField NAME##_fields[] = {__VA_ARGS__};                           \
   static ::ainfer::Registrar NAME##_registrar(::ainfer::KernelDesc{                          \
       #NAME, (const void *)NAME, (uint32_t)sizeof(T), NAME##_fields,                         \
-      (int)(sizeof(NAME##_fields) / sizeof(NAME##_fields[0])), THREADS, ITEMS, SMEM, SMEMFN})
+      (int)(sizeof(NAME##_fields) / sizeof(NAME##_fields[0])), THREADS, ITEMS, SMEM, SMEMFN, 0})
+
+#define AINFER_REGISTER_COOP(NAME, T, THREADS, ITEMS, SMEM, SMEMFN, ...)                     \
+  static const ::ainfer::ArgField NAME##_fields[] = {__VA_ARGS__};                           \
+  static ::ainfer::Registrar NAME##_registrar(::ainfer::KernelDesc{                          \
+      #NAME, (const void *)NAME, (uint32_t)sizeof(T), NAME##_fields,                         \
+      (int)(sizeof(NAME##_fields) / sizeof(NAME##_fields[0])), THREADS, ITEMS, SMEM, SMEMFN, 1})

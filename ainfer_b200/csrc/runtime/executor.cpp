@@ -5,6 +5,7 @@
 #include <algorithm>
 #include <cstring>
 
+#include "../common/mega_plan.h"
 #include "../common/tables.h"
 
 namespace ainfer {
@@ -265,6 +266,137 @@ void record_tail(Recorder &r, bool advance) {
            s->history, (int32_t)s->argmax_parts, (int32_t)(advance ? 1 : 0), (int32_t)s->max_ctx);
 }
 
+GemvMat make_mat(Session *s, int &status, const std::string &name, int K, float *Y, int epi,
+                 const float *e0, float *e1, const float *e2) {
+  GemvMat g;
+  std::memset(&g, 0, sizeof g);
+  DeviceTensor t = s->m->tensor(name);
+  if (!t.entry) { s->err = "missing " + name; status = 1; return g; }
+  if ((int)t.entry->shape[1] != K || t.entry->storage != DT_INT4_SYM_G128) {
+    s->err = "unexpected shape/storage of " + name;
+    status = 2;
+    return g;
+  }
+  g.P = (const uint8_t *)t.data;
+  g.S = (const uint16_t *)t.scales;
+  g.Y = Y; g.e0 = e0; g.e1 = e1; g.e2 = e2;
+  g.N = (int)t.entry->shape[0];
+  g.epi = epi;
+  g.ldy = g.N;
+  return g;
+}
+
+// Builds the device plan of the persistent decode kernel and records the two
+// one-launch lists (token step with tail, prompt step).
+int build_mega(Session *s) {
+  DeviceModel *m = s->m;
+  const ModelConfig &c = m->cfg;
+  const int H = c.hidden, D = c.head_dim, nQ = c.q_heads, nKV = c.kv_heads, nV = c.lin_v_heads;
+  const int C = c.conv_dim(), VD = c.value_dim(), E = c.experts;
+  int status = 0;
+  std::vector<MegaLayer> layers((size_t)c.layers);
+  for (int L = 0; L < c.layers && !status; ++L) {
+    MegaLayer &ly = layers[(size_t)L];
+    std::memset(&ly, 0, sizeof ly);
+    const std::string p = layer_prefix(L);
+    const int slot = m->slot[L];
+    ly.in_norm = m->in_norm + (size_t)L * H;
+    ly.post_norm = m->post_norm + (size_t)L * H;
+    if (c.layer_types[L] == 'A') {
+      ly.type = 1;
+      ly.m[0] = make_mat(s, status, p + "self_attn.q_proj.weight", H, s->Q16, EPI_STORE, nullptr, nullptr, nullptr);
+      ly.m[1] = make_mat(s, status, p + "self_attn.k_proj.weight", H, s->K16, EPI_STORE, nullptr, nullptr, nullptr);
+      ly.m[2] = make_mat(s, status, p + "self_attn.v_proj.weight", H, s->V16, EPI_STORE, nullptr, nullptr, nullptr);
+      ly.m[4] = make_mat(s, status, p + "self_attn.o_proj.weight", nQ * D, s->Tmp, EPI_RESADD, s->X, nullptr, nullptr);
+      ly.q_norm = m->q_norm + (size_t)slot * D;
+      ly.k_norm = m->k_norm + (size_t)slot * D;
+      size_t kv_off = (size_t)slot * s->max_ctx * nKV;
+      ly.Kc = s->Kc + kv_off * D; ly.Vc = s->Vc + kv_off * D;
+      ly.Ks = s->Ks + kv_off; ly.Vs = s->Vs + kv_off;
+    } else {
+      ly.type = 0;
+      ly.m[0] = make_mat(s, status, p + "linear_attn.in_proj_qkv.weight", H, s->Mx, EPI_CONV_SILU,
+                         m->conv_w + (size_t)slot * C * 4, s->conv + (size_t)slot * C * 3, nullptr);
+      ly.m[1] = make_mat(s, status, p + "linear_attn.in_proj_z.weight", H, s->Z, EPI_STORE, nullptr, nullptr, nullptr);
+      ly.m[2] = make_mat(s, status, p + "linear_attn.in_proj_b.weight", H, s->Bt, EPI_BETA, nullptr, nullptr, nullptr);
+      ly.m[3] = make_mat(s, status, p + "linear_attn.in_proj_a.weight", H, s->Gt, EPI_GDECAY,
+                         m->a_log + (size_t)slot * nV, nullptr, m->dt_bias + (size_t)slot * nV);
+      ly.m[4] = make_mat(s, status, p + "linear_attn.out_proj.weight", VD, s->Tmp, EPI_RESADD, s->X, nullptr, nullptr);
+      ly.S = s->S + (size_t)slot * nV * 128 * 128;
+      ly.lin_norm = m->lin_norm + (size_t)slot * c.lin_head_dim;
+    }
+    DeviceTensor router = m->tensor(p + "mlp.gate.weight"), sg = m->tensor(p + "mlp.shared_expert_gate.weight");
+    if (!router.entry || (c.shared_experts && !sg.entry)) { s->err = "missing " + p + "mlp.gate.weight"; status = 1; break; }
+    ly.router = (const uint16_t *)router.data;
+    ly.shared_gate = c.shared_experts ? (const uint16_t *)sg.data : nullptr;
+    ly.experts = (const ExpertW *)m->expert_tables + (size_t)L * (E + 1);
+  }
+  if (status) return status;
+  MegaPlan P;
+  std::memset(&P, 0, sizeof P);
+  P.H = H; P.layers = c.layers; P.vocab = c.vocab;
+  P.nQ = nQ; P.nKV = nKV; P.rot = c.rotary_dim; P.nK = c.lin_k_heads; P.nV = nV;
+  P.E = E; P.topk = c.top_k; P.slots = c.top_k + (c.shared_experts ? 1 : 0); P.I = c.expert_inter;
+  P.max_ctx = s->max_ctx; P.max_chunks = s->max_chunks; P.history_cap = s->max_ctx;
+  P.argmax_parts = s->argmax_parts;
+  P.eps = (float)c.rms_eps;
+  DeviceTensor emb = m->tensor("model.language_model.embed_tokens.weight");
+  if (!emb.entry) { s->err = "missing model.language_model.embed_tokens.weight"; return 1; }
+  P.emb = (const uint16_t *)emb.data;
+  P.final_norm = m->final_norm;
+  P.lm_head = make_mat(s, status, "lm_head.weight", H, s->Logits, EPI_STORE, nullptr, nullptr, nullptr);
+  if (status) return status;
+  P.Cos = m->rope_cos; P.Sin = m->rope_sin;
+  P.X = s->X; P.Tmp = s->Tmp; P.Mx = s->Mx; P.Z = s->Z; P.Bt = s->Bt; P.Gt = s->Gt; P.O = s->O;
+  P.Q16 = s->Q16; P.K16 = s->K16; P.V16 = s->V16; P.Qn = s->Qn; P.Pm = s->Pm; P.Pse = s->Pse; P.Pacc = s->Pacc;
+  P.RLogits = s->RLogits; P.Act = s->Act; P.Logits = s->Logits; P.PV = s->PV; P.PI = s->PI;
+  P.Q8 = s->Q8; P.SQ = s->SQ; P.SelIdx = s->SelIdx; P.SelW = s->SelW; P.NearGap = s->NearGap;
+  P.ctrl = s->ctrl; P.history = s->history; P.out_tok = s->out_tok; P.ids = s->ids;
+  P.layer_out = s->layer_out; P.routed = s->routed; P.near_gap = s->near_gap;
+  if (salloc(s, 1, &s->bar_count) || salloc(s, 1, &s->mega_error)) return 1;
+  P.bar_count = s->bar_count; P.error = s->mega_error;
+  MegaLayer *dl = nullptr;
+  if (salloc(s, layers.size(), &dl, false)) return 1;
+  s->mega_layers = dl;
+  P.L = dl;
+  MegaPlan *dp = nullptr;
+  if (salloc(s, 1, &dp, false)) return 1;
+  s->mega_plan = dp;
+  if (ainfer_memcpy_h2d(s->dev, dl, layers.data(), layers.size() * sizeof(MegaLayer)) != AINFER_OK ||
+      ainfer_memcpy_h2d(s->dev, dp, &P, sizeof P) != AINFER_OK) {
+    s->err = ainfer_last_error(s->dev);
+    return 1;
+  }
+  ainfer_kernel_t k = nullptr;
+  if (ainfer_kernel_get(s->dev, "DecodeStepMega", &k) != AINFER_OK) { s->err = "entry DecodeStepMega not found"; return 1; }
+  s->kernels["DecodeStepMega"] = k;
+  const MegaPlan *cdp = dp;
+  int32_t mode = 1;
+  ainfer_kernel_set_arg(k, 0, sizeof cdp, &cdp);
+  ainfer_kernel_set_arg(k, 1, sizeof mode, &mode);
+  uint32_t groups = 0;
+  if (ainfer_kernel_max_groups(k, &groups) != AINFER_OK || groups == 0) {
+    s->err = std::string("DecodeStepMega cannot be made resident: ") + ainfer_last_error(s->dev);
+    return 1;
+  }
+  groups = std::min<uint32_t>(groups, (uint32_t)s->sm_count * 2);
+  if ((int)groups > s->argmax_parts) { s->err = "internal: argmax partial buffers too small"; return 3; }
+  for (int md = 1; md >= 0; --md) {
+    ainfer_list_t *l = md ? &s->gen_list : &s->body_list;
+    if (ainfer_list_create(s->dev, l) != AINFER_OK) { s->err = "list create failed"; return 1; }
+    mode = md;
+    ainfer_kernel_set_arg(k, 1, sizeof mode, &mode);
+    if (ainfer_list_append_fill(*l, s->bar_count, 0, 4) != AINFER_OK ||
+        ainfer_list_append_launch(*l, k, groups) != AINFER_OK || ainfer_list_close(*l) != AINFER_OK) {
+      s->err = std::string("recording the persistent step failed: ") + ainfer_last_error(s->dev);
+      return 1;
+    }
+  }
+  s->launches_per_token = 1;
+  s->mega = true;
+  return 0;
+}
+
 int close_list(Session *s, ainfer_list_t l) {
   if (ainfer_list_close(l) != AINFER_OK) { s->err = std::string("list close failed: ") + ainfer_last_error(s->dev); return 1; }
   return 0;
@@ -303,7 +435,7 @@ int session_create(DeviceModel *m, int max_ctx, int flags, Session **out, std::s
   const int C = std::max(c.conv_dim(), 1), VD = std::max(c.value_dim(), 1);
   const int n_kv_layers = c.n_attn() + c.mtp_layers;
   s->max_chunks = (max_ctx + 63) / 64;
-  s->argmax_parts = std::min(s->sm_count * 2, std::max(1, (c.vocab + 255) / 256));
+  s->argmax_parts = s->sm_count * 2;  // also the partial count of the persistent kernel (one per block)
   if (model_ensure_rope(m, max_ctx, s->err)) return fail(1);
   int r = 0;
   size_t n_kv = (size_t)n_kv_layers * max_ctx * nKV;
@@ -367,7 +499,9 @@ int session_create(DeviceModel *m, int max_ctx, int flags, Session **out, std::s
     if (ainfer_list_create(s->dev, l) != AINFER_OK) { s->err = "list create failed"; rec.status = 1; }
     rec.list = *l;
   };
-  if (flags & SESSION_PER_LAYER_LISTS) {
+  if (!(flags & (SESSION_PER_LAYER_LISTS | SESSION_MULTI_KERNEL))) {
+    rec.status = build_mega(s);
+  } else if (flags & SESSION_PER_LAYER_LISTS) {
     new_list(&s->embed_list);
     record_embed(rec);
     if (!rec.status) rec.status = close_list(s, s->embed_list);
@@ -464,6 +598,20 @@ static int run_token(Session *s, bool with_tail) {
   return 0;
 }
 
+// The persistent kernel reports a barrier that ran out of polls through a sticky
+// error word instead of hanging; surface it as a device error.
+static int check_mega_error(Session *s) {
+  if (!s->mega) return 0;
+  int32_t e = 0;
+  S_CHECK(ainfer_memcpy_d2h(s->dev, &e, s->mega_error, 4));
+  if (e != 0) {
+    s->err = "device error: a grid barrier of the persistent decode kernel timed out (status " +
+             std::to_string(e) + ")";
+    return 1;
+  }
+  return 0;
+}
+
 int session_step(Session *s, int token, int pos, int *out_token) {
   if (pos < 0 || pos >= s->max_ctx) {
     s->err = "context overflow: pos " + std::to_string(pos) + " >= MAXCTX " + std::to_string(s->max_ctx);
@@ -475,7 +623,7 @@ int session_step(Session *s, int token, int pos, int *out_token) {
   if (r) return r;
   S_CHECK(ainfer_memcpy_d2h(s->dev, s->host_tok, s->out_tok, 4));
   if (out_token) *out_token = s->host_tok[0];
-  return 0;
+  return check_mega_error(s);
 }
 
 int session_generate(Session *s, const int *prompt, int P, int G, int start_pos, int *out_tokens,
@@ -516,7 +664,7 @@ int session_generate(Session *s, const int *prompt, int P, int G, int start_pos,
   } else {
     S_CHECK(ainfer_sync(s->dev, UINT64_MAX));
   }
-  return 0;
+  return check_mega_error(s);
 }
 
 }  // namespace ainfer

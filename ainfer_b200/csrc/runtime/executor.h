@@ -18,7 +18,8 @@ namespace ainfer {
 
 enum SessionFlags {
   SESSION_DIAG = 1,             // keep per-layer residual stream, routed experts, near-tie gaps
-  SESSION_PER_LAYER_LISTS = 2   // one list per layer + embed + tail, executed and fenced one by one
+  SESSION_PER_LAYER_LISTS = 2,  // one list per layer + embed + tail, executed and fenced one by one
+  SESSION_MULTI_KERNEL = 4      // one list per token of ~450 stand-alone launches (default: one persistent launch)
 };
 
 struct Session {
@@ -62,6 +63,11 @@ struct Session {
   ainfer_list_t body_list = nullptr;   // embed + layers + ControlAdvance (prompt steps)
   std::vector<ainfer_list_t> layer_lists;  // per-layer mode
   ainfer_list_t embed_list = nullptr, tail_list = nullptr, advance_list = nullptr;
+  // persistent-kernel path: device plan, barrier counter, sticky error word
+  void *mega_plan = nullptr, *mega_layers = nullptr;
+  uint32_t *bar_count = nullptr;
+  int32_t *mega_error = nullptr;
+  bool mega = false;
   std::map<std::string, ainfer_kernel_t> kernels;
   std::vector<void *> owned;
   uint64_t launches_per_token = 0;

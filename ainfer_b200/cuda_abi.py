@@ -52,6 +52,7 @@ SIGNATURES = {
     "ainfer_kernel_query": (_i, [_vp, C.POINTER(_i), C.POINTER(_i), C.POINTER(_i)]),
     "ainfer_kernel_arg_size": (_i, [_vp, _u32, C.POINTER(_sz)]),
     "ainfer_kernel_set_arg": (_i, [_vp, _u32, _sz, _vp]),
+    "ainfer_kernel_max_groups": (_i, [_vp, C.POINTER(_u32)]),
     "ainfer_list_create": (_i, [_vp, _pp]),
     "ainfer_list_append_launch": (_i, [_vp, _vp, _u32]),
     "ainfer_list_append_memcpy": (_i, [_vp, _vp, _vp, _sz]),

@@ -83,6 +83,7 @@ def main(argv=None):
     d.add_argument("--prompt", type=int, default=4)
     d.add_argument("--steps", type=int, default=8)
     d.add_argument("--per-layer", action="store_true")
+    d.add_argument("--multi-kernel", action="store_true")
     args = ap.parse_args(argv)
     dev = cuda_abi.Device(0)
     if args.cmd == "gemv":
@@ -93,7 +94,8 @@ def main(argv=None):
     else:
         model = runtime.Model(dev, f"synth:{args.model}:seed=0")
         sess = runtime.Session(model, args.prompt + args.steps + 8,
-                               runtime.Session.PER_LAYER_LISTS if args.per_layer else 0)
+                               runtime.Session.PER_LAYER_LISTS if args.per_layer else
+                               (runtime.Session.MULTI_KERNEL if args.multi_kernel else 0))
         prompt = (np.arange(args.prompt, dtype=np.int32) * 7919 + 13) % model.config["vocab"]
         toks, ms = sess.generate(prompt, args.steps, timed=True)
         print(json.dumps({"op": "decode", "model": args.model, "prompt": args.prompt, "steps": args.steps,

@@ -135,6 +135,7 @@ class Model:
 class Session:
     DIAG = 1
     PER_LAYER_LISTS = 2
+    MULTI_KERNEL = 4
 
     def __init__(self, model, max_ctx, flags=0):
         self.model = model

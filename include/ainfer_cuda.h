@@ -90,6 +90,11 @@ const char *ainfer_kernel_name(int index);
  * (rows, heads, ...; 0 = the kernel strides over any group count). */
 int ainfer_kernel_query(ainfer_kernel_t k, int *arg_count, int *group_threads, int *items_per_group);
 int ainfer_kernel_arg_size(ainfer_kernel_t k, uint32_t index, size_t *size);
+/* Largest group count whose groups are all resident at once (occupancy x SM
+ * count, with the shared memory the current arguments ask for). Kernels whose
+ * groups wait on each other are launched cooperatively and refuse more. No
+ * counterpart in the reference: its kernels never synchronise across groups. */
+int ainfer_kernel_max_groups(ainfer_kernel_t k, uint32_t *groups);
 /* zeKernelSetArgumentValue, decode_l0.cpp:474-480. size must equal the
  * argument's size; value points at the bytes to copy. */
 int ainfer_kernel_set_arg(ainfer_kernel_t k, uint32_t index, size_t size, const void *value);

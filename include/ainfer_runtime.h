@@ -66,7 +66,9 @@ int ainfer_model_bytes(ainfer_model_t m, uint64_t *payload_bytes, uint64_t *scal
 /* ---- block-executor + token loop (decode_l0.cpp:270-295,544-825) ---- */
 enum {
   AINFER_SESSION_DIAG = 1,            /* per-layer residual dump (AINFER_DUMP0), routed experts, near-tie gaps */
-  AINFER_SESSION_PER_LAYER_LISTS = 2  /* one list per layer, fenced one by one, as the reference executes */
+  AINFER_SESSION_PER_LAYER_LISTS = 2, /* one list per layer, fenced one by one, as the reference executes */
+  AINFER_SESSION_MULTI_KERNEL = 4     /* one list per token of stand-alone launches; default is ONE persistent
+                                         cooperative launch per token (DecodeStepMega) */
 };
 int ainfer_session_create(ainfer_model_t m, int max_ctx, int flags, ainfer_session_t *out);
 int ainfer_session_destroy(ainfer_session_t s);

@@ -86,13 +86,14 @@ def test_device_fill_equals_file_upload(dev, mini_file):
     a.close(); b.close()
 
 
-def test_config1_mini_one_step_at_511_prior_tokens(dev, mini_file):
+@pytest.mark.parametrize("flags", [0, 4], ids=["persistent", "multi_kernel"])
+def test_config1_mini_one_step_at_511_prior_tokens(dev, mini_file, flags):
     """BASELINE config 1: mini model, one decode step at batch 1, seed 0, 511 cached tokens."""
     from ainfer_b200 import runtime
     model = runtime.Model(dev, mini_file)
     cfg = model.config
     max_ctx, prior = 520, 511
-    sess = runtime.Session(model, max_ctx, runtime.Session.DIAG)
+    sess = runtime.Session(model, max_ctx, runtime.Session.DIAG | flags)
     om = O.Model(path=mini_file)
     osess = O.Session(om, max_ctx)
     load_state(sess, osess, seeded_state(cfg, max_ctx, prior))
@@ -113,13 +114,14 @@ def test_config1_mini_one_step_at_511_prior_tokens(dev, mini_file):
     sess.close(); model.close(); osess.close(); om.close()
 
 
-def test_mini_greedy_256_steps_identical(dev, mini_file):
+@pytest.mark.parametrize("flags", [0, 4], ids=["persistent", "multi_kernel"])
+def test_mini_greedy_256_steps_identical(dev, mini_file, flags):
     """Greedy tokens identical over 256 decode steps after a seeded 16-token prompt."""
     from ainfer_b200 import runtime
     model = runtime.Model(dev, mini_file)
     V = model.config["vocab"]
     prompt = np.array([O.lib().orc_draw_u32(b"input.prompt", 0, i) % V for i in range(16)], np.int32)
-    sess = runtime.Session(model, 16 + 256 + 8)
+    sess = runtime.Session(model, 16 + 256 + 8, flags)
     got = sess.generate(prompt, 256)
     om = O.Model(path=mini_file)
     osess = O.Session(om, 16 + 256 + 8)
@@ -142,11 +144,17 @@ def test_tiny_fused_list_equals_per_layer_lists(dev, tiny_file):
     from ainfer_b200 import runtime
     model = runtime.Model(dev, tiny_file)
     prompt = np.array([5, 77, 300, 12], np.int32)
-    a = runtime.Session(model, 64)
+    a = runtime.Session(model, 64)                                    # one persistent launch per token
     b = runtime.Session(model, 64, runtime.Session.PER_LAYER_LISTS)
-    ta, tb = a.generate(prompt, 24), b.generate(prompt, 24)
-    assert ta.tolist() == tb.tolist()
+    c = runtime.Session(model, 64, runtime.Session.MULTI_KERNEL)      # one list of stand-alone launches
+    ta, tb, tc = a.generate(prompt, 24), b.generate(prompt, 24), c.generate(prompt, 24)
+    assert ta.tolist() == tb.tolist() == tc.tolist()
+    assert a.launches_per_token() == 1 and c.launches_per_token() > 20
     assert np.array_equal(a.read("S", np.float32), b.read("S", np.float32))
+    assert np.array_equal(a.read("S", np.float32), c.read("S", np.float32))
+    assert np.array_equal(a.read("Kc", np.int8), c.read("Kc", np.int8))
+    assert np.array_equal(a.logits(), c.logits())
+    c.close()
     om = O.Model(path=tiny_file)
     osess = O.Session(om, 64)
     want, _ = osess.decode_loop(prompt, 24)
