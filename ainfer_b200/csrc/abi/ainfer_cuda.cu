@@ -266,7 +266,7 @@ static int check_launch(ainfer_kernel_t k, uint32_t groups, uint32_t *smem) {
     }
   if (groups == 0) return fail(k->dev, AINFER_ERR_INVALID, "group count 0");
   *smem = k->desc->smem_fn ? k->desc->smem_fn(k->args.data()) : k->desc->smem_bytes;
-  if (*smem > 48 * 1024) {
+  if (*smem > 16 * 1024) {  // static + dynamic may pass 48 KB: opt in early
     cudaError_t e = cudaFuncSetAttribute(k->desc->fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)*smem);
     if (e != cudaSuccess) {
@@ -295,7 +295,7 @@ static int check_launch(ainfer_kernel_t k, uint32_t groups, uint32_t *smem) {
 int ainfer_kernel_max_groups(ainfer_kernel_t k, uint32_t *groups) {
   if (!k || !groups) return AINFER_ERR_INVALID;
   uint32_t smem = k->desc->smem_fn ? k->desc->smem_fn(k->args.data()) : k->desc->smem_bytes;
-  if (smem > 48 * 1024) {
+  if (smem > 16 * 1024) {
     if (cudaFuncSetAttribute(k->desc->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
       cudaGetLastError();
       return fail(k->dev, AINFER_ERR_INVALID, std::string("shared memory request too large for ") + k->desc->name);

@@ -55,6 +55,11 @@ struct MegaPlan {
   float *layer_out;         // [layers][H]
   int32_t *routed;          // [layers][topk+1]
   float *near_gap;          // [layers]
+  // optional stage clock (null when off): block 0 stores %globaltimer (ns) after every
+  // grid barrier, in order, up to stage_stamp_cap entries per launch
+  unsigned long long *stage_stamps;
+  int32_t stage_stamp_cap;
+  int32_t pad1;
   // grid barrier state: count is zeroed before every launch; error is sticky
   uint32_t *bar_count;
   int32_t *error;           // 0 ok, 1 a barrier wait ran out of spins

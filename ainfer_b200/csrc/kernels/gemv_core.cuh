@@ -12,6 +12,12 @@
 // Memory: a row is K/2 contiguous bytes; lanes read consecutive 16-byte chunks
 // (128-bit coalesced loads, kept out of L1), unpack nibbles in registers with
 // two logic ops per 8 weights and feed dp4a.
+//
+// Code shape: row loops are rolled (one pass of the warp per iteration, the
+// next pass' loads issued before the current pass' math) and the slow scalar
+// helpers are not inlined, so that the instructions a layer executes stay
+// resident in the instruction caches. A first version unrolled whole tiles
+// (34 KB of straight-line code per shape) and was bound by instruction fetch.
 #pragma once
 #include "common.cuh"
 
@@ -34,120 +40,65 @@ struct RowGeom {
   static constexpr int GPI = LPR / 4;                  // groups finished per iteration
 };
 
-// One lane's view of the rows it works on in a warp tile: for each of RT
-// passes the row's packed bytes, its scales and whether the row exists. Lanes
-// of a warp may point into different matrices.
-template <int RT>
-struct LaneRows {
-  const uint8_t *P[RT];
-  const uint16_t *S[RT];
-  bool ok[RT];
+// Registers of one pass: the lane's 16-byte chunks of its row (ITERS of them)
+// and, on the first lane of each quad, the group's weight scale.
+template <int K>
+struct PassRegs {
+  uint4 w[RowGeom<K>::ITERS];
+  float sc[RowGeom<K>::ITERS];
 };
 
-// Computes acc[p][m] for RT passes of RPW rows each (the lane's row in pass p
-// is described by rows.P[p]/S[p], already offset to the row start). All loads
-// of the tile are issued before any math.
-template <int K, int M, int RT>
-__device__ __forceinline__ void warp_rows_dot(const LaneRows<RT> &rows, const StagedAct &a,
-                                              float (&acc)[RT][M]) {
+// Issues the loads of one pass. P/S point at the lane's row; ok = the row exists.
+template <int K>
+__device__ __forceinline__ void pass_load(PassRegs<K> &r, const uint8_t *P, const uint16_t *S, bool ok) {
   using Gm = RowGeom<K>;
-  const int lane = threadIdx.x & 31;
-  const int cl = lane % Gm::LPR;
-  uint4 w[RT][Gm::ITERS];
-  float sc[RT][Gm::ITERS];
+  const int cl = (threadIdx.x & 31) % Gm::LPR;
 #pragma unroll
-  for (int p = 0; p < RT; ++p) {
-#pragma unroll
-    for (int it = 0; it < Gm::ITERS; ++it) {
-      int c = cl + Gm::LPR * it;
-      if (rows.ok[p] && c < Gm::CPR) {
-        w[p][it] = ldg_stream16(rows.P[p] + (long)c * 16);
-        sc[p][it] = (cl & 3) == 0 ? bf16_to_f32(__ldg(rows.S[p] + (c >> 2))) : 0.0f;
-      } else {
-        w[p][it] = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
-        sc[p][it] = 0.0f;
-      }
-    }
-  }
-#pragma unroll
-  for (int p = 0; p < RT; ++p) {
-#pragma unroll
-    for (int m = 0; m < M; ++m) acc[p][m] = 0.0f;
-#pragma unroll
-    for (int it = 0; it < Gm::ITERS; ++it) {
-      int c = cl + Gm::LPR * it;
-      int cc = c < Gm::CPR ? c : 0;
-      int g = cc >> 2;
-      float t[M];
-#pragma unroll
-      for (int m = 0; m < M; ++m) {
-        const uint4 *xm = a.x + (size_t)m * (K / 16);
-        int s = dot_chunk_biased(w[p][it], xm[2 * cc], xm[2 * cc + 1], 0);
-        s += __shfl_xor_sync(kFull, s, 1);
-        s += __shfl_xor_sync(kFull, s, 2);
-        int gs = s - 8 * a.gsum[m * Gm::G + g];
-        float v = (float)gs * sc[p][it];
-        t[m] = v * a.sq[m * Gm::G + g];
-      }
-      // replay the fp32 accumulation in ascending group order
-#pragma unroll
-      for (int j = 0; j < Gm::GPI; ++j) {
-        if (Gm::GPI * it + j < Gm::G) {
-#pragma unroll
-          for (int m = 0; m < M; ++m) {
-            float tj = __shfl_sync(kFull, t[m], (lane & ~(Gm::LPR - 1)) + 4 * j);
-            acc[p][m] = acc[p][m] + tj;
-          }
-        }
-      }
+  for (int it = 0; it < Gm::ITERS; ++it) {
+    int c = cl + Gm::LPR * it;
+    if (ok && c < Gm::CPR) {
+      r.w[it] = ldg_stream16(P + (long)c * 16);
+      r.sc[it] = (cl & 3) == 0 ? bf16_to_f32(__ldg(S + (c >> 2))) : 0.0f;
+    } else {
+      r.w[it] = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
+      r.sc[it] = 0.0f;
     }
   }
 }
 
-// Paired form: pass p is dotted with activation vector p only (each pass may
-// stream a different matrix, e.g. the down projections of the routed experts).
-template <int K, int RT>
-__device__ __forceinline__ void warp_rows_dot_paired(const LaneRows<RT> &rows, const StagedAct &a,
-                                                     float (&acc)[RT]) {
+// Dot of one pass with M activation vectors starting at vector v0: exact int32
+// group sums (four lanes per group), then the fp32 accumulation replayed in
+// ascending group order.
+template <int K, int M>
+__device__ __forceinline__ void pass_dot(const PassRegs<K> &r, const StagedAct &a, int v0, float (&acc)[M]) {
   using Gm = RowGeom<K>;
   const int lane = threadIdx.x & 31;
   const int cl = lane % Gm::LPR;
-  uint4 w[RT][Gm::ITERS];
-  float sc[RT][Gm::ITERS];
 #pragma unroll
-  for (int p = 0; p < RT; ++p) {
+  for (int m = 0; m < M; ++m) acc[m] = 0.0f;
 #pragma unroll
-    for (int it = 0; it < Gm::ITERS; ++it) {
-      int c = cl + Gm::LPR * it;
-      if (rows.ok[p] && c < Gm::CPR) {
-        w[p][it] = ldg_stream16(rows.P[p] + (long)c * 16);
-        sc[p][it] = (cl & 3) == 0 ? bf16_to_f32(__ldg(rows.S[p] + (c >> 2))) : 0.0f;
-      } else {
-        w[p][it] = make_uint4(0x88888888u, 0x88888888u, 0x88888888u, 0x88888888u);
-        sc[p][it] = 0.0f;
-      }
-    }
-  }
+  for (int it = 0; it < Gm::ITERS; ++it) {
+    int c = cl + Gm::LPR * it;
+    int cc = c < Gm::CPR ? c : 0;
+    int g = cc >> 2;
+    float t[M];
 #pragma unroll
-  for (int p = 0; p < RT; ++p) {
-    acc[p] = 0.0f;
-    const uint4 *xm = a.x + (size_t)p * (K / 16);
-#pragma unroll
-    for (int it = 0; it < Gm::ITERS; ++it) {
-      int c = cl + Gm::LPR * it;
-      int cc = c < Gm::CPR ? c : 0;
-      int g = cc >> 2;
-      int s = dot_chunk_biased(w[p][it], xm[2 * cc], xm[2 * cc + 1], 0);
+    for (int m = 0; m < M; ++m) {
+      const uint4 *xm = a.x + (size_t)(v0 + m) * (K / 16);
+      int s = dot_chunk_biased(r.w[it], xm[2 * cc], xm[2 * cc + 1], 0);
       s += __shfl_xor_sync(kFull, s, 1);
       s += __shfl_xor_sync(kFull, s, 2);
-      int gs = s - 8 * a.gsum[p * Gm::G + g];
-      float v = (float)gs * sc[p][it];
-      float t = v * a.sq[p * Gm::G + g];
+      int gs = s - 8 * a.gsum[(v0 + m) * Gm::G + g];
+      float v = (float)gs * r.sc[it];
+      t[m] = v * a.sq[(v0 + m) * Gm::G + g];
+    }
 #pragma unroll
-      for (int j = 0; j < Gm::GPI; ++j) {
-        if (Gm::GPI * it + j < Gm::G) {
-          float tj = __shfl_sync(kFull, t, (lane & ~(Gm::LPR - 1)) + 4 * j);
-          acc[p] = acc[p] + tj;
+    for (int j = 0; j < Gm::GPI; ++j) {
+      if (Gm::GPI * it + j < Gm::G) {
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+          float tj = __shfl_sync(kFull, t[m], (lane & ~(Gm::LPR - 1)) + 4 * j);
+          acc[m] = acc[m] + tj;
         }
       }
     }

@@ -1,6 +1,6 @@
 // Kernel entries of the INT4 x INT8 GEMV; row code in gemv_stage.cuh (shared
 // with the persistent decode kernel).
-#include "gemv_stage.cuh"
+#include "block_stages.cuh"
 
 namespace ainfer {
 
@@ -15,8 +15,18 @@ __device__ __forceinline__ void gemv_kernel(const Int4GemvA8Args &a) {
 }
 
 // One entry point per batch width so that register allocation follows M.
-__global__ void __launch_bounds__(256) Int4GemvA8(const Int4GemvA8Args a) { gemv_kernel<1>(a); }
-__global__ void __launch_bounds__(256) Int4GemvA8M2(const Int4GemvA8Args a) { gemv_kernel<2>(a); }
+// M = 1: the block-flattened form (block_dot.cuh); wider batches keep the warp-pass form.
+__global__ void __launch_bounds__(256, 2) Int4GemvA8(const Int4GemvA8Args a) {
+  __shared__ GemvMat smats[8];
+  __shared__ RowSeg segs[kMaxSegs];
+  __shared__ float T[kTCap];
+  __shared__ int ibox[4];
+  if (threadIdx.x < a.nmats) smats[threadIdx.x] = a.mats[threadIdx.x];  // synced by stage_act
+  StagedAct4 act = stage4(gemv_smem, a.XQ, a.SQ, a.K, 1, a.K, a.K / 128);
+  BlockScratch bs{segs, T, ibox};
+  gemv_block_dispatch(a.K, smats, a.nmats, a.total_rows, act, bs, blockIdx.x, gridDim.x);
+}
+__global__ void __launch_bounds__(256, 3) Int4GemvA8M2(const Int4GemvA8Args a) { gemv_kernel<2>(a); }
 __global__ void __launch_bounds__(256) Int4GemvA8M4(const Int4GemvA8Args a) { gemv_kernel<4>(a); }
 __global__ void __launch_bounds__(256) Int4GemvA8M8(const Int4GemvA8Args a) { gemv_kernel<8>(a); }
 

@@ -19,8 +19,7 @@
 #include "../common/mega_plan.h"
 #include "attention_core.cuh"
 #include "deltanet_core.cuh"
-#include "gemv_stage.cuh"
-#include "moe_core.cuh"
+#include "block_stages.cuh"
 #include "tail_core.cuh"
 
 namespace ainfer {
@@ -40,7 +39,22 @@ struct GridSync {
   int *error;
   unsigned epoch;
   unsigned nblk;
+  unsigned long long *stamps;  // optional stage clock (block 0 only)
+  int stamp_cap;
+  int nstamp;
 };
+
+// Stage clock: block 0 / thread 0 appends %globaltimer (ns) when the plan asks for it.
+__device__ __forceinline__ void stage_stamp(GridSync &g) {
+  if (g.stamps && threadIdx.x == 0) {
+    if (g.nstamp < g.stamp_cap) {
+      unsigned long long t;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+      g.stamps[g.nstamp] = t;
+    }
+    g.nstamp += 1;
+  }
+}
 
 __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned *p) {
   unsigned v;
@@ -76,6 +90,7 @@ __device__ __forceinline__ bool grid_barrier(GridSync &g) {
     s_fail = fail;
   }
   __syncthreads();
+  stage_stamp(g);
   return s_fail != 0;
 }
 
@@ -86,30 +101,28 @@ __device__ __forceinline__ void prefetch_l2(const void *p, size_t bytes) {
     asm volatile("prefetch.global.L2 [%0];" ::"l"(c + off));
 }
 
-// Prefetches the weight rows this block will read in a GEMV stage.
+// Prefetches the weight rows this block will read in a GEMV stage (same
+// contiguous row range as gemv_block deals out).
 __device__ __forceinline__ void prefetch_gemv(const GemvMat *mats, int nmats, int K, int blk, int nblk) {
-  const int tile = gemv_tile_rows(K);
-  int total = 0;
+  long total = 0;
   for (int i = 0; i < nmats; ++i) total += mats[i].N;
-  for (long base = (long)blk * tile; base < total; base += (long)nblk * tile) {
-    long r1 = base + tile < total ? base + tile : total;
-    int rs = 0;
-    for (int i = 0; i < nmats; ++i) {
-      long lo = base > rs ? base : rs, hi = r1 < rs + mats[i].N ? r1 : rs + mats[i].N;
-      if (lo < hi) {
-        prefetch_l2(mats[i].P + (lo - rs) * (K / 2), (size_t)(hi - lo) * (K / 2));
-        prefetch_l2(mats[i].S + (lo - rs) * (K / 128), (size_t)(hi - lo) * (K / 128) * 2);
-      }
-      rs += mats[i].N;
+  long lo, hi;
+  block_range(total, blk, nblk, lo, hi);
+  long rs = 0;
+  for (int i = 0; i < nmats; ++i) {
+    long a = lo > rs ? lo : rs, b = hi < rs + mats[i].N ? hi : rs + mats[i].N;
+    if (a < b) {
+      prefetch_l2(mats[i].P + (a - rs) * (K / 2), (size_t)(b - a) * (K / 2));
+      prefetch_l2(mats[i].S + (a - rs) * (K / 128), (size_t)(b - a) * (K / 128) * 2);
     }
+    rs += mats[i].N;
   }
 }
 
-// Runs one GEMV stage for this block: builds the launch's matrix table in
-// shared memory (row_start assigned here) and walks the block's row tiles.
-__device__ __forceinline__ void gemv_stage(const GemvMat *mats, int nmats, int K, const StagedAct &act,
-                                           GemvMat *smats, int blk, int nblk) {
-  __shared__ int s_total_rows;
+// Runs one GEMV stage for this block: builds the stage's matrix table in shared
+// memory (row_start assigned here) and processes the block's contiguous rows.
+__device__ __forceinline__ void gemv_stage(const GemvMat *mats, int nmats, int K, const StagedAct4 &act,
+                                           GemvMat *smats, const BlockScratch &bs, int blk, int nblk) {
   __syncthreads();  // smats may still be read by the previous stage
   if (threadIdx.x == 0) {
     int row = 0;
@@ -118,25 +131,26 @@ __device__ __forceinline__ void gemv_stage(const GemvMat *mats, int nmats, int K
       smats[i].row_start = row;
       row += mats[i].N;
     }
-    s_total_rows = row;
+    bs.ibox[2] = row;
   }
   __syncthreads();
-  Int4GemvA8Args a;
-  a.mats = nullptr;
-  a.nmats = nmats;
-  a.total_rows = s_total_rows;
-  a.XQ = nullptr;
-  a.SQ = nullptr;
-  a.K = K;
-  a.M = 1;
-  gemv_dispatch_k<1>(a, act, smats, blk, nblk);
+  const long total = bs.ibox[2];
+  // only the contraction widths a decode layer can have (the host refuses other shapes)
+  switch (K) {
+    case 256: gemv_block<256>(smats, nmats, total, act, bs, blk, nblk); break;
+    case 512: gemv_block<512>(smats, nmats, total, act, bs, blk, nblk); break;
+    case 1024: gemv_block<1024>(smats, nmats, total, act, bs, blk, nblk); break;
+    case 2048: gemv_block<2048>(smats, nmats, total, act, bs, blk, nblk); break;
+    case 4096: gemv_block<4096>(smats, nmats, total, act, bs, blk, nblk); break;
+    default: break;
+  }
 }
 
 // (1+w) RMSNorm + activation quantiser of one fp32 vector, result staged in
 // shared memory for the GEMV rows; ys keeps the normalised fp32 vector (the
 // router reads it). Same arithmetic as RmsNormQuant (k_norm.cu). src is either
 // a global fp32 vector or a BF16 embedding row.
-__device__ __forceinline__ StagedAct norm_quant_stage(const float *xg, const uint16_t *emb_row,
+__device__ __forceinline__ StagedAct4 norm_quant_stage(const float *xg, const uint16_t *emb_row,
                                                       const float *w, int N, float eps,
                                                       unsigned char *stage, float *ys,
                                                       float *x_copy_out) {
@@ -168,13 +182,13 @@ __device__ __forceinline__ StagedAct norm_quant_stage(const float *xg, const uin
   const float inv = s_inv;
   for (int j = lid; j < N; j += 256) ys[j] = (ys[j] * inv) * (1.0f + w[j]);
   __syncthreads();
-  return stage_act_from_f32<false>(stage, ys, N, 1, N);
+  return stage4_from_f32<false>(stage, ys, N, 1, N);
 }
 
 // Per-head gated RMSNorm (RmsInv + NormGated, tools/cmdlist/kernels.cpp:619-644)
 // of all heads into ys, then the activation quantiser staged for out_proj.
 // Same arithmetic as GatedNormQuant (k_norm.cu).
-__device__ __forceinline__ StagedAct gated_norm_stage(const float *O, const float *Z, const float *W,
+__device__ __forceinline__ StagedAct4 gated_norm_stage(const float *O, const float *Z, const float *W,
                                                       int heads, float eps, unsigned char *stage,
                                                       float *ys) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -197,7 +211,7 @@ __device__ __forceinline__ StagedAct gated_norm_stage(const float *O, const floa
     }
   }
   __syncthreads();
-  return stage_act_from_f32<false>(stage, ys, heads * 128, 1, heads * 128);
+  return stage4_from_f32<false>(stage, ys, heads * 128, 1, heads * 128);
 }
 
 // Router logits with the normalised activations held in shared memory.
@@ -227,18 +241,16 @@ __device__ __forceinline__ void router_rows_smem(const uint16_t *Wr, const uint1
   }
 }
 
-// Prefetch of one expert slot set: the down-projection rows this block reads in the next stage.
+// Prefetch of the down-projection rows this block reads in the next stage.
 __device__ __forceinline__ void prefetch_down(const ExpertW *experts, const int32_t *sel, int slots, int I,
                                               int H, int blk, int nblk) {
-  const int lpr = I / 32 < 32 ? I / 32 : 32;
-  const int tile = 8 * (32 / lpr);
-  for (long base = (long)blk * tile; base < H; base += (long)nblk * tile) {
-    long n1 = base + tile < H ? base + tile : H;
-    for (int s = 0; s < slots; ++s) {
-      const ExpertW &ew = experts[sel[s]];
-      prefetch_l2(ew.dP + base * (I / 2), (size_t)(n1 - base) * (I / 2));
-      prefetch_l2(ew.dS + base * (I / 128), (size_t)(n1 - base) * (I / 128) * 2);
-    }
+  long lo, hi;
+  block_range(H, blk, nblk, lo, hi);
+  if (lo >= hi) return;
+  for (int s = 0; s < slots; ++s) {
+    const ExpertW &ew = experts[sel[s]];
+    prefetch_l2(ew.dP + lo * (I / 2), (size_t)(hi - lo) * (I / 2));
+    prefetch_l2(ew.dS + lo * (I / 128), (size_t)(hi - lo) * (I / 128) * 2);
   }
 }
 
@@ -247,6 +259,8 @@ extern __shared__ __align__(16) unsigned char mega_smem[];
 __global__ void __launch_bounds__(256, 2) DecodeStepMega(const DecodeStepMegaArgs args) {
   const MegaPlan &P = *args.plan;
   __shared__ GemvMat smats[8];
+  __shared__ RowSeg s_segs[kMaxSegs];
+  __shared__ int s_ibox[4];
   __shared__ int32_t s_sel_idx[16];
   __shared__ float s_sel_w[16];
   __shared__ float s_gap;
@@ -254,8 +268,10 @@ __global__ void __launch_bounds__(256, 2) DecodeStepMega(const DecodeStepMegaArg
   __shared__ int s_ai[8];
   unsigned char *stage = mega_smem;
   float *ys = reinterpret_cast<float *>(mega_smem + kStageBytes);
+  const BlockScratch bs{s_segs, reinterpret_cast<float *>(mega_smem + kStageBytes + kYsFloats * 4), s_ibox};
   const int blk = blockIdx.x, nblk = gridDim.x;
-  GridSync gs{P.bar_count, P.error, 0u, (unsigned)nblk};
+  GridSync gs{P.bar_count, P.error, 0u, (unsigned)nblk, blk == 0 ? P.stage_stamps : nullptr, P.stage_stamp_cap, 0};
+  stage_stamp(gs);
   if (*(volatile int *)P.error != 0) return;  // a previous launch failed: stay out
   const int H = P.H;
   const int token = __ldcg(P.ctrl + CTRL_TOKEN);
@@ -264,23 +280,25 @@ __global__ void __launch_bounds__(256, 2) DecodeStepMega(const DecodeStepMegaArg
   for (int L = 0; L < P.layers; ++L) {
     const MegaLayer &ly = P.L[L];
     // ---- mixer input: (1+w) RMSNorm + quantiser, redundantly per block ----
-    StagedAct act = norm_quant_stage(P.X, L == 0 ? P.emb + (size_t)tok * H : nullptr, ly.in_norm, H, P.eps,
+    StagedAct4 act = norm_quant_stage(P.X, L == 0 ? P.emb + (size_t)tok * H : nullptr, ly.in_norm, H, P.eps,
                                      stage, ys, (L == 0 && blk == 0) ? P.X : nullptr);
     if (P.layer_out && L > 0 && blk == 0)
       for (int j = threadIdx.x; j < H; j += 256) P.layer_out[(size_t)(L - 1) * H + j] = __ldcg(P.X + j);
     if (ly.type == 0) {
       // in_proj qkv (+conv+SiLU), z, b (sigmoid), a (decay)
       prefetch_gemv(&ly.m[4], 1, P.nV * 128, blk, nblk);  // out_proj rows for two stages ahead
-      gemv_stage(&ly.m[0], 4, H, act, smats, blk, nblk);
+      stage_stamp(gs);  // norm + quant done
+      gemv_stage(&ly.m[0], 4, H, act, smats, bs, blk, nblk);
+      stage_stamp(gs);  // this block's rows done
       if (grid_barrier(gs)) return;
       DeltaNetStepArgs da{P.O, P.Mx, ly.S, P.Bt, P.Gt, P.nK, P.nV};
       deltanet_step_body(da, blk, nblk);
       if (grid_barrier(gs)) return;
       act = gated_norm_stage(P.O, P.Z, ly.lin_norm, P.nV, P.eps, stage, ys);
-      gemv_stage(&ly.m[4], 1, P.nV * 128, act, smats, blk, nblk);
+      gemv_stage(&ly.m[4], 1, P.nV * 128, act, smats, bs, blk, nblk);
     } else {
       prefetch_gemv(&ly.m[4], 1, P.nQ * 256, blk, nblk);
-      gemv_stage(&ly.m[0], 3, H, act, smats, blk, nblk);
+      gemv_stage(&ly.m[0], 3, H, act, smats, bs, blk, nblk);
       if (grid_barrier(gs)) return;
       AttnPrepArgs pa{P.Q16, P.K16, P.V16, ly.q_norm, ly.k_norm, P.Cos, P.Sin, P.ctrl, P.Qn,
                       ly.Kc, ly.Vc, ly.Ks, ly.Vs, P.nQ, P.nKV, P.rot, P.max_ctx, P.eps};
@@ -294,8 +312,8 @@ __global__ void __launch_bounds__(256, 2) DecodeStepMega(const DecodeStepMegaArg
       attn_combine_body(ca, blk, nblk);
       if (grid_barrier(gs)) return;
       __syncthreads();
-      act = stage_act(stage, P.Q8, P.SQ, P.nQ * 256, 1, P.nQ * 256, P.nQ * 2);
-      gemv_stage(&ly.m[4], 1, P.nQ * 256, act, smats, blk, nblk);
+      act = stage4(stage, P.Q8, P.SQ, P.nQ * 256, 1, P.nQ * 256, P.nQ * 2);
+      gemv_stage(&ly.m[4], 1, P.nQ * 256, act, smats, bs, blk, nblk);
     }
     // router rows of this block: ask for them while the projection's results settle
     {
@@ -312,7 +330,9 @@ __global__ void __launch_bounds__(256, 2) DecodeStepMega(const DecodeStepMegaArg
     if (grid_barrier(gs)) return;
     // ---- MoE: post norm, router, top-k, experts ----
     act = norm_quant_stage(P.Tmp, nullptr, ly.post_norm, H, P.eps, stage, ys, nullptr);
+    stage_stamp(gs);
     router_rows_smem(ly.router, ly.shared_gate, ys, P.RLogits, P.E, H, blk, nblk);
+    stage_stamp(gs);
     // next layer's first projections (or the LM head) stream in during the MoE stages
     if (L + 1 < P.layers) {
       const MegaLayer &nx = P.L[L + 1];
@@ -320,9 +340,10 @@ __global__ void __launch_bounds__(256, 2) DecodeStepMega(const DecodeStepMegaArg
     }
     if (grid_barrier(gs)) return;
     if (threadIdx.x < 32) {
-      router_select(P.RLogits, P.E, P.topk, ly.shared_gate != nullptr, s_sel_idx, s_sel_w, &s_gap);
+      router_select(P.RLogits, P.E, P.topk, ly.shared_gate != nullptr, ys, s_sel_idx, s_sel_w, &s_gap);
     }
     __syncthreads();
+    stage_stamp(gs);  // selection done
     if (blk == 0 && threadIdx.x <= P.topk) {
       P.SelIdx[threadIdx.x] = s_sel_idx[threadIdx.x];
       P.SelW[threadIdx.x] = s_sel_w[threadIdx.x];
@@ -334,15 +355,18 @@ __global__ void __launch_bounds__(256, 2) DecodeStepMega(const DecodeStepMegaArg
     }
     {
       ExpertGateUpArgs ga{ly.experts, s_sel_idx, nullptr, nullptr, P.Act, P.slots, P.I, H, 0};
-      gateup_dispatch(ga, act, blk, nblk);
+      gateup_block_dispatch(ga, act, bs, blk, nblk);
+      stage_stamp(gs);
       prefetch_down(ly.experts, s_sel_idx, P.slots, P.I, H, blk, nblk);
     }
     if (grid_barrier(gs)) return;
     {
       __syncthreads();
-      StagedAct dact = stage_act_from_f32<true>(stage, P.Act, P.I, P.slots, P.I);
+      StagedAct4 dact = stage4_from_f32<true>(stage, P.Act, P.I, P.slots, P.I);
+      stage_stamp(gs);
       ExpertDownCombineArgs xa{ly.experts, s_sel_idx, s_sel_w, P.Act, P.Tmp, P.X, nullptr, P.slots, P.I, H};
-      down_dispatch(xa, dact, blk, nblk);
+      down_block_dispatch(xa, dact, bs, blk, nblk);
+      stage_stamp(gs);
     }
     if (grid_barrier(gs)) return;
   }
@@ -363,8 +387,8 @@ __global__ void __launch_bounds__(256, 2) DecodeStepMega(const DecodeStepMegaArg
   }
   // ---- tail: final norm, LM head, first-max-wins argmax, control update ----
   {
-    StagedAct act = norm_quant_stage(P.X, nullptr, P.final_norm, H, P.eps, stage, ys, nullptr);
-    gemv_stage(&P.lm_head, 1, H, act, smats, blk, nblk);
+    StagedAct4 act = norm_quant_stage(P.X, nullptr, P.final_norm, H, P.eps, stage, ys, nullptr);
+    gemv_stage(&P.lm_head, 1, H, act, smats, bs, blk, nblk);
   }
   if (grid_barrier(gs)) return;
   {
@@ -396,7 +420,7 @@ __global__ void __launch_bounds__(256, 2) DecodeStepMega(const DecodeStepMegaArg
   }
 }
 
-static uint32_t mega_smem_fn(const void *) { return (uint32_t)(kStageBytes + kYsFloats * 4); }
+static uint32_t mega_smem_fn(const void *) { return (uint32_t)(kStageBytes + kYsFloats * 4 + kTCap * 4); }
 
 #define F(f) AINFER_ARG(DecodeStepMegaArgs, f)
 AINFER_REGISTER_COOP(DecodeStepMega, DecodeStepMegaArgs, 256, 0, 0, mega_smem_fn, F(plan), F(mode));

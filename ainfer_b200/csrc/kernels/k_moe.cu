@@ -1,6 +1,7 @@
 // Kernel entries of the mixture-of-experts block; bodies in moe_core.cuh
 // (shared with the persistent decode kernel).
-#include "moe_core.cuh"
+#define AINFER_BLOCK_DOT_INLINE 1
+#include "block_stages.cuh"
 
 namespace ainfer {
 
@@ -8,6 +9,7 @@ extern __shared__ __align__(16) unsigned char moe_smem[];
 
 __global__ void __launch_bounds__(256) RouterTopK(const RouterTopKArgs a) {
   __shared__ bool is_last;
+  __shared__ float sp[1024];
   router_logits_rows(a, blockIdx.x, gridDim.x);
   // last block to arrive does the selection
   __threadfence();
@@ -20,17 +22,23 @@ __global__ void __launch_bounds__(256) RouterTopK(const RouterTopKArgs a) {
   __syncthreads();
   if (!is_last || threadIdx.x >= 32) return;
   __threadfence();
-  router_select(a.Logits, a.E, a.k, a.Wsg != nullptr, a.SelIdx, a.SelW, a.NearGap);
+  router_select(a.Logits, a.E, a.k, a.Wsg != nullptr, sp, a.SelIdx, a.SelW, a.NearGap);
 }
 
 __global__ void __launch_bounds__(256) ExpertGateUp(const ExpertGateUpArgs a) {
-  StagedAct act = stage_act(moe_smem, a.XQ, a.SQ, a.H, 1, a.H, a.H / 128);
-  gateup_dispatch(a, act, blockIdx.x, gridDim.x);
+  __shared__ RowSeg segs[kMaxSegs];
+  __shared__ float T[kTCap];
+  __shared__ int ibox[4];
+  StagedAct4 act = stage4(moe_smem, a.XQ, a.SQ, a.H, 1, a.H, a.H / 128);
+  gateup_block_dispatch(a, act, BlockScratch{segs, T, ibox}, blockIdx.x, gridDim.x);
 }
 
 __global__ void __launch_bounds__(256) ExpertDownCombine(const ExpertDownCombineArgs a) {
-  StagedAct act = stage_act_from_f32(moe_smem, a.Act, a.I, a.slots, a.I);
-  down_dispatch(a, act, blockIdx.x, gridDim.x);
+  __shared__ RowSeg segs[kMaxSegs];
+  __shared__ float T[kTCap];
+  __shared__ int ibox[4];
+  StagedAct4 act = stage4_from_f32<true>(moe_smem, a.Act, a.I, a.slots, a.I);
+  down_block_dispatch(a, act, BlockScratch{segs, T, ibox}, blockIdx.x, gridDim.x);
 }
 
 #define F(f) AINFER_ARG(RouterTopKArgs, f)
@@ -47,10 +55,8 @@ AINFER_REGISTER(ExpertGateUp, ExpertGateUpArgs, 256, 0, 0, gateup_smem_fn, F(Exp
 #undef F
 
 static uint32_t down_smem_fn(const void *args) {
-  // sized for the template's pass count (6 or 12): passes beyond the active
-  // slots are masked but still index the staged arrays
   const ExpertDownCombineArgs *a = (const ExpertDownCombineArgs *)args;
-  return staged_act_bytes(a->I, a->slots <= 6 ? 6 : 12);
+  return staged_act_bytes(a->I, a->slots);
 }
 #define F(f) AINFER_ARG(ExpertDownCombineArgs, f)
 AINFER_REGISTER(ExpertDownCombine, ExpertDownCombineArgs, 256, 0, 0, down_smem_fn, F(Experts),

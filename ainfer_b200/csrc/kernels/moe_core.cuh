@@ -9,6 +9,9 @@
 
 namespace ainfer {
 
+// (g / (1 + exp(-g))) * u, the reference's SiluMul (tools/cmdlist/kernels.cpp:29-37).
+static __device__ __noinline__ float silu_mul(float g, float u) { return (g / (1.0f + det_expf(-g))) * u; }
+
 // ----------------------------------------------------------- RouterTopK ---
 // logits[e] = sum_k bf16(Wr[e][k]) * hn[k]: 32 lanes, lane l takes k =
 // (i*32+l)*8+j, fma chain in (i, j) order, then the lane tree. The last block
@@ -53,44 +56,43 @@ __device__ __forceinline__ void router_logits_rows(const RouterTopKArgs &a, int 
 }
 
 // Selection by one warp: softmax over E logits, top-k by (probability desc,
-// index asc), renormalised weights, shared-expert gate. NI = ceil(E/32) values
-// per lane. Outputs may live in shared or global memory.
-template <int NI>
-__device__ __forceinline__ void router_select_warp(const float *lg, int E, int k, bool has_shared,
-                                                   int32_t *sel_idx, float *sel_w, float *near_gap) {
+// index asc), renormalised weights, shared-expert gate. sp is E floats of
+// shared-memory scratch (probabilities; a selected entry is overwritten by -1).
+// Loops are rolled: the code stays small, lane l owns entries l, l+32, ...
+// Outputs may live in shared or global memory.
+static __device__ __noinline__ void router_select(const float *lg, int E, int k, bool has_shared, float *sp,
+                                           int32_t *sel_idx, float *sel_w, float *near_gap) {
   const int lane = threadIdx.x & 31;
-  float p[NI];
-  bool used[NI];
   float m = -INFINITY;
-#pragma unroll
-  for (int i = 0; i < NI; ++i) {
-    int e = lane + 32 * i;
-    p[i] = e < E ? __ldcg(lg + e) : -INFINITY;
-    used[i] = e >= E;
-    m = fmaxf(m, p[i]);
+#pragma unroll 1
+  for (int e = lane; e < E; e += 32) {
+    float v = __ldcg(lg + e);
+    sp[e] = v;
+    m = fmaxf(m, v);
   }
   m = warp_max(m);
   float sum = 0.0f;
-#pragma unroll
-  for (int i = 0; i < NI; ++i) {
-    int e = lane + 32 * i;
-    if (e < E) {
-      p[i] = det_expf(p[i] - m);
-      sum = sum + p[i];
-    }
+#pragma unroll 1
+  for (int e = lane; e < E; e += 32) {
+    float p = det_expf(sp[e] - m);
+    sp[e] = p;
+    sum = sum + p;
   }
   sum = warp_tree_sum(sum);
-#pragma unroll
-  for (int i = 0; i < NI; ++i)
-    if (lane + 32 * i < E) p[i] = p[i] / sum;
+#pragma unroll 1
+  for (int e = lane; e < E; e += 32) sp[e] = sp[e] / sum;
+  __syncwarp();
   float s = 0.0f, lastp = 0.0f;
   float wsel = 0.0f;  // lane j keeps the weight of rank j (k <= 32)
+#pragma unroll 1
   for (int j = 0; j <= k && j < E; ++j) {
     float bv = -1.0f;
     int bi = 0x7FFFFFFF;
-#pragma unroll
-    for (int i = 0; i < NI; ++i)
-      if (!used[i] && p[i] > bv) { bv = p[i]; bi = lane + 32 * i; }
+#pragma unroll 1
+    for (int e = lane; e < E; e += 32) {
+      float p = sp[e];
+      if (p > bv) { bv = p; bi = e; }
+    }
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) {
       float ov = __shfl_xor_sync(kFull, bv, off);
@@ -101,11 +103,8 @@ __device__ __forceinline__ void router_select_warp(const float *lg, int E, int k
       if (lane == 0) *near_gap = lastp > 0.0f ? (lastp - bv) / lastp : 0.0f;
       break;
     }
-    if ((bi & 31) == lane) {
-#pragma unroll
-      for (int i = 0; i < NI; ++i)
-        if (i == (bi >> 5)) used[i] = true;
-    }
+    if ((bi & 31) == lane) sp[bi] = -1.0f;  // probabilities are >= 0: never selected again
+    __syncwarp();
     if (lane == j) wsel = bv;
     if (lane == 0) sel_idx[j] = bi;
     s = s + bv;
@@ -118,15 +117,6 @@ __device__ __forceinline__ void router_select_warp(const float *lg, int E, int k
     sel_w[k] = has_shared ? 1.0f / (1.0f + det_expf(-__ldcg(lg + E))) : 0.0f;
   }
 }
-__device__ __forceinline__ void router_select(const float *lg, int E, int k, bool has_shared,
-                                              int32_t *sel_idx, float *sel_w, float *near_gap) {
-  if (E <= 64) router_select_warp<2>(lg, E, k, has_shared, sel_idx, sel_w, near_gap);
-  else if (E <= 512) router_select_warp<16>(lg, E, k, has_shared, sel_idx, sel_w, near_gap);
-  else router_select_warp<32>(lg, E, k, has_shared, sel_idx, sel_w, near_gap);
-}
-
-
-
 
 // --------------------------------------------------------- ExpertGateUp ---
 // For every active slot s (routed experts in rank order, then the shared
@@ -148,25 +138,22 @@ __device__ __forceinline__ void gateup_rows(const ExpertGateUpArgs &a, const Sta
   using Gm = RowGeom<K>;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
   const long total = (long)a.slots * a.I;
-  const long tile = (long)warps * Gm::RPW;
-  for (long base = (long)blk * tile; base < total; base += (long)nblk * tile) {
-    long r = base + (long)warp * Gm::RPW + lane / Gm::LPR;
-    if (base + (long)warp * Gm::RPW >= total) continue;
+  const long stride = (long)nblk * warps * Gm::RPW;
+  const int rs = lane / Gm::LPR;
+#pragma unroll 1
+  for (long wrow = ((long)blk * warps + warp) * Gm::RPW; wrow < total; wrow += stride) {
+    long r = wrow + rs;
     bool ok = r < total;
     int s = ok ? (int)(r / a.I) : 0, n = ok ? (int)(r % a.I) : 0;
     const ExpertW &ew = a.Experts[a.SelIdx[a.slot_begin + s]];
-    LaneRows<2> rows;
-    rows.ok[0] = rows.ok[1] = ok;
-    rows.P[0] = ew.gP + (long)n * (K / 2);
-    rows.S[0] = ew.gS + (long)n * Gm::G;
-    rows.P[1] = ew.uP + (long)n * (K / 2);
-    rows.S[1] = ew.uS + (long)n * Gm::G;
-    float acc[2][1];
-    warp_rows_dot<K, 1, 2>(rows, act, acc);
-    if (ok && (lane % Gm::LPR) == 0) {
-      float g = acc[0][0], u = acc[1][0];
-      a.Act[(size_t)(a.slot_begin + s) * a.I + n] = (g / (1.0f + det_expf(-g))) * u;
-    }
+    PassRegs<K> rg, ru;  // the row of gate_proj and the same row of up_proj
+    pass_load<K>(rg, ew.gP + (long)n * (K / 2), ew.gS + (long)n * Gm::G, ok);
+    pass_load<K>(ru, ew.uP + (long)n * (K / 2), ew.uS + (long)n * Gm::G, ok);
+    float g[1], u[1];
+    pass_dot<K, 1>(rg, act, 0, g);
+    pass_dot<K, 1>(ru, act, 0, u);
+    if (ok && (lane % Gm::LPR) == 0)
+      a.Act[(size_t)(a.slot_begin + s) * a.I + n] = silu_mul(g[0], u[0]);
   }
 }
 __device__ __forceinline__ void gateup_dispatch(const ExpertGateUpArgs &a, const StagedAct &act, int blk,
@@ -196,31 +183,41 @@ struct ExpertDownCombineArgs {
   float *Moe;             // optional [H]: the MoE output before the residual add
   int32_t slots, I, H;
 };
-template <int K, int RT>
+// Output rows of the down projections: for row n every active slot's matrix is
+// dotted with that slot's quantised activation (slots in groups of four, so that
+// four loads are in flight), then combined in rank order.
+template <int K>
 __device__ __forceinline__ void down_rows(const ExpertDownCombineArgs &a, const StagedAct &act, int blk,
                                           int nblk) {
   using Gm = RowGeom<K>;
+  constexpr int SG = 4;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-  const long tile = (long)warps * Gm::RPW;
-  for (long base = (long)blk * tile; base < a.H; base += (long)nblk * tile) {
-    if (base + (long)warp * Gm::RPW >= a.H) continue;
-    long n = base + (long)warp * Gm::RPW + lane / Gm::LPR;
+  const long stride = (long)nblk * warps * Gm::RPW;
+  const int rs = lane / Gm::LPR;
+#pragma unroll 1
+  for (long wrow = ((long)blk * warps + warp) * Gm::RPW; wrow < a.H; wrow += stride) {
+    long n = wrow + rs;
     bool ok = n < a.H;
-    LaneRows<RT> rows;
+    long nn = ok ? n : 0;
+    float acc = 0.0f;
+#pragma unroll 1
+    for (int p0 = 0; p0 < a.slots; p0 += SG) {
+      PassRegs<K> r[SG];
 #pragma unroll
-    for (int p = 0; p < RT; ++p) {
-      rows.ok[p] = ok && p < a.slots;
-      const ExpertW &ew = a.Experts[a.SelIdx[p < a.slots ? p : 0]];
-      rows.P[p] = ew.dP + (ok ? n : 0) * (K / 2);
-      rows.S[p] = ew.dS + (ok ? n : 0) * Gm::G;
+      for (int j = 0; j < SG; ++j) {
+        int p = p0 + j < a.slots ? p0 + j : 0;
+        const ExpertW &ew = a.Experts[a.SelIdx[p]];
+        pass_load<K>(r[j], ew.dP + nn * (K / 2), ew.dS + nn * Gm::G, ok && p0 + j < a.slots);
+      }
+#pragma unroll
+      for (int j = 0; j < SG; ++j) {
+        int p = p0 + j < a.slots ? p0 + j : 0;
+        float y[1];
+        pass_dot<K, 1>(r[j], act, p, y);
+        if (p0 + j < a.slots) acc = acc + a.SelW[p] * y[0];
+      }
     }
-    float y[RT];
-    warp_rows_dot_paired<K, RT>(rows, act, y);
     if (ok && (lane % Gm::LPR) == 0) {
-      float acc = 0.0f;
-#pragma unroll
-      for (int p = 0; p < RT; ++p)
-        if (p < a.slots) acc = acc + a.SelW[p] * y[p];
       if (a.Moe) a.Moe[n] = acc;
       a.X[n] = __ldcg(a.Res + n) + acc;
     }
@@ -229,8 +226,7 @@ __device__ __forceinline__ void down_rows(const ExpertDownCombineArgs &a, const 
 template <int K>
 __device__ __forceinline__ void down_dispatch_k(const ExpertDownCombineArgs &a, const StagedAct &act,
                                                 int blk, int nblk) {
-  if (a.slots <= 6) down_rows<K, 6>(a, act, blk, nblk);
-  else down_rows<K, 12>(a, act, blk, nblk);
+  down_rows<K>(a, act, blk, nblk);
 }
 __device__ __forceinline__ void down_dispatch(const ExpertDownCombineArgs &a, const StagedAct &act, int blk,
                                               int nblk) {

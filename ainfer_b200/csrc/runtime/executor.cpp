@@ -354,6 +354,12 @@ int build_mega(Session *s) {
   P.ctrl = s->ctrl; P.history = s->history; P.out_tok = s->out_tok; P.ids = s->ids;
   P.layer_out = s->layer_out; P.routed = s->routed; P.near_gap = s->near_gap;
   if (salloc(s, 1, &s->bar_count) || salloc(s, 1, &s->mega_error)) return 1;
+  if (s->flags & SESSION_STAGE_CLOCK) {
+    s->stage_stamp_cap = c.layers * 24 + 16;
+    if (salloc(s, (size_t)s->stage_stamp_cap, &s->stage_stamps)) return 1;
+    P.stage_stamps = s->stage_stamps;
+    P.stage_stamp_cap = s->stage_stamp_cap;
+  }
   P.bar_count = s->bar_count; P.error = s->mega_error;
   MegaLayer *dl = nullptr;
   if (salloc(s, layers.size(), &dl, false)) return 1;

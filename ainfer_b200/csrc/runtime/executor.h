@@ -19,7 +19,8 @@ namespace ainfer {
 enum SessionFlags {
   SESSION_DIAG = 1,             // keep per-layer residual stream, routed experts, near-tie gaps
   SESSION_PER_LAYER_LISTS = 2,  // one list per layer + embed + tail, executed and fenced one by one
-  SESSION_MULTI_KERNEL = 4      // one list per token of ~450 stand-alone launches (default: one persistent launch)
+  SESSION_MULTI_KERNEL = 4,     // one list per token of ~450 stand-alone launches (default: one persistent launch)
+  SESSION_STAGE_CLOCK = 8       // persistent step: keep a device timestamp after every grid barrier
 };
 
 struct Session {
@@ -68,6 +69,8 @@ struct Session {
   uint32_t *bar_count = nullptr;
   int32_t *mega_error = nullptr;
   bool mega = false;
+  unsigned long long *stage_stamps = nullptr;  // [stage_stamp_cap] of the last launch
+  int stage_stamp_cap = 0;
   std::map<std::string, ainfer_kernel_t> kernels;
   std::vector<void *> owned;
   uint64_t launches_per_token = 0;

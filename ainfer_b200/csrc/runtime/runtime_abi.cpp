@@ -141,6 +141,7 @@ int ainfer_session_buffer(ainfer_session_t h, const char *which, void **dptr, ui
   else if (w == "history") { *dptr = s->history; *bytes = (uint64_t)s->max_ctx * 4; }
   else if (w == "layer_out") { *dptr = s->layer_out; *bytes = s->layer_out ? (uint64_t)c.layers * c.hidden * 4 : 0; }
   else if (w == "routed") { *dptr = s->routed; *bytes = s->routed ? (uint64_t)c.layers * (c.top_k + 1) * 4 : 0; }
+  else if (w == "stage_stamps") { *dptr = s->stage_stamps; *bytes = (uint64_t)s->stage_stamp_cap * 8; }
   else if (w == "near_gap") { *dptr = s->near_gap; *bytes = s->near_gap ? (uint64_t)c.layers * 4 : 0; }
   else return set_err(2, "unknown session buffer: " + w);
   return 0;

@@ -84,6 +84,7 @@ def main(argv=None):
     d.add_argument("--steps", type=int, default=8)
     d.add_argument("--per-layer", action="store_true")
     d.add_argument("--multi-kernel", action="store_true")
+    d.add_argument("--stage-clock", action="store_true", help="print the time between grid barriers of the last token")
     args = ap.parse_args(argv)
     dev = cuda_abi.Device(0)
     if args.cmd == "gemv":
@@ -95,12 +96,18 @@ def main(argv=None):
         model = runtime.Model(dev, f"synth:{args.model}:seed=0")
         sess = runtime.Session(model, args.prompt + args.steps + 8,
                                runtime.Session.PER_LAYER_LISTS if args.per_layer else
-                               (runtime.Session.MULTI_KERNEL if args.multi_kernel else 0))
+                               (runtime.Session.MULTI_KERNEL if args.multi_kernel else
+                                (runtime.Session.STAGE_CLOCK if args.stage_clock else 0)))
         prompt = (np.arange(args.prompt, dtype=np.int32) * 7919 + 13) % model.config["vocab"]
         toks, ms = sess.generate(prompt, args.steps, timed=True)
         print(json.dumps({"op": "decode", "model": args.model, "prompt": args.prompt, "steps": args.steps,
                           "ms_per_token": ms / args.steps, "launches_per_token": sess.launches_per_token(),
                           "tokens": [int(t) for t in toks]}), flush=True)
+        if args.stage_clock:
+            st = sess.read("stage_stamps", np.uint64)
+            n = int(np.count_nonzero(st))
+            d = np.diff(st[:n].astype(np.int64)) / 1000.0
+            print(json.dumps({"op": "stage_clock", "unit": "us", "stages": [round(float(x), 2) for x in d]}), flush=True)
         sess.close(); model.close()
     dev.close()
     return 0

@@ -136,6 +136,7 @@ class Session:
     DIAG = 1
     PER_LAYER_LISTS = 2
     MULTI_KERNEL = 4
+    STAGE_CLOCK = 8
 
     def __init__(self, model, max_ctx, flags=0):
         self.model = model

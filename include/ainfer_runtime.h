@@ -69,13 +69,15 @@ enum {
   AINFER_SESSION_PER_LAYER_LISTS = 2, /* one list per layer, fenced one by one, as the reference executes */
   AINFER_SESSION_MULTI_KERNEL = 4     /* one list per token of stand-alone launches; default is ONE persistent
                                          cooperative launch per token (DecodeStepMega) */
+  , AINFER_SESSION_STAGE_CLOCK = 8    /* persistent step: device timestamp after every grid barrier, read
+                                         back through the "stage_stamps" buffer (u64 ns, entry 0 = start) */
 };
 int ainfer_session_create(ainfer_model_t m, int max_ctx, int flags, ainfer_session_t *out);
 int ainfer_session_destroy(ainfer_session_t s);
 int ainfer_session_reset(ainfer_session_t s);
 /* Device buffers of the session, for state upload/download by tests:
  * "conv", "S", "Kc", "Vc", "Ks", "Vs", "logits", "x", "ctrl", "layer_out",
- * "routed", "near_gap", "history". */
+ * "routed", "near_gap", "history", "stage_stamps". */
 int ainfer_session_buffer(ainfer_session_t s, const char *which, void **dptr, uint64_t *bytes);
 /* One token at a position; returns the greedy token (4-byte readback). */
 int ainfer_session_step(ainfer_session_t s, int token, int pos, int *out_token);
