@@ -20,6 +20,13 @@ static std::vector<KernelDesc> &registry() {
   return r;
 }
 void register_kernel(const KernelDesc &d) { registry().push_back(d); }
+static std::vector<FaultHook> &fault_hooks() {
+  static std::vector<FaultHook> h;
+  return h;
+}
+void register_fault_hook(FaultHook h) { fault_hooks().push_back(h); }
+int fault_hook_count() { return (int)fault_hooks().size(); }
+FaultHook fault_hook_at(int i) { return fault_hooks()[(size_t)i]; }
 int kernel_count() { return (int)registry().size(); }
 const KernelDesc *kernel_at(int i) {
   return i >= 0 && i < kernel_count() ? &registry()[i] : nullptr;
@@ -42,7 +49,26 @@ struct ainfer_device_s {
   void *flush_buf = nullptr;
   size_t flush_bytes = 0;
   int sm_count = 0;
+  volatile unsigned int *fault_word = nullptr;  // host view of the stream fault word of this GPU
 };
+
+// One host-mapped fault word per GPU for the life of the process: kernels that
+// stream weights store a code there when one of their bounded waits runs out.
+static volatile unsigned int *g_fault_words[64];
+static int fault_word_setup(int ordinal, volatile unsigned int **out) {
+  if (ordinal < 0 || ordinal >= 64) return 1;
+  if (!g_fault_words[ordinal]) {
+    unsigned int *h = nullptr, *d = nullptr;
+    if (cudaHostAlloc((void **)&h, 64, cudaHostAllocMapped) != cudaSuccess) return 1;
+    *h = 0;
+    if (cudaHostGetDevicePointer((void **)&d, h, 0) != cudaSuccess) return 1;
+    for (int i = 0; i < fault_hook_count(); ++i)
+      if (fault_hook_at(i)(d) != 0) return 1;
+    g_fault_words[ordinal] = h;
+  }
+  *out = g_fault_words[ordinal];
+  return 0;
+}
 struct ainfer_kernel_s {
   ainfer_device_t dev;
   const KernelDesc *desc;
@@ -109,6 +135,12 @@ int ainfer_device_open(int ordinal, ainfer_device_t *out) {
                 "device is not sm_100 class: kernels are built for sm_100a only");
   }
   CU(nullptr, cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking));
+  if (fault_word_setup(ordinal, &d->fault_word) != 0) {
+    cudaGetLastError();
+    cudaStreamDestroy(d->stream);
+    delete d;
+    return fail(nullptr, AINFER_ERR_DEVICE, "could not set up the stream fault word");
+  }
   *out = d;
   return AINFER_OK;
 }
@@ -416,17 +448,26 @@ int ainfer_list_execute(ainfer_list_t l) {
   return AINFER_OK;
 }
 
+// Sticky: once a kernel reported a stream fault, every later sync fails.
+static int stream_fault_check(ainfer_device_t dev) {
+  unsigned int code = dev->fault_word ? *dev->fault_word : 0;
+  if (code == 0) return AINFER_OK;
+  return fail(dev, AINFER_ERR_DEVICE,
+              code == 2 ? "weight stream fault: a weight row address was not 16-byte aligned"
+                        : "weight stream fault: a bounded wait on a shared-memory copy ran out");
+}
+
 int ainfer_sync(ainfer_device_t dev, uint64_t timeout_ns) {
   if (!dev) return AINFER_ERR_INVALID;
   if (timeout_ns == UINT64_MAX) {
     CU(dev, cudaStreamSynchronize(dev->stream));
-    return AINFER_OK;
+    return stream_fault_check(dev);
   }
   struct timespec t0, t;
   clock_gettime(CLOCK_MONOTONIC, &t0);
   for (;;) {
     cudaError_t e = cudaStreamQuery(dev->stream);
-    if (e == cudaSuccess) return AINFER_OK;
+    if (e == cudaSuccess) return stream_fault_check(dev);
     if (e != cudaErrorNotReady) CU(dev, e);
     clock_gettime(CLOCK_MONOTONIC, &t);
     uint64_t el = (uint64_t)(t.tv_sec - t0.tv_sec) * 1000000000ull + (uint64_t)(t.tv_nsec - t0.tv_nsec);

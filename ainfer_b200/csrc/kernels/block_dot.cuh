@@ -1,13 +1,14 @@
-// Block-level INT4 (group 128) x INT8 dot over a set of row segments.
+// Block-level INT4 (group 128) x INT8 dot over a list of row segments, fed by
+// the weight ring (weight_ring.cuh).
 //
-// The kernel is bound by instruction issue, not by HBM, unless the inner loop
-// is lean: at 6.5 TB/s an SM receives 16 bytes of weights every 0.7 cycles,
-// which leaves about 90 thread instructions per 16 bytes at perfect issue. A
-// first version spent 88 (two shuffles per 16 bytes, a 16-step shuffle replay
-// per row, shared-memory reads and address arithmetic per chunk) and reached
-// 51 % of the HBM roofline. This version spends about 24:
-//   * a lane owns HALF a group: 32 contiguous bytes = 64 weights, fetched with
-//     one 256-bit load; a warp instruction reads 1 KB contiguous;
+// Unless its inner loop is lean the kernel is bound by instruction issue, not
+// by HBM: at 6.5 TB/s an SM receives 16 bytes of weights every 0.7 cycles,
+// which leaves about 90 thread instructions per 16 bytes at perfect issue.
+//   * a lane owns HALF a group: 32 contiguous bytes = 64 weights of a tile that
+//     a bulk copy has put in shared memory; it moves them into registers and
+//     releases the stage at once;
+//   * the lane's 64 activations, the group's activation sum and scale stay in
+//     registers for as long as consecutive tiles use the same staged vector;
 //   * nibbles are never shifted: low nibbles are masked in place, high nibbles
 //     are masked in place as 16*n and their dot is divided by 16 at the end
 //     (exact: it is a multiple of 16); both are biased by xor 8 to unsigned so
@@ -21,26 +22,13 @@
 // Integer sums are associative and the fp32 sum keeps the reference order, so
 // results are bit-identical to the one-work-item-per-row loop.
 //
-// A block owns contiguous rows (possibly of several matrices: "segments");
-// rows are dealt to threads as row = tid / HPR + j * (threads / HPR) with the
-// half-group column hc = tid % HPR fixed per thread (HPR = K/64 divides 256).
+// Lane tid of the block holds bytes [32*tid, 32*tid+32) of a tile: row
+// tid / HPR of the tile, half-group hc = tid % HPR (HPR = K/64 divides 256).
 #pragma once
 #include "common.cuh"
+#include "weight_ring.cuh"
 
 namespace ainfer {
-
-// Contiguous rows of one matrix, dotted with one staged activation vector.
-struct RowSeg {
-  const uint8_t *P;   // packed nibbles of the segment's first row
-  const uint16_t *S;  // bf16 scales of the segment's first row
-  int32_t nrows;
-  int32_t vec;        // staged activation vector this segment is dotted with
-  int32_t trow;       // first row of this segment in the t[][] scratch
-  int32_t row0;       // first flat row index of this segment (filled by seg_finalize)
-};
-
-constexpr int kMaxSegs = 16;
-constexpr int kDotLD = 6;  // rows (32-byte loads) in flight per thread
 
 // Staged activations, half-group layout: for vector v, half-group hc and j in
 // 0..3 the uint4 x[(v*4 + j) * HPR + hc] holds the de-interleaved INT8 bytes of
@@ -129,28 +117,12 @@ __device__ __forceinline__ StagedAct4 stage4_from_f32(unsigned char *smem, const
   return StagedAct4{reinterpret_cast<const uint4 *>(smem), gs, sqs};
 }
 
-// Fills row0 (prefix sums); returns the total number of rows. One thread.
-__device__ __forceinline__ int seg_finalize(RowSeg *segs, int nseg) {
-  int r = 0;
-  for (int i = 0; i < nseg; ++i) {
-    segs[i].row0 = r;
-    r += segs[i].nrows;
-  }
-  return r;
-}
-
-// 256-bit streaming load of a lane's 32 bytes (64 weights).
-__device__ __forceinline__ void ldg_stream32(const void *p, uint32_t (&w)[8]) {
-  asm("ld.global.nc.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-      : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
-      : "l"(p));
-}
-
 // sum over 64 weights of (nibble ^ 8) * x: low nibbles exactly, high nibbles as 16*(n^8).
-__device__ __forceinline__ void dot64_biased(const uint32_t (&w)[8], const uint4 &x0, const uint4 &x1,
-                                             const uint4 &x2, const uint4 &x3, int &lo, int &hi) {
-  const uint32_t xe[8] = {x0.x, x0.z, x1.x, x1.z, x2.x, x2.z, x3.x, x3.z};
-  const uint32_t xo[8] = {x0.y, x0.w, x1.y, x1.w, x2.y, x2.w, x3.y, x3.w};
+__device__ __forceinline__ void dot64_biased(const uint4 &wa, const uint4 &wb, const uint4 (&x)[4], int &lo,
+                                             int &hi) {
+  const uint32_t w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+  const uint32_t xe[8] = {x[0].x, x[0].z, x[1].x, x[1].z, x[2].x, x[2].z, x[3].x, x[3].z};
+  const uint32_t xo[8] = {x[0].y, x[0].w, x[1].y, x[1].w, x[2].y, x[2].w, x[3].y, x[3].w};
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     uint32_t l = (w[i] & 0x0F0F0F0Fu) ^ 0x08080808u;
@@ -163,11 +135,14 @@ __device__ __forceinline__ void dot64_biased(const uint32_t (&w)[8], const uint4
   }
 }
 
-// t[(trow + local_row) * G + g] for every (row, group) of the segments.
-// segs/T live in shared memory; total_rows = seg_finalize(). Ends with a
-// __syncthreads, after which T is complete. One instance per K, shared by every
-// stage (not inlined: the code a layer executes has to stay resident in the
-// instruction cache).
+// t[(trow + local_row) * G + g] for every (row, group) of the list `cur`.
+// cur/next/ring/T live in shared memory and cur->ntiles is final. While it
+// consumes, the issuing thread keeps the ring full, running on into `next`
+// (the list of the following call, any K; may be null) once `cur` is fully
+// issued. Ends with a __syncthreads, after which T is complete and every tile
+// of `cur` has been consumed. One instance per K, shared by every stage (not
+// inlined: the code a layer executes has to stay resident in the instruction
+// cache).
 // (nvcc 12.9 crashes on the non-inlined template with -lineinfo in one translation
 // unit; that unit defines AINFER_BLOCK_DOT_INLINE.)
 #ifdef AINFER_BLOCK_DOT_INLINE
@@ -176,50 +151,113 @@ __device__ __forceinline__ void dot64_biased(const uint32_t (&w)[8], const uint4
 #define AINFER_BLOCK_DOT_LINKAGE static __device__ __noinline__
 #endif
 template <int K>
-AINFER_BLOCK_DOT_LINKAGE void block_dot(const RowSeg *segs, int nseg, int total_rows,
-                                              const StagedAct4 &act, float *T) {
+AINFER_BLOCK_DOT_LINKAGE void block_dot(Ring *ring, const SegList *cur, const SegList *next,
+                                        const StagedAct4 &act, float *T) {
   constexpr int HPR = K / 64, G = K / 128;
-  constexpr int NTHR = 256, RPI = NTHR / HPR;  // rows per block iteration
+  constexpr int NTHR = 256, RPI = NTHR / HPR;  // rows per tile
   static_assert(NTHR % HPR == 0, "K/64 must divide the block size");
-  const int hc = threadIdx.x % HPR, rt = threadIdx.x / HPR;
+  const int tid = threadIdx.x, hc = tid % HPR, rt = tid / HPR;
+  const uint32_t nst = ring->nst;
+  unsigned char *const data = ring->data;
+  uint32_t cs = ring->c_stage, cph = ring->c_phase;
+  const int ntiles = cur->ntiles;
+  const bool even = (hc & 1) == 0;
+
+  // ---- issuing thread: fill the ring ----
+  Producer pr;
+  uint32_t issued = 0;  // tiles issued, counted from tile 0 of cur (runs on into next)
+  uint32_t ntot = (uint32_t)ntiles;
+  bool in_next = false;
+  if (tid == 0) {
+    if (next) ntot += (uint32_t)next->ntiles;
+    pr.stage = cs;
+    pr.phase = cph;
+    if (ntiles > 0) pr.open(cur);
+    else if (next) { pr.open(next); in_next = true; }
+    for (; issued < ring->pre; ++issued) {
+      pr.skip();
+      pr.next_stage(nst);
+    }
+    const uint32_t cap = ntot < nst ? ntot : nst;
+    const uint32_t first = issued;
+    for (; issued < cap; ++issued) {
+      if (!in_next && issued == (uint32_t)ntiles) { pr.open(next); in_next = true; }
+      pr.issue(ring, data, nst);
+    }
+    ring->issued += issued - first;
+  }
+
+  // ---- consume ----
+  int seg = 0, r0 = 0;  // segment and first row of the current tile
+  int nrows = 0, vec = -1;
+  bool s_aligned = false;
+  const uint16_t *sglob = nullptr;  // this lane's scale in global memory, row 0 of the segment
+  float *tp = nullptr;              // this lane's T entry, row 0 of the segment
+  uint4 x[4];
+  int gs8 = 0;
+  float sqg = 0.0f;
+  const unsigned char *st = data + cs * kStageStride;
 #pragma unroll 1
-  for (int base = 0; base < total_rows; base += RPI * kDotLD) {
-    uint32_t w[kDotLD][8];
-    float sc[kDotLD];
-    int meta[kDotLD];  // (t index << 4) | vector, or -1
-    int s = 0;
-    // ---- issue every load of this batch ----
-#pragma unroll
-    for (int j = 0; j < kDotLD; ++j) {
-      const int r = base + j * RPI + rt;
-      if (r < total_rows) {
-        while (s + 1 < nseg && r >= segs[s + 1].row0) ++s;
-        const int lr = r - segs[s].row0;
-        ldg_stream32(segs[s].P + ((size_t)lr * HPR + hc) * 32, w[j]);
-        sc[j] = (hc & 1) == 0 ? bf16_to_f32(__ldg(segs[s].S + (size_t)lr * G + (hc >> 1))) : 0.0f;
-        meta[j] = (((segs[s].trow + lr) * G + (hc >> 1)) << 4) | segs[s].vec;
-      } else {
-#pragma unroll
-        for (int q = 0; q < 8; ++q) w[j][q] = 0x88888888u;
-        sc[j] = 0.0f;
-        meta[j] = -1;
+  for (int t = 0; t < ntiles; ++t) {
+    if (r0 == 0) {  // first tile of a segment: block-uniform
+      const RowSeg &sg = cur->seg[seg];
+      nrows = sg.nrows;
+      sglob = sg.S + (size_t)rt * G + (hc >> 1);
+      s_aligned = (reinterpret_cast<uintptr_t>(sg.S) & 15u) == 0;
+      tp = T + (size_t)(sg.trow + rt) * G + (hc >> 1);
+      if (sg.vec != vec) {
+        vec = sg.vec;
+        const uint4 *xv = act.x + (size_t)vec * 4 * HPR + hc;
+        x[0] = xv[0]; x[1] = xv[HPR]; x[2] = xv[2 * HPR]; x[3] = xv[3 * HPR];
+        gs8 = 8 * act.gsum[vec * G + (hc >> 1)];
+        sqg = act.sq[vec * G + (hc >> 1)];
       }
     }
-    // ---- group sums: two lanes (hc even/odd) hold one group ----
-#pragma unroll
-    for (int j = 0; j < kDotLD; ++j) {
-      const int vec = meta[j] < 0 ? 0 : (meta[j] & 15);
-      const uint4 *xv = act.x + (size_t)vec * 4 * HPR + hc;
-      int lo = 0, hi = 0;
-      dot64_biased(w[j], xv[0], xv[HPR], xv[2 * HPR], xv[3 * HPR], lo, hi);
-      int d = lo + (hi >> 4);
-      d += __shfl_xor_sync(kFull, d, 1);
-      if ((hc & 1) == 0 && meta[j] >= 0) {
-        const int gi = vec * G + (hc >> 1);
-        float v = (float)(d - 8 * act.gsum[gi]) * sc[j];
-        T[meta[j] >> 4] = v * act.sq[gi];
-      }
+    const int rows = nrows - r0 < RPI ? nrows - r0 : RPI;
+    const bool live = even && rt < rows;
+    mbar_wait(ring, &ring->full[cs], cph);
+    const uint4 wa = *reinterpret_cast<const uint4 *>(st + tid * 32);
+    const uint4 wb = *reinterpret_cast<const uint4 *>(st + tid * 32 + 16);
+    uint32_t sraw = 0;
+    if (live) {
+      if (s_aligned && ((rows * G * 2) & 15) == 0) sraw = reinterpret_cast<const uint16_t *>(st + kTileBytes)[tid >> 1];
+      else sraw = __ldg(sglob + (size_t)r0 * G);
     }
+    __syncwarp();
+    if ((tid & 31) == 0) mbar_arrive(&ring->empty[cs]);
+    // the issuing thread refills the stage of the previous tile
+    if (tid == 0 && t >= 1 && issued < ntot) {
+      const uint32_t ps = cs == 0 ? nst - 1 : cs - 1, pph = cs == 0 ? cph ^ 1u : cph;
+      mbar_wait(ring, &ring->empty[ps], pph);
+      if (!in_next && issued == (uint32_t)ntiles) { pr.open(next); in_next = true; }
+      pr.issue(ring, data, nst);
+      ++issued;
+      ring->issued += 1;
+    }
+    int lo = 0, hi = 0;
+    dot64_biased(wa, wb, x, lo, hi);
+    int d = lo + (hi >> 4);
+    d += __shfl_xor_sync(kFull, d, 1);
+    if (live) {
+      float v = (float)(d - gs8) * __uint_as_float(sraw << 16);
+      tp[(size_t)r0 * G] = v * sqg;
+    }
+    r0 += RPI;
+    if (r0 >= nrows) {
+      ++seg;
+      r0 = 0;
+    }
+    st += kStageStride;
+    if (++cs == nst) {
+      cs = 0;
+      cph ^= 1u;
+      st = data;
+    }
+  }
+  if (tid == 0) {
+    ring->c_stage = cs;
+    ring->c_phase = cph;
+    ring->pre = issued > (uint32_t)ntiles ? issued - (uint32_t)ntiles : 0;
   }
   __syncthreads();
 }

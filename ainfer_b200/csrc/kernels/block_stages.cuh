@@ -12,51 +12,75 @@ namespace ainfer {
 
 constexpr int kTCap = 4096;  // floats of t[][] scratch a block needs (16 KB)
 
+// Shared-memory working set of a block plus the thread's view of which of the
+// two segment lists is current. `primed` says lists[cur] has already been built
+// (and possibly prefetched into the ring) for the stage about to run.
 struct BlockScratch {
-  RowSeg *segs;   // [kMaxSegs] shared
-  float *T;       // [kTCap] shared
-  int *ibox;      // [4] shared ints for block-uniform values
+  Ring *ring;      // shared
+  SegList *lists;  // [2] shared
+  float *T;        // [kTCap] shared
+  int cur;
+  bool primed;
 };
 
 // Rows [lo, hi) of `total` dealt to block blk of nblk, in multiples of 4 rows.
 __device__ __forceinline__ void block_range(long total, int blk, int nblk, long &lo, long &hi) {
-  long per = ((total + nblk - 1) / nblk + 3) / 4 * 4;
+  const int per = (((int)total + nblk - 1) / nblk + 3) / 4 * 4;  // row counts fit 32 bits
   lo = (long)blk * per;
   hi = lo + per < total ? lo + per : total;
   if (lo > total) lo = total;
 }
 
 // ---- GEMV over a table of matrices (global rows concatenated), M = 1 ----
-template <int K>
-__device__ __forceinline__ void gemv_block(const GemvMat *smats, int nmats, long total_rows,
-                                           const StagedAct4 &act, const BlockScratch &bs, int blk, int nblk) {
-  constexpr int G = K / 128;
-  constexpr int SB = kTCap / G < 256 ? kTCap / G : 256;  // rows per sub-block (one finishing thread per row)
+__host__ __device__ constexpr int gemv_sub_rows(int K) { return kTCap / (K / 128) < 256 ? kTCap / (K / 128) : 256; }
+
+// Segment list of global rows [sb, se). One thread.
+__device__ __forceinline__ void gemv_list(SegList *l, const GemvMat *smats, int nmats, int K, long sb, long se) {
+  const int G = K / 128;
+  int n = 0;
+  for (int i = 0; i < nmats; ++i) {
+    long a = sb > smats[i].row_start ? sb : smats[i].row_start;
+    long b = se < smats[i].row_start + smats[i].N ? se : smats[i].row_start + smats[i].N;
+    if (a < b && n < kMaxSegs) {
+      RowSeg &s = l->seg[n++];
+      s.P = smats[i].P + (a - smats[i].row_start) * (K / 2);
+      s.S = smats[i].S + (a - smats[i].row_start) * G;
+      s.nrows = (int)(b - a);
+      s.vec = 0;
+      s.trow = (int)(a - sb);
+    }
+  }
+  l->nseg = n;
+  l->K = K;
+  seglist_finalize(l);
+}
+// First list of a block's share, for prefetching ahead of the stage. One thread.
+__device__ __forceinline__ void gemv_first_list(SegList *l, const GemvMat *smats, int nmats, int K,
+                                                long total_rows, int blk, int nblk) {
   long lo, hi;
   block_range(total_rows, blk, nblk, lo, hi);
+  const long se = lo + gemv_sub_rows(K) < hi ? lo + gemv_sub_rows(K) : hi;
+  gemv_list(l, smats, nmats, K, lo, se);
+}
+
+template <int K>
+__device__ __forceinline__ void gemv_block(const GemvMat *smats, int nmats, long total_rows,
+                                           const StagedAct4 &act, BlockScratch &bs, int blk, int nblk) {
+  constexpr int SB = gemv_sub_rows(K);  // rows per sub-block (one finishing thread per row)
+  long lo, hi;
+  block_range(total_rows, blk, nblk, lo, hi);
+  if (!bs.primed) {
+    __syncthreads();  // the lists are no longer read by an earlier stage
+    if (threadIdx.x == 0) gemv_list(&bs.lists[bs.cur], smats, nmats, K, lo, lo + SB < hi ? lo + SB : hi);
+  }
+  bs.primed = false;
 #pragma unroll 1
   for (long sb = lo; sb < hi; sb += SB) {
     const long se = sb + SB < hi ? sb + SB : hi;
-    __syncthreads();  // segs / T of the previous sub-block are no longer read
-    if (threadIdx.x == 0) {
-      int n = 0;
-      for (int i = 0; i < nmats; ++i) {
-        long a = sb > smats[i].row_start ? sb : smats[i].row_start;
-        long b = se < smats[i].row_start + smats[i].N ? se : smats[i].row_start + smats[i].N;
-        if (a < b) {
-          RowSeg &s = bs.segs[n++];
-          s.P = smats[i].P + (a - smats[i].row_start) * (K / 2);
-          s.S = smats[i].S + (a - smats[i].row_start) * G;
-          s.nrows = (int)(b - a);
-          s.vec = 0;
-          s.trow = (int)(a - sb);
-        }
-      }
-      bs.ibox[0] = n;
-      bs.ibox[1] = seg_finalize(bs.segs, n);
-    }
-    __syncthreads();
-    block_dot<K>(bs.segs, bs.ibox[0], bs.ibox[1], act, bs.T);
+    const bool more = se < hi;
+    if (threadIdx.x == 0 && more) gemv_list(&bs.lists[bs.cur ^ 1], smats, nmats, K, se, se + SB < hi ? se + SB : hi);
+    __syncthreads();  // lists built; T of the previous sub-block is no longer read
+    block_dot<K>(bs.ring, &bs.lists[bs.cur], more ? &bs.lists[bs.cur ^ 1] : nullptr, act, bs.T);
     // one thread per row: ordered sum, then the matrix's epilogue
     const long r = sb + threadIdx.x;
     if (r < se) {
@@ -65,11 +89,12 @@ __device__ __forceinline__ void gemv_block(const GemvMat *smats, int nmats, long
         if (r >= smats[i].row_start) mi = i;
       gemv_epilogue(smats + mi, (int)(r - smats[mi].row_start), 0, row_sum<K>(bs.T, threadIdx.x));
     }
+    bs.cur ^= 1;
   }
 }
 
 __device__ __forceinline__ void gemv_block_dispatch(int K, const GemvMat *smats, int nmats, long total_rows,
-                                                    const StagedAct4 &act, const BlockScratch &bs, int blk,
+                                                    const StagedAct4 &act, BlockScratch &bs, int blk,
                                                     int nblk) {
   switch (K) {
     case 128: gemv_block<128>(smats, nmats, total_rows, act, bs, blk, nblk); break;
@@ -84,45 +109,59 @@ __device__ __forceinline__ void gemv_block_dispatch(int K, const GemvMat *smats,
 }
 
 // ---- expert gate/up + SiLU-mul: "pair rows" (slot, n), n in [0, I) ----
+__host__ __device__ constexpr int gateup_sub_rows(int K) {
+  return kTCap / (2 * (K / 128)) < 256 ? kTCap / (2 * (K / 128)) : 256;
+}
+// Gate and up segments of pair rows [sb, se). One thread.
+__device__ __forceinline__ void gateup_list(SegList *l, const ExpertGateUpArgs &a, long sb, long se) {
+  const int K = a.H, G = K / 128, SB = gateup_sub_rows(K);
+  int n = 0;
+  if (sb < se)
+    for (int s = (int)(sb / a.I); s <= (int)((se - 1) / a.I) && n + 2 <= kMaxSegs; ++s) {
+      long aa = sb > (long)s * a.I ? sb : (long)s * a.I;
+      long bb = se < (long)(s + 1) * a.I ? se : (long)(s + 1) * a.I;
+      const ExpertW &ew = a.Experts[a.SelIdx[a.slot_begin + s]];
+      long r0 = aa - (long)s * a.I;
+      RowSeg &g = l->seg[n++];
+      g.P = ew.gP + r0 * (K / 2); g.S = ew.gS + r0 * G; g.nrows = (int)(bb - aa); g.vec = 0;
+      g.trow = (int)(aa - sb);
+      RowSeg &u = l->seg[n++];
+      u.P = ew.uP + r0 * (K / 2); u.S = ew.uS + r0 * G; u.nrows = (int)(bb - aa); u.vec = 0;
+      u.trow = SB + (int)(aa - sb);
+    }
+  l->nseg = n;
+  l->K = K;
+  seglist_finalize(l);
+}
+
 template <int K>
 __device__ __forceinline__ void gateup_block(const ExpertGateUpArgs &a, const StagedAct4 &act,
-                                             const BlockScratch &bs, int blk, int nblk) {
-  constexpr int G = K / 128;
-  constexpr int SB = kTCap / (2 * G) < 256 ? kTCap / (2 * G) : 256;  // pair rows per sub-block
+                                             BlockScratch &bs, int blk, int nblk) {
+  constexpr int SB = gateup_sub_rows(K);  // pair rows per sub-block
   long lo, hi;
   block_range((long)a.slots * a.I, blk, nblk, lo, hi);
+  if (!bs.primed) {
+    __syncthreads();
+    if (threadIdx.x == 0) gateup_list(&bs.lists[bs.cur], a, lo, lo + SB < hi ? lo + SB : hi);
+  }
+  bs.primed = false;
 #pragma unroll 1
   for (long sb = lo; sb < hi; sb += SB) {
     const long se = sb + SB < hi ? sb + SB : hi;
+    const bool more = se < hi;
+    if (threadIdx.x == 0 && more) gateup_list(&bs.lists[bs.cur ^ 1], a, se, se + SB < hi ? se + SB : hi);
     __syncthreads();
-    if (threadIdx.x == 0) {
-      int n = 0;
-      for (int s = (int)(sb / a.I); s <= (int)((se - 1) / a.I) && n + 2 <= kMaxSegs; ++s) {
-        long aa = sb > (long)s * a.I ? sb : (long)s * a.I;
-        long bb = se < (long)(s + 1) * a.I ? se : (long)(s + 1) * a.I;
-        const ExpertW &ew = a.Experts[a.SelIdx[a.slot_begin + s]];
-        long r0 = aa - (long)s * a.I;
-        RowSeg &g = bs.segs[n++];
-        g.P = ew.gP + r0 * (K / 2); g.S = ew.gS + r0 * G; g.nrows = (int)(bb - aa); g.vec = 0;
-        g.trow = (int)(aa - sb);
-        RowSeg &u = bs.segs[n++];
-        u.P = ew.uP + r0 * (K / 2); u.S = ew.uS + r0 * G; u.nrows = (int)(bb - aa); u.vec = 0;
-        u.trow = SB + (int)(aa - sb);
-      }
-      bs.ibox[0] = n;
-      bs.ibox[1] = seg_finalize(bs.segs, n);
-    }
-    __syncthreads();
-    block_dot<K>(bs.segs, bs.ibox[0], bs.ibox[1], act, bs.T);
+    block_dot<K>(bs.ring, &bs.lists[bs.cur], more ? &bs.lists[bs.cur ^ 1] : nullptr, act, bs.T);
     const long r = sb + threadIdx.x;
     if (r < se) {
       float g = row_sum<K>(bs.T, threadIdx.x), u = row_sum<K>(bs.T, SB + threadIdx.x);
       a.Act[(size_t)a.slot_begin * a.I + r] = silu_mul(g, u);
     }
+    bs.cur ^= 1;
   }
 }
 __device__ __forceinline__ void gateup_block_dispatch(const ExpertGateUpArgs &a, const StagedAct4 &act,
-                                                      const BlockScratch &bs, int blk, int nblk) {
+                                                      BlockScratch &bs, int blk, int nblk) {
   switch (a.H) {
     case 256: gateup_block<256>(a, act, bs, blk, nblk); break;
     case 512: gateup_block<512>(a, act, bs, blk, nblk); break;
@@ -134,29 +173,44 @@ __device__ __forceinline__ void gateup_block_dispatch(const ExpertGateUpArgs &a,
 }
 
 // ---- expert down + combine + residual: output rows n in [0, H), all slots ----
+__device__ __forceinline__ int down_sub_rows(int K, int slots) {
+  const int per = kTCap / ((K / 128) * (slots > 0 ? slots : 1));
+  return per < 256 ? per : 256;
+}
+// One segment per slot over output rows [sb, se). One thread.
+__device__ __forceinline__ void down_list(SegList *l, const ExpertDownCombineArgs &a, long sb, long se) {
+  const int K = a.I, G = K / 128, nr = (int)(se - sb);
+  int n = 0;
+  if (nr > 0)
+    for (int s = 0; s < a.slots && n < kMaxSegs; ++s) {
+      const ExpertW &ew = a.Experts[a.SelIdx[s]];
+      RowSeg &d = l->seg[n++];
+      d.P = ew.dP + sb * (K / 2); d.S = ew.dS + sb * G; d.nrows = nr; d.vec = s; d.trow = s * nr;
+    }
+  l->nseg = n;
+  l->K = K;
+  seglist_finalize(l);
+}
+
 template <int K>
 __device__ __forceinline__ void down_block(const ExpertDownCombineArgs &a, const StagedAct4 &act,
-                                           const BlockScratch &bs, int blk, int nblk) {
-  constexpr int G = K / 128;
+                                           BlockScratch &bs, int blk, int nblk) {
   long lo, hi;
   block_range(a.H, blk, nblk, lo, hi);
-  const int sb_rows = kTCap / (G * (a.slots > 0 ? a.slots : 1)) < 256 ? kTCap / (G * (a.slots > 0 ? a.slots : 1)) : 256;
+  const int SB = down_sub_rows(K, a.slots);
+  if (!bs.primed) {
+    __syncthreads();
+    if (threadIdx.x == 0) down_list(&bs.lists[bs.cur], a, lo, lo + SB < hi ? lo + SB : hi);
+  }
+  bs.primed = false;
 #pragma unroll 1
-  for (long sb = lo; sb < hi; sb += sb_rows) {
-    const long se = sb + sb_rows < hi ? sb + sb_rows : hi;
+  for (long sb = lo; sb < hi; sb += SB) {
+    const long se = sb + SB < hi ? sb + SB : hi;
     const int nr = (int)(se - sb);
+    const bool more = se < hi;
+    if (threadIdx.x == 0 && more) down_list(&bs.lists[bs.cur ^ 1], a, se, se + SB < hi ? se + SB : hi);
     __syncthreads();
-    if (threadIdx.x == 0) {
-      for (int s = 0; s < a.slots; ++s) {
-        const ExpertW &ew = a.Experts[a.SelIdx[s]];
-        RowSeg &d = bs.segs[s];
-        d.P = ew.dP + sb * (K / 2); d.S = ew.dS + sb * G; d.nrows = nr; d.vec = s; d.trow = s * nr;
-      }
-      bs.ibox[0] = a.slots;
-      bs.ibox[1] = seg_finalize(bs.segs, a.slots);
-    }
-    __syncthreads();
-    block_dot<K>(bs.segs, bs.ibox[0], bs.ibox[1], act, bs.T);
+    block_dot<K>(bs.ring, &bs.lists[bs.cur], more ? &bs.lists[bs.cur ^ 1] : nullptr, act, bs.T);
     const long n = sb + threadIdx.x;
     if (n < se) {
       float acc = 0.0f;
@@ -164,10 +218,11 @@ __device__ __forceinline__ void down_block(const ExpertDownCombineArgs &a, const
       if (a.Moe) a.Moe[n] = acc;
       a.X[n] = __ldcg(a.Res + n) + acc;
     }
+    bs.cur ^= 1;
   }
 }
 __device__ __forceinline__ void down_block_dispatch(const ExpertDownCombineArgs &a, const StagedAct4 &act,
-                                                    const BlockScratch &bs, int blk, int nblk) {
+                                                    BlockScratch &bs, int blk, int nblk) {
   switch (a.I) {
     case 128: down_block<128>(a, act, bs, blk, nblk); break;
     case 256: down_block<256>(a, act, bs, blk, nblk); break;

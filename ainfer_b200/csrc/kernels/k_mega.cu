@@ -122,7 +122,7 @@ __device__ __forceinline__ void prefetch_gemv(const GemvMat *mats, int nmats, in
 // Runs one GEMV stage for this block: builds the stage's matrix table in shared
 // memory (row_start assigned here) and processes the block's contiguous rows.
 __device__ __forceinline__ void gemv_stage(const GemvMat *mats, int nmats, int K, const StagedAct4 &act,
-                                           GemvMat *smats, const BlockScratch &bs, int blk, int nblk) {
+                                           GemvMat *smats, BlockScratch &bs, int blk, int nblk) {
   __syncthreads();  // smats may still be read by the previous stage
   if (threadIdx.x == 0) {
     int row = 0;
@@ -131,10 +131,10 @@ __device__ __forceinline__ void gemv_stage(const GemvMat *mats, int nmats, int K
       smats[i].row_start = row;
       row += mats[i].N;
     }
-    bs.ibox[2] = row;
   }
   __syncthreads();
-  const long total = bs.ibox[2];
+  long total = 0;
+  for (int i = 0; i < nmats; ++i) total += smats[i].N;
   // only the contraction widths a decode layer can have (the host refuses other shapes)
   switch (K) {
     case 256: gemv_block<256>(smats, nmats, total, act, bs, blk, nblk); break;
@@ -254,13 +254,15 @@ __device__ __forceinline__ void prefetch_down(const ExpertW *experts, const int3
   }
 }
 
-extern __shared__ __align__(16) unsigned char mega_smem[];
+extern __shared__ __align__(128) unsigned char mega_smem[];
+constexpr int kMegaStages = 5;
+constexpr int kMegaRingOff = (kStageBytes + kYsFloats * 4 + kTCap * 4 + 127) / 128 * 128;
 
 __global__ void __launch_bounds__(256, 2) DecodeStepMega(const DecodeStepMegaArgs args) {
   const MegaPlan &P = *args.plan;
   __shared__ GemvMat smats[8];
-  __shared__ RowSeg s_segs[kMaxSegs];
-  __shared__ int s_ibox[4];
+  __shared__ SegList s_lists[2];
+  __shared__ Ring s_ring;
   __shared__ int32_t s_sel_idx[16];
   __shared__ float s_sel_w[16];
   __shared__ float s_gap;
@@ -268,7 +270,8 @@ __global__ void __launch_bounds__(256, 2) DecodeStepMega(const DecodeStepMegaArg
   __shared__ int s_ai[8];
   unsigned char *stage = mega_smem;
   float *ys = reinterpret_cast<float *>(mega_smem + kStageBytes);
-  const BlockScratch bs{s_segs, reinterpret_cast<float *>(mega_smem + kStageBytes + kYsFloats * 4), s_ibox};
+  ring_init(&s_ring, mega_smem + kMegaRingOff, kMegaStages);
+  BlockScratch bs{&s_ring, s_lists, reinterpret_cast<float *>(mega_smem + kStageBytes + kYsFloats * 4), 0, false};
   const int blk = blockIdx.x, nblk = gridDim.x;
   GridSync gs{P.bar_count, P.error, 0u, (unsigned)nblk, blk == 0 ? P.stage_stamps : nullptr, P.stage_stamp_cap, 0};
   stage_stamp(gs);
@@ -420,7 +423,7 @@ __global__ void __launch_bounds__(256, 2) DecodeStepMega(const DecodeStepMegaArg
   }
 }
 
-static uint32_t mega_smem_fn(const void *) { return (uint32_t)(kStageBytes + kYsFloats * 4 + kTCap * 4); }
+static uint32_t mega_smem_fn(const void *) { return (uint32_t)(kMegaRingOff + kMegaStages * kStageStride); }
 
 #define F(f) AINFER_ARG(DecodeStepMegaArgs, f)
 AINFER_REGISTER_COOP(DecodeStepMega, DecodeStepMegaArgs, 256, 0, 0, mega_smem_fn, F(plan), F(mode));

@@ -5,7 +5,7 @@
 
 namespace ainfer {
 
-extern __shared__ __align__(16) unsigned char moe_smem[];
+extern __shared__ __align__(128) unsigned char moe_smem[];
 
 __global__ void __launch_bounds__(256) RouterTopK(const RouterTopKArgs a) {
   __shared__ bool is_last;
@@ -25,20 +25,29 @@ __global__ void __launch_bounds__(256) RouterTopK(const RouterTopKArgs a) {
   router_select(a.Logits, a.E, a.k, a.Wsg != nullptr, sp, a.SelIdx, a.SelW, a.NearGap);
 }
 
-__global__ void __launch_bounds__(256) ExpertGateUp(const ExpertGateUpArgs a) {
-  __shared__ RowSeg segs[kMaxSegs];
+constexpr int kMoeStages = 6;
+__host__ __device__ inline uint32_t moe_round128(uint32_t v) { return (v + 127u) & ~127u; }
+
+__global__ void __launch_bounds__(256, 2) ExpertGateUp(const ExpertGateUpArgs a) {
+  __shared__ SegList lists[2];
   __shared__ float T[kTCap];
-  __shared__ int ibox[4];
+  __shared__ Ring ring;
+  ring_init(&ring, moe_smem + moe_round128(staged4_bytes(a.H, 1)), kMoeStages);
+  BlockScratch bs{&ring, lists, T, 0, false};
   StagedAct4 act = stage4(moe_smem, a.XQ, a.SQ, a.H, 1, a.H, a.H / 128);
-  gateup_block_dispatch(a, act, BlockScratch{segs, T, ibox}, blockIdx.x, gridDim.x);
+  gateup_block_dispatch(a, act, bs, blockIdx.x, gridDim.x);
+  if (threadIdx.x == 0) ring_drain_after_fault(&ring);
 }
 
-__global__ void __launch_bounds__(256) ExpertDownCombine(const ExpertDownCombineArgs a) {
-  __shared__ RowSeg segs[kMaxSegs];
+__global__ void __launch_bounds__(256, 2) ExpertDownCombine(const ExpertDownCombineArgs a) {
+  __shared__ SegList lists[2];
   __shared__ float T[kTCap];
-  __shared__ int ibox[4];
+  __shared__ Ring ring;
+  ring_init(&ring, moe_smem + moe_round128(staged4_bytes(a.I, a.slots)), kMoeStages);
+  BlockScratch bs{&ring, lists, T, 0, false};
   StagedAct4 act = stage4_from_f32<true>(moe_smem, a.Act, a.I, a.slots, a.I);
-  down_block_dispatch(a, act, BlockScratch{segs, T, ibox}, blockIdx.x, gridDim.x);
+  down_block_dispatch(a, act, bs, blockIdx.x, gridDim.x);
+  if (threadIdx.x == 0) ring_drain_after_fault(&ring);
 }
 
 #define F(f) AINFER_ARG(RouterTopKArgs, f)
@@ -47,7 +56,7 @@ AINFER_REGISTER(RouterTopK, RouterTopKArgs, 256, 8, 0, nullptr, F(Wr), F(Wsg), F
 #undef F
 
 static uint32_t gateup_smem_fn(const void *args) {
-  return staged_act_bytes(((const ExpertGateUpArgs *)args)->H, 1);
+  return moe_round128(staged4_bytes(((const ExpertGateUpArgs *)args)->H, 1)) + kMoeStages * kStageStride;
 }
 #define F(f) AINFER_ARG(ExpertGateUpArgs, f)
 AINFER_REGISTER(ExpertGateUp, ExpertGateUpArgs, 256, 0, 0, gateup_smem_fn, F(Experts), F(SelIdx),
@@ -56,7 +65,7 @@ AINFER_REGISTER(ExpertGateUp, ExpertGateUpArgs, 256, 0, 0, gateup_smem_fn, F(Exp
 
 static uint32_t down_smem_fn(const void *args) {
   const ExpertDownCombineArgs *a = (const ExpertDownCombineArgs *)args;
-  return staged_act_bytes(a->I, a->slots);
+  return moe_round128(staged4_bytes(a->I, a->slots)) + kMoeStages * kStageStride;
 }
 #define F(f) AINFER_ARG(ExpertDownCombineArgs, f)
 AINFER_REGISTER(ExpertDownCombine, ExpertDownCombineArgs, 256, 0, 0, down_smem_fn, F(Experts),

@@ -34,6 +34,17 @@ int kernel_count();
 const KernelDesc *kernel_at(int i);
 const KernelDesc *kernel_find(const char *name);
 
+// A translation unit whose kernels can report a stream fault registers a hook
+// that stores the device address of the library's host-visible fault word in
+// that unit's own __device__ pointer. Called once per device, device current.
+typedef int (*FaultHook)(unsigned int *device_ptr);
+void register_fault_hook(FaultHook h);
+int fault_hook_count();
+FaultHook fault_hook_at(int i);
+struct FaultRegistrar {
+  explicit FaultRegistrar(FaultHook h) { register_fault_hook(h); }
+};
+
 struct Registrar {
   explicit Registrar(const KernelDesc &d) { register_kernel(d); }
 };

@@ -1,0 +1,249 @@
+// Weight ring: a block streams its contiguous rows of packed INT4 weights (and
+// their bf16 scales) from HBM into shared memory with bulk asynchronous copies
+// (cp.async.bulk, the untiled TMA path) that complete on mbarriers. One thread
+// issues the copies; all 256 threads consume tiles. The copies do not depend on
+// activations, so they keep running while the block waits for whatever produces
+// its activations (a grid barrier, a staging step): HBM traffic is decoupled
+// from the dependency chain of a decode step.
+//
+// A tile is 8 KB of weights = 256 lanes x 32 bytes = 16384/K whole rows, plus
+// the 256 bytes of scales of those rows. Stage i of the ring holds the tile
+// with running index t where t % nst == i. full[i] completes when the tile's
+// bytes have landed (transaction count); empty[i] completes when all 8 warps
+// have copied their bytes into registers (one arrival per warp: arrivals on
+// one barrier serialise). Both are waited on with a
+// bounded number of polls: a wait that runs out sets the fault word and carries
+// on (reading whatever the stage holds), so control flow stays uniform and the
+// kernel always terminates; the host reports the fault at the next sync.
+#pragma once
+#include "common.cuh"
+#include "registry.h"
+
+namespace ainfer {
+
+constexpr int kTileBytes = 8192;
+constexpr int kTileScaleBytes = 256;
+constexpr int kStageStride = kTileBytes + kTileScaleBytes;
+constexpr int kMaxStages = 12;
+constexpr uint32_t kRingSpinLimit = 1u << 18;
+
+// Contiguous rows of one matrix, dotted with one staged activation vector.
+struct RowSeg {
+  const uint8_t *P;   // packed nibbles of the segment's first row
+  const uint16_t *S;  // bf16 scales of the segment's first row
+  int32_t nrows;
+  int32_t vec;        // staged activation vector this segment is dotted with
+  int32_t trow;       // first row of this segment in the t[][] scratch
+  int32_t pad;
+};
+constexpr int kMaxSegs = 16;
+
+// A list of segments of matrices with the same K. Lives in shared memory.
+struct SegList {
+  RowSeg seg[kMaxSegs];
+  int32_t nseg;
+  int32_t K;
+  int32_t ntiles;  // filled by seglist_finalize
+  int32_t pad;
+};
+
+struct Ring {
+  unsigned long long full[kMaxStages];
+  unsigned long long empty[kMaxStages];
+  unsigned char *data;  // nst * kStageStride bytes, 128-byte aligned shared memory
+  uint32_t nst;         // stages in use
+  uint32_t c_stage;     // stage of the next tile to consume
+  uint32_t c_phase;     // parity of that stage's current use
+  uint32_t pre;         // leading tiles of the next list that are already in flight
+  uint32_t issued;      // tiles issued so far, over all calls (for the drain after a fault)
+  uint32_t fault;       // sticky: 1 a wait ran out, 2 a source was not 16-byte aligned
+};
+
+// Per-translation-unit pointer to the host-visible fault word (set once per
+// device by the library when the device is opened; null = not reported).
+static __device__ unsigned int *g_stream_fault_word;
+static int set_stream_fault_word(unsigned int *device_ptr) {
+  return cudaMemcpyToSymbol(g_stream_fault_word, &device_ptr, sizeof device_ptr) == cudaSuccess ? 0 : 1;
+}
+static FaultRegistrar g_stream_fault_registrar(set_stream_fault_word);
+
+__device__ __forceinline__ uint32_t smem_addr(const void *p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(unsigned long long *b, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(b)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned long long *b) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(b)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect(unsigned long long *b, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(b)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try(unsigned long long *b, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_addr(b)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void ring_fault(Ring *ring, uint32_t code) {
+  ring->fault = code;
+  if (g_stream_fault_word) *reinterpret_cast<volatile unsigned int *>(g_stream_fault_word) = code;
+}
+// Bounded wait; false (and the fault word set) when it ran out.
+__device__ __forceinline__ bool mbar_wait(Ring *ring, unsigned long long *b, uint32_t parity) {
+  if (mbar_try(b, parity)) return true;
+  // after a first fault no wait in this block spins again: the launch is lost, end it quickly
+  const uint32_t limit = *reinterpret_cast<volatile uint32_t *>(&ring->fault) ? 0u : kRingSpinLimit;
+  for (uint32_t i = 0; i < limit; ++i)
+    if (mbar_try(b, parity)) return true;
+  ring_fault(ring, 1);
+  return false;
+}
+__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, unsigned long long *b) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_addr(dst)),
+               "l"(src), "r"(bytes), "r"(smem_addr(b))
+               : "memory");
+}
+
+// Called by every thread once, before the first use. `data` is nst*kStageStride bytes.
+__device__ __forceinline__ void ring_init(Ring *ring, unsigned char *data, int nst) {
+  if (threadIdx.x == 0) {
+    ring->data = data;
+    ring->nst = (uint32_t)nst;
+    ring->c_stage = 0;
+    ring->c_phase = 0;
+    ring->pre = 0;
+    ring->issued = 0;
+    ring->fault = 0;
+    for (int i = 0; i < nst; ++i) {
+      mbar_init(&ring->full[i], 1);
+      mbar_init(&ring->empty[i], blockDim.x / 32);  // one arrival per warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+}
+
+// Tile count of a list; one thread.
+__device__ __forceinline__ void seglist_finalize(SegList *l) {
+  const int rpi = 16384 / l->K;
+  int n = 0;
+  for (int i = 0; i < l->nseg; ++i) n += (l->seg[i].nrows + rpi - 1) / rpi;
+  l->ntiles = n;
+}
+
+// True when a tile's scales can travel by bulk copy (16-byte aligned source
+// and size); otherwise the consumers read them from global memory themselves.
+__device__ __forceinline__ bool tile_scales_bulk(const uint16_t *seg_scales, uint32_t bytes) {
+  return ((reinterpret_cast<uintptr_t>(seg_scales) | bytes) & 15u) == 0;
+}
+
+// The issuing thread's cursor: where in a list the next tile starts and which
+// stage it goes to. Everything it needs per tile sits in registers.
+struct Producer {
+  const SegList *l;
+  const uint8_t *P;
+  const uint16_t *S;
+  int s, r0, nrows;          // segment, first row of the next tile, rows of the segment
+  int rpi, row_bytes, srow;  // rows per tile, weight bytes per row, scale bytes per row
+  uint32_t stage, phase;
+
+  __device__ __forceinline__ void load_seg() {
+    if (s < l->nseg) {
+      P = l->seg[s].P;
+      S = l->seg[s].S;
+      nrows = l->seg[s].nrows;
+    }
+  }
+  __device__ __forceinline__ void open(const SegList *list) {
+    l = list;
+    rpi = 16384 / list->K;
+    row_bytes = list->K / 2;
+    srow = list->K / 64;
+    s = 0;
+    r0 = 0;
+    load_seg();
+  }
+  __device__ __forceinline__ void skip() {  // the next tile is already in flight
+    r0 += rpi;
+    if (r0 >= nrows) {
+      ++s;
+      r0 = 0;
+      load_seg();
+    }
+  }
+  __device__ __forceinline__ void next_stage(uint32_t nst) {
+    if (++stage == nst) {
+      stage = 0;
+      phase ^= 1u;
+    }
+  }
+  // Issues the copy of the next tile into `stage` and moves on.
+  __device__ __forceinline__ void issue(Ring *ring, unsigned char *data, uint32_t nst) {
+    const int rows = nrows - r0 < rpi ? nrows - r0 : rpi;
+    unsigned char *dst = data + stage * kStageStride;
+    const uint8_t *src = P + (size_t)r0 * row_bytes;
+    const uint16_t *ssrc = reinterpret_cast<const uint16_t *>(reinterpret_cast<const uint8_t *>(S) + (size_t)r0 * srow);
+    const uint32_t wbytes = (uint32_t)(rows * row_bytes), sbytes = (uint32_t)(rows * srow);
+    unsigned long long *bar = &ring->full[stage];
+    if (reinterpret_cast<uintptr_t>(src) & 15u) {  // cannot be copied in bulk: report, keep the phase moving
+      ring_fault(ring, 2);
+      mbar_arrive(bar);
+    } else {
+      const bool sb = tile_scales_bulk(S, sbytes);
+      mbar_arrive_expect(bar, wbytes + (sb ? sbytes : 0));
+      bulk_g2s(dst, src, wbytes, bar);
+      if (sb) bulk_g2s(dst + kTileBytes, ssrc, sbytes, bar);
+    }
+    r0 += rpi;
+    if (r0 >= nrows) {
+      ++s;
+      r0 = 0;
+      load_seg();
+    }
+    next_stage(nst);
+  }
+};
+
+// Tops up the ring with leading tiles of `next` (the list the next block_dot
+// call will consume). Call between block_dot calls, when every stage not
+// counted in ring->pre is free. One thread; no synchronisation.
+__device__ __forceinline__ void ring_prefetch(Ring *ring, const SegList *next) {
+  const uint32_t nst = ring->nst;
+  const uint32_t cap = (uint32_t)next->ntiles < nst ? (uint32_t)next->ntiles : nst;
+  if (ring->pre >= cap) return;
+  Producer pr;
+  pr.open(next);
+  pr.stage = ring->c_stage;
+  pr.phase = ring->c_phase;
+  uint32_t i = 0;
+  for (; i < ring->pre; ++i) {
+    pr.skip();
+    pr.next_stage(nst);
+  }
+  for (; i < cap; ++i) pr.issue(ring, ring->data, nst);
+  ring->issued += cap - ring->pre;
+  ring->pre = cap;
+}
+
+// After a fault: waits (bounded) for whatever may still be in flight into this
+// block's shared memory, so that the block does not retire under a landing copy.
+// One thread, at the end of the kernel.
+__device__ __forceinline__ void ring_drain_after_fault(Ring *ring) {
+  if (ring->fault == 0) return;
+  const uint32_t end = ring->issued;
+  for (uint32_t st = 0; st < ring->nst && st < end; ++st) {
+    uint32_t t = end - 1 - ((end - 1 - st) % ring->nst);  // latest issued tile held by stage st
+    for (uint32_t i = 0; i < kRingSpinLimit; ++i)
+      if (mbar_try(&ring->full[st], (t / ring->nst) & 1u)) break;
+  }
+}
+
+}  // namespace ainfer

@@ -2,8 +2,9 @@
 
   python -m ainfer_b200.opbench gemv [--m 1] [--n 151936] [--k 2048] [--reps 20] [--sweep]
       INT4 g128 GEMV (Int4GemvA8) on seeded device-generated weights: ms and GB/s
-      of algorithmic bytes per launch, cold L2 (a >126 MB buffer is rewritten
-      between launches). --sweep runs the operator sweep shapes
+      of algorithmic bytes per launch, cold L2 (launches of a recorded list rotate over
+      more than 256 MB of distinct weight buffers; --flush: single launches, each after a
+      256 MB rewrite). --sweep runs the operator sweep shapes
       M in {1,2,4,8} x (N,K) in {(512,2048),(4096,2048),(8192,2048),(151936,2048),(2048,512)}.
   python -m ainfer_b200.opbench decode [--model small] [--prompt 4] [--steps 8]
       A short greedy decode of a synthetic model preset through the runtime
@@ -36,36 +37,58 @@ def rows_per_group(K):
     return 8 * rt * (32 // min(K // 32, 32))
 
 
-def gemv_once(dev, N, K, M=1, reps=20, flush=True):
-    dP, dS, dY = dev.alloc(N * K // 2), dev.alloc(N * K // 128 * 2), dev.zeros(M * N * 4)
-    k = dev.kernel("SynthInt4")
-    k.set_arg(0, dP); k.set_arg(1, dS); k.set_arg(2, synth_key(0, f"opbench.{N}.{K}"), "u64")
-    k.set_arg(3, N * K // 128, "u64"); k.set_arg(4, 0.02)
-    k.launch(dev.info().sm_count * 8)
+def gemv_once(dev, N, K, M=1, reps=20, flush=False, groups=None):
+    """Times one GEMV shape. Default: a recorded command list of `reps` launches that rotate over
+    enough distinct weight buffers to exceed L2 (>= 256 MB in total), timed as a whole on the device,
+    so neither host launch latency nor L2 hits enter the figure. flush=True instead times single
+    launches, each after a 256 MB rewrite."""
+    wbytes = N * K // 2 + N * K // 128 * 2
+    nbuf = 1 if flush else max(1, min(64, -(-(256 << 20) // wbytes)))
+    sm = dev.info().sm_count
     rng = np.random.default_rng(0)
     xq = dev.upload(rng.integers(-127, 128, (M, K), dtype=np.int8))
     sq = dev.upload(np.full((M, K // 128), 0.01, np.float32))
-    tab = np.zeros(1, GEMV_MAT)
-    tab[0]["P"], tab[0]["S"], tab[0]["Y"], tab[0]["N"], tab[0]["ldy"] = dP, dS, dY, N, N
-    g = dev.kernel(KERNEL_BY_M[M])
-    groups = max(1, min((N + rows_per_group(K) - 1) // rows_per_group(K), dev.info().sm_count * 8))
-    g.set_args(dev.upload(tab.view(np.uint8)), 1, N, xq, sq, K, M)
+    if not groups:
+        groups = max(1, min((N + rows_per_group(K) - 1) // rows_per_group(K), sm * 8))
+    bufs, kernels = [], []
+    for b in range(nbuf):
+        dP, dS, dY = dev.alloc(N * K // 2), dev.alloc(N * K // 128 * 2), dev.zeros(M * N * 4)
+        k = dev.kernel("SynthInt4")
+        k.set_arg(0, dP); k.set_arg(1, dS); k.set_arg(2, synth_key(b, f"opbench.{N}.{K}"), "u64")
+        k.set_arg(3, N * K // 128, "u64"); k.set_arg(4, 0.02)
+        k.launch(sm * 8)
+        tab = np.zeros(1, GEMV_MAT)
+        tab[0]["P"], tab[0]["S"], tab[0]["Y"], tab[0]["N"], tab[0]["ldy"] = dP, dS, dY, N, N
+        g = dev.kernel(KERNEL_BY_M[M])
+        g.set_args(dev.upload(tab.view(np.uint8)), 1, N, xq, sq, K, M)
+        bufs.append((dP, dS, dY)); kernels.append(g)
     e0, e1 = dev.event(), dev.event()
-    for _ in range(3):
-        g.launch(groups)
-    total = 0.0
-    for _ in range(reps):
-        if flush:
+    for i in range(3):
+        kernels[i % nbuf].launch(groups)
+    if flush:
+        total = 0.0
+        for _ in range(reps):
             dev.flush_l2()
-        e0.record(); g.launch(groups); e1.record()
-        total += e0.elapsed_ms(e1)
+            e0.record(); kernels[0].launch(groups); e1.record()
+            total += e0.elapsed_ms(e1)
+        ms = total / reps
+    else:
+        cl = dev.new_list()
+        for i in range(reps):
+            cl.append(kernels[i % nbuf], groups)
+        cl.close()
+        cl.execute()
+        e0.record(); cl.execute(); e1.record()
+        ms = e0.elapsed_ms(e1) / reps
+        cl.destroy()
     dev.sync()
-    for p in (dP, dS, dY):
-        dev.free(p)
-    ms = total / reps
+    for t in bufs:
+        for p in t:
+            dev.free(p)
     b = gemv_bytes(N, K, M)
     return {"op": "int4_gemv_a8", "M": M, "N": N, "K": K, "ms": ms, "gbs": b / ms / 1e6, "bytes": b,
-            "groups": groups, "flops": 2.0 * M * N * K, "tflops": 2.0 * M * N * K / ms / 1e9}
+            "groups": groups, "buffers": nbuf, "mode": "flush" if flush else "list",
+            "flops": 2.0 * M * N * K, "tflops": 2.0 * M * N * K / ms / 1e9}
 
 
 def main(argv=None):
@@ -77,7 +100,8 @@ def main(argv=None):
     g.add_argument("--k", type=int, default=2048)
     g.add_argument("--reps", type=int, default=20)
     g.add_argument("--sweep", action="store_true")
-    g.add_argument("--no-flush", action="store_true")
+    g.add_argument("--groups", type=int, default=0, help="thread groups per launch (default: by shape)")
+    g.add_argument("--flush", action="store_true", help="time single launches after an L2 rewrite")
     d = sub.add_parser("decode")
     d.add_argument("--model", default="small")
     d.add_argument("--prompt", type=int, default=4)
@@ -91,7 +115,7 @@ def main(argv=None):
         shapes = ([(m, n, k) for (n, k) in [(512, 2048), (4096, 2048), (8192, 2048), (151936, 2048), (2048, 512)]
                    for m in (1, 2, 4, 8)] if args.sweep else [(args.m, args.n, args.k)])
         for (m, n, k) in shapes:
-            print(json.dumps(gemv_once(dev, n, k, m, args.reps, not args.no_flush)), flush=True)
+            print(json.dumps(gemv_once(dev, n, k, m, args.reps, args.flush, args.groups)), flush=True)
     else:
         model = runtime.Model(dev, f"synth:{args.model}:seed=0")
         sess = runtime.Session(model, args.prompt + args.steps + 8,
