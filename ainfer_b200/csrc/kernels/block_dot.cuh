@@ -1,52 +1,54 @@
 // Block-level INT4 (group 128) x INT8 dot over a list of row segments, fed by
 // the weight ring (weight_ring.cuh).
 //
-// Unless its inner loop is lean the kernel is bound by instruction issue, not
-// by HBM: at 6.5 TB/s an SM receives 16 bytes of weights every 0.7 cycles,
-// which leaves about 90 thread instructions per 16 bytes at perfect issue.
-//   * a lane owns HALF a group: 32 contiguous bytes = 64 weights of a tile that
-//     a bulk copy has put in shared memory; it moves them into registers and
-//     releases the stage at once;
-//   * the lane's 64 activations, the group's activation sum and scale stay in
-//     registers for as long as consecutive tiles use the same staged vector;
-//   * nibbles are never shifted: low nibbles are masked in place, high nibbles
-//     are masked in place as 16*n and their dot is divided by 16 at the end
-//     (exact: it is a multiple of 16); both are biased by xor 8 to unsigned so
-//     that one LOP3 prepares each dp4a operand, and 8*sum(x) is subtracted per
-//     group;
-//   * one shuffle joins the two halves of a group; the even lane stores
-//       t[row][g] = ((float)group_sum * weight_scale) * act_scale[g];
+// On B200 the kernel is bound by the integer pipe, not by HBM, unless its inner
+// loop is lean: at 6.5 TB/s an SM receives a 16 KB tile every ~710 cycles and
+// the integer pipe retires 64 lane-operations per cycle, so a tile may cost at
+// most ~180 integer operations per thread (64 of them are the dp4a and masks). The loop is built around that:
+//   * a lane owns a WHOLE group of a row: 64 contiguous bytes = 128 weights of a
+//     16 KB tile that a bulk copy has put in shared memory. It moves them into
+//     registers (four 16-byte reads in a lane-rotated order that keeps every
+//     quarter-warp on distinct banks) and releases the stage at once (one
+//     arrival per warp);
+//   * the lane's 128 activations and their scale stay in registers for as long
+//     as consecutive tiles use the same staged vector;
+//   * nibbles are two's complement, so a nibble moved to the top of its byte IS
+//     the signed byte 16*v: high nibbles are masked in place, low nibbles are
+//     shifted by a multiply (which runs on the other arithmetic pipe) and
+//     masked; both feed signed dp4a and the sum is divided by 16 at the end
+//     (exact: it is a multiple of 16). No bias term, no shuffle;
+//   * the lane stores t[row][g] = ((float)group_sum * weight_scale) * act_scale[g];
 //   * after one __syncthreads a single thread per row adds t[row][0..G) in
 //     ascending group order (the reference's accumulation order,
 //     tools/cmdlist/kernels.cpp:157-191) and runs the row's epilogue.
 // Integer sums are associative and the fp32 sum keeps the reference order, so
 // results are bit-identical to the one-work-item-per-row loop.
 //
-// Lane tid of the block holds bytes [32*tid, 32*tid+32) of a tile: row
-// tid / HPR of the tile, half-group hc = tid % HPR (HPR = K/64 divides 256).
+// Lane l (0..255) of the block holds bytes [64*l, 64*l+64) of a tile: row
+// l / G of the tile, group l % G (G = K/128 divides 256).
 #pragma once
 #include "common.cuh"
 #include "weight_ring.cuh"
 
 namespace ainfer {
 
-// Staged activations, half-group layout: for vector v, half-group hc and j in
-// 0..3 the uint4 x[(v*4 + j) * HPR + hc] holds the de-interleaved INT8 bytes of
-// weights hc*64 + 16j .. +15: {even(0..7), odd(0..7), even(8..15), odd(8..15)}
-// where even = bytes (x0,x2,x4,x6), odd = (x1,x3,x5,x7) of an 8-weight word.
+// Staged activations, group-major layout: for vector v, group g and q in 0..7
+// the uint4 x[(v*8 + q) * G + g] holds the de-interleaved INT8 bytes of weights
+// g*128 + 16q .. +15: {even(0..7), odd(0..7), even(8..15), odd(8..15)} where
+// even = bytes (x0,x2,x4,x6), odd = (x1,x3,x5,x7) of an 8-weight word. Lanes of
+// a warp own consecutive groups, so their 16-byte reads are conflict-free.
 struct StagedAct4 {
   const uint4 *x;
-  const int *gsum;   // [M][K/128] sum of INT8 activations per group
   const float *sq;   // [M][K/128] activation scales
 };
 __host__ __device__ inline uint32_t staged4_bytes(int K, int M) {
-  return (uint32_t)((size_t)M * K + (size_t)M * (K / 128) * 8);
+  return (uint32_t)((size_t)M * K + (size_t)M * (K / 128) * 4);
 }
 // word index (in 32-bit words) of 8-weight piece pc of vector v, parity 0 even / 1 odd
 __device__ __forceinline__ int staged4_word(int K, int v, int pc, int parity) {
-  const int HPR = K / 64;
-  int hc = pc >> 3, j = (pc >> 1) & 3;
-  return (((v * 4 + j) * HPR + hc) << 2) + ((pc & 1) << 1) + parity;
+  const int G = K / 128;
+  int g = pc >> 4, i = pc & 15;
+  return (((v * 8 + (i >> 1)) * G + g) << 2) + ((i & 1) << 1) + parity;
 }
 
 // Stages M natural-order INT8 vectors (global memory) with their fp32 group scales.
@@ -54,8 +56,7 @@ __device__ __forceinline__ StagedAct4 stage4(unsigned char *smem, const int8_t *
                                              int M, long xq_stride, long sq_stride) {
   uint32_t *xw = reinterpret_cast<uint32_t *>(smem);
   const int G = K / 128;
-  int *gs = reinterpret_cast<int *>(smem + (size_t)M * K);
-  float *sqs = reinterpret_cast<float *>(smem + (size_t)M * K + (size_t)M * G * 4);
+  float *sqs = reinterpret_cast<float *>(smem + (size_t)M * K);
   for (int i = threadIdx.x; i < M * (K / 8); i += blockDim.x) {
     int m = i / (K / 8), pc = i % (K / 8);
     uint2 v = __ldcg(reinterpret_cast<const uint2 *>(xq + m * xq_stride + (long)pc * 8));
@@ -65,20 +66,9 @@ __device__ __forceinline__ StagedAct4 stage4(unsigned char *smem, const int8_t *
   for (int i = threadIdx.x; i < M * G; i += blockDim.x) {
     int m = i / G, g = i % G;
     sqs[i] = __ldcg(sq + m * sq_stride + g);
-    const uint4 *grp = reinterpret_cast<const uint4 *>(xq + m * xq_stride + (long)g * 128);
-    int s = 0;
-#pragma unroll
-    for (int q = 0; q < 8; ++q) {
-      uint4 u = __ldcg(grp + q);
-      s = __dp4a((int)u.x, 0x01010101, s);
-      s = __dp4a((int)u.y, 0x01010101, s);
-      s = __dp4a((int)u.z, 0x01010101, s);
-      s = __dp4a((int)u.w, 0x01010101, s);
-    }
-    gs[i] = s;
   }
   __syncthreads();
-  return StagedAct4{reinterpret_cast<const uint4 *>(smem), gs, sqs};
+  return StagedAct4{reinterpret_cast<const uint4 *>(smem), sqs};
 }
 
 // Quantises M fp32 vectors (per-128 activation quantiser, tools/cmdlist/
@@ -88,8 +78,7 @@ __device__ __forceinline__ StagedAct4 stage4_from_f32(unsigned char *smem, const
                                                       long x_stride) {
   uint32_t *xw = reinterpret_cast<uint32_t *>(smem);
   const int G = K / 128;
-  int *gs = reinterpret_cast<int *>(smem + (size_t)M * K);
-  float *sqs = reinterpret_cast<float *>(smem + (size_t)M * K + (size_t)M * G * 4);
+  float *sqs = reinterpret_cast<float *>(smem + (size_t)M * K);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
   for (int i = warp; i < M * G; i += warps) {
     int m = i / G, g = i % G;
@@ -107,32 +96,38 @@ __device__ __forceinline__ StagedAct4 stage4_from_f32(unsigned char *smem, const
     int pc = g * 16 + (lane >> 1);  // 8-weight piece: two lanes of 4 weights each
     if (lane & 1) xw[staged4_word(K, m, pc, 1)] = __byte_perm(other, own, 0x7531);
     else xw[staged4_word(K, m, pc, 0)] = __byte_perm(own, other, 0x6420);
-    int sum = warp_sum_int(q0 + q1 + q2 + q3);
-    if (lane == 0) {
-      gs[i] = sum;
-      sqs[i] = s;
-    }
+    if (lane == 0) sqs[i] = s;
   }
   __syncthreads();
-  return StagedAct4{reinterpret_cast<const uint4 *>(smem), gs, sqs};
+  return StagedAct4{reinterpret_cast<const uint4 *>(smem), sqs};
 }
 
-// sum over 64 weights of (nibble ^ 8) * x: low nibbles exactly, high nibbles as 16*(n^8).
-__device__ __forceinline__ void dot64_biased(const uint4 &wa, const uint4 &wb, const uint4 (&x)[4], int &lo,
-                                             int &hi) {
-  const uint32_t w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
-  const uint32_t xe[8] = {x[0].x, x[0].z, x[1].x, x[1].z, x[2].x, x[2].z, x[3].x, x[3].z};
-  const uint32_t xo[8] = {x[0].y, x[0].w, x[1].y, x[1].w, x[2].y, x[2].w, x[3].y, x[3].w};
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    uint32_t l = (w[i] & 0x0F0F0F0Fu) ^ 0x08080808u;
-    uint32_t h = (w[i] & 0xF0F0F0F0u) ^ 0x80808080u;
-    int lo2, hi2;
-    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(lo2) : "r"(l), "r"(xe[i]), "r"(lo));
-    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(hi2) : "r"(h), "r"(xo[i]), "r"(hi));
-    lo = lo2;
-    hi = hi2;
-  }
+// 32-bit shared-window loads and stores (no generic address arithmetic in the loop).
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t lds_u16(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void sts_f32(uint32_t addr, float v) {
+  asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+
+// acc += 16 * sum over the 16 weights of two packed words of v*x, v the two's
+// complement nibble: a nibble at the top of its byte is the signed byte 16*v.
+// The low nibbles get there by a multiply by 16 (an integer multiply-add, which
+// does not run on the pipe the logic and dot instructions share).
+__device__ __forceinline__ int dot16_x16(const uint4 &w4, int which, const uint4 &x, int acc) {
+  const uint32_t w0 = which == 0 ? w4.x : w4.z, w1 = which == 0 ? w4.y : w4.w;
+  acc = __dp4a((int)((w0 * 16u) & 0xF0F0F0F0u), (int)x.x, acc);
+  acc = __dp4a((int)(w0 & 0xF0F0F0F0u), (int)x.y, acc);
+  acc = __dp4a((int)((w1 * 16u) & 0xF0F0F0F0u), (int)x.z, acc);
+  acc = __dp4a((int)(w1 & 0xF0F0F0F0u), (int)x.w, acc);
+  return acc;
 }
 
 // t[(trow + local_row) * G + g] for every (row, group) of the list `cur`.
@@ -153,15 +148,20 @@ __device__ __forceinline__ void dot64_biased(const uint4 &wa, const uint4 &wb, c
 template <int K>
 AINFER_BLOCK_DOT_LINKAGE void block_dot(Ring *ring, const SegList *cur, const SegList *next,
                                         const StagedAct4 &act, float *T) {
-  constexpr int HPR = K / 64, G = K / 128;
-  constexpr int NTHR = 256, RPI = NTHR / HPR;  // rows per tile
-  static_assert(NTHR % HPR == 0, "K/64 must divide the block size");
-  const int tid = threadIdx.x, hc = tid % HPR, rt = tid / HPR;
+  constexpr int G = K / 128;
+  constexpr int RPI = 256 / G;  // rows per tile
+  static_assert(256 % G == 0 && G <= 256, "K/128 must divide 256");
+  const int tid = threadIdx.x;
+  const int g = tid % G, rt = tid / G;
+  const bool warp_lead = (tid & 31) == 0;
   const uint32_t nst = ring->nst;
-  unsigned char *const data = ring->data;
+  const uint32_t data_a = smem_addr(ring->data), full_a = smem_addr(&ring->full[0]),
+                 empty_a = smem_addr(&ring->empty[0]), T_a = smem_addr(T);
   uint32_t cs = ring->c_stage, cph = ring->c_phase;
   const int ntiles = cur->ntiles;
-  const bool even = (hc & 1) == 0;
+  // piece order of this lane: at step s it reads piece (s + (tid >> 1)) & 3 of its 64 bytes
+  const int rot = (tid >> 1) & 3;
+  const uint32_t lane_off = (uint32_t)tid * 64u;
 
   // ---- issuing thread: fill the ring ----
   Producer pr;
@@ -182,76 +182,86 @@ AINFER_BLOCK_DOT_LINKAGE void block_dot(Ring *ring, const SegList *cur, const Se
     const uint32_t first = issued;
     for (; issued < cap; ++issued) {
       if (!in_next && issued == (uint32_t)ntiles) { pr.open(next); in_next = true; }
-      pr.issue(ring, data, nst);
+      pr.issue(ring, ring->data, nst);
     }
     ring->issued += issued - first;
   }
 
   // ---- consume ----
-  int seg = 0, r0 = 0;  // segment and first row of the current tile
-  int nrows = 0, vec = -1;
-  bool s_aligned = false;
-  const uint16_t *sglob = nullptr;  // this lane's scale in global memory, row 0 of the segment
-  float *tp = nullptr;              // this lane's T entry, row 0 of the segment
-  uint4 x[4];
-  int gs8 = 0;
+  // A tile holds RPI consecutive flat rows of the list; this lane's row of tile t is t*RPI + rt.
+  const int total = cur->total;
+  int f = rt;                 // flat row of this lane in the current tile
+  int seg = 0, seg_lo = 0, seg_hi = 0, vec = -1;  // segment of this lane's row (cached bounds)
+  const uint16_t *sseg = nullptr;  // scales of the cached segment
+  uint32_t tseg = 0;               // shared address of t[trow of the cached segment][g]
+  uint4 x[8];                      // x[2s], x[2s+1]: activations of the piece read at step s
   float sqg = 0.0f;
-  const unsigned char *st = data + cs * kStageStride;
 #pragma unroll 1
-  for (int t = 0; t < ntiles; ++t) {
-    if (r0 == 0) {  // first tile of a segment: block-uniform
+  for (int t = 0; t < ntiles; ++t, f += RPI) {
+    const bool live = f < total;
+    if (live && f >= seg_hi) {  // this lane's row entered another segment
+      while (f >= cur->seg[seg].row0 + cur->seg[seg].nrows) ++seg;
       const RowSeg &sg = cur->seg[seg];
-      nrows = sg.nrows;
-      sglob = sg.S + (size_t)rt * G + (hc >> 1);
-      s_aligned = (reinterpret_cast<uintptr_t>(sg.S) & 15u) == 0;
-      tp = T + (size_t)(sg.trow + rt) * G + (hc >> 1);
+      seg_lo = sg.row0;
+      seg_hi = sg.row0 + sg.nrows;
+      sseg = sg.S;
+      tseg = T_a + (uint32_t)((sg.trow * G + g) * 4);
       if (sg.vec != vec) {
         vec = sg.vec;
-        const uint4 *xv = act.x + (size_t)vec * 4 * HPR + hc;
-        x[0] = xv[0]; x[1] = xv[HPR]; x[2] = xv[2 * HPR]; x[3] = xv[3 * HPR];
-        gs8 = 8 * act.gsum[vec * G + (hc >> 1)];
-        sqg = act.sq[vec * G + (hc >> 1)];
+        const uint4 *xv = act.x + (size_t)vec * 8 * G + g;
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+          const int j = (s + rot) & 3;
+          x[2 * s] = xv[(2 * j) * G];
+          x[2 * s + 1] = xv[(2 * j + 1) * G];
+        }
+        sqg = act.sq[vec * G + g];
       }
     }
-    const int rows = nrows - r0 < RPI ? nrows - r0 : RPI;
-    const bool live = even && rt < rows;
-    mbar_wait(ring, &ring->full[cs], cph);
-    const uint4 wa = *reinterpret_cast<const uint4 *>(st + tid * 32);
-    const uint4 wb = *reinterpret_cast<const uint4 *>(st + tid * 32 + 16);
+    const uint32_t st = data_a + cs * kStageStride;
+    mbar_wait_a(ring, full_a + cs * 8, cph);
+    const uint32_t wbase = st + lane_off;
+    const uint4 w0 = lds128(wbase + (uint32_t)((rot & 3) << 4)),
+                w1 = lds128(wbase + (uint32_t)(((1 + rot) & 3) << 4)),
+                w2 = lds128(wbase + (uint32_t)(((2 + rot) & 3) << 4)),
+                w3 = lds128(wbase + (uint32_t)(((3 + rot) & 3) << 4));
     uint32_t sraw = 0;
     if (live) {
-      if (s_aligned && ((rows * G * 2) & 15) == 0) sraw = reinterpret_cast<const uint16_t *>(st + kTileBytes)[tid >> 1];
-      else sraw = __ldg(sglob + (size_t)r0 * G);
+      // the piece of this lane's segment inside this tile, as the issuing thread cut it
+      const int f0 = f - rt;
+      const int pa = seg_lo > f0 ? seg_lo : f0, pb = seg_hi < f0 + RPI ? seg_hi : f0 + RPI;
+      const uint16_t *psrc = sseg + (size_t)(pa - seg_lo) * G;
+      if (piece_scales_bulk(psrc, (uint32_t)((pb - pa) * G * 2), (uint32_t)((pa - f0) * G * 2)))
+        sraw = lds_u16(st + kTileBytes + tid * 2);
+      else
+        sraw = __ldg(sseg + (size_t)(f - seg_lo) * G + g);
     }
     __syncwarp();
-    if ((tid & 31) == 0) mbar_arrive(&ring->empty[cs]);
+    if (warp_lead) mbar_arrive_a(empty_a + cs * 8);
     // the issuing thread refills the stage of the previous tile
     if (tid == 0 && t >= 1 && issued < ntot) {
-      const uint32_t ps = cs == 0 ? nst - 1 : cs - 1, pph = cs == 0 ? cph ^ 1u : cph;
-      mbar_wait(ring, &ring->empty[ps], pph);
+      mbar_wait_a(ring, empty_a + pr.stage * 8, pr.phase ^ 1u);
       if (!in_next && issued == (uint32_t)ntiles) { pr.open(next); in_next = true; }
-      pr.issue(ring, data, nst);
+      pr.issue(ring, ring->data, nst);
       ++issued;
       ring->issued += 1;
     }
-    int lo = 0, hi = 0;
-    dot64_biased(wa, wb, x, lo, hi);
-    int d = lo + (hi >> 4);
-    d += __shfl_xor_sync(kFull, d, 1);
+    int d0 = 0, d1 = 0;
+    d0 = dot16_x16(w0, 0, x[0], d0);
+    d1 = dot16_x16(w0, 1, x[1], d1);
+    d0 = dot16_x16(w1, 0, x[2], d0);
+    d1 = dot16_x16(w1, 1, x[3], d1);
+    d0 = dot16_x16(w2, 0, x[4], d0);
+    d1 = dot16_x16(w2, 1, x[5], d1);
+    d0 = dot16_x16(w3, 0, x[6], d0);
+    d1 = dot16_x16(w3, 1, x[7], d1);
     if (live) {
-      float v = (float)(d - gs8) * __uint_as_float(sraw << 16);
-      tp[(size_t)r0 * G] = v * sqg;
+      const float v = (float)((d0 + d1) >> 4) * __uint_as_float(sraw << 16);
+      sts_f32(tseg + (uint32_t)((f - seg_lo) * G * 4), v * sqg);
     }
-    r0 += RPI;
-    if (r0 >= nrows) {
-      ++seg;
-      r0 = 0;
-    }
-    st += kStageStride;
     if (++cs == nst) {
       cs = 0;
       cph ^= 1u;
-      st = data;
     }
   }
   if (tid == 0) {

@@ -16,7 +16,7 @@ __device__ __forceinline__ void gemv_kernel(const Int4GemvA8Args &a) {
 
 // One entry point per batch width so that register allocation follows M.
 // M = 1: the block-flattened form (block_dot.cuh); wider batches keep the warp-pass form.
-constexpr int kGemvStages = 8;
+constexpr int kGemvStages = 5;
 __host__ __device__ inline uint32_t round128(uint32_t v) { return (v + 127u) & ~127u; }
 
 __global__ void __launch_bounds__(256, 2) Int4GemvA8(const Int4GemvA8Args a) {

@@ -32,7 +32,7 @@ struct DecodeStepMegaArgs {
 
 constexpr unsigned kSpinLimit = 1u << 22;
 constexpr int kStageBytes = 13056;   // staged activations: max(K<=8192 x1, I<=1024 x12)
-constexpr int kYsFloats = 8192;      // fp32 vector of a norm stage (hidden, value_dim, q_heads*256)
+constexpr int kYsFloats = 4096;      // fp32 vector of a norm stage (hidden, value_dim, q_heads*256)
 
 struct GridSync {
   unsigned *count;
@@ -255,7 +255,7 @@ __device__ __forceinline__ void prefetch_down(const ExpertW *experts, const int3
 }
 
 extern __shared__ __align__(128) unsigned char mega_smem[];
-constexpr int kMegaStages = 5;
+constexpr int kMegaStages = 3;
 constexpr int kMegaRingOff = (kStageBytes + kYsFloats * 4 + kTCap * 4 + 127) / 128 * 128;
 
 __global__ void __launch_bounds__(256, 2) DecodeStepMega(const DecodeStepMegaArgs args) {

@@ -25,7 +25,7 @@ __global__ void __launch_bounds__(256) RouterTopK(const RouterTopKArgs a) {
   router_select(a.Logits, a.E, a.k, a.Wsg != nullptr, sp, a.SelIdx, a.SelW, a.NearGap);
 }
 
-constexpr int kMoeStages = 6;
+constexpr int kMoeStages = 4;
 __host__ __device__ inline uint32_t moe_round128(uint32_t v) { return (v + 127u) & ~127u; }
 
 __global__ void __launch_bounds__(256, 2) ExpertGateUp(const ExpertGateUpArgs a) {

@@ -1,13 +1,15 @@
 // Weight ring: a block streams its contiguous rows of packed INT4 weights (and
 // their bf16 scales) from HBM into shared memory with bulk asynchronous copies
 // (cp.async.bulk, the untiled TMA path) that complete on mbarriers. One thread
-// issues the copies; all 256 threads consume tiles. The copies do not depend on
+// issues the copies; all 256 threads consume every tile. The copies do not depend on
 // activations, so they keep running while the block waits for whatever produces
 // its activations (a grid barrier, a staging step): HBM traffic is decoupled
 // from the dependency chain of a decode step.
 //
-// A tile is 8 KB of weights = 256 lanes x 32 bytes = 16384/K whole rows, plus
-// the 256 bytes of scales of those rows. Stage i of the ring holds the tile
+// A tile is 16 KB of weights = 256 lanes x 64 bytes = 32768/K whole rows, plus
+// the 512 bytes of scales of those rows. (Measured on B200: a block gets about
+// one bulk copy per 0.6 us whatever its size up to 32 KB, so 8 KB copies cap a
+// 2-blocks-per-SM kernel near 3.7 TB/s while 16 KB copies reach 6.9 TB/s.) Stage i of the ring holds the tile
 // with running index t where t % nst == i. full[i] completes when the tile's
 // bytes have landed (transaction count); empty[i] completes when all 8 warps
 // have copied their bytes into registers (one arrival per warp: arrivals on
@@ -21,8 +23,8 @@
 
 namespace ainfer {
 
-constexpr int kTileBytes = 8192;
-constexpr int kTileScaleBytes = 256;
+constexpr int kTileBytes = 16384;
+constexpr int kTileScaleBytes = 512;
 constexpr int kStageStride = kTileBytes + kTileScaleBytes;
 constexpr int kMaxStages = 12;
 constexpr uint32_t kRingSpinLimit = 1u << 18;
@@ -34,7 +36,7 @@ struct RowSeg {
   int32_t nrows;
   int32_t vec;        // staged activation vector this segment is dotted with
   int32_t trow;       // first row of this segment in the t[][] scratch
-  int32_t pad;
+  int32_t row0;       // first flat row of this segment in the list (filled by seglist_finalize)
 };
 constexpr int kMaxSegs = 16;
 
@@ -44,7 +46,7 @@ struct SegList {
   int32_t nseg;
   int32_t K;
   int32_t ntiles;  // filled by seglist_finalize
-  int32_t pad;
+  int32_t total;   // rows of all segments together (filled by seglist_finalize)
 };
 
 struct Ring {
@@ -91,6 +93,20 @@ __device__ __forceinline__ bool mbar_try(unsigned long long *b, uint32_t parity)
       : "memory");
   return ok != 0;
 }
+__device__ __forceinline__ bool mbar_try_a(uint32_t addr, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(addr), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ void mbar_arrive_a(uint32_t addr) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(addr) : "memory");
+}
 __device__ __forceinline__ void ring_fault(Ring *ring, uint32_t code) {
   ring->fault = code;
   if (g_stream_fault_word) *reinterpret_cast<volatile unsigned int *>(g_stream_fault_word) = code;
@@ -102,6 +118,15 @@ __device__ __forceinline__ bool mbar_wait(Ring *ring, unsigned long long *b, uin
   const uint32_t limit = *reinterpret_cast<volatile uint32_t *>(&ring->fault) ? 0u : kRingSpinLimit;
   for (uint32_t i = 0; i < limit; ++i)
     if (mbar_try(b, parity)) return true;
+  ring_fault(ring, 1);
+  return false;
+}
+// Same, barrier given by its shared-window address.
+__device__ __forceinline__ bool mbar_wait_a(Ring *ring, uint32_t addr, uint32_t parity) {
+  if (mbar_try_a(addr, parity)) return true;
+  const uint32_t limit = *reinterpret_cast<volatile uint32_t *>(&ring->fault) ? 0u : kRingSpinLimit;
+  for (uint32_t i = 0; i < limit; ++i)
+    if (mbar_try_a(addr, parity)) return true;
   ring_fault(ring, 1);
   return false;
 }
@@ -131,83 +156,81 @@ __device__ __forceinline__ void ring_init(Ring *ring, unsigned char *data, int n
   __syncthreads();
 }
 
-// Tile count of a list; one thread.
+// Flat row numbering and tile count of a list; one thread. A tile is the next
+// kTileBytes*2/K rows of the list's segments laid end to end, so it may hold
+// pieces of several segments (each piece is one bulk copy).
 __device__ __forceinline__ void seglist_finalize(SegList *l) {
-  const int rpi = 16384 / l->K;
+  const int rpi = kTileBytes * 2 / l->K;
   int n = 0;
-  for (int i = 0; i < l->nseg; ++i) n += (l->seg[i].nrows + rpi - 1) / rpi;
-  l->ntiles = n;
+  for (int i = 0; i < l->nseg; ++i) {
+    l->seg[i].row0 = n;
+    n += l->seg[i].nrows;
+  }
+  l->total = n;
+  l->ntiles = (n + rpi - 1) / rpi;
 }
 
-// True when a tile's scales can travel by bulk copy (16-byte aligned source
-// and size); otherwise the consumers read them from global memory themselves.
-__device__ __forceinline__ bool tile_scales_bulk(const uint16_t *seg_scales, uint32_t bytes) {
-  return ((reinterpret_cast<uintptr_t>(seg_scales) | bytes) & 15u) == 0;
+// True when a piece's scales can travel by bulk copy (16-byte aligned source,
+// size and offset in the stage); otherwise the consumers read them from global
+// memory themselves. Producer and consumers evaluate this on the same values.
+__device__ __forceinline__ bool piece_scales_bulk(const uint16_t *src, uint32_t bytes, uint32_t dst_off) {
+  return ((reinterpret_cast<uintptr_t>(src) | bytes | dst_off) & 15u) == 0;
 }
 
-// The issuing thread's cursor: where in a list the next tile starts and which
-// stage it goes to. Everything it needs per tile sits in registers.
+__device__ __forceinline__ void mbar_expect_tx(unsigned long long *b, uint32_t bytes) {
+  asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(b)), "r"(bytes)
+               : "memory");
+}
+
+// The issuing thread's cursor over the tiles of one list.
 struct Producer {
   const SegList *l;
-  const uint8_t *P;
-  const uint16_t *S;
-  int s, r0, nrows;          // segment, first row of the next tile, rows of the segment
+  int s;                     // first segment that can overlap the next tile
+  int tile;                  // next tile of the list
   int rpi, row_bytes, srow;  // rows per tile, weight bytes per row, scale bytes per row
   uint32_t stage, phase;
 
-  __device__ __forceinline__ void load_seg() {
-    if (s < l->nseg) {
-      P = l->seg[s].P;
-      S = l->seg[s].S;
-      nrows = l->seg[s].nrows;
-    }
-  }
   __device__ __forceinline__ void open(const SegList *list) {
     l = list;
-    rpi = 16384 / list->K;
+    rpi = kTileBytes * 2 / list->K;
     row_bytes = list->K / 2;
     srow = list->K / 64;
     s = 0;
-    r0 = 0;
-    load_seg();
+    tile = 0;
   }
-  __device__ __forceinline__ void skip() {  // the next tile is already in flight
-    r0 += rpi;
-    if (r0 >= nrows) {
-      ++s;
-      r0 = 0;
-      load_seg();
-    }
-  }
+  __device__ __forceinline__ void skip() { ++tile; }  // the next tile is already in flight
   __device__ __forceinline__ void next_stage(uint32_t nst) {
     if (++stage == nst) {
       stage = 0;
       phase ^= 1u;
     }
   }
-  // Issues the copy of the next tile into `stage` and moves on.
+  // Issues the copies of the next tile into `stage` and moves on.
   __device__ __forceinline__ void issue(Ring *ring, unsigned char *data, uint32_t nst) {
-    const int rows = nrows - r0 < rpi ? nrows - r0 : rpi;
+    const int f0 = tile * rpi, f1 = f0 + rpi < l->total ? f0 + rpi : l->total;
     unsigned char *dst = data + stage * kStageStride;
-    const uint8_t *src = P + (size_t)r0 * row_bytes;
-    const uint16_t *ssrc = reinterpret_cast<const uint16_t *>(reinterpret_cast<const uint8_t *>(S) + (size_t)r0 * srow);
-    const uint32_t wbytes = (uint32_t)(rows * row_bytes), sbytes = (uint32_t)(rows * srow);
     unsigned long long *bar = &ring->full[stage];
-    if (reinterpret_cast<uintptr_t>(src) & 15u) {  // cannot be copied in bulk: report, keep the phase moving
-      ring_fault(ring, 2);
-      mbar_arrive(bar);
-    } else {
-      const bool sb = tile_scales_bulk(S, sbytes);
-      mbar_arrive_expect(bar, wbytes + (sb ? sbytes : 0));
-      bulk_g2s(dst, src, wbytes, bar);
-      if (sb) bulk_g2s(dst + kTileBytes, ssrc, sbytes, bar);
+    while (s < l->nseg && l->seg[s].row0 + l->seg[s].nrows <= f0) ++s;
+    for (int i = s; i < l->nseg; ++i) {
+      const RowSeg &sg = l->seg[i];
+      if (sg.row0 >= f1) break;
+      const int a = sg.row0 > f0 ? sg.row0 : f0;
+      const int b = sg.row0 + sg.nrows < f1 ? sg.row0 + sg.nrows : f1;
+      const int lr = a - sg.row0, rows = b - a, off = a - f0;
+      const uint8_t *src = sg.P + (size_t)lr * row_bytes;
+      const uint16_t *ssrc = reinterpret_cast<const uint16_t *>(reinterpret_cast<const uint8_t *>(sg.S) + (size_t)lr * srow);
+      if (reinterpret_cast<uintptr_t>(src) & 15u) {  // cannot be copied in bulk: report and skip
+        ring_fault(ring, 2);
+        continue;
+      }
+      const uint32_t wbytes = (uint32_t)(rows * row_bytes), sbytes = (uint32_t)(rows * srow);
+      const bool sb = piece_scales_bulk(ssrc, sbytes, (uint32_t)(off * srow));
+      mbar_expect_tx(bar, wbytes + (sb ? sbytes : 0));
+      bulk_g2s(dst + (size_t)off * row_bytes, src, wbytes, bar);
+      if (sb) bulk_g2s(dst + kTileBytes + (size_t)off * srow, ssrc, sbytes, bar);
     }
-    r0 += rpi;
-    if (r0 >= nrows) {
-      ++s;
-      r0 = 0;
-      load_seg();
-    }
+    mbar_arrive(bar);
+    ++tile;
     next_stage(nst);
   }
 };

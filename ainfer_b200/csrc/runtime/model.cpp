@@ -99,13 +99,13 @@ bool ModelConfig::check(std::string &err) const {
     if (kv_heads <= 0 || q_heads % kv_heads) return bad("q_heads must be a multiple of kv_heads");
     int g = q_heads / kv_heads;
     if (g != 1 && g != 2 && g != 4 && g != 6 && g != 8) return bad("q_heads/kv_heads must be 1, 2, 4, 6 or 8");
-    if (!pow2_between(q_heads * head_dim, 128, 8192)) return bad("q_heads*head_dim must be a power of two <= 8192");
+    if (!pow2_between(q_heads * head_dim, 128, 4096)) return bad("q_heads*head_dim must be a power of two <= 4096");
   }
   if (n_lin()) {
     if (lin_head_dim != 128) return bad("lin_head_dim must be 128");
     if (conv_kernel != 4) return bad("conv_kernel must be 4");
     if (lin_k_heads <= 0 || lin_v_heads % lin_k_heads) return bad("lin_v_heads must be a multiple of lin_k_heads");
-    if (!pow2_between(value_dim(), 128, 8192)) return bad("lin_v_heads*128 must be a power of two <= 8192");
+    if (!pow2_between(value_dim(), 128, 4096)) return bad("lin_v_heads*128 must be a power of two <= 4096");
   }
   if (experts < 32 || experts > 1024 || experts % 32) return bad("experts must be a multiple of 32 in [32, 1024]");
   if (top_k <= 0 || top_k > 11 || top_k > experts) return bad("top_k must be in [1, 11]");
