@@ -71,8 +71,28 @@ __device__ __forceinline__ StagedAct4 stage4(unsigned char *smem, const int8_t *
   return StagedAct4{reinterpret_cast<const uint4 *>(smem), sqs};
 }
 
-// Quantises M fp32 vectors (per-128 activation quantiser, tools/cmdlist/
-// kernels.cpp:551-579) straight into the staged form. One warp per group.
+// Quantises one group of 128 fp32 values held four per lane (per-128 activation
+// quantiser, tools/cmdlist/kernels.cpp:551-579) into the staged form. One warp;
+// one out-of-line copy of this code however many loops call it.
+static __device__ __noinline__ void quant_group_staged(uint32_t *xw, float *sqs, int K, int m, int g, float4 v) {
+  const int lane = threadIdx.x & 31;
+  float mx = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+  mx = warp_max(mx);
+  float s = mx / 127.0f;
+  if (s == 0.0f) s = 1.0f;
+  int q0 = quant_round(v.x, s), q1 = quant_round(v.y, s), q2 = quant_round(v.z, s), q3 = quant_round(v.w, s);
+  uint32_t own = (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) | ((uint32_t)(q2 & 0xFF) << 16) |
+                 ((uint32_t)(q3 & 0xFF) << 24);
+  uint32_t other = __shfl_xor_sync(kFull, own, 1);
+  int pc = g * 16 + (lane >> 1);  // 8-weight piece: two lanes of 4 weights each
+  if (lane & 1) xw[staged4_word(K, m, pc, 1)] = __byte_perm(other, own, 0x7531);
+  else xw[staged4_word(K, m, pc, 0)] = __byte_perm(own, other, 0x6420);
+  if (lane == 0) sqs[m * (K / 128) + g] = s;
+}
+
+// Quantises M fp32 vectors straight into the staged form, one warp per group.
+// A global source is fetched four groups per warp at a time so that the loads
+// overlap; a shared-memory source is simply walked.
 template <bool kGlobalSrc>
 __device__ __forceinline__ StagedAct4 stage4_from_f32(unsigned char *smem, const float *x, int K, int M,
                                                       long x_stride) {
@@ -80,23 +100,29 @@ __device__ __forceinline__ StagedAct4 stage4_from_f32(unsigned char *smem, const
   const int G = K / 128;
   float *sqs = reinterpret_cast<float *>(smem + (size_t)M * K);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-  for (int i = warp; i < M * G; i += warps) {
-    int m = i / G, g = i % G;
-    const float4 *src = reinterpret_cast<const float4 *>(x + m * x_stride + (long)g * 128 + lane * 4);
-    float4 v = kGlobalSrc ? __ldcg(src) : *src;
-    float mx = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
-    mx = warp_max(mx);
-    float s = mx / 127.0f;
-    if (s == 0.0f) s = 1.0f;
-    int q0 = quant_round(v.x, s), q1 = quant_round(v.y, s), q2 = quant_round(v.z, s),
-        q3 = quant_round(v.w, s);
-    uint32_t own = (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) |
-                   ((uint32_t)(q2 & 0xFF) << 16) | ((uint32_t)(q3 & 0xFF) << 24);
-    uint32_t other = __shfl_xor_sync(kFull, own, 1);
-    int pc = g * 16 + (lane >> 1);  // 8-weight piece: two lanes of 4 weights each
-    if (lane & 1) xw[staged4_word(K, m, pc, 1)] = __byte_perm(other, own, 0x7531);
-    else xw[staged4_word(K, m, pc, 0)] = __byte_perm(own, other, 0x6420);
-    if (lane == 0) sqs[i] = s;
+  if (kGlobalSrc) {
+    constexpr int kRB = 4;
+#pragma unroll 1
+    for (int i0 = warp; i0 < M * G; i0 += warps * kRB) {
+      float4 vv[kRB];
+#pragma unroll
+      for (int r = 0; r < kRB; ++r) {
+        const int i = i0 + r * warps;
+        if (i < M * G)
+          vv[r] = __ldcg(reinterpret_cast<const float4 *>(x + (i / G) * x_stride + (long)(i % G) * 128 + lane * 4));
+      }
+#pragma unroll
+      for (int r = 0; r < kRB; ++r) {
+        const int i = i0 + r * warps;
+        if (i < M * G) quant_group_staged(xw, sqs, K, i / G, i % G, vv[r]);
+      }
+    }
+  } else {
+#pragma unroll 1
+    for (int i = warp; i < M * G; i += warps) {
+      const float4 v = *reinterpret_cast<const float4 *>(x + (i / G) * x_stride + (long)(i % G) * 128 + lane * 4);
+      quant_group_staged(xw, sqs, K, i / G, i % G, v);
+    }
   }
   __syncthreads();
   return StagedAct4{reinterpret_cast<const uint4 *>(smem), sqs};
@@ -145,7 +171,7 @@ __device__ __forceinline__ int dot16_x16(const uint4 &w4, int which, const uint4
 #else
 #define AINFER_BLOCK_DOT_LINKAGE static __device__ __noinline__
 #endif
-template <int K>
+template <int K, bool kRegCursor>
 AINFER_BLOCK_DOT_LINKAGE void block_dot(Ring *ring, const SegList *cur, const SegList *next,
                                         const StagedAct4 &act, float *T) {
   constexpr int G = K / 128;
@@ -164,29 +190,31 @@ AINFER_BLOCK_DOT_LINKAGE void block_dot(Ring *ring, const SegList *cur, const Se
   const uint32_t lane_off = (uint32_t)tid * 64u;
 
   // ---- issuing thread: fill the ring ----
+  // kRegCursor: the cursor lives in registers and the issue code is inlined (streaming
+  // kernels, where the issue sits on the critical path of a consuming warp); otherwise it
+  // stays in the Ring and one out-of-line function issues (small code for the persistent
+  // step, whose stages are a few prefetched tiles each).
+  // in_flight = tiles issued and not yet consumed (this call's and, towards its end, the next list's)
   Producer pr;
-  uint32_t issued = 0;  // tiles issued, counted from tile 0 of cur (runs on into next)
-  uint32_t ntot = (uint32_t)ntiles;
-  bool in_next = false;
+  uint32_t in_flight = 0, issued_here = 0;
+  bool more = false;  // the cursor may still have tiles to issue
   if (tid == 0) {
-    if (next) ntot += (uint32_t)next->ntiles;
-    pr.stage = cs;
-    pr.phase = cph;
-    if (ntiles > 0) pr.open(cur);
-    else if (next) { pr.open(next); in_next = true; }
-    for (; issued < ring->pre; ++issued) {
-      pr.skip();
-      pr.next_stage(nst);
+    in_flight = ring->pre;
+    if (in_flight == 0) ring_open(ring, cur);
+    ring->p_next = next;
+    if (kRegCursor) pr.load(ring);
+    more = true;
+    while (more && in_flight < nst) {
+      if (kRegCursor) {
+        more = pr.issue(ring, ring->data, nst);
+        if (more) ++issued_here;
+      } else {
+        more = ring_issue_next(ring);
+      }
+      if (more) ++in_flight;
     }
-    const uint32_t cap = ntot < nst ? ntot : nst;
-    const uint32_t first = issued;
-    for (; issued < cap; ++issued) {
-      if (!in_next && issued == (uint32_t)ntiles) { pr.open(next); in_next = true; }
-      pr.issue(ring, ring->data, nst);
-    }
-    ring->issued += issued - first;
   }
-
+  AINFER_STAMP(50);
   // ---- consume ----
   // A tile holds RPI consecutive flat rows of the list; this lane's row of tile t is t*RPI + rt.
   const int total = cur->total;
@@ -219,7 +247,9 @@ AINFER_BLOCK_DOT_LINKAGE void block_dot(Ring *ring, const SegList *cur, const Se
       }
     }
     const uint32_t st = data_a + cs * kStageStride;
+    AINFER_STAMP(51);
     mbar_wait_a(ring, full_a + cs * 8, cph);
+    AINFER_STAMP(52);
     const uint32_t wbase = st + lane_off;
     const uint4 w0 = lds128(wbase + (uint32_t)((rot & 3) << 4)),
                 w1 = lds128(wbase + (uint32_t)(((1 + rot) & 3) << 4)),
@@ -239,12 +269,19 @@ AINFER_BLOCK_DOT_LINKAGE void block_dot(Ring *ring, const SegList *cur, const Se
     __syncwarp();
     if (warp_lead) mbar_arrive_a(empty_a + cs * 8);
     // the issuing thread refills the stage of the previous tile
-    if (tid == 0 && t >= 1 && issued < ntot) {
-      mbar_wait_a(ring, empty_a + pr.stage * 8, pr.phase ^ 1u);
-      if (!in_next && issued == (uint32_t)ntiles) { pr.open(next); in_next = true; }
-      pr.issue(ring, ring->data, nst);
-      ++issued;
-      ring->issued += 1;
+    if (tid == 0) {
+      if (t >= 1) --in_flight;  // tile t-1 has been consumed by this thread; the wait below covers the others
+      if (more && t >= 1) {
+        if (kRegCursor) {
+          mbar_wait_a(ring, empty_a + pr.stage * 8, pr.phase ^ 1u);
+          more = pr.issue(ring, ring->data, nst);
+          if (more) ++issued_here;
+        } else {
+          mbar_wait_a(ring, empty_a + ring->p_stage * 8, ring->p_phase ^ 1u);
+          more = ring_issue_next(ring);
+        }
+        if (more) ++in_flight;
+      }
     }
     int d0 = 0, d1 = 0;
     d0 = dot16_x16(w0, 0, x[0], d0);
@@ -263,11 +300,17 @@ AINFER_BLOCK_DOT_LINKAGE void block_dot(Ring *ring, const SegList *cur, const Se
       cs = 0;
       cph ^= 1u;
     }
+    AINFER_STAMP(53);
   }
   if (tid == 0) {
+    if (kRegCursor) {
+      pr.store(ring);
+      ring->issued += issued_here;
+    }
     ring->c_stage = cs;
     ring->c_phase = cph;
-    ring->pre = issued > (uint32_t)ntiles ? issued - (uint32_t)ntiles : 0;
+    // what is still in flight belongs to the next list (the last tile of cur was consumed above)
+    ring->pre = ntiles > 0 ? in_flight - 1 : in_flight;
   }
   __syncthreads();
 }

@@ -7,6 +7,12 @@
 #include "../common/detmath.h"
 #include "registry.h"
 
+// Optional fine-grained stage clock: a translation unit that wants time stamps
+// inside the shared stage code defines AINFER_STAMP(id) before including it.
+#ifndef AINFER_STAMP
+#define AINFER_STAMP(id)
+#endif
+
 namespace ainfer {
 
 constexpr unsigned kFull = 0xFFFFFFFFu;

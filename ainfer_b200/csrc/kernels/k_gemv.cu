@@ -26,7 +26,7 @@ __global__ void __launch_bounds__(256, 2) Int4GemvA8(const Int4GemvA8Args a) {
   __shared__ Ring ring;
   if (threadIdx.x < a.nmats) smats[threadIdx.x] = a.mats[threadIdx.x];
   ring_init(&ring, gemv_smem + round128(staged4_bytes(a.K, 1)), kGemvStages);  // syncs: smats visible
-  BlockScratch bs{&ring, lists, T, 0, false};
+  BlockScratch bs{&ring, lists, T, nullptr, 0, false};
   // start the weight stream before the activations are staged
   if (threadIdx.x == 0) {
     gemv_first_list(&lists[0], smats, a.nmats, a.K, a.total_rows, blockIdx.x, gridDim.x);

@@ -16,6 +16,10 @@
 //
 // Every wait is bounded: a barrier that does not complete within kSpinLimit
 // polls sets plan->error and all blocks leave the kernel.
+#define AINFER_STAMP(id) ::ainfer::fine_stamp(id)
+namespace ainfer {
+static __device__ void fine_stamp(int id);
+}
 #include "../common/mega_plan.h"
 #include "attention_core.cuh"
 #include "deltanet_core.cuh"
@@ -33,6 +37,22 @@ struct DecodeStepMegaArgs {
 constexpr unsigned kSpinLimit = 1u << 22;
 constexpr int kStageBytes = 13056;   // staged activations: max(K<=8192 x1, I<=1024 x12)
 constexpr int kYsFloats = 4096;      // fp32 vector of a norm stage (hidden, value_dim, q_heads*256)
+
+// Fine stage clock (second half of the stamp buffer): block 0 / thread 0 appends
+// (id << 48) | low 48 bits of %globaltimer at points inside the stages.
+__shared__ unsigned long long *s_fine;
+__shared__ int s_fine_n, s_fine_cap;
+static __device__ __noinline__ void fine_stamp(int id) {
+  if (threadIdx.x == 0 && s_fine != nullptr && s_fine_n < s_fine_cap) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    s_fine[s_fine_n++] = ((unsigned long long)id << 48) | (t & 0xFFFFFFFFFFFFull);
+    if (id >= 60 && s_fine_n < s_fine_cap) {  // ids >= 60 also record the SM cycle counter (for the clock rate)
+      long long c = clock64();
+      s_fine[s_fine_n++] = ((unsigned long long)(id + 1) << 48) | ((unsigned long long)c & 0xFFFFFFFFFFFFull);
+    }
+  }
+}
 
 struct GridSync {
   unsigned *count;
@@ -65,14 +85,22 @@ __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned *p) {
 // Grid-wide barrier over a monotonically increasing counter (zeroed before the
 // launch). Returns true when the kernel must stop (a wait ran out of polls
 // here or in another block).
-__device__ __forceinline__ bool grid_barrier(GridSync &g) {
-  __shared__ int s_fail;
+// The barrier comes in two halves so that work which does not depend on other
+// blocks (building the next stage's tables, starting its weight copies) can run
+// between announcing arrival and waiting for the others.
+__device__ __forceinline__ void grid_arrive(GridSync &g) {
   __syncthreads();
+  AINFER_STAMP(40);
   g.epoch += 1;
   if (threadIdx.x == 0) {
-    int fail = 0;
     __threadfence();
     atomicAdd(g.count, 1u);
+  }
+}
+__device__ __forceinline__ bool grid_wait(GridSync &g) {
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) {
+    int fail = 0;
     const unsigned target = g.epoch * g.nblk;
     unsigned spins = 0;
     while (ld_acquire_u32(g.count) < target) {
@@ -92,6 +120,10 @@ __device__ __forceinline__ bool grid_barrier(GridSync &g) {
   __syncthreads();
   stage_stamp(g);
   return s_fail != 0;
+}
+__device__ __forceinline__ bool grid_barrier(GridSync &g) {
+  grid_arrive(g);
+  return grid_wait(g);
 }
 
 // Asks L2 to fetch [p, p+bytes): one 128-byte line per request, spread over the block.
@@ -119,55 +151,95 @@ __device__ __forceinline__ void prefetch_gemv(const GemvMat *mats, int nmats, in
   }
 }
 
-// Runs one GEMV stage for this block: builds the stage's matrix table in shared
-// memory (row_start assigned here) and processes the block's contiguous rows.
-__device__ __forceinline__ void gemv_stage(const GemvMat *mats, int nmats, int K, const StagedAct4 &act,
-                                           GemvMat *smats, BlockScratch &bs, int blk, int nblk) {
-  __syncthreads();  // smats may still be read by the previous stage
+// Leaves the kernel early (a grid barrier gave up): prefetched copies may still be landing.
+__device__ __forceinline__ void mega_bail(Ring *ring) {
+  if (threadIdx.x == 0) ring_drain(ring);
+}
+
+// Prepares a GEMV stage ahead of time: builds the stage's matrix table in shared
+// memory (row_start assigned here) and the block's first segment list, and
+// starts the bulk copies of its first tiles. Called once the previous user of
+// smats / the lists / the ring is done, typically BEFORE the grid barrier that
+// guards the stage's activations: the weights do not depend on them, so they
+// stream into shared memory while the block waits.
+static __device__ __noinline__ void gemv_prepare(const GemvMat *mats, int nmats, int K, GemvMat *smats,
+                                             BlockScratch &bs, int blk, int nblk) {
+  __syncthreads();  // smats / lists may still be read by the previous stage's epilogue
+  if (threadIdx.x < nmats) smats[threadIdx.x] = mats[threadIdx.x];  // one round trip for all records
+  __syncthreads();
   if (threadIdx.x == 0) {
     int row = 0;
     for (int i = 0; i < nmats; ++i) {
-      smats[i] = mats[i];
       smats[i].row_start = row;
-      row += mats[i].N;
+      row += smats[i].N;
     }
+    gemv_first_list(&bs.lists[bs.cur], smats, nmats, K, row, blk, nblk);
+    ring_prefetch(bs.ring, &bs.lists[bs.cur]);
   }
+  bs.primed = true;
+}
+
+// Runs one GEMV stage for this block over its contiguous rows.
+static __device__ __noinline__ void gemv_stage(const GemvMat *mats, int nmats, int K, const StagedAct4 &act,
+                                           GemvMat *smats, BlockScratch &bs, int blk, int nblk) {
+  if (!bs.primed) gemv_prepare(mats, nmats, K, smats, bs, blk, nblk);
   __syncthreads();
+  AINFER_STAMP(10);
   long total = 0;
   for (int i = 0; i < nmats; ++i) total += smats[i].N;
-  // only the contraction widths a decode layer can have (the host refuses other shapes)
-  switch (K) {
-    case 256: gemv_block<256>(smats, nmats, total, act, bs, blk, nblk); break;
-    case 512: gemv_block<512>(smats, nmats, total, act, bs, blk, nblk); break;
-    case 1024: gemv_block<1024>(smats, nmats, total, act, bs, blk, nblk); break;
-    case 2048: gemv_block<2048>(smats, nmats, total, act, bs, blk, nblk); break;
-    case 4096: gemv_block<4096>(smats, nmats, total, act, bs, blk, nblk); break;
-    default: break;
+  gemv_block<false>(K, smats, nmats, total, act, bs, blk, nblk);
+}
+
+// Same for the expert down projection, once the routing is known.
+static __device__ __noinline__ void down_prepare(const ExpertDownCombineArgs &xa, BlockScratch &bs, int blk,
+                                             int nblk) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    long lo, hi;
+    block_range(xa.H, blk, nblk, lo, hi);
+    const int SB = down_sub_rows(xa.I, xa.slots);
+    down_list(&bs.lists[bs.cur], xa, bs.sew, (int)lo, (int)(lo + SB < hi ? lo + SB : hi));
+    ring_prefetch(bs.ring, &bs.lists[bs.cur]);
   }
+  bs.primed = true;
 }
 
 // (1+w) RMSNorm + activation quantiser of one fp32 vector, result staged in
 // shared memory for the GEMV rows; ys keeps the normalised fp32 vector (the
 // router reads it). Same arithmetic as RmsNormQuant (k_norm.cu). src is either
 // a global fp32 vector or a BF16 embedding row.
-__device__ __forceinline__ StagedAct4 norm_quant_stage(const float *xg, const uint16_t *emb_row,
+static __device__ __noinline__ StagedAct4 norm_quant_stage(const float *xg, const uint16_t *emb_row,
                                                       const float *w, int N, float eps,
                                                       unsigned char *stage, float *ys,
                                                       float *x_copy_out) {
   __shared__ double ps[256];
   __shared__ float s_inv;
   const int lid = threadIdx.x;
+  constexpr int kPer = kYsFloats / 256;  // elements per lane at the largest N
+  // every load of this lane is issued before the first use: one round trip to L2
+  float xv[kPer], wv[kPer];
+#pragma unroll
+  for (int i = 0; i < kPer; ++i) {
+    const int j = lid + 256 * i;
+    if (j < N) {
+      xv[i] = emb_row ? bf16_to_f32(emb_row[j]) : __ldcg(xg + j);
+      wv[i] = __ldg(w + j);
+    }
+  }
   __syncthreads();  // ys / stage may still be in use by the previous stage
   double ss = 0;
-  for (int j = lid; j < N; j += 256) {
-    float v = emb_row ? bf16_to_f32(emb_row[j]) : __ldcg(xg + j);
-    ys[j] = v;
-    if (x_copy_out) x_copy_out[j] = v;
-    double d = (double)v;
-    ss = ss + d * d;
+#pragma unroll
+  for (int i = 0; i < kPer; ++i) {
+    const int j = lid + 256 * i;
+    if (j < N) {
+      if (x_copy_out) x_copy_out[j] = xv[i];
+      double d = (double)xv[i];
+      ss = ss + d * d;
+    }
   }
   ps[lid] = ss;
   __syncthreads();
+  AINFER_STAMP(1);
   for (int st = 128; st >= 32; st >>= 1) {
     if (lid < st) ps[lid] = ps[lid] + ps[lid + st];
     __syncthreads();
@@ -180,42 +252,73 @@ __device__ __forceinline__ StagedAct4 norm_quant_stage(const float *xg, const ui
   }
   __syncthreads();
   const float inv = s_inv;
-  for (int j = lid; j < N; j += 256) ys[j] = (ys[j] * inv) * (1.0f + w[j]);
+  AINFER_STAMP(2);
+#pragma unroll
+  for (int i = 0; i < kPer; ++i) {
+    const int j = lid + 256 * i;
+    if (j < N) ys[j] = (xv[i] * inv) * (1.0f + wv[i]);
+  }
   __syncthreads();
-  return stage4_from_f32<false>(stage, ys, N, 1, N);
+  AINFER_STAMP(3);
+  StagedAct4 r = stage4_from_f32<false>(stage, ys, N, 1, N);
+  AINFER_STAMP(4);
+  return r;
 }
 
 // Per-head gated RMSNorm (RmsInv + NormGated, tools/cmdlist/kernels.cpp:619-644)
 // of all heads into ys, then the activation quantiser staged for out_proj.
 // Same arithmetic as GatedNormQuant (k_norm.cu).
-__device__ __forceinline__ StagedAct4 gated_norm_stage(const float *O, const float *Z, const float *W,
+// One head of the gated norm: 128 values, four per lane.
+static __device__ __noinline__ void gated_norm_head(float4 o, float4 z, float4 w, float eps, float *out) {
+  const int lane = threadIdx.x & 31;
+  float ss = 0.0f;
+  ss = fmaf(o.x, o.x, ss);
+  ss = fmaf(o.y, o.y, ss);
+  ss = fmaf(o.z, o.z, ss);
+  ss = fmaf(o.w, o.w, ss);
+  ss = warp_tree_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / 128.0f + eps);
+  out[lane] = ((w.x * o.x) * inv) * (z.x / (1.0f + det_expf(-z.x)));
+  out[lane + 32] = ((w.y * o.y) * inv) * (z.y / (1.0f + det_expf(-z.y)));
+  out[lane + 64] = ((w.z * o.z) * inv) * (z.z / (1.0f + det_expf(-z.z)));
+  out[lane + 96] = ((w.w * o.w) * inv) * (z.w / (1.0f + det_expf(-z.w)));
+}
+
+static __device__ __noinline__ StagedAct4 gated_norm_stage(const float *O, const float *Z, const float *W,
                                                       int heads, float eps, unsigned char *stage,
                                                       float *ys) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int kHB = 4;  // heads a warp fetches together (one round trip to L2 for all of them)
+  // lane l holds elements l, l+32, l+64, l+96 of a head (.x .y .z .w)
+  const float4 wl = make_float4(__ldg(W + lane), __ldg(W + lane + 32), __ldg(W + lane + 64), __ldg(W + lane + 96));
   __syncthreads();
-  for (int h = warp; h < heads; h += 8) {
-    float ov[4];
-    float ss = 0.0f;
+#pragma unroll 1
+  for (int h0 = warp; h0 < heads; h0 += 8 * kHB) {
+    float4 ov[kHB], zv[kHB];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      ov[i] = __ldcg(O + (size_t)h * 128 + lane + 32 * i);
-      ss = fmaf(ov[i], ov[i], ss);
+    for (int b = 0; b < kHB; ++b) {
+      const int h = h0 + 8 * b;
+      if (h < heads) {
+        const float *o = O + (size_t)h * 128 + lane, *z = Z + (size_t)h * 128 + lane;
+        ov[b] = make_float4(__ldcg(o), __ldcg(o + 32), __ldcg(o + 64), __ldcg(o + 96));
+        zv[b] = make_float4(__ldcg(z), __ldcg(z + 32), __ldcg(z + 64), __ldcg(z + 96));
+      }
     }
-    ss = warp_tree_sum(ss);
-    float inv = 1.0f / sqrtf(ss / 128.0f + eps);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      int d = lane + 32 * i;
-      float zv = __ldcg(Z + (size_t)h * 128 + d);
-      ys[h * 128 + d] = ((W[d] * ov[i]) * inv) * (zv / (1.0f + det_expf(-zv)));
+    for (int b = 0; b < kHB; ++b) {
+      const int h = h0 + 8 * b;
+      if (h < heads) gated_norm_head(ov[b], zv[b], wl, eps, ys + h * 128);
     }
   }
   __syncthreads();
-  return stage4_from_f32<false>(stage, ys, heads * 128, 1, heads * 128);
+  AINFER_STAMP(5);
+  StagedAct4 r = stage4_from_f32<false>(stage, ys, heads * 128, 1, heads * 128);
+  AINFER_STAMP(6);
+  return r;
 }
 
 // Router logits with the normalised activations held in shared memory.
-__device__ __forceinline__ void router_rows_smem(const uint16_t *Wr, const uint16_t *Wsg, const float *hn,
+static __device__ __noinline__ void router_rows_smem(const uint16_t *Wr, const uint16_t *Wsg, const float *hn,
                                                  float *logits, int E, int H, int blk, int nblk) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rows = E + (Wsg ? 1 : 0);
@@ -254,6 +357,34 @@ __device__ __forceinline__ void prefetch_down(const ExpertW *experts, const int3
   }
 }
 
+// The stage bodies shared with the stand-alone kernels, as separate functions:
+// each gets its own register allocation instead of competing inside one huge
+// kernel body (which spilled in the hot loops).
+static __device__ __noinline__ void mega_deltanet(const DeltaNetStepArgs &a, int blk, int nblk) {
+  deltanet_step_body(a, blk, nblk);
+}
+static __device__ __noinline__ void mega_attn_prep(const AttnPrepArgs &a, int blk, int nblk) {
+  attn_prep_body(a, blk, nblk);
+}
+static __device__ __noinline__ void mega_attn_split(const AttnSplitArgs &a, int blk, int nblk) {
+  attn_split_dispatch(a, blk, nblk);
+}
+static __device__ __noinline__ void mega_attn_combine(const AttnCombineArgs &a, int blk, int nblk) {
+  attn_combine_body(a, blk, nblk);
+}
+static __device__ __noinline__ void mega_gateup(const ExpertGateUpArgs &a, const StagedAct4 &act, BlockScratch &bs,
+                                                int blk, int nblk) {
+  gateup_block_dispatch<false>(a, act, bs, blk, nblk);
+}
+static __device__ __noinline__ void mega_down(const ExpertDownCombineArgs &a, const StagedAct4 &act,
+                                              BlockScratch &bs, int blk, int nblk) {
+  down_block_dispatch<false>(a, act, bs, blk, nblk);
+}
+static __device__ __noinline__ StagedAct4 mega_stage_rows(unsigned char *stage, const float *x, int K, int M) {
+  __syncthreads();
+  return stage4_from_f32<true>(stage, x, K, M, K);
+}
+
 extern __shared__ __align__(128) unsigned char mega_smem[];
 constexpr int kMegaStages = 3;
 constexpr int kMegaRingOff = (kStageBytes + kYsFloats * 4 + kTCap * 4 + 127) / 128 * 128;
@@ -271,15 +402,24 @@ __global__ void __launch_bounds__(256, 2) DecodeStepMega(const DecodeStepMegaArg
   unsigned char *stage = mega_smem;
   float *ys = reinterpret_cast<float *>(mega_smem + kStageBytes);
   ring_init(&s_ring, mega_smem + kMegaRingOff, kMegaStages);
-  BlockScratch bs{&s_ring, s_lists, reinterpret_cast<float *>(mega_smem + kStageBytes + kYsFloats * 4), 0, false};
+  __shared__ ExpertW s_sew[kMaxSegs];
+  BlockScratch bs{&s_ring, s_lists, reinterpret_cast<float *>(mega_smem + kStageBytes + kYsFloats * 4), s_sew, 0, false};
   const int blk = blockIdx.x, nblk = gridDim.x;
-  GridSync gs{P.bar_count, P.error, 0u, (unsigned)nblk, blk == 0 ? P.stage_stamps : nullptr, P.stage_stamp_cap, 0};
+  if (threadIdx.x == 0) {
+    s_fine = (blk == 0 && P.stage_stamps) ? P.stage_stamps + P.stage_stamp_cap / 2 : nullptr;
+    s_fine_n = 0;
+    s_fine_cap = P.stage_stamp_cap / 2;
+  }
+  GridSync gs{P.bar_count, P.error, 0u, (unsigned)nblk, blk == 0 ? P.stage_stamps : nullptr, P.stage_stamp_cap / 2, 0};
   stage_stamp(gs);
+  __syncthreads();
+  AINFER_STAMP(60);
   if (*(volatile int *)P.error != 0) return;  // a previous launch failed: stay out
   const int H = P.H;
   const int token = __ldcg(P.ctrl + CTRL_TOKEN);
   int tok = token < 0 ? 0 : (token >= P.vocab ? P.vocab - 1 : token);
 
+  gemv_prepare(&P.L[0].m[0], P.L[0].type == 0 ? 4 : 3, H, smats, bs, blk, nblk);
   for (int L = 0; L < P.layers; ++L) {
     const MegaLayer &ly = P.L[L];
     // ---- mixer input: (1+w) RMSNorm + quantiser, redundantly per block ----
@@ -289,31 +429,33 @@ __global__ void __launch_bounds__(256, 2) DecodeStepMega(const DecodeStepMegaArg
       for (int j = threadIdx.x; j < H; j += 256) P.layer_out[(size_t)(L - 1) * H + j] = __ldcg(P.X + j);
     if (ly.type == 0) {
       // in_proj qkv (+conv+SiLU), z, b (sigmoid), a (decay)
-      prefetch_gemv(&ly.m[4], 1, P.nV * 128, blk, nblk);  // out_proj rows for two stages ahead
       stage_stamp(gs);  // norm + quant done
       gemv_stage(&ly.m[0], 4, H, act, smats, bs, blk, nblk);
       stage_stamp(gs);  // this block's rows done
-      if (grid_barrier(gs)) return;
+      grid_arrive(gs);
+      gemv_prepare(&ly.m[4], 1, P.nV * 128, smats, bs, blk, nblk);  // out_proj streams in during the recurrence
+      if (grid_wait(gs)) return mega_bail(&s_ring);
       DeltaNetStepArgs da{P.O, P.Mx, ly.S, P.Bt, P.Gt, P.nK, P.nV};
-      deltanet_step_body(da, blk, nblk);
-      if (grid_barrier(gs)) return;
+      mega_deltanet(da, blk, nblk);
+      if (grid_barrier(gs)) return mega_bail(&s_ring);
       act = gated_norm_stage(P.O, P.Z, ly.lin_norm, P.nV, P.eps, stage, ys);
       gemv_stage(&ly.m[4], 1, P.nV * 128, act, smats, bs, blk, nblk);
     } else {
-      prefetch_gemv(&ly.m[4], 1, P.nQ * 256, blk, nblk);
       gemv_stage(&ly.m[0], 3, H, act, smats, bs, blk, nblk);
-      if (grid_barrier(gs)) return;
+      grid_arrive(gs);
+      gemv_prepare(&ly.m[4], 1, P.nQ * 256, smats, bs, blk, nblk);  // o_proj streams in during attention
+      if (grid_wait(gs)) return mega_bail(&s_ring);
       AttnPrepArgs pa{P.Q16, P.K16, P.V16, ly.q_norm, ly.k_norm, P.Cos, P.Sin, P.ctrl, P.Qn,
                       ly.Kc, ly.Vc, ly.Ks, ly.Vs, P.nQ, P.nKV, P.rot, P.max_ctx, P.eps};
-      attn_prep_body(pa, blk, nblk);
-      if (grid_barrier(gs)) return;
+      mega_attn_prep(pa, blk, nblk);
+      if (grid_barrier(gs)) return mega_bail(&s_ring);
       AttnSplitArgs sa{P.Qn, ly.Kc, ly.Vc, ly.Ks, ly.Vs, P.ctrl, P.Pm, P.Pse, P.Pacc,
                        P.nQ, P.nKV, P.max_ctx, P.max_chunks};
-      attn_split_dispatch(sa, blk, nblk);
-      if (grid_barrier(gs)) return;
+      mega_attn_split(sa, blk, nblk);
+      if (grid_barrier(gs)) return mega_bail(&s_ring);
       AttnCombineArgs ca{P.Pm, P.Pse, P.Pacc, P.Q16, P.ctrl, P.Q8, P.SQ, nullptr, P.nQ, P.max_ctx, P.max_chunks};
-      attn_combine_body(ca, blk, nblk);
-      if (grid_barrier(gs)) return;
+      mega_attn_combine(ca, blk, nblk);
+      if (grid_barrier(gs)) return mega_bail(&s_ring);
       __syncthreads();
       act = stage4(stage, P.Q8, P.SQ, P.nQ * 256, 1, P.nQ * 256, P.nQ * 2);
       gemv_stage(&ly.m[4], 1, P.nQ * 256, act, smats, bs, blk, nblk);
@@ -330,7 +472,7 @@ __global__ void __launch_bounds__(256, 2) DecodeStepMega(const DecodeStepMegaArg
         }
       }
     }
-    if (grid_barrier(gs)) return;
+    if (grid_barrier(gs)) return mega_bail(&s_ring);
     // ---- MoE: post norm, router, top-k, experts ----
     act = norm_quant_stage(P.Tmp, nullptr, ly.post_norm, H, P.eps, stage, ys, nullptr);
     stage_stamp(gs);
@@ -341,11 +483,9 @@ __global__ void __launch_bounds__(256, 2) DecodeStepMega(const DecodeStepMegaArg
       const MegaLayer &nx = P.L[L + 1];
       prefetch_gemv(&nx.m[0], nx.type == 0 ? 4 : 3, H, blk, nblk);
     }
-    if (grid_barrier(gs)) return;
-    if (threadIdx.x < 32) {
-      router_select(P.RLogits, P.E, P.topk, ly.shared_gate != nullptr, ys, s_sel_idx, s_sel_w, &s_gap);
-    }
-    __syncthreads();
+    if (grid_barrier(gs)) return mega_bail(&s_ring);
+    router_select(P.RLogits, P.E, P.topk, ly.shared_gate != nullptr, ys, s_sel_idx, s_sel_w, &s_gap);
+    fetch_expert_rows(s_sew, ly.experts, s_sel_idx, P.slots);  // synchronised inside the gate/up stage
     stage_stamp(gs);  // selection done
     if (blk == 0 && threadIdx.x <= P.topk) {
       P.SelIdx[threadIdx.x] = s_sel_idx[threadIdx.x];
@@ -358,20 +498,24 @@ __global__ void __launch_bounds__(256, 2) DecodeStepMega(const DecodeStepMegaArg
     }
     {
       ExpertGateUpArgs ga{ly.experts, s_sel_idx, nullptr, nullptr, P.Act, P.slots, P.I, H, 0};
-      gateup_block_dispatch(ga, act, bs, blk, nblk);
+      mega_gateup(ga, act, bs, blk, nblk);
       stage_stamp(gs);
-      prefetch_down(ly.experts, s_sel_idx, P.slots, P.I, H, blk, nblk);
     }
-    if (grid_barrier(gs)) return;
     {
-      __syncthreads();
-      StagedAct4 dact = stage4_from_f32<true>(stage, P.Act, P.I, P.slots, P.I);
-      stage_stamp(gs);
       ExpertDownCombineArgs xa{ly.experts, s_sel_idx, s_sel_w, P.Act, P.Tmp, P.X, nullptr, P.slots, P.I, H};
-      down_block_dispatch(xa, dact, bs, blk, nblk);
+      grid_arrive(gs);
+      down_prepare(xa, bs, blk, nblk);  // the routing is known: down rows stream in during the barrier
+      if (grid_wait(gs)) return mega_bail(&s_ring);
+      StagedAct4 dact = mega_stage_rows(stage, P.Act, P.I, P.slots);
+      stage_stamp(gs);
+      mega_down(xa, dact, bs, blk, nblk);
       stage_stamp(gs);
     }
-    if (grid_barrier(gs)) return;
+    grid_arrive(gs);
+    // the next layer's first projections (or the LM head) stream in during the barrier and its norm
+    if (L + 1 < P.layers) gemv_prepare(&P.L[L + 1].m[0], P.L[L + 1].type == 0 ? 4 : 3, H, smats, bs, blk, nblk);
+    else if (args.mode != 0) gemv_prepare(&P.lm_head, 1, H, smats, bs, blk, nblk);
+    if (grid_wait(gs)) return mega_bail(&s_ring);
   }
   if (P.layer_out && blk == 0)
     for (int j = threadIdx.x; j < H; j += 256)
@@ -389,11 +533,12 @@ __global__ void __launch_bounds__(256, 2) DecodeStepMega(const DecodeStepMegaArg
     return;
   }
   // ---- tail: final norm, LM head, first-max-wins argmax, control update ----
+  AINFER_STAMP(62);
   {
     StagedAct4 act = norm_quant_stage(P.X, nullptr, P.final_norm, H, P.eps, stage, ys, nullptr);
     gemv_stage(&P.lm_head, 1, H, act, smats, bs, blk, nblk);
   }
-  if (grid_barrier(gs)) return;
+  if (grid_barrier(gs)) return mega_bail(&s_ring);
   {
     float bv = -INFINITY;
     int bi = 0x7FFFFFFF;
@@ -404,7 +549,7 @@ __global__ void __launch_bounds__(256, 2) DecodeStepMega(const DecodeStepMegaArg
       P.PI[blk] = bi;
     }
   }
-  if (grid_barrier(gs)) return;
+  if (grid_barrier(gs)) return mega_bail(&s_ring);
   if (blk == 0) {
     float bv = -INFINITY;
     int bi = 0x7FFFFFFF;

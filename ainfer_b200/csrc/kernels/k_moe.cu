@@ -9,7 +9,7 @@ extern __shared__ __align__(128) unsigned char moe_smem[];
 
 __global__ void __launch_bounds__(256) RouterTopK(const RouterTopKArgs a) {
   __shared__ bool is_last;
-  __shared__ float sp[1024];
+  __shared__ float sp[1024 + 1];
   router_logits_rows(a, blockIdx.x, gridDim.x);
   // last block to arrive does the selection
   __threadfence();
@@ -20,7 +20,7 @@ __global__ void __launch_bounds__(256) RouterTopK(const RouterTopKArgs a) {
     if (is_last) *a.Counter = 0u;
   }
   __syncthreads();
-  if (!is_last || threadIdx.x >= 32) return;
+  if (!is_last) return;
   __threadfence();
   router_select(a.Logits, a.E, a.k, a.Wsg != nullptr, sp, a.SelIdx, a.SelW, a.NearGap);
 }
@@ -32,10 +32,12 @@ __global__ void __launch_bounds__(256, 2) ExpertGateUp(const ExpertGateUpArgs a)
   __shared__ SegList lists[2];
   __shared__ float T[kTCap];
   __shared__ Ring ring;
+  __shared__ ExpertW sew[kMaxSegs];
+  fetch_expert_rows(sew, a.Experts, a.SelIdx + a.slot_begin, a.slots);
   ring_init(&ring, moe_smem + moe_round128(staged4_bytes(a.H, 1)), kMoeStages);
-  BlockScratch bs{&ring, lists, T, 0, false};
+  BlockScratch bs{&ring, lists, T, sew, 0, false};
   StagedAct4 act = stage4(moe_smem, a.XQ, a.SQ, a.H, 1, a.H, a.H / 128);
-  gateup_block_dispatch(a, act, bs, blockIdx.x, gridDim.x);
+  gateup_block_dispatch_t(a, act, bs, blockIdx.x, gridDim.x);
   if (threadIdx.x == 0) ring_drain_after_fault(&ring);
 }
 
@@ -43,10 +45,12 @@ __global__ void __launch_bounds__(256, 2) ExpertDownCombine(const ExpertDownComb
   __shared__ SegList lists[2];
   __shared__ float T[kTCap];
   __shared__ Ring ring;
+  __shared__ ExpertW sew[kMaxSegs];
+  fetch_expert_rows(sew, a.Experts, a.SelIdx, a.slots);
   ring_init(&ring, moe_smem + moe_round128(staged4_bytes(a.I, a.slots)), kMoeStages);
-  BlockScratch bs{&ring, lists, T, 0, false};
+  BlockScratch bs{&ring, lists, T, sew, 0, false};
   StagedAct4 act = stage4_from_f32<true>(moe_smem, a.Act, a.I, a.slots, a.I);
-  down_block_dispatch(a, act, bs, blockIdx.x, gridDim.x);
+  down_block_dispatch_t(a, act, bs, blockIdx.x, gridDim.x);
   if (threadIdx.x == 0) ring_drain_after_fault(&ring);
 }
 

@@ -55,67 +55,84 @@ __device__ __forceinline__ void router_logits_rows(const RouterTopKArgs &a, int 
   }
 }
 
-// Selection by one warp: softmax over E logits, top-k by (probability desc,
-// index asc), renormalised weights, shared-expert gate. sp is E floats of
-// shared-memory scratch (probabilities; a selected entry is overwritten by -1).
-// Loops are rolled: the code stays small, lane l owns entries l, l+32, ...
-// Outputs may live in shared or global memory.
+// Selection by a whole block (every thread calls; contains __syncthreads):
+// softmax over E logits, top-k by (probability desc, index asc), renormalised
+// weights, shared-expert gate. sp is E+1 floats of shared-memory scratch
+// (probabilities; a selected entry is overwritten by -1). The logits are fetched
+// by all threads at once (one round trip to L2) and exponentials are taken
+// element-wise by all threads; the sums keep the one-warp partition (lane l
+// adds entries l, l+32, ... in ascending order, then an xor butterfly), so the
+// result does not depend on how many threads help. Outputs may live in shared
+// or global memory; they are complete after the function returns (block-wide).
 static __device__ __noinline__ void router_select(const float *lg, int E, int k, bool has_shared, float *sp,
                                            int32_t *sel_idx, float *sel_w, float *near_gap) {
-  const int lane = threadIdx.x & 31;
-  float m = -INFINITY;
+  __shared__ float s_m, s_sum;
+  const int tid = threadIdx.x, lane = tid & 31, nthr = blockDim.x;
 #pragma unroll 1
-  for (int e = lane; e < E; e += 32) {
-    float v = __ldcg(lg + e);
-    sp[e] = v;
-    m = fmaxf(m, v);
+  for (int e = tid; e <= E; e += nthr)
+    if (e < E || has_shared) sp[e] = __ldcg(lg + e);
+  __syncthreads();
+  if (tid < 32) {
+    float m = -INFINITY;
+#pragma unroll 4
+    for (int e = lane; e < E; e += 32) m = fmaxf(m, sp[e]);
+    m = warp_max(m);
+    if (lane == 0) s_m = m;
   }
-  m = warp_max(m);
-  float sum = 0.0f;
+  __syncthreads();
+  const float m = s_m;
 #pragma unroll 1
-  for (int e = lane; e < E; e += 32) {
-    float p = det_expf(sp[e] - m);
-    sp[e] = p;
-    sum = sum + p;
+  for (int e = tid; e < E; e += nthr) sp[e] = det_expf(sp[e] - m);
+  __syncthreads();
+  if (tid < 32) {
+    float sum = 0.0f;
+#pragma unroll 4
+    for (int e = lane; e < E; e += 32) sum = sum + sp[e];
+    sum = warp_tree_sum(sum);
+    if (lane == 0) s_sum = sum;
   }
-  sum = warp_tree_sum(sum);
+  __syncthreads();
+  const float sum = s_sum;
 #pragma unroll 1
-  for (int e = lane; e < E; e += 32) sp[e] = sp[e] / sum;
-  __syncwarp();
-  float s = 0.0f, lastp = 0.0f;
-  float wsel = 0.0f;  // lane j keeps the weight of rank j (k <= 32)
+  for (int e = tid; e < E; e += nthr) sp[e] = sp[e] / sum;
+  __syncthreads();
+  if (tid < 32) {
+    float s = 0.0f, lastp = 0.0f;
+    float wsel = 0.0f;  // lane j keeps the weight of rank j (k <= 32)
 #pragma unroll 1
-  for (int j = 0; j <= k && j < E; ++j) {
-    float bv = -1.0f;
-    int bi = 0x7FFFFFFF;
-#pragma unroll 1
-    for (int e = lane; e < E; e += 32) {
-      float p = sp[e];
-      if (p > bv) { bv = p; bi = e; }
-    }
+    for (int j = 0; j <= k && j < E; ++j) {
+      float bv = -1.0f;
+      int bi = 0x7FFFFFFF;
+#pragma unroll 4
+      for (int e = lane; e < E; e += 32) {
+        float p = sp[e];
+        if (p > bv) { bv = p; bi = e; }
+      }
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-      float ov = __shfl_xor_sync(kFull, bv, off);
-      int oi = __shfl_xor_sync(kFull, bi, off);
-      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+      for (int off = 16; off > 0; off >>= 1) {
+        float ov = __shfl_xor_sync(kFull, bv, off);
+        int oi = __shfl_xor_sync(kFull, bi, off);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+      }
+      if (j == k) {
+        if (lane == 0) *near_gap = lastp > 0.0f ? (lastp - bv) / lastp : 0.0f;
+        break;
+      }
+      if ((bi & 31) == lane) sp[bi] = -1.0f;  // probabilities are >= 0: never selected again
+      __syncwarp();
+      if (lane == j) wsel = bv;
+      if (lane == 0) sel_idx[j] = bi;
+      s = s + bv;
+      lastp = bv;
     }
-    if (j == k) {
-      if (lane == 0) *near_gap = lastp > 0.0f ? (lastp - bv) / lastp : 0.0f;
-      break;
+    if (k >= E && lane == 0) *near_gap = 1.0f;
+    if (lane < k) sel_w[lane] = wsel / s;
+    if (lane == 0) {
+      sel_idx[k] = E;
+      sel_w[k] = has_shared ? 1.0f / (1.0f + det_expf(-sp[E])) : 0.0f;
     }
-    if ((bi & 31) == lane) sp[bi] = -1.0f;  // probabilities are >= 0: never selected again
-    __syncwarp();
-    if (lane == j) wsel = bv;
-    if (lane == 0) sel_idx[j] = bi;
-    s = s + bv;
-    lastp = bv;
   }
-  if (k >= E && lane == 0) *near_gap = 1.0f;
-  if (lane < k) sel_w[lane] = wsel / s;
-  if (lane == 0) {
-    sel_idx[k] = E;
-    sel_w[k] = has_shared ? 1.0f / (1.0f + det_expf(-__ldcg(lg + E))) : 0.0f;
-  }
+  __syncthreads();
 }
 
 // --------------------------------------------------------- ExpertGateUp ---

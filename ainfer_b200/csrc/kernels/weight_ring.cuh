@@ -41,7 +41,7 @@ struct RowSeg {
 constexpr int kMaxSegs = 16;
 
 // A list of segments of matrices with the same K. Lives in shared memory.
-struct SegList {
+struct __align__(16) SegList {
   RowSeg seg[kMaxSegs];
   int32_t nseg;
   int32_t K;
@@ -57,8 +57,14 @@ struct Ring {
   uint32_t c_stage;     // stage of the next tile to consume
   uint32_t c_phase;     // parity of that stage's current use
   uint32_t pre;         // leading tiles of the next list that are already in flight
-  uint32_t issued;      // tiles issued so far, over all calls (for the drain after a fault)
+  uint32_t issued;      // tiles issued so far, over all calls (for the drain before an early exit)
   uint32_t fault;       // sticky: 1 a wait ran out, 2 a source was not 16-byte aligned
+  // the issuing thread's cursor (kept here so that the issue code is one out-of-line function)
+  const SegList *p_list;  // list the next tile comes from
+  const SegList *p_next;  // list to continue with when p_list is exhausted (or null)
+  int32_t p_tile;         // next tile of p_list
+  int32_t p_seg;          // first segment of p_list that can overlap that tile
+  uint32_t p_stage, p_phase;  // where it goes
 };
 
 // Per-translation-unit pointer to the host-visible fault word (set once per
@@ -111,24 +117,20 @@ __device__ __forceinline__ void ring_fault(Ring *ring, uint32_t code) {
   ring->fault = code;
   if (g_stream_fault_word) *reinterpret_cast<volatile unsigned int *>(g_stream_fault_word) = code;
 }
-// Bounded wait; false (and the fault word set) when it ran out.
-__device__ __forceinline__ bool mbar_wait(Ring *ring, unsigned long long *b, uint32_t parity) {
-  if (mbar_try(b, parity)) return true;
-  // after a first fault no wait in this block spins again: the launch is lost, end it quickly
-  const uint32_t limit = *reinterpret_cast<volatile uint32_t *>(&ring->fault) ? 0u : kRingSpinLimit;
-  for (uint32_t i = 0; i < limit; ++i)
-    if (mbar_try(b, parity)) return true;
-  ring_fault(ring, 1);
-  return false;
-}
-// Same, barrier given by its shared-window address.
+// Bounded wait; false (and the fault word set) when it ran out. (Kept inline: a
+// call inside the streaming loop would force its live registers to be spilled.)
 __device__ __forceinline__ bool mbar_wait_a(Ring *ring, uint32_t addr, uint32_t parity) {
   if (mbar_try_a(addr, parity)) return true;
+  // after a first fault no wait in this block spins again: the launch is lost, end it quickly
   const uint32_t limit = *reinterpret_cast<volatile uint32_t *>(&ring->fault) ? 0u : kRingSpinLimit;
+#pragma unroll 1
   for (uint32_t i = 0; i < limit; ++i)
     if (mbar_try_a(addr, parity)) return true;
   ring_fault(ring, 1);
   return false;
+}
+__device__ __forceinline__ bool mbar_wait(Ring *ring, unsigned long long *b, uint32_t parity) {
+  return mbar_wait_a(ring, smem_addr(b), parity);
 }
 __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, unsigned long long *b) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
@@ -147,6 +149,12 @@ __device__ __forceinline__ void ring_init(Ring *ring, unsigned char *data, int n
     ring->pre = 0;
     ring->issued = 0;
     ring->fault = 0;
+    ring->p_list = nullptr;
+    ring->p_next = nullptr;
+    ring->p_tile = 0;
+    ring->p_seg = 0;
+    ring->p_stage = 0;
+    ring->p_phase = 0;
     for (int i = 0; i < nst; ++i) {
       mbar_init(&ring->full[i], 1);
       mbar_init(&ring->empty[i], blockDim.x / 32);  // one arrival per warp
@@ -182,43 +190,60 @@ __device__ __forceinline__ void mbar_expect_tx(unsigned long long *b, uint32_t b
                : "memory");
 }
 
-// The issuing thread's cursor over the tiles of one list.
+// The issuing thread's cursor. Between calls it rests in the Ring (shared
+// memory); the streaming loop keeps it in registers, because the issue sits on
+// the critical path of the warp that also consumes.
 struct Producer {
-  const SegList *l;
-  int s;                     // first segment that can overlap the next tile
-  int tile;                  // next tile of the list
-  int rpi, row_bytes, srow;  // rows per tile, weight bytes per row, scale bytes per row
+  const SegList *l;   // list the next tile comes from (its successor, if any, is ring->p_next)
+  int tile, s;        // next tile of l; first segment of l that can overlap it
   uint32_t stage, phase;
 
-  __device__ __forceinline__ void open(const SegList *list) {
-    l = list;
-    rpi = kTileBytes * 2 / list->K;
-    row_bytes = list->K / 2;
-    srow = list->K / 64;
-    s = 0;
-    tile = 0;
+  __device__ __forceinline__ void load(const Ring *ring) {
+    l = ring->p_list;
+    tile = ring->p_tile;
+    s = ring->p_seg;
+    stage = ring->p_stage;
+    phase = ring->p_phase;
   }
-  __device__ __forceinline__ void skip() { ++tile; }  // the next tile is already in flight
-  __device__ __forceinline__ void next_stage(uint32_t nst) {
-    if (++stage == nst) {
-      stage = 0;
-      phase ^= 1u;
+  __device__ __forceinline__ void store(Ring *ring) const {
+    ring->p_list = l;
+    ring->p_tile = tile;
+    ring->p_seg = s;
+    ring->p_stage = stage;
+    ring->p_phase = phase;
+  }
+  // Issues the copies of the next tile (moving on to ring->p_next when l is
+  // exhausted) into `stage`. Returns false when there is nothing left to issue.
+  // Few values live in registers between issues: the list's constants are one
+  // 16-byte shared-memory read per issue.
+  __device__ __forceinline__ bool issue(Ring *ring, unsigned char *data, uint32_t nst) {
+    int4 hdr = l ? *reinterpret_cast<const int4 *>(&l->nseg) : make_int4(0, 128, 0, 0);  // nseg, K, ntiles, total
+    if (tile >= hdr.z) {
+      const SegList *nx = ring->p_next;
+      if (nx == nullptr) return false;
+      hdr = *reinterpret_cast<const int4 *>(&nx->nseg);
+      if (hdr.z == 0) return false;
+      l = nx;
+      ring->p_next = nullptr;
+      tile = 0;
+      s = 0;
     }
-  }
-  // Issues the copies of the next tile into `stage` and moves on.
-  __device__ __forceinline__ void issue(Ring *ring, unsigned char *data, uint32_t nst) {
-    const int f0 = tile * rpi, f1 = f0 + rpi < l->total ? f0 + rpi : l->total;
+    const int nseg = hdr.x, K = hdr.y, total = hdr.w;
+    const int rpi = kTileBytes * 2 / K, row_bytes = K / 2, srow = K / 64;
+    const int f0 = tile * rpi, f1 = f0 + rpi < total ? f0 + rpi : total;
     unsigned char *dst = data + stage * kStageStride;
     unsigned long long *bar = &ring->full[stage];
-    while (s < l->nseg && l->seg[s].row0 + l->seg[s].nrows <= f0) ++s;
-    for (int i = s; i < l->nseg; ++i) {
+    while (s < nseg && l->seg[s].row0 + l->seg[s].nrows <= f0) ++s;
+#pragma unroll 1
+    for (int i = s; i < nseg; ++i) {
       const RowSeg &sg = l->seg[i];
       if (sg.row0 >= f1) break;
       const int a = sg.row0 > f0 ? sg.row0 : f0;
       const int b = sg.row0 + sg.nrows < f1 ? sg.row0 + sg.nrows : f1;
       const int lr = a - sg.row0, rows = b - a, off = a - f0;
       const uint8_t *src = sg.P + (size_t)lr * row_bytes;
-      const uint16_t *ssrc = reinterpret_cast<const uint16_t *>(reinterpret_cast<const uint8_t *>(sg.S) + (size_t)lr * srow);
+      const uint16_t *ssrc =
+          reinterpret_cast<const uint16_t *>(reinterpret_cast<const uint8_t *>(sg.S) + (size_t)lr * srow);
       if (reinterpret_cast<uintptr_t>(src) & 15u) {  // cannot be copied in bulk: report and skip
         ring_fault(ring, 2);
         continue;
@@ -231,42 +256,58 @@ struct Producer {
     }
     mbar_arrive(bar);
     ++tile;
-    next_stage(nst);
+    if (++stage == nst) {
+      stage = 0;
+      phase ^= 1u;
+    }
+    return true;
   }
 };
+
+// Out-of-line form for the places that are not in a streaming loop. One thread.
+static __device__ __noinline__ bool ring_issue_next(Ring *ring) {
+  Producer pr;
+  pr.load(ring);
+  const bool ok = pr.issue(ring, ring->data, ring->nst);
+  pr.store(ring);
+  if (ok) ring->issued += 1;
+  return ok;
+}
+
+// Points the cursor at the start of `list`, at the consumer's position.
+__device__ __forceinline__ void ring_open(Ring *ring, const SegList *list) {
+  ring->p_list = list;
+  ring->p_tile = 0;
+  ring->p_seg = 0;
+  ring->p_stage = ring->c_stage;
+  ring->p_phase = ring->c_phase;
+}
 
 // Tops up the ring with leading tiles of `next` (the list the next block_dot
 // call will consume). Call between block_dot calls, when every stage not
 // counted in ring->pre is free. One thread; no synchronisation.
 __device__ __forceinline__ void ring_prefetch(Ring *ring, const SegList *next) {
-  const uint32_t nst = ring->nst;
-  const uint32_t cap = (uint32_t)next->ntiles < nst ? (uint32_t)next->ntiles : nst;
-  if (ring->pre >= cap) return;
-  Producer pr;
-  pr.open(next);
-  pr.stage = ring->c_stage;
-  pr.phase = ring->c_phase;
-  uint32_t i = 0;
-  for (; i < ring->pre; ++i) {
-    pr.skip();
-    pr.next_stage(nst);
+  if (ring->pre == 0) ring_open(ring, next);
+  ring->p_next = nullptr;
+  while (ring->pre < ring->nst && ring->p_list == next && ring->p_tile < next->ntiles) {
+    ring_issue_next(ring);
+    ring->pre += 1;
   }
-  for (; i < cap; ++i) pr.issue(ring, ring->data, nst);
-  ring->issued += cap - ring->pre;
-  ring->pre = cap;
 }
 
-// After a fault: waits (bounded) for whatever may still be in flight into this
-// block's shared memory, so that the block does not retire under a landing copy.
-// One thread, at the end of the kernel.
-__device__ __forceinline__ void ring_drain_after_fault(Ring *ring) {
-  if (ring->fault == 0) return;
+// Before a block leaves its kernel early or after a fault: waits (bounded) for
+// whatever may still be in flight into this block's shared memory, so that the
+// block does not retire under a landing copy. One thread.
+__device__ __forceinline__ void ring_drain(Ring *ring) {
   const uint32_t end = ring->issued;
   for (uint32_t st = 0; st < ring->nst && st < end; ++st) {
     uint32_t t = end - 1 - ((end - 1 - st) % ring->nst);  // latest issued tile held by stage st
     for (uint32_t i = 0; i < kRingSpinLimit; ++i)
       if (mbar_try(&ring->full[st], (t / ring->nst) & 1u)) break;
   }
+}
+__device__ __forceinline__ void ring_drain_after_fault(Ring *ring) {
+  if (ring->fault != 0) ring_drain(ring);
 }
 
 }  // namespace ainfer

@@ -355,7 +355,7 @@ int build_mega(Session *s) {
   P.layer_out = s->layer_out; P.routed = s->routed; P.near_gap = s->near_gap;
   if (salloc(s, 1, &s->bar_count) || salloc(s, 1, &s->mega_error)) return 1;
   if (s->flags & SESSION_STAGE_CLOCK) {
-    s->stage_stamp_cap = c.layers * 24 + 16;
+    s->stage_stamp_cap = 2 * (c.layers * 64 + 64);  // first half: barrier clock, second half: fine clock
     if (salloc(s, (size_t)s->stage_stamp_cap, &s->stage_stamps)) return 1;
     P.stage_stamps = s->stage_stamps;
     P.stage_stamp_cap = s->stage_stamp_cap;
