@@ -64,10 +64,13 @@ struct Recorder {
   }
 };
 
-int gemv_rows_per_group(int K) {
-  int cpr = K / 32, lpr = std::min(cpr, 32), rpw = 32 / lpr;
-  int rt = K <= 1024 ? 4 : (K == 2048 ? 2 : 1);
-  return 8 * rt * rpw;
+// Thread groups for a weight-streaming launch: a group should own at least one
+// whole 16 KB tile (32768/K rows) and there is no point in more than two groups
+// per SM (that many are resident; each pays its own start-up).
+int stream_groups(long weight_rows, int K, int sm_count) {
+  const long rpt = 32768 / K;
+  long g = (weight_rows + rpt - 1) / rpt;
+  return (int)std::max<long>(1, std::min<long>(g, 2L * sm_count));
 }
 
 struct MatSpec {
@@ -111,8 +114,7 @@ void record_gemv(Recorder &r, const std::vector<MatSpec> &mats, int K, const int
   s->gemv_tables_host.resize(off + bytes);
   std::memcpy(s->gemv_tables_host.data() + off, tab.data(), bytes);
   const GemvMat *dtab = (const GemvMat *)((char *)s->gemv_tables + off);
-  int rpg = gemv_rows_per_group(K);
-  uint32_t groups = (uint32_t)std::min((row + rpg - 1) / rpg, s->sm_count * 8);
+  uint32_t groups = (uint32_t)stream_groups(row, K, s->sm_count);
   r.launch("Int4GemvA8", groups, dtab, (int32_t)mats.size(), (int32_t)row, XQ, SQ, (int32_t)K,
            (int32_t)1);
 }
@@ -153,12 +155,10 @@ void record_moe(Recorder &r, int L, const std::string &p, const float *post_norm
            (const uint16_t *)(c.shared_experts ? sgate.data : nullptr), (const float *)s->Hn,
            s->RLogits, s->Counter, s->SelIdx, s->SelW, s->NearGap, (int32_t)E, (int32_t)H, (int32_t)k);
   const ExpertW *tab = (const ExpertW *)s->m->expert_tables + (size_t)L * (E + 1);
-  int rpg_up = 8 * (32 / std::min(H / 32, 32));
-  uint32_t g_up = (uint32_t)std::min((slots * I + rpg_up - 1) / rpg_up, s->sm_count * 8);
+  uint32_t g_up = (uint32_t)stream_groups(2L * slots * I, H, s->sm_count);
   r.launch("ExpertGateUp", g_up, tab, (const int32_t *)s->SelIdx, (const int8_t *)s->Q8,
            (const float *)s->SQ, s->Act, (int32_t)slots, (int32_t)I, (int32_t)H, (int32_t)0);
-  int rpg_dn = 8 * (32 / std::min(I / 32, 32));
-  uint32_t g_dn = (uint32_t)std::min((H + rpg_dn - 1) / rpg_dn, s->sm_count * 8);
+  uint32_t g_dn = (uint32_t)std::min<long>(stream_groups((long)H * slots, I, s->sm_count), (H + 3) / 4);
   r.launch("ExpertDownCombine", g_dn, tab, (const int32_t *)s->SelIdx, (const float *)s->SelW,
            (const float *)s->Act, (const float *)s->Tmp, s->X, (float *)nullptr, (int32_t)slots,
            (int32_t)I, (int32_t)H);

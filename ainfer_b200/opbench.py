@@ -32,9 +32,11 @@ def gemv_bytes(N, K, M):
     return N * K * 0.515625 + M * (K + (K // 128) * 4) + M * N * 4
 
 
-def rows_per_group(K):
-    rt = 4 if K <= 1024 else (2 if K == 2048 else 1)
-    return 8 * rt * (32 // min(K // 32, 32))
+def stream_groups(rows, K, sm_count):
+    """Thread groups of a weight-streaming launch: at least one 16 KB tile (32768/K rows) per group,
+    at most two groups per SM (the runtime's rule)."""
+    rpt = 32768 // K
+    return max(1, min(-(-rows // rpt), 2 * sm_count))
 
 
 def gemv_once(dev, N, K, M=1, reps=20, flush=False, groups=None):
@@ -49,7 +51,7 @@ def gemv_once(dev, N, K, M=1, reps=20, flush=False, groups=None):
     xq = dev.upload(rng.integers(-127, 128, (M, K), dtype=np.int8))
     sq = dev.upload(np.full((M, K // 128), 0.01, np.float32))
     if not groups:
-        groups = max(1, min((N + rows_per_group(K) - 1) // rows_per_group(K), sm * 8))
+        groups = stream_groups(N, K, sm) if M == 1 else max(1, min(-(-N // 32), sm * 8))
     bufs, kernels = [], []
     for b in range(nbuf):
         dP, dS, dY = dev.alloc(N * K // 2), dev.alloc(N * K // 128 * 2), dev.zeros(M * N * 4)
