@@ -8,10 +8,20 @@
 
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 #include <string>
 #include <vector>
 
 #include "../kernels/registry.h"
+
+namespace ainfer {
+// defined beside the fixed scratch array (k_moe.cu)
+constexpr int kRouterStaticMaxExperts = 1024;
+cudaError_t router_static_scratch_address(void **ptr);
+cudaError_t router_static_launch(cudaStream_t stream, void *scratch, const void *Wr, const void *Wsg,
+                                 const float *Hn, int32_t *SelIdx, float *SelW, float *NearGap, int E, int H,
+                                 int k);
+}  // namespace ainfer
 
 namespace ainfer {
 
@@ -530,6 +540,51 @@ int ainfer_flush_l2(ainfer_device_t dev) {
 int ainfer_device_stream(ainfer_device_t dev, void **stream) {
   if (!dev || !stream) return AINFER_ERR_INVALID;
   *stream = (void *)dev->stream;
+  return AINFER_OK;
+}
+
+// ---- router + top-k without any allocation (scratch in a fixed device array) ----
+// Address of the fixed scratch array on each GPU, looked up once per GPU.
+static void *g_router_static_ptr[64];
+static std::mutex g_router_static_mu;
+
+int ainfer_router_topk_static(ainfer_device_t dev, const void *router, const void *shared_gate,
+                              const float *hn, int32_t *sel_idx, float *sel_w, float *near_gap,
+                              int32_t experts, int32_t hidden, int32_t top_k) {
+  if (!dev) return AINFER_ERR_INVALID;
+  if (!router || !hn || !sel_idx || !sel_w || !near_gap)
+    return fail(dev, AINFER_ERR_INVALID, "ainfer_router_topk_static: null pointer argument");
+  if (experts < 1 || experts > kRouterStaticMaxExperts)
+    return fail(dev, AINFER_ERR_INVALID,
+                "ainfer_router_topk_static: experts = " + std::to_string(experts) +
+                    " is outside [1, " + std::to_string(kRouterStaticMaxExperts) +
+                    "], the size the fixed scratch array was built for");
+  if (top_k < 1 || top_k > 32 || top_k > experts)
+    return fail(dev, AINFER_ERR_INVALID, "ainfer_router_topk_static: top_k must be in [1, min(32, experts)]");
+  if (hidden < 256 || hidden % 256)
+    return fail(dev, AINFER_ERR_INVALID, "ainfer_router_topk_static: hidden must be a positive multiple of 256");
+  if (dev->ordinal < 0 || dev->ordinal >= 64) return fail(dev, AINFER_ERR_INVALID, "bad device ordinal");
+  void *scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_router_static_mu);
+    if (!g_router_static_ptr[dev->ordinal]) {
+      // set-up, once per GPU, with that GPU current: where does this GPU keep the array?
+      CU(dev, cudaSetDevice(dev->ordinal));
+      void *p = nullptr;
+      cudaError_t e = router_static_scratch_address(&p);
+      if (e != cudaSuccess || p == nullptr) {
+        cudaGetLastError();
+        return fail(dev, AINFER_ERR_DEVICE,
+                    std::string("ainfer_router_topk_static: cudaGetSymbolAddress failed: ") + cudaGetErrorString(e));
+      }
+      g_router_static_ptr[dev->ordinal] = p;
+    }
+    scratch = g_router_static_ptr[dev->ordinal];
+  }
+  cudaError_t e = router_static_launch(dev->stream, scratch, router, shared_gate, hn, sel_idx, sel_w, near_gap,
+                                       experts, hidden, top_k);
+  if (e != cudaSuccess) return fail(dev, AINFER_ERR_DEVICE, std::string("ainfer_router_topk_static: ") + cudaGetErrorString(e));
+  dev->launches += 1;
   return AINFER_OK;
 }
 

@@ -54,6 +54,57 @@ __global__ void __launch_bounds__(256, 2) ExpertDownCombine(const ExpertDownComb
   if (threadIdx.x == 0) ring_drain_after_fault(&ring);
 }
 
+// ---- RouterTopK with its scratch in a fixed device array (no allocation) ----
+// Same work as RouterTopK, but the router logits and the block counter live in
+// this file-scope array instead of caller-provided buffers. The array belongs to
+// the device, so calls on one device share it: the host entry point clears the
+// counter before every launch, and two calls in flight at once would race.
+static __device__ __align__(256) unsigned char g_router_static_scratch[kRouterStaticScratchBytes];
+
+__global__ void __launch_bounds__(256) RouterTopKStatic(const RouterTopKArgs a, unsigned char *scratch) {
+  RouterTopKArgs b = a;
+  b.Logits = reinterpret_cast<float *>(scratch);
+  b.Counter = reinterpret_cast<unsigned *>(scratch + kRouterStaticCounterOffset);
+  __shared__ bool is_last;
+  __shared__ float sp[1024 + 1];
+  router_logits_rows(b, blockIdx.x, gridDim.x);
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned prev = atomicAdd(b.Counter, 1u);
+    is_last = prev == gridDim.x - 1;
+    if (is_last) *b.Counter = 0u;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  router_select(b.Logits, b.E, b.k, b.Wsg != nullptr, sp, b.SelIdx, b.SelW, b.NearGap);
+}
+
+// Host helpers for the C entry point (which lives with the rest of the ABI).
+cudaError_t router_static_scratch_address(void **ptr) {
+  return cudaGetSymbolAddress(ptr, g_router_static_scratch);
+}
+cudaError_t router_static_launch(cudaStream_t stream, void *scratch, const void *Wr, const void *Wsg,
+                                 const float *Hn, int32_t *SelIdx, float *SelW, float *NearGap, int E, int H,
+                                 int k) {
+  cudaError_t e = cudaMemsetAsync(static_cast<unsigned char *>(scratch) + kRouterStaticCounterOffset, 0, 4, stream);
+  if (e != cudaSuccess) return e;
+  RouterTopKArgs a{};
+  a.Wr = static_cast<const uint16_t *>(Wr);
+  a.Wsg = static_cast<const uint16_t *>(Wsg);
+  a.Hn = Hn;
+  a.SelIdx = SelIdx;
+  a.SelW = SelW;
+  a.NearGap = NearGap;
+  a.E = E;
+  a.H = H;
+  a.k = k;
+  const unsigned groups = (unsigned)((E + 1 + 7) / 8);
+  RouterTopKStatic<<<groups, 256, 0, stream>>>(a, static_cast<unsigned char *>(scratch));
+  return cudaGetLastError();
+}
+
 #define F(f) AINFER_ARG(RouterTopKArgs, f)
 AINFER_REGISTER(RouterTopK, RouterTopKArgs, 256, 8, 0, nullptr, F(Wr), F(Wsg), F(Hn), F(Logits),
                 F(Counter), F(SelIdx), F(SelW), F(NearGap), F(E), F(H), F(k));

@@ -72,6 +72,7 @@ SIGNATURES = {
     "ainfer_launch_counter": (_i, [_vp, C.POINTER(_u64)]),
     "ainfer_flush_l2": (_i, [_vp]),
     "ainfer_device_stream": (_i, [_vp, _pp]),
+    "ainfer_router_topk_static": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, C.c_int32, C.c_int32, C.c_int32]),
 }
 
 _lib = None

@@ -135,6 +135,36 @@ int ainfer_flush_l2(ainfer_device_t dev);
 /* The raw execution stream (cudaStream_t) for interop with NCCL. */
 int ainfer_device_stream(ainfer_device_t dev, void **stream);
 
+/* Router logits + softmax + top-k + renormalised weights + shared-expert gate
+ * (the work of the "RouterTopK" kernel) WITHOUT any allocation and without
+ * caller-provided scratch. NO COUNTERPART IN THE REFERENCE: its token loop
+ * allocates every buffer up front (decode_l0.cpp:270-285) and has no router.
+ *
+ *   router      [experts][hidden] bf16      shared_gate [hidden] bf16 or NULL
+ *   hn          [hidden] fp32 normalised activations
+ *   sel_idx     [top_k+1] out: routed expert ids in rank order, then `experts`
+ *   sel_w       [top_k+1] out: renormalised weights, then sigmoid(shared gate)
+ *   near_gap    [1] out
+ * All pointers are device memory. Results are identical to "RouterTopK".
+ *
+ * The kernel's scratch (logits of all experts and a block counter) lives in a
+ * fixed 8192-byte array in device memory that is part of the library image, so
+ * the call never calls cudaMalloc/cudaFree or any routine that allocates.
+ * Limits and rules:
+ *  - experts <= 1024 (what the array holds), top_k <= min(32, experts), hidden
+ *    a multiple of 256; anything else returns AINFER_ERR_INVALID with a message.
+ *  - The FIRST call on a GPU does one-time set-up (it asks the runtime for the
+ *    array's address on that GPU); make that call before starting any stream
+ *    capture.
+ *  - Every call on one GPU uses the same array. The entry point clears the
+ *    counter before each launch; calls that overlap in time on one GPU (other
+ *    streams, other handles, other threads) race on the array and must be
+ *    serialised by the caller. Calls on this handle's queue are ordered.
+ *  - Asynchronous: returns after enqueueing on the handle's queue. */
+int ainfer_router_topk_static(ainfer_device_t dev, const void *router, const void *shared_gate,
+                              const float *hn, int32_t *sel_idx, float *sel_w, float *near_gap,
+                              int32_t experts, int32_t hidden, int32_t top_k);
+
 #ifdef __cplusplus
 }
 #endif
