@@ -7,6 +7,7 @@
 #include <time.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -30,6 +31,10 @@ static std::vector<KernelDesc> &registry() {
   return r;
 }
 void register_kernel(const KernelDesc &d) { registry().push_back(d); }
+void mark_kernel_early_launch(const char *name) {
+  for (auto &d : registry())
+    if (std::strcmp(d.name, name) == 0) d.early_launch = 1;
+}
 static std::vector<FaultHook> &fault_hooks() {
   static std::vector<FaultHook> h;
   return h;
@@ -60,6 +65,7 @@ struct ainfer_device_s {
   size_t flush_bytes = 0;
   int sm_count = 0;
   volatile unsigned int *fault_word = nullptr;  // host view of the stream fault word of this GPU
+  bool early_launch = true;  // recorded lists use programmatic dependencies (AINFER_NO_EARLY_LAUNCH=1 turns it off)
 };
 
 // One host-mapped fault word per GPU for the life of the process: kernels that
@@ -82,6 +88,7 @@ static int fault_word_setup(int ordinal, volatile unsigned int **out) {
 struct ainfer_kernel_s {
   ainfer_device_t dev;
   const KernelDesc *desc;
+  bool carveout_set = false;
   std::vector<unsigned char> args;
   std::vector<bool> set;
 };
@@ -91,6 +98,7 @@ struct ainfer_list_s {
   cudaGraphExec_t exec = nullptr;
   cudaGraphNode_t last = nullptr;
   bool has_last = false;
+  bool last_is_kernel = false;
   bool closed = false;
   uint32_t launches = 0;
 };
@@ -145,6 +153,10 @@ int ainfer_device_open(int ordinal, ainfer_device_t *out) {
                 "device is not sm_100 class: kernels are built for sm_100a only");
   }
   CU(nullptr, cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking));
+  {
+    const char *off = std::getenv("AINFER_NO_EARLY_LAUNCH");
+    d->early_launch = !(off && off[0] == '1');
+  }
   if (fault_word_setup(ordinal, &d->fault_word) != 0) {
     cudaGetLastError();
     cudaStreamDestroy(d->stream);
@@ -308,6 +320,14 @@ static int check_launch(ainfer_kernel_t k, uint32_t groups, uint32_t *smem) {
     }
   if (groups == 0) return fail(k->dev, AINFER_ERR_INVALID, "group count 0");
   *smem = k->desc->smem_fn ? k->desc->smem_fn(k->args.data()) : k->desc->smem_bytes;
+  // Every kernel asks for the same L1/shared-memory split (all shared): consecutive kernels of a
+  // decode step then never make an SM wait for the split to be changed.
+  if (!k->carveout_set) {
+    if (cudaFuncSetAttribute(k->desc->fn, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             (int)cudaSharedmemCarveoutMaxShared) != cudaSuccess)
+      cudaGetLastError();
+    k->carveout_set = true;
+  }
   if (*smem > 16 * 1024) {  // static + dynamic may pass 48 KB: opt in early
     cudaError_t e = cudaFuncSetAttribute(k->desc->fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)*smem);
@@ -392,7 +412,27 @@ int ainfer_list_append_launch(ainfer_list_t l, ainfer_kernel_t k, uint32_t group
   np.sharedMemBytes = smem;
   np.kernelParams = params;
   cudaGraphNode_t node;
-  CU(l->dev, cudaGraphAddKernelNode(&node, l->graph, deps(l), l->has_last ? 1 : 0, &np));
+  if (k->desc->early_launch && l->has_last && l->last_is_kernel && l->dev->early_launch) {
+    // Programmatic dependency: this kernel may start while its predecessor still runs (its
+    // blocks wait in griddepcontrol.wait before touching dependent data), which hides launch
+    // latency and lets a GEMV start streaming its weights early.
+    alignas(cudaGraphNodeParams) unsigned char gp_raw[sizeof(cudaGraphNodeParams)];
+    std::memset(gp_raw, 0, sizeof gp_raw);
+    cudaGraphNodeParams &gp = *reinterpret_cast<cudaGraphNodeParams *>(gp_raw);
+    gp.type = cudaGraphNodeTypeKernel;
+    gp.kernel.func = const_cast<void *>(k->desc->fn);
+    gp.kernel.gridDim = dim3(groups);
+    gp.kernel.blockDim = dim3(k->desc->threads);
+    gp.kernel.sharedMemBytes = smem;
+    gp.kernel.kernelParams = params;
+    cudaGraphEdgeData ed = {};
+    ed.from_port = cudaGraphKernelNodePortProgrammatic;
+    ed.to_port = cudaGraphKernelNodePortDefault;
+    ed.type = cudaGraphDependencyTypeProgrammatic;
+    CU(l->dev, cudaGraphAddNode_v2(&node, l->graph, &l->last, &ed, 1, &gp));
+  } else {
+    CU(l->dev, cudaGraphAddKernelNode(&node, l->graph, deps(l), l->has_last ? 1 : 0, &np));
+  }
   if (k->desc->cooperative) {
     cudaKernelNodeAttrValue v;
     std::memset(&v, 0, sizeof v);
@@ -401,6 +441,7 @@ int ainfer_list_append_launch(ainfer_list_t l, ainfer_kernel_t k, uint32_t group
   }
   l->last = node;
   l->has_last = true;
+  l->last_is_kernel = true;
   l->launches += 1;
   return AINFER_OK;
 }
@@ -412,6 +453,7 @@ int ainfer_list_append_memcpy(ainfer_list_t l, void *dst, const void *src, size_
                                       cudaMemcpyDeviceToDevice));
   l->last = node;
   l->has_last = true;
+  l->last_is_kernel = false;
   return AINFER_OK;
 }
 int ainfer_list_append_fill(ainfer_list_t l, void *dst, int byte_value, size_t bytes) {
@@ -427,6 +469,7 @@ int ainfer_list_append_fill(ainfer_list_t l, void *dst, int byte_value, size_t b
   mp.pitch = bytes;
   cudaGraphNode_t node;
   CU(l->dev, cudaGraphAddMemsetNode(&node, l->graph, deps(l), l->has_last ? 1 : 0, &mp));
+  l->last_is_kernel = false;
   l->last = node;
   l->has_last = true;
   return AINFER_OK;

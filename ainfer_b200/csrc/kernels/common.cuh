@@ -15,6 +15,13 @@
 
 namespace ainfer {
 
+// Programmatic dependent launch: a kernel first lets its successor start launching,
+// and waits for its predecessor (completion and memory flush) before it reads or
+// writes anything the predecessor touches. Both are no-ops for an ordinary launch.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+
 constexpr unsigned kFull = 0xFFFFFFFFu;
 
 // Control block words, tools/decode/decode_l0.cpp:41-43.

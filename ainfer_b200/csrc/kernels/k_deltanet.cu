@@ -5,11 +5,15 @@
 namespace ainfer {
 
 __global__ void __launch_bounds__(256) DeltaNetStep(const DeltaNetStepArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   deltanet_step_body(a, blockIdx.x, gridDim.x);
 }
 #define F(f) AINFER_ARG(DeltaNetStepArgs, f)
 AINFER_REGISTER(DeltaNetStep, DeltaNetStepArgs, 256, 1, 0, nullptr, F(Out), F(Mx), F(S), F(Bt),
                 F(Gt), F(nK), F(nV));
 #undef F
+
+AINFER_EARLY_LAUNCH(DeltaNetStep);
 
 }  // namespace ainfer

@@ -9,6 +9,8 @@ extern __shared__ __align__(128) unsigned char gemv_smem[];
 template <int M>
 __device__ __forceinline__ void gemv_kernel(const Int4GemvA8Args &a) {
   __shared__ GemvMat smats[8];
+  pdl_launch_dependents();
+  pdl_wait();
   if (threadIdx.x < a.nmats) smats[threadIdx.x] = a.mats[threadIdx.x];  // synced by stage_act
   StagedAct act = stage_act(gemv_smem, a.XQ, a.SQ, a.K, M, a.K, a.K / 128);
   gemv_dispatch_k<M>(a, act, smats, blockIdx.x, gridDim.x);
@@ -24,6 +26,8 @@ __global__ void __launch_bounds__(256, 2) Int4GemvA8(const Int4GemvA8Args a) {
   __shared__ SegList lists[2];
   __shared__ float T[kTCap];
   __shared__ Ring ring;
+  pdl_launch_dependents();
+  // the matrix table and the weights are constants of the model: fetched before the wait
   if (threadIdx.x < a.nmats) smats[threadIdx.x] = a.mats[threadIdx.x];
   ring_init(&ring, gemv_smem + round128(staged4_bytes(a.K, 1)), kGemvStages);  // syncs: smats visible
   BlockScratch bs{&ring, lists, T, nullptr, 0, false};
@@ -33,6 +37,7 @@ __global__ void __launch_bounds__(256, 2) Int4GemvA8(const Int4GemvA8Args a) {
     ring_prefetch(&ring, &lists[0]);
   }
   bs.primed = true;
+  pdl_wait();  // the activations come from the previous kernel
   StagedAct4 act = stage4(gemv_smem, a.XQ, a.SQ, a.K, 1, a.K, a.K / 128);
   gemv_block_dispatch(a.K, smats, a.nmats, a.total_rows, act, bs, blockIdx.x, gridDim.x);
   if (threadIdx.x == 0) ring_drain_after_fault(&ring);
@@ -57,5 +62,10 @@ AINFER_REGISTER(Int4GemvA8M2, Int4GemvA8Args, 256, 0, 0, gemv_smem_fn, GEMV_FIEL
 AINFER_REGISTER(Int4GemvA8M4, Int4GemvA8Args, 256, 0, 0, gemv_smem_fn, GEMV_FIELDS);
 AINFER_REGISTER(Int4GemvA8M8, Int4GemvA8Args, 256, 0, 0, gemv_smem_fn, GEMV_FIELDS);
 #undef F
+
+AINFER_EARLY_LAUNCH(Int4GemvA8);
+AINFER_EARLY_LAUNCH(Int4GemvA8M2);
+AINFER_EARLY_LAUNCH(Int4GemvA8M4);
+AINFER_EARLY_LAUNCH(Int4GemvA8M8);
 
 }  // namespace ainfer

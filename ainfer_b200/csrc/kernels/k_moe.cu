@@ -8,6 +8,8 @@ namespace ainfer {
 extern __shared__ __align__(128) unsigned char moe_smem[];
 
 __global__ void __launch_bounds__(256) RouterTopK(const RouterTopKArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ bool is_last;
   __shared__ float sp[1024 + 1];
   router_logits_rows(a, blockIdx.x, gridDim.x);
@@ -29,6 +31,8 @@ constexpr int kMoeStages = 4;
 __host__ __device__ inline uint32_t moe_round128(uint32_t v) { return (v + 127u) & ~127u; }
 
 __global__ void __launch_bounds__(256, 2) ExpertGateUp(const ExpertGateUpArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ SegList lists[2];
   __shared__ float T[kTCap];
   __shared__ Ring ring;
@@ -42,6 +46,8 @@ __global__ void __launch_bounds__(256, 2) ExpertGateUp(const ExpertGateUpArgs a)
 }
 
 __global__ void __launch_bounds__(256, 2) ExpertDownCombine(const ExpertDownCombineArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ SegList lists[2];
   __shared__ float T[kTCap];
   __shared__ Ring ring;
@@ -126,5 +132,9 @@ static uint32_t down_smem_fn(const void *args) {
 AINFER_REGISTER(ExpertDownCombine, ExpertDownCombineArgs, 256, 0, 0, down_smem_fn, F(Experts),
                 F(SelIdx), F(SelW), F(Act), F(Res), F(X), F(Moe), F(slots), F(I), F(H));
 #undef F
+
+AINFER_EARLY_LAUNCH(RouterTopK);
+AINFER_EARLY_LAUNCH(ExpertGateUp);
+AINFER_EARLY_LAUNCH(ExpertDownCombine);
 
 }  // namespace ainfer

@@ -19,6 +19,8 @@ struct EmbedRowArgs {
   int32_t ctrl_stride;  // ints between control blocks of consecutive batch rows
 };
 __global__ void __launch_bounds__(256) EmbedRow(const EmbedRowArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   int row = blockIdx.x;  // one group per batch row
   int tok = a.Ctrl[row * a.ctrl_stride + CTRL_TOKEN];
   tok = tok < 0 ? 0 : (tok >= a.V ? a.V - 1 : tok);
@@ -48,6 +50,8 @@ struct RmsNormQuantArgs {
   float eps;
 };
 __global__ void __launch_bounds__(256) RmsNormQuant(const RmsNormQuantArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ __align__(16) unsigned char norm_smem[];
   float *xs = reinterpret_cast<float *>(norm_smem);  // [N]
   __shared__ double ps[256];
@@ -126,6 +130,8 @@ struct GatedNormQuantArgs {
   float eps;
 };
 __global__ void __launch_bounds__(128) GatedNormQuant(const GatedNormQuantArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int h = blockIdx.x * 4 + warp; h < a.heads; h += gridDim.x * 4) {
     const float *o = a.O + (size_t)h * 128;
@@ -174,6 +180,8 @@ struct QuantRowsArgs {
   int32_t groups;
 };
 __global__ void __launch_bounds__(256) QuantRows(const QuantRowsArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int g = blockIdx.x * 8 + warp; g < a.groups; g += gridDim.x * 8) {
     float4 x = *reinterpret_cast<const float4 *>(a.X + (size_t)g * 128 + lane * 4);
@@ -192,5 +200,10 @@ __global__ void __launch_bounds__(256) QuantRows(const QuantRowsArgs a) {
 #define F(f) AINFER_ARG(QuantRowsArgs, f)
 AINFER_REGISTER(QuantRows, QuantRowsArgs, 256, 8, 0, nullptr, F(X), F(Q8), F(SQ), F(groups));
 #undef F
+
+AINFER_EARLY_LAUNCH(EmbedRow);
+AINFER_EARLY_LAUNCH(RmsNormQuant);
+AINFER_EARLY_LAUNCH(GatedNormQuant);
+AINFER_EARLY_LAUNCH(QuantRows);
 
 }  // namespace ainfer

@@ -14,6 +14,8 @@ struct ArgmaxStage1Args {
   int32_t V;
 };
 __global__ void __launch_bounds__(256) ArgmaxStage1(const ArgmaxStage1Args a) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float sv[8];
   __shared__ int si[8];
   float bv = -INFINITY;
@@ -38,6 +40,8 @@ struct ArgmaxStage2Args {
   int32_t history_cap;
 };
 __global__ void __launch_bounds__(256) ArgmaxStage2(const ArgmaxStage2Args a) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float sv[8];
   __shared__ int si[8];
   float bv = -INFINITY;
@@ -72,6 +76,8 @@ struct ControlAdvanceArgs {
   int32_t n_ids;
 };
 __global__ void ControlAdvance(const ControlAdvanceArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   if (threadIdx.x == 0 && blockIdx.x == 0) {
     int pos = a.Ctrl[CTRL_POS] + 1;
     a.Ctrl[CTRL_POS] = pos;
@@ -83,5 +89,9 @@ __global__ void ControlAdvance(const ControlAdvanceArgs a) {
 #define F(f) AINFER_ARG(ControlAdvanceArgs, f)
 AINFER_REGISTER(ControlAdvance, ControlAdvanceArgs, 32, 0, 0, nullptr, F(Ctrl), F(Ids), F(n_ids));
 #undef F
+
+AINFER_EARLY_LAUNCH(ArgmaxStage1);
+AINFER_EARLY_LAUNCH(ArgmaxStage2);
+AINFER_EARLY_LAUNCH(ControlAdvance);
 
 }  // namespace ainfer

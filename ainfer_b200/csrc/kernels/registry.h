@@ -27,6 +27,9 @@ struct KernelDesc {
   // 1: blocks synchronise with each other, so the launch must be cooperative
   // (all groups co-resident) and the group count may not exceed what fits
   int cooperative;
+  // 1: the kernel orders itself after its predecessor with griddepcontrol.wait, so a
+  // command list may launch it early (programmatic dependency) to overlap its start-up
+  int early_launch = 0;
 };
 
 void register_kernel(const KernelDesc &d);
@@ -43,6 +46,12 @@ int fault_hook_count();
 FaultHook fault_hook_at(int i);
 struct FaultRegistrar {
   explicit FaultRegistrar(FaultHook h) { register_fault_hook(h); }
+};
+
+// Marks an already registered kernel as safe to launch early (see KernelDesc::early_launch).
+void mark_kernel_early_launch(const char *name);
+struct EarlyLaunchMark {
+  explicit EarlyLaunchMark(const char *name) { mark_kernel_early_launch(name); }
 };
 
 struct Registrar {
@@ -66,3 +75,7 @@ struct Registrar {
   static ::ainfer::Registrar NAME##_registrar(::ainfer::KernelDesc{                          \
       #NAME, (const void *)NAME, (uint32_t)sizeof(T), NAME##_fields,                         \
       (int)(sizeof(NAME##_fields) / sizeof(NAME##_fields[0])), THREADS, ITEMS, SMEM, SMEMFN, 1})
+
+// After AINFER_REGISTER(NAME, ...): the kernel calls pdl_wait() before it touches anything a
+// predecessor writes (or that a predecessor still reads and it overwrites).
+#define AINFER_EARLY_LAUNCH(NAME) static ::ainfer::EarlyLaunchMark NAME##_early(#NAME)

@@ -505,7 +505,7 @@ int session_create(DeviceModel *m, int max_ctx, int flags, Session **out, std::s
     if (ainfer_list_create(s->dev, l) != AINFER_OK) { s->err = "list create failed"; rec.status = 1; }
     rec.list = *l;
   };
-  if (!(flags & (SESSION_PER_LAYER_LISTS | SESSION_MULTI_KERNEL))) {
+  if ((flags & (SESSION_PERSISTENT | SESSION_STAGE_CLOCK)) && !(flags & SESSION_PER_LAYER_LISTS)) {
     rec.status = build_mega(s);
   } else if (flags & SESSION_PER_LAYER_LISTS) {
     new_list(&s->embed_list);

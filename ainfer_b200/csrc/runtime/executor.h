@@ -19,8 +19,9 @@ namespace ainfer {
 enum SessionFlags {
   SESSION_DIAG = 1,             // keep per-layer residual stream, routed experts, near-tie gaps
   SESSION_PER_LAYER_LISTS = 2,  // one list per layer + embed + tail, executed and fenced one by one
-  SESSION_MULTI_KERNEL = 4,     // one list per token of ~450 stand-alone launches (default: one persistent launch)
-  SESSION_STAGE_CLOCK = 8       // persistent step: keep a device timestamp after every grid barrier
+  SESSION_MULTI_KERNEL = 4,     // one list per token of ~450 stand-alone launches (the default; flag kept for callers)
+  SESSION_STAGE_CLOCK = 8,      // persistent step (implies it): keep a device timestamp after every grid barrier
+  SESSION_PERSISTENT = 16       // one persistent cooperative launch per token (DecodeStepMega)
 };
 
 struct Session {

@@ -104,12 +104,15 @@ def main(argv=None):
     g.add_argument("--sweep", action="store_true")
     g.add_argument("--groups", type=int, default=0, help="thread groups per launch (default: by shape)")
     g.add_argument("--flush", action="store_true", help="time single launches after an L2 rewrite")
+    ll = sub.add_parser("listlat", help="device time per node of a recorded list of tiny dependent launches")
+    ll.add_argument("--n", type=int, default=400)
     d = sub.add_parser("decode")
     d.add_argument("--model", default="small")
     d.add_argument("--prompt", type=int, default=4)
     d.add_argument("--steps", type=int, default=8)
     d.add_argument("--per-layer", action="store_true")
     d.add_argument("--multi-kernel", action="store_true")
+    d.add_argument("--persistent", action="store_true", help="one cooperative launch per token")
     d.add_argument("--stage-clock", action="store_true", help="print the time between grid barriers of the last token")
     args = ap.parse_args(argv)
     dev = cuda_abi.Device(0)
@@ -118,11 +121,26 @@ def main(argv=None):
                    for m in (1, 2, 4, 8)] if args.sweep else [(args.m, args.n, args.k)])
         for (m, n, k) in shapes:
             print(json.dumps(gemv_once(dev, n, k, m, args.reps, args.flush, args.groups)), flush=True)
+    elif args.cmd == "listlat":
+        ctrl = dev.zeros(16); ids = dev.zeros(64)
+        k = dev.kernel("ControlAdvance")
+        k.set_args(ctrl, ids, 16)
+        cl = dev.new_list()
+        for _ in range(args.n):
+            cl.append(k, 1)
+        cl.close()
+        e0, e1 = dev.event(), dev.event()
+        cl.execute()
+        e0.record(); cl.execute(); e1.record()
+        dev.sync()
+        print(json.dumps({"op": "listlat", "nodes": args.n, "us_per_node": e0.elapsed_ms(e1) * 1000.0 / args.n}), flush=True)
+        cl.destroy()
     else:
         model = runtime.Model(dev, f"synth:{args.model}:seed=0")
         sess = runtime.Session(model, args.prompt + args.steps + 8,
                                runtime.Session.PER_LAYER_LISTS if args.per_layer else
                                (runtime.Session.MULTI_KERNEL if args.multi_kernel else
+                                runtime.Session.PERSISTENT if args.persistent else
                                 (runtime.Session.STAGE_CLOCK if args.stage_clock else 0)))
         prompt = (np.arange(args.prompt, dtype=np.int32) * 7919 + 13) % model.config["vocab"]
         toks, ms = sess.generate(prompt, args.steps, timed=True)

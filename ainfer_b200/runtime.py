@@ -137,6 +137,7 @@ class Session:
     PER_LAYER_LISTS = 2
     MULTI_KERNEL = 4
     STAGE_CLOCK = 8
+    PERSISTENT = 16
 
     def __init__(self, model, max_ctx, flags=0):
         self.model = model

@@ -188,7 +188,7 @@ def run_ours(args):
     t_load = time.time() - t_load
     P = args.prompt_len
     max_ctx = P + WINDOW + 8
-    sess = runtime.Session(model, max_ctx, runtime.Session.MULTI_KERNEL if args.multi_kernel else 0)
+    sess = runtime.Session(model, max_ctx, runtime.Session.PERSISTENT if args.persistent else 0)
     prompt = prompt_ids(cfg["vocab"], P, seed=rank)
 
     def barrier():
@@ -297,7 +297,7 @@ def run_ours(args):
                                f"top-10 + shared, vocab 151936) batch-1 greedy decode after a {P}-token seeded prompt"
                    if args.model == "full" else f"{args.model} model batch-1 greedy decode after a {P}-token prompt",
                    "context": f"{P}..{P + WINDOW}", "kv_cache": "int8 + fp16 per-token-per-head scales",
-                   "mtp": "off", "step": "multi-kernel list" if args.multi_kernel else "one persistent cooperative launch", "parallelism": "replicas" if world > 1 else "single GPU",
+                   "mtp": "off", "step": "one persistent cooperative launch" if args.persistent else "one recorded list of stand-alone launches chained by programmatic dependencies", "parallelism": "replicas" if world > 1 else "single GPU",
                    "l2": "inputs larger than L2: about 2.1 GB of weights and state streamed per step",
                    "launches_per_token": sess.launches_per_token()},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 16, "d2h_bytes_per_step": 4,
@@ -325,7 +325,7 @@ def main():
     ap.add_argument("--cpu-steps", type=int, default=4)
     ap.add_argument("--cpu-budget", type=float, default=150.0, help="seconds of timed CPU work in the reference arm")
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--multi-kernel", action="store_true", help="stand-alone launches instead of the persistent step")
+    ap.add_argument("--persistent", action="store_true", help="one persistent cooperative launch per token instead of the recorded list")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

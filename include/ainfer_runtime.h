@@ -67,10 +67,11 @@ int ainfer_model_bytes(ainfer_model_t m, uint64_t *payload_bytes, uint64_t *scal
 enum {
   AINFER_SESSION_DIAG = 1,            /* per-layer residual dump (AINFER_DUMP0), routed experts, near-tie gaps */
   AINFER_SESSION_PER_LAYER_LISTS = 2, /* one list per layer, fenced one by one, as the reference executes */
-  AINFER_SESSION_MULTI_KERNEL = 4     /* one list per token of stand-alone launches; default is ONE persistent
-                                         cooperative launch per token (DecodeStepMega) */
-  , AINFER_SESSION_STAGE_CLOCK = 8    /* persistent step: device timestamp after every grid barrier, read
-                                         back through the "stage_stamps" buffer (u64 ns, entry 0 = start) */
+  AINFER_SESSION_MULTI_KERNEL = 4,    /* one recorded list per token of stand-alone launches chained by
+                                         programmatic dependencies: the default (flag kept for callers) */
+  AINFER_SESSION_STAGE_CLOCK = 8,     /* persistent step (implies it): device timestamp after every grid
+                                         barrier, read back through the "stage_stamps" buffer (u64 ns) */
+  AINFER_SESSION_PERSISTENT = 16      /* ONE persistent cooperative launch per token (DecodeStepMega) */
 };
 int ainfer_session_create(ainfer_model_t m, int max_ctx, int flags, ainfer_session_t *out);
 int ainfer_session_destroy(ainfer_session_t s);

@@ -86,7 +86,7 @@ def test_device_fill_equals_file_upload(dev, mini_file):
     a.close(); b.close()
 
 
-@pytest.mark.parametrize("flags", [0, 4], ids=["persistent", "multi_kernel"])
+@pytest.mark.parametrize("flags", [16, 4], ids=["persistent", "multi_kernel"])
 def test_config1_mini_one_step_at_511_prior_tokens(dev, mini_file, flags):
     """BASELINE config 1: mini model, one decode step at batch 1, seed 0, 511 cached tokens."""
     from ainfer_b200 import runtime
@@ -114,7 +114,7 @@ def test_config1_mini_one_step_at_511_prior_tokens(dev, mini_file, flags):
     sess.close(); model.close(); osess.close(); om.close()
 
 
-@pytest.mark.parametrize("flags", [0, 4], ids=["persistent", "multi_kernel"])
+@pytest.mark.parametrize("flags", [16, 4], ids=["persistent", "multi_kernel"])
 def test_mini_greedy_256_steps_identical(dev, mini_file, flags):
     """Greedy tokens identical over 256 decode steps after a seeded 16-token prompt."""
     from ainfer_b200 import runtime
@@ -144,7 +144,7 @@ def test_tiny_fused_list_equals_per_layer_lists(dev, tiny_file):
     from ainfer_b200 import runtime
     model = runtime.Model(dev, tiny_file)
     prompt = np.array([5, 77, 300, 12], np.int32)
-    a = runtime.Session(model, 64)                                    # one persistent launch per token
+    a = runtime.Session(model, 64, runtime.Session.PERSISTENT)        # one persistent launch per token
     b = runtime.Session(model, 64, runtime.Session.PER_LAYER_LISTS)
     c = runtime.Session(model, 64, runtime.Session.MULTI_KERNEL)      # one list of stand-alone launches
     ta, tb, tc = a.generate(prompt, 24), b.generate(prompt, 24), c.generate(prompt, 24)
