@@ -17,6 +17,12 @@ struct Recorder {
   Session *s;
   ainfer_list_t list;
   int status = 0;
+  // Residual stream and control block the recorded layer works on: the trunk's by default,
+  // the MTP head's own when its list is recorded.
+  float *x_override = nullptr;
+  int32_t *ctrl_override = nullptr;
+  float *X() const { return x_override ? x_override : s->X; }
+  int32_t *ctrl() const { return ctrl_override ? ctrl_override : s->ctrl; }
 
   ainfer_kernel_t kernel(const char *name) {
     auto it = s->kernels.find(name);
@@ -160,7 +166,7 @@ void record_moe(Recorder &r, int L, const std::string &p, const float *post_norm
            (const float *)s->SQ, s->Act, (int32_t)slots, (int32_t)I, (int32_t)H, (int32_t)0);
   uint32_t g_dn = (uint32_t)std::min<long>(stream_groups((long)H * slots, I, s->sm_count), (H + 3) / 4);
   r.launch("ExpertDownCombine", g_dn, tab, (const int32_t *)s->SelIdx, (const float *)s->SelW,
-           (const float *)s->Act, (const float *)s->Tmp, s->X, (float *)nullptr, (int32_t)slots,
+           (const float *)s->Act, (const float *)s->Tmp, r.X(), (float *)nullptr, (int32_t)slots,
            (int32_t)I, (int32_t)H);
   if (s->flags & SESSION_DIAG) {
     if (L < c.layers) {
@@ -210,7 +216,7 @@ void record_attn_layer(Recorder &r, int L, const std::string &p) {
   const int H = c.hidden, nQ = c.q_heads, nKV = c.kv_heads, D = c.head_dim;
   const int slot = m->slot[L];
   const float eps = (float)c.rms_eps;
-  r.launch("RmsNormQuant", 1, (const float *)s->X, (const float *)nullptr, (float *)nullptr,
+  r.launch("RmsNormQuant", 1, (const float *)r.X(), (const float *)nullptr, (float *)nullptr,
            (const float *)(m->in_norm + (size_t)L * H), (float *)nullptr, s->Q8, s->SQ, (int32_t)H, eps);
   record_gemv(r,
               {{m->tensor(p + "self_attn.q_proj.weight"), s->Q16, EPI_STORE, nullptr, nullptr, nullptr},
@@ -223,16 +229,16 @@ void record_attn_layer(Recorder &r, int L, const std::string &p) {
   r.launch("AttnPrep", (uint32_t)((nQ + 2 * nKV + 7) / 8), (const float *)s->Q16, (const float *)s->K16,
            (const float *)s->V16, (const float *)(m->q_norm + (size_t)slot * D),
            (const float *)(m->k_norm + (size_t)slot * D), (const float *)m->rope_cos,
-           (const float *)m->rope_sin, (const int32_t *)s->ctrl, s->Qn, Kc, Vc, Ks, Vs, (int32_t)nQ,
+           (const float *)m->rope_sin, (const int32_t *)r.ctrl(), s->Qn, Kc, Vc, Ks, Vs, (int32_t)nQ,
            (int32_t)nKV, (int32_t)c.rotary_dim, (int32_t)s->max_ctx, eps);
   uint32_t g_split = (uint32_t)std::min(s->max_chunks * nKV, s->sm_count * 8);
   r.launch("AttnSplit", g_split, (const float *)s->Qn, (const int8_t *)Kc, (const int8_t *)Vc,
-           (const uint16_t *)Ks, (const uint16_t *)Vs, (const int32_t *)s->ctrl, s->Pm, s->Pse, s->Pacc,
+           (const uint16_t *)Ks, (const uint16_t *)Vs, (const int32_t *)r.ctrl(), s->Pm, s->Pse, s->Pacc,
            (int32_t)nQ, (int32_t)nKV, (int32_t)s->max_ctx, (int32_t)s->max_chunks);
   r.launch("AttnCombine", (uint32_t)nQ, (const float *)s->Pm, (const float *)s->Pse,
-           (const float *)s->Pacc, (const float *)s->Q16, (const int32_t *)s->ctrl, s->Q8, s->SQ,
+           (const float *)s->Pacc, (const float *)s->Q16, (const int32_t *)r.ctrl(), s->Q8, s->SQ,
            (float *)nullptr, (int32_t)nQ, (int32_t)s->max_ctx, (int32_t)s->max_chunks);
-  record_gemv(r, {{m->tensor(p + "self_attn.o_proj.weight"), s->Tmp, EPI_RESADD, s->X, nullptr, nullptr}},
+  record_gemv(r, {{m->tensor(p + "self_attn.o_proj.weight"), s->Tmp, EPI_RESADD, r.X(), nullptr, nullptr}},
               nQ * D, s->Q8, s->SQ);
   record_moe(r, L, p, m->post_norm + (size_t)L * H);
 }
@@ -264,6 +270,43 @@ void record_tail(Recorder &r, bool advance) {
            (int32_t)c.vocab);
   r.launch("ArgmaxStage2", 1, (const float *)s->PV, (const int32_t *)s->PI, s->out_tok, s->ctrl,
            s->history, (int32_t)s->argmax_parts, (int32_t)(advance ? 1 : 0), (int32_t)s->max_ctx);
+}
+
+// MTP head (tools/t72/mtp_accept.py:11-16,142-151): x = fc . quant([rms1w(embed(next)) ; rms1w(h)]),
+// one full-attention decoder layer with its own KV cache and MoE, mtp.norm, shared lm_head, argmax.
+// Works on its own residual buffer (Xm), control block (ctrl_m) and logits (LogitsM); the hidden
+// input h is Hm, and the layer's output is copied back into Hm so that drafts can be chained.
+void record_mtp(Recorder &r) {
+  Session *s = r.s;
+  DeviceModel *m = s->m;
+  const ModelConfig &c = m->cfg;
+  const int H = c.hidden, L = c.layers;
+  const float eps = (float)c.rms_eps;
+  DeviceTensor emb = m->tensor("model.language_model.embed_tokens.weight");
+  if (!emb.entry) { s->err = "missing model.language_model.embed_tokens.weight"; r.status = 1; return; }
+  r.x_override = s->Xm;
+  r.ctrl_override = s->ctrl_m;
+  r.launch("EmbedRow", 1, s->Xm, (const uint16_t *)emb.data, (const int32_t *)s->ctrl_m, (int32_t)H,
+           (int32_t)c.vocab, (int32_t)4);
+  r.launch("RmsNormQuant", 1, (const float *)s->Xm, (const float *)nullptr, (float *)nullptr,
+           (const float *)m->mtp_norms, s->Cat, s->Q8, s->SQ, (int32_t)H, eps);
+  r.launch("RmsNormQuant", 1, (const float *)s->Hm, (const float *)nullptr, (float *)nullptr,
+           (const float *)(m->mtp_norms + H), s->Cat + H, s->Q8, s->SQ, (int32_t)H, eps);
+  r.launch("QuantRows", (uint32_t)((2 * H / 128 + 7) / 8), (const float *)s->Cat, s->Q8, s->SQ,
+           (int32_t)(2 * H / 128));
+  record_gemv(r, {{m->tensor("mtp.fc.weight"), s->Xm, EPI_STORE, nullptr, nullptr, nullptr}}, 2 * H, s->Q8, s->SQ);
+  record_attn_layer(r, L, "mtp.layers.0.");
+  r.launch("RmsNormQuant", 1, (const float *)s->Xm, (const float *)nullptr, (float *)nullptr,
+           (const float *)(m->mtp_norms + 2 * (size_t)H), (float *)nullptr, s->Q8, s->SQ, (int32_t)H, eps);
+  record_gemv(r, {{m->tensor("lm_head.weight"), s->LogitsM, EPI_STORE, nullptr, nullptr, nullptr}}, H, s->Q8,
+              s->SQ);
+  r.launch("ArgmaxStage1", (uint32_t)s->argmax_parts, (const float *)s->LogitsM, s->PV, s->PI, (int32_t)c.vocab);
+  // advance = 0: the draft token goes to out_tok_m only; the host owns ctrl_m
+  r.launch("ArgmaxStage2", 1, (const float *)s->PV, (const int32_t *)s->PI, s->out_tok_m, s->ctrl_m,
+           (int32_t *)nullptr, (int32_t)s->argmax_parts, (int32_t)0, (int32_t)s->max_ctx);
+  r.copy(s->Hm, s->Xm, (size_t)H * 4);
+  r.x_override = nullptr;
+  r.ctrl_override = nullptr;
 }
 
 GemvMat make_mat(Session *s, int &status, const std::string &name, int K, float *Y, int epi,
@@ -481,6 +524,14 @@ int session_create(DeviceModel *m, int max_ctx, int flags, Session **out, std::s
   r |= salloc(s, 1, &s->NearGap);
   r |= salloc(s, (size_t)(c.top_k + 1) * c.expert_inter, &s->Act);
   r |= salloc(s, (size_t)c.vocab, &s->Logits);
+  if (c.mtp_layers) {
+    r |= salloc(s, (size_t)H, &s->Xm);
+    r |= salloc(s, (size_t)H, &s->Hm);
+    r |= salloc(s, (size_t)2 * H, &s->Cat);
+    r |= salloc(s, (size_t)c.vocab, &s->LogitsM);
+    r |= salloc(s, 4, &s->ctrl_m);
+    r |= salloc(s, 1, &s->out_tok_m);
+  }
   r |= salloc(s, (size_t)s->argmax_parts, &s->PV);
   r |= salloc(s, (size_t)s->argmax_parts, &s->PI);
   if (flags & SESSION_DIAG) {
@@ -545,6 +596,13 @@ int session_create(DeviceModel *m, int max_ctx, int flags, Session **out, std::s
     }
     s->launches_per_token = per_token;
   }
+  if (!rec.status && c.mtp_layers) {
+    const uint64_t per_token = s->launches_per_token;
+    new_list(&s->mtp_list);
+    record_mtp(rec);
+    if (!rec.status) rec.status = close_list(s, s->mtp_list);
+    s->launches_per_token = per_token;
+  }
   if (rec.status) return fail(rec.status);
   if (!s->gemv_tables_host.empty() &&
       ainfer_memcpy_h2d(s->dev, s->gemv_tables, s->gemv_tables_host.data(), s->gemv_tables_host.size()) != AINFER_OK) {
@@ -559,7 +617,7 @@ void session_destroy(Session *s) {
   if (!s) return;
   ainfer_sync(s->dev, UINT64_MAX);
   for (auto l : s->layer_lists) ainfer_list_destroy(l);
-  for (ainfer_list_t l : {s->gen_list, s->body_list, s->embed_list, s->tail_list, s->advance_list})
+  for (ainfer_list_t l : {s->gen_list, s->body_list, s->embed_list, s->tail_list, s->advance_list, s->mtp_list})
     if (l) ainfer_list_destroy(l);
   for (auto &kv : s->kernels) ainfer_kernel_release(kv.second);
   for (void *p : s->owned) ainfer_mem_free(s->dev, p);
@@ -630,6 +688,69 @@ int session_step(Session *s, int token, int pos, int *out_token) {
   S_CHECK(ainfer_memcpy_d2h(s->dev, s->host_tok, s->out_tok, 4));
   if (out_token) *out_token = s->host_tok[0];
   return check_mega_error(s);
+}
+
+int session_mtp_draft(Session *s, int next_token, int pos, int from_trunk, int *draft_token) {
+  if (!s->mtp_list) { s->err = "usage: the model has no MTP head"; return 2; }
+  if (pos < 0 || pos >= s->max_ctx) {
+    s->err = "context overflow: pos " + std::to_string(pos) + " >= MAXCTX " + std::to_string(s->max_ctx);
+    return 3;
+  }
+  if (from_trunk) S_CHECK(ainfer_memcpy_d2d(s->dev, s->Hm, s->X, (size_t)s->m->cfg.hidden * 4));
+  ainfer_control c{next_token, pos, pos + 1, -1};
+  S_CHECK(ainfer_control_write(s->dev, s->ctrl_m, &c));
+  S_CHECK(ainfer_list_execute(s->mtp_list));
+  S_CHECK(ainfer_memcpy_d2h(s->dev, s->host_tok, s->out_tok_m, 4));
+  if (draft_token) *draft_token = s->host_tok[0];
+  return 0;
+}
+
+int session_generate_mtp(Session *s, const int *prompt, int P, int G, int start_pos, int draft_k,
+                         int *out_tokens, int *stats) {
+  if (!s->mtp_list) { s->err = "usage: the model has no MTP head"; return 2; }
+  if (P < 1 || G < 1 || draft_k < 1 || draft_k > 8) { s->err = "usage: need a prompt, G >= 1 and 1 <= draft_k <= 8"; return 2; }
+  if (start_pos < 0 || start_pos + P + G - 1 + draft_k > s->max_ctx) {
+    s->err = "context overflow: pos " + std::to_string(start_pos + P + G - 1 + draft_k) + " >= MAXCTX " +
+             std::to_string(s->max_ctx);
+    return 3;
+  }
+  int rounds = 0, drafted = 0, accepted = 0;
+  // prompt: every step but the last without tail
+  int y = -1;
+  for (int i = 0; i < P; ++i) {
+    int r = session_step(s, prompt[i], start_pos + i, &y);  // tail only matters for the last one
+    if (r) return r;
+  }
+  int p = start_pos + P - 1;  // position of the trunk step that produced y
+  int g = 0;
+  out_tokens[g++] = y;
+  while (g < G) {
+    // draft chain from (y, h_p)
+    int drafts[8];
+    int inp = y;
+    const int k = std::min(draft_k, G - g);
+    for (int i = 0; i < k; ++i) {
+      int r = session_mtp_draft(s, inp, p + 1 + i, i == 0, &drafts[i]);
+      if (r) return r;
+      inp = drafts[i];
+    }
+    ++rounds;
+    drafted += k;
+    // verify one by one with trunk steps; stop the round at the first miss
+    for (int i = 0; i < k && g < G; ++i) {
+      int y2 = -1;
+      int r = session_step(s, y, p + 1, &y2);
+      if (r) return r;
+      ++p;
+      const bool hit = y2 == drafts[i];
+      y = y2;
+      out_tokens[g++] = y;
+      if (!hit) break;
+      ++accepted;
+    }
+  }
+  if (stats) { stats[0] = rounds; stats[1] = drafted; stats[2] = accepted; }
+  return 0;
 }
 
 int session_generate(Session *s, const int *prompt, int P, int G, int start_pos, int *out_tokens,

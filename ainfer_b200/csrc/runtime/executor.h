@@ -52,6 +52,11 @@ struct Session {
   float *RLogits = nullptr; uint32_t *Counter = nullptr; int32_t *SelIdx = nullptr;
   float *SelW = nullptr, *NearGap = nullptr, *Act = nullptr;
   float *Logits = nullptr, *PV = nullptr; int32_t *PI = nullptr;
+  // MTP head (only when the model has one): its residual stream, chained hidden input,
+  // [embedding ; hidden] vector, logits, control block and draft token
+  float *Xm = nullptr, *Hm = nullptr, *Cat = nullptr, *LogitsM = nullptr;
+  int32_t *ctrl_m = nullptr, *out_tok_m = nullptr;
+  ainfer_list_t mtp_list = nullptr;
   // diagnostics
   float *layer_out = nullptr;   // [layers][H]
   int32_t *routed = nullptr;    // [layers][top_k+1]
@@ -94,6 +99,15 @@ int session_step(Session *s, int token, int pos, int *out_token);
 // prompt token, decode_l0.cpp:771), then G generated tokens; control advances
 // on the device, tokens are read back once at the end. elapsed_ms (optional)
 // receives the device time of the G generation steps.
+// One draft of the MTP head: input token `next_token` at position `pos`, hidden input taken
+// from the trunk's final residual of the last step (from_trunk != 0) or chained from the
+// previous draft. Fails with code 2 when the model has no MTP head.
+int session_mtp_draft(Session *s, int next_token, int pos, int from_trunk, int *draft_token);
+// Greedy generation with `draft_k` MTP drafts per round, verified one by one by trunk steps
+// (acceptance is draft == trunk argmax, tools/t72/mtp_accept.py:142-151). The emitted tokens
+// are exactly session_generate's. stats = {rounds, drafted, accepted}.
+int session_generate_mtp(Session *s, const int *prompt, int P, int G, int start_pos, int draft_k,
+                         int *out_tokens, int *stats);
 int session_generate(Session *s, const int *prompt, int P, int G, int start_pos, int *out_tokens,
                      float *gen_elapsed_ms);
 

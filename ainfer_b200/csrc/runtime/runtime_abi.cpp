@@ -137,6 +137,7 @@ int ainfer_session_buffer(ainfer_session_t h, const char *which, void **dptr, ui
   else if (w == "Vs") { *dptr = s->Vs; *bytes = n_kv * 2; }
   else if (w == "logits") { *dptr = s->Logits; *bytes = (uint64_t)c.vocab * 4; }
   else if (w == "x") { *dptr = s->X; *bytes = (uint64_t)c.hidden * 4; }
+  else if (w == "mtp_hidden") { *dptr = s->Hm; *bytes = s->Hm ? (uint64_t)c.hidden * 4 : 0; }
   else if (w == "ctrl") { *dptr = s->ctrl; *bytes = 16; }
   else if (w == "history") { *dptr = s->history; *bytes = (uint64_t)s->max_ctx * 4; }
   else if (w == "layer_out") { *dptr = s->layer_out; *bytes = s->layer_out ? (uint64_t)c.layers * c.hidden * 4 : 0; }
@@ -162,6 +163,24 @@ int ainfer_session_logits(ainfer_session_t s, float *host_out) {
   if (ainfer_memcpy_d2h(s->s->dev, host_out, s->s->Logits, (size_t)s->s->m->cfg.vocab * 4) != AINFER_OK)
     return set_err(1, ainfer_last_error(s->s->dev));
   return 0;
+}
+int ainfer_session_mtp_draft(ainfer_session_t s, int next_token, int pos, int from_trunk, int *draft_token) {
+  if (!s) return 2;
+  int r = session_mtp_draft(s->s, next_token, pos, from_trunk, draft_token);
+  return set_err(r, s->s->err);
+}
+int ainfer_session_mtp_logits(ainfer_session_t s, float *host_out) {
+  if (!s || !host_out) return 2;
+  if (!s->s->LogitsM) return set_err(2, "usage: the model has no MTP head");
+  if (ainfer_memcpy_d2h(s->s->dev, host_out, s->s->LogitsM, (size_t)s->s->m->cfg.vocab * 4) != AINFER_OK)
+    return set_err(1, ainfer_last_error(s->s->dev));
+  return 0;
+}
+int ainfer_session_generate_mtp(ainfer_session_t s, const int *prompt, int P, int G, int start_pos, int draft_k,
+                                int *out_tokens, int *stats) {
+  if (!s || !prompt || !out_tokens) return set_err(2, "usage: null argument");
+  int r = session_generate_mtp(s->s, prompt, P, G, start_pos, draft_k, out_tokens, stats);
+  return set_err(r, s->s->err);
 }
 int ainfer_session_launches_per_token(ainfer_session_t s, uint64_t *launches) {
   if (!s || !launches) return 2;

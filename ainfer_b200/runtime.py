@@ -44,6 +44,9 @@ SIGNATURES = {
     "ainfer_session_generate": (_i, [_vp, C.POINTER(_i), _i, _i, _i, C.POINTER(_i), C.POINTER(C.c_float)]),
     "ainfer_session_logits": (_i, [_vp, _vp]),
     "ainfer_session_launches_per_token": (_i, [_vp, C.POINTER(_u64)]),
+    "ainfer_session_mtp_draft": (_i, [_vp, _i, _i, _i, C.POINTER(_i)]),
+    "ainfer_session_mtp_logits": (_i, [_vp, _vp]),
+    "ainfer_session_generate_mtp": (_i, [_vp, _vp, _i, _i, _i, _i, _vp, _vp]),
     "ainfer_apply_rep_penalty": (_i, [_vp, _i, _vp, _i, C.c_float]),
     "ainfer_sample_token": (_i, [_vp, _i, C.POINTER(SampleParams), C.POINTER(_u64), _vp]),
 }
@@ -184,6 +187,26 @@ class Session:
         out = np.zeros(V, np.float32)
         _check(load().ainfer_session_logits(self.h, out.ctypes.data))
         return out
+
+    def mtp_draft(self, next_token, pos, from_trunk=True):
+        """One draft of the MTP head (hidden input: the trunk's last residual, or chained)."""
+        d = _i()
+        _check(load().ainfer_session_mtp_draft(self.h, int(next_token), int(pos), 1 if from_trunk else 0, C.byref(d)))
+        return d.value
+
+    def mtp_logits(self):
+        out = np.zeros(self.model.config["vocab"], np.float32)
+        _check(load().ainfer_session_mtp_logits(self.h, out.ctypes.data))
+        return out
+
+    def generate_mtp(self, prompt, n_gen, draft_k=3, start_pos=0):
+        """Greedy generation with draft_k MTP drafts per round. Returns (tokens, {rounds, drafted, accepted})."""
+        prompt = np.ascontiguousarray(prompt, dtype=np.int32)
+        out = np.zeros(n_gen, np.int32)
+        st = np.zeros(3, np.int32)
+        _check(load().ainfer_session_generate_mtp(self.h, prompt.ctypes.data, len(prompt), n_gen, start_pos, draft_k,
+                                                  out.ctypes.data, st.ctypes.data))
+        return out, {"rounds": int(st[0]), "drafted": int(st[1]), "accepted": int(st[2])}
 
     def launches_per_token(self):
         n = C.c_uint64()

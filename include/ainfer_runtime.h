@@ -86,6 +86,20 @@ int ainfer_session_step(ainfer_session_t s, int token, int pos, int *out_token);
  * block, one readback at the end. gen_ms (optional): device time of the G steps. */
 int ainfer_session_generate(ainfer_session_t s, const int *prompt, int P, int G, int start_pos,
                             int *out_tokens, float *gen_ms);
+/* ---- MTP head (multi-token prediction; dataflow of tools/t72/mtp_accept.py:11-16,142-151) ----
+ * x = fc . quant([rms1w(embed(next_token)) ; rms1w(h)]) -> one full-attention decoder layer with
+ * its own KV cache and MoE -> mtp.norm -> shared lm_head -> argmax. h is the trunk's final
+ * residual of the last ainfer_session_step (from_trunk != 0) or the MTP layer's own previous
+ * output (chained drafts). The reference only measures acceptance offline and has no
+ * draft/verify loop; the loop here is this library's. All three return 2 when the model has
+ * no MTP head. */
+int ainfer_session_mtp_draft(ainfer_session_t s, int next_token, int pos, int from_trunk, int *draft_token);
+int ainfer_session_mtp_logits(ainfer_session_t s, float *host_out);
+/* Greedy generation of G tokens with draft_k (1..8) chained drafts per round, each verified by a
+ * trunk step (accept iff draft == trunk argmax; a round ends at the first miss). out_tokens are
+ * exactly ainfer_session_generate's. stats[3] = {rounds, drafted, accepted}. */
+int ainfer_session_generate_mtp(ainfer_session_t s, const int *prompt, int P, int G, int start_pos, int draft_k,
+                                int *out_tokens, int *stats);
 /* Copies the last step's logits to the host (V floats). */
 int ainfer_session_logits(ainfer_session_t s, float *host_out);
 int ainfer_session_launches_per_token(ainfer_session_t s, uint64_t *launches);
