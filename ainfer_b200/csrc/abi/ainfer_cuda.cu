@@ -9,6 +9,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <map>
 #include <mutex>
 #include <string>
 #include <vector>
@@ -311,6 +312,20 @@ int ainfer_kernel_set_arg(ainfer_kernel_t k, uint32_t index, size_t size, const 
   return AINFER_OK;
 }
 
+// The dynamic shared-memory limit is a property of the function, not of one launch: only ever
+// raise it, so that a recorded launch with a larger request stays valid after a later, smaller
+// one was recorded.
+static cudaError_t raise_smem_limit(const void *fn, uint32_t smem) {
+  static std::mutex mu;
+  static std::map<const void *, uint32_t> raised;
+  std::lock_guard<std::mutex> lock(mu);
+  uint32_t &cur = raised[fn];
+  if (smem <= cur) return cudaSuccess;
+  cudaError_t e = cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e == cudaSuccess) cur = smem;
+  return e;
+}
+
 static int check_launch(ainfer_kernel_t k, uint32_t groups, uint32_t *smem) {
   for (int i = 0; i < k->desc->nfields; ++i)
     if (!k->set[i]) {
@@ -329,8 +344,7 @@ static int check_launch(ainfer_kernel_t k, uint32_t groups, uint32_t *smem) {
     k->carveout_set = true;
   }
   if (*smem > 16 * 1024) {  // static + dynamic may pass 48 KB: opt in early
-    cudaError_t e = cudaFuncSetAttribute(k->desc->fn, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)*smem);
+    cudaError_t e = raise_smem_limit(k->desc->fn, *smem);
     if (e != cudaSuccess) {
       cudaGetLastError();
       return fail(k->dev, AINFER_ERR_INVALID, std::string("shared memory request too large for ") + k->desc->name);
@@ -358,7 +372,7 @@ int ainfer_kernel_max_groups(ainfer_kernel_t k, uint32_t *groups) {
   if (!k || !groups) return AINFER_ERR_INVALID;
   uint32_t smem = k->desc->smem_fn ? k->desc->smem_fn(k->args.data()) : k->desc->smem_bytes;
   if (smem > 16 * 1024) {
-    if (cudaFuncSetAttribute(k->desc->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    if (raise_smem_limit(k->desc->fn, smem) != cudaSuccess) {
       cudaGetLastError();
       return fail(k->dev, AINFER_ERR_INVALID, std::string("shared memory request too large for ") + k->desc->name);
     }
