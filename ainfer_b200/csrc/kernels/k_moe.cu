@@ -60,6 +60,28 @@ __global__ void __launch_bounds__(256, 2) ExpertDownCombine(const ExpertDownComb
   if (threadIdx.x == 0) ring_drain_after_fault(&ring);
 }
 
+// ---- CombineSlots: the combine step of ExpertDownCombine on its own ----
+// X[n] = Res[n] + sum over slots s, in slot order, of W[s] * Y[s][n]: the same
+// additions in the same order as ExpertDownCombine performs on its row sums.
+// Used by the expert-parallel path, where the per-slot down-projection outputs
+// Y come back from the ranks that own the experts.
+struct CombineSlotsArgs {
+  const float *Y;    // [slots][H] unweighted down-projection outputs
+  const float *W;    // [slots] routing weights (rank order, shared expert last)
+  const float *Res;  // [H]
+  float *X;          // [H]
+  int32_t slots, H;
+};
+__global__ void __launch_bounds__(256) CombineSlots(const CombineSlotsArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (int n = blockIdx.x * 256 + threadIdx.x; n < a.H; n += gridDim.x * 256) {
+    float acc = 0.0f;
+    for (int s = 0; s < a.slots; ++s) acc = acc + a.W[s] * a.Y[(size_t)s * a.H + n];
+    a.X[n] = a.Res[n] + acc;
+  }
+}
+
 // ---- RouterTopK with its scratch in a fixed device array (no allocation) ----
 // Same work as RouterTopK, but the router logits and the block counter live in
 // this file-scope array instead of caller-provided buffers. The array belongs to
@@ -110,6 +132,11 @@ cudaError_t router_static_launch(cudaStream_t stream, void *scratch, const void 
   RouterTopKStatic<<<groups, 256, 0, stream>>>(a, static_cast<unsigned char *>(scratch));
   return cudaGetLastError();
 }
+
+#define F(f) AINFER_ARG(CombineSlotsArgs, f)
+AINFER_REGISTER(CombineSlots, CombineSlotsArgs, 256, 256, 0, nullptr, F(Y), F(W), F(Res), F(X), F(slots), F(H));
+#undef F
+AINFER_EARLY_LAUNCH(CombineSlots);
 
 #define F(f) AINFER_ARG(RouterTopKArgs, f)
 AINFER_REGISTER(RouterTopK, RouterTopKArgs, 256, 8, 0, nullptr, F(Wr), F(Wsg), F(Hn), F(Logits),
