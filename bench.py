@@ -179,7 +179,10 @@ def run_ours(args):
         import torch
         import torch.distributed as dist
         torch.cuda.set_device(local_rank)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        import datetime
+        # a short timeout: a rank that leaves early must end the others' next collective, not hang them
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank),
+                                timeout=datetime.timedelta(seconds=180))
     from ainfer_b200 import cuda_abi, runtime
     dev = cuda_abi.Device(local_rank)
     t_load = time.time()
@@ -230,7 +233,33 @@ def run_ours(args):
         t = torch.tensor([gen_ms, t_e2e], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         gen_ms, t_e2e = float(t[0]), float(t[1])
+    # Expert-parallel MoE block over all ranks (only when there is more than one): a decode batch of
+    # 64 token rows through layer 0's MoE with experts sharded E/N per rank, NCCL all-to-all for
+    # dispatch and combine. Functional probe (host-staged exchange, one expert item at a time):
+    # it reports what moved and that every replica ended up with the same rows, not a speed.
+    ep_probe = None
+    if world > 1:
+        try:
+            import torch
+            from ainfer_b200 import ep
+            be = ep.GpuMoeBackend(dev, model, layer=0)
+            blk = ep.EpMoeBlock(be, ep.TorchComm(device=torch.device("cuda", local_rank)))
+            rows = np.random.default_rng(1234).standard_normal((64, cfg["hidden"])).astype(np.float32)
+            out = blk.forward(rows)
+            chk = torch.tensor([float(np.abs(out).sum())], dtype=torch.float64, device=torch.device("cuda", local_rank))
+            lo_, hi_ = chk.clone(), chk.clone()
+            dist.all_reduce(lo_, op=dist.ReduceOp.MIN); dist.all_reduce(hi_, op=dist.ReduceOp.MAX)
+            st = torch.tensor([blk.stats["items_computed"], blk.stats["dispatch_bytes"], blk.stats["combine_bytes"]],
+                              dtype=torch.int64, device=torch.device("cuda", local_rank))
+            dist.all_reduce(st)
+            ep_probe = {"ranks": world, "batch": 64, "layer": 0, "experts_per_rank": cfg["experts"] // world,
+                        "items": int(st[0]), "dispatch_bytes": int(st[1]), "combine_bytes": int(st[2]),
+                        "replicas_identical": bool(lo_.item() == hi_.item()), "collective": "nccl all_to_all_single"}
+        except Exception as e:
+            ep_probe = {"error": str(e)[:200]}
     if rank != 0:
+        model.close(); dev.close()
+        dist.destroy_process_group()
         return 0
     value = world * args.steps / (gen_ms / 1000.0)
     e2e_value = world * n_e2e / t_e2e
@@ -322,7 +351,7 @@ def run_ours(args):
                 "steps": n_e2e, "api": "ainfer_session_step (control write + replay + token readback)"},
         "gpu_launches": int(sess.launches_per_token() * args.steps),
         "clocks": clk, "roofline": roof, "token_roofline": token_roof, "gemv_sweep": sweep,
-        "cpu_baseline": cpu, "parity": parity, "mtp_probe": mtp,
+        "cpu_baseline": cpu, "parity": parity, "mtp_probe": mtp, "ep_probe": ep_probe,
         "timing": {"model_fill_s": t_load, "prompt_s": t_prompt, "timed_wall_s": t_wall, "first_tokens": [int(t) for t in toks0[:8]]},
     }
     print(json.dumps(line))
