@@ -6,6 +6,7 @@
       more than 256 MB of distinct weight buffers; --flush: single launches, each after a
       256 MB rewrite). --sweep runs the operator sweep shapes
       M in {1,2,4,8} x (N,K) in {(512,2048),(4096,2048),(8192,2048),(151936,2048),(2048,512)}.
+      --a16 runs the bf16-activation operator Int4GemmA16 instead (sweep: M in {1,2,4,8,64}).
   python -m ainfer_b200.opbench decode [--model small] [--prompt 4] [--steps 8]
       A short greedy decode of a synthetic model preset through the runtime
       (small enough to sit under a profiler).
@@ -93,6 +94,46 @@ def gemv_once(dev, N, K, M=1, reps=20, flush=False, groups=None):
             "flops": 2.0 * M * N * K, "tflops": 2.0 * M * N * K / ms / 1e9}
 
 
+def gemm_a16_once(dev, N, K, M, reps=20):
+    """Int4GemmA16 (bf16 activations, 1 <= M <= 64) on one shape: recorded list rotating over enough
+    weight buffers to exceed L2, timed as a whole on the device."""
+    wbytes = N * K // 2 + N * K // 128 * 2
+    nbuf = max(1, min(64, -(-(256 << 20) // wbytes)))
+    rng = np.random.default_rng(0)
+    xb = rng.standard_normal((M, K)).astype(np.float32).view(np.uint32)
+    xb = ((xb + 0x7FFF + ((xb >> 16) & 1)) >> 16).astype(np.uint16)
+    dX = dev.upload(xb)
+    kernels, bufs = [], []
+    for b in range(nbuf):
+        dP, dS, dY = dev.alloc(N * K // 2), dev.alloc(N * K // 128 * 2), dev.zeros(M * N * 4)
+        k = dev.kernel("SynthInt4")
+        k.set_arg(0, dP); k.set_arg(1, dS); k.set_arg(2, synth_key(b, f"opbench.a16.{N}.{K}"), "u64")
+        k.set_arg(3, N * K // 128, "u64"); k.set_arg(4, 0.02)
+        k.launch(dev.info().sm_count * 8)
+        g = dev.kernel("Int4GemmA16")
+        g.set_args(dP, dS, dX, dY, N, K, M)
+        kernels.append(g); bufs.append((dP, dS, dY))
+    groups = (N + 127) // 128
+    for i in range(3):
+        kernels[i % nbuf].launch(groups)
+    cl = dev.new_list()
+    for i in range(reps):
+        cl.append(kernels[i % nbuf], groups)
+    cl.close()
+    e0, e1 = dev.event(), dev.event()
+    cl.execute()
+    e0.record(); cl.execute(); e1.record()
+    ms = e0.elapsed_ms(e1) / reps
+    cl.destroy()
+    dev.sync()
+    for t in bufs:
+        for p in t:
+            dev.free(p)
+    b = N * K * 0.515625 + M * K * 2 + M * N * 4
+    return {"op": "int4_gemm_a16", "M": M, "N": N, "K": K, "ms": ms, "gbs": b / ms / 1e6, "bytes": b,
+            "groups": groups, "buffers": nbuf, "flops": 2.0 * M * N * K, "tflops": 2.0 * M * N * K / ms / 1e9}
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -102,6 +143,7 @@ def main(argv=None):
     g.add_argument("--k", type=int, default=2048)
     g.add_argument("--reps", type=int, default=20)
     g.add_argument("--sweep", action="store_true")
+    g.add_argument("--a16", action="store_true", help="bf16 activations (Int4GemmA16, M up to 64) instead of W4A8")
     g.add_argument("--groups", type=int, default=0, help="thread groups per launch (default: by shape)")
     g.add_argument("--flush", action="store_true", help="time single launches after an L2 rewrite")
     ll = sub.add_parser("listlat", help="device time per node of a recorded list of tiny dependent launches")
@@ -117,10 +159,12 @@ def main(argv=None):
     args = ap.parse_args(argv)
     dev = cuda_abi.Device(0)
     if args.cmd == "gemv":
+        ms_ = (1, 2, 4, 8, 64) if args.a16 else (1, 2, 4, 8)
         shapes = ([(m, n, k) for (n, k) in [(512, 2048), (4096, 2048), (8192, 2048), (151936, 2048), (2048, 512)]
-                   for m in (1, 2, 4, 8)] if args.sweep else [(args.m, args.n, args.k)])
+                   for m in ms_] if args.sweep else [(args.m, args.n, args.k)])
         for (m, n, k) in shapes:
-            print(json.dumps(gemv_once(dev, n, k, m, args.reps, args.flush, args.groups)), flush=True)
+            r = gemm_a16_once(dev, n, k, m, args.reps) if args.a16 else gemv_once(dev, n, k, m, args.reps, args.flush, args.groups)
+            print(json.dumps(r), flush=True)
     elif args.cmd == "listlat":
         ctrl = dev.zeros(16); ids = dev.zeros(64)
         k = dev.kernel("ControlAdvance")

@@ -390,3 +390,22 @@ def test_command_list_replay_is_deterministic(dev):
     lst.destroy()
     assert np.array_equal(outs[0], O.gemv_a8(P, S, xq, sq))
     assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[1], outs[2])
+
+
+@pytest.mark.parametrize("N,K,M", [(512, 2048, 1), (512, 2048, 5), (4096, 2048, 64), (1000, 512, 3),
+                                   (2048, 512, 8), (130, 256, 64)])
+def test_gemm_a16_within_reference_tolerance(dev, N, K, M):
+    """Int4GemmA16 (bf16 activations, tensor-core products) vs the double-precision host form of the
+    float-activation policy. Tolerance: rel 2e-2 / abs 1e-2, the bar of the reference's own GEMV test."""
+    rng = np.random.default_rng(N + K + M)
+    P, S = rnd_weights(rng, N, K)
+    xb = O.bf16_bits(rng.standard_normal((M, K)).astype(np.float32))
+    want = O.gemv_a16(P, S, O.bf16_to_f32(xb))
+    dY = dev.zeros(M * N * 4)
+    dev.kernel("Int4GemmA16")((N + 127) // 128, dev.upload(P), dev.upload(S), dev.upload(xb), dY, N, K, M)
+    dev.sync()
+    got = dev.download(dY, (M, N), np.float32)
+    err = np.abs(got - want)
+    assert np.all(err <= 1e-2 + 2e-2 * np.abs(want)), float(err.max())
+    # far inside the bar in practice: fp32 accumulation of exact bf16 products
+    assert float(err.max()) <= 1e-4 * max(1.0, float(np.abs(want).max()))
