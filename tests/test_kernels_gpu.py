@@ -74,6 +74,25 @@ def test_gemv_a8_bit_exact_all_k(dev, K):
     assert np.array_equal(got, want)
 
 
+@pytest.mark.parametrize("N,K,groups", [(3000, 2048, 1), (3000, 2048, 2), (3000, 2048, 5), (4100, 512, 3),
+                                        (1030, 4096, 1), (777, 128, 2), (1, 2048, 1), (5, 256, 4)])
+def test_gemv_a8_streams_many_sub_blocks(dev, N, K, groups):
+    """Few thread groups over many rows: every group walks several sub-blocks, so its weight ring
+    runs on from one segment list into the next (and wraps many times); plus single-row and
+    fewer-rows-than-groups cases."""
+    rng = np.random.default_rng(N * 7 + K)
+    P, S = rnd_weights(rng, N, K)
+    x = rng.standard_normal(K).astype(np.float32) * 2
+    xq, sq = O.aquant(x)
+    want = O.gemv_a8(P, S, xq, sq)
+    dY = dev.zeros(N * 4)
+    tab = np.zeros(1, GEMV_MAT)
+    tab[0]["P"], tab[0]["S"], tab[0]["Y"], tab[0]["N"], tab[0]["ldy"] = dev.upload(P), dev.upload(S), dY, N, N
+    dev.kernel("Int4GemvA8")(groups, dev.upload(tab.view(np.uint8)), 1, N, dev.upload(xq), dev.upload(sq), K, 1)
+    dev.sync()
+    assert np.array_equal(dev.download(dY, N, np.float32), want)
+
+
 @pytest.mark.parametrize("M", [2, 4, 8])
 def test_gemv_a8_batched(dev, M):
     rng = np.random.default_rng(M)
