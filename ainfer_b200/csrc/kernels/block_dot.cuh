@@ -17,7 +17,7 @@
 //     shifted by a multiply (which runs on the other arithmetic pipe) and
 //     masked; both feed signed dp4a and the sum is divided by 16 at the end
 //     (exact: it is a multiple of 16). No bias term, no shuffle;
-//   * the lane stores t[row][g] = ((float)group_sum * weight_scale) * act_scale[g];
+//   * the lane stores t[g][row] = ((float)group_sum * weight_scale) * act_scale[g];
 //   * after one __syncthreads a single thread per row adds t[row][0..G) in
 //     ascending group order (the reference's accumulation order,
 //     tools/cmdlist/kernels.cpp:157-191) and runs the row's epilogue.
@@ -128,6 +128,13 @@ __device__ __forceinline__ StagedAct4 stage4_from_f32(unsigned char *smem, const
   return StagedAct4{reinterpret_cast<const uint4 *>(smem), sqs};
 }
 
+// t[][] scratch of a block: kTCap (row, group) terms, stored GROUP-major with a row stride
+// of kTCap/G + 1 floats: t[g * (kTCap/G + 1) + row]. The lanes of a warp (consecutive
+// groups of two rows) then write with at most a 2-way bank conflict, and the finishing
+// threads (consecutive rows) read each group's term conflict-free.
+constexpr int kTCap = 4096;
+constexpr int kTFloats = kTCap + 64;  // allocation: kTCap plus one padding float per group
+
 // 32-bit shared-window loads and stores (no generic address arithmetic in the loop).
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
   uint4 v;
@@ -233,7 +240,7 @@ AINFER_BLOCK_DOT_LINKAGE void block_dot(Ring *ring, const SegList *cur, const Se
       seg_lo = sg.row0;
       seg_hi = sg.row0 + sg.nrows;
       sseg = sg.S;
-      tseg = T_a + (uint32_t)((sg.trow * G + g) * 4);
+      tseg = T_a + (uint32_t)((g * (kTCap / G + 1) + sg.trow) * 4);
       if (sg.vec != vec) {
         vec = sg.vec;
         const uint4 *xv = act.x + (size_t)vec * 8 * G + g;
@@ -294,7 +301,7 @@ AINFER_BLOCK_DOT_LINKAGE void block_dot(Ring *ring, const SegList *cur, const Se
     d1 = dot16_x16(w3, 1, x[7], d1);
     if (live) {
       const float v = (float)((d0 + d1) >> 4) * __uint_as_float(sraw << 16);
-      sts_f32(tseg + (uint32_t)((f - seg_lo) * G * 4), v * sqg);
+      sts_f32(tseg + (uint32_t)((f - seg_lo) * 4), v * sqg);
     }
     if (++cs == nst) {
       cs = 0;
@@ -318,11 +325,11 @@ AINFER_BLOCK_DOT_LINKAGE void block_dot(Ring *ring, const SegList *cur, const Se
 // Sum of one row's group terms in ascending group order.
 template <int K>
 __device__ __forceinline__ float row_sum(const float *T, int trow) {
-  constexpr int G = K / 128;
-  const float *t = T + (size_t)trow * G;
+  constexpr int G = K / 128, TS = kTCap / G + 1;
+  const float *t = T + trow;
   float acc = 0.0f;
 #pragma unroll
-  for (int g = 0; g < G; ++g) acc = acc + t[g];
+  for (int g = 0; g < G; ++g) acc = acc + t[g * TS];
   return acc;
 }
 

@@ -10,7 +10,6 @@
 
 namespace ainfer {
 
-constexpr int kTCap = 4096;  // floats of t[][] scratch a block needs (16 KB)
 
 // Shared-memory working set of a block plus the thread's view of which of the
 // two segment lists is current. `primed` says lists[cur] has already been built
@@ -18,7 +17,7 @@ constexpr int kTCap = 4096;  // floats of t[][] scratch a block needs (16 KB)
 struct BlockScratch {
   Ring *ring;      // shared
   SegList *lists;  // [2] shared
-  float *T;        // [kTCap] shared
+  float *T;        // [kTFloats] shared
   ExpertW *sew;    // [kMaxSegs] shared: weight pointers of the active expert slots (null if unused)
   int cur;
   bool primed;
@@ -63,10 +62,11 @@ __device__ __forceinline__ void block_dot_any(int K, Ring *ring, const SegList *
 }
 // Sum of one row's group terms in ascending group order (G = K/128 at run time).
 __device__ __forceinline__ float row_sum_rt(const float *T, int trow, int G) {
-  const float *t = T + (size_t)trow * G;
+  const int TS = kTCap / G + 1;
+  const float *t = T + trow;
   float acc = 0.0f;
 #pragma unroll 4
-  for (int g = 0; g < G; ++g) acc = acc + t[g];
+  for (int g = 0; g < G; ++g) acc = acc + t[(size_t)g * TS];
   return acc;
 }
 

@@ -24,7 +24,7 @@ __host__ __device__ inline uint32_t round128(uint32_t v) { return (v + 127u) & ~
 __global__ void __launch_bounds__(256, 2) Int4GemvA8(const Int4GemvA8Args a) {
   __shared__ GemvMat smats[8];
   __shared__ SegList lists[2];
-  __shared__ float T[kTCap];
+  __shared__ float T[kTFloats];
   __shared__ Ring ring;
   pdl_launch_dependents();
   // the matrix table and the weights are constants of the model: fetched before the wait

@@ -247,7 +247,7 @@ static __device__ __noinline__ StagedAct4 mega_stage_rows(unsigned char *stage, 
 
 extern __shared__ __align__(128) unsigned char mega_smem[];
 constexpr int kMegaStages = 3;
-constexpr int kMegaRingOff = (kStageBytes + kYsFloats * 4 + kTCap * 4 + 127) / 128 * 128;
+constexpr int kMegaRingOff = (kStageBytes + kYsFloats * 4 + kTFloats * 4 + 127) / 128 * 128;
 
 __global__ void __launch_bounds__(256, 2) DecodeStepMega(const DecodeStepMegaArgs args) {
   const MegaPlan &P = *args.plan;

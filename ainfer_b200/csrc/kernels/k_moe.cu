@@ -34,7 +34,7 @@ __global__ void __launch_bounds__(256, 2) ExpertGateUp(const ExpertGateUpArgs a)
   pdl_launch_dependents();
   pdl_wait();
   __shared__ SegList lists[2];
-  __shared__ float T[kTCap];
+  __shared__ float T[kTFloats];
   __shared__ Ring ring;
   __shared__ ExpertW sew[kMaxSegs];
   fetch_expert_rows(sew, a.Experts, a.SelIdx + a.slot_begin, a.slots);
@@ -49,7 +49,7 @@ __global__ void __launch_bounds__(256, 2) ExpertDownCombine(const ExpertDownComb
   pdl_launch_dependents();
   pdl_wait();
   __shared__ SegList lists[2];
-  __shared__ float T[kTCap];
+  __shared__ float T[kTFloats];
   __shared__ Ring ring;
   __shared__ ExpertW sew[kMaxSegs];
   fetch_expert_rows(sew, a.Experts, a.SelIdx, a.slots);
