@@ -253,7 +253,7 @@ __device__ __forceinline__ void down_block_dispatch(const ExpertDownCombineArgs 
 // ---- the same three drivers with K fixed at compile time (stand-alone streaming kernels) ----
 template <int K>
 __device__ __forceinline__ void gemv_block_t(const GemvMat *smats, int nmats, long total_rows,
-                                           const StagedAct4 &act, BlockScratch &bs, int blk, int nblk) {
+                                           const StagedAct4 &act, BlockScratch &bs, int blk, int nblk, int m) {
   constexpr int SB = gemv_sub_rows(K);  // rows per sub-block (one finishing thread per row)
   long lo, hi;
   block_range(total_rows, blk, nblk, lo, hi);
@@ -275,7 +275,7 @@ __device__ __forceinline__ void gemv_block_t(const GemvMat *smats, int nmats, lo
       int mi = 0;
       for (int i = 1; i < nmats; ++i)
         if (r >= smats[i].row_start) mi = i;
-      gemv_epilogue(smats + mi, (int)(r - smats[mi].row_start), 0, row_sum<K>(bs.T, threadIdx.x));
+      gemv_epilogue(smats + mi, (int)(r - smats[mi].row_start), m, row_sum<K>(bs.T, threadIdx.x));
     }
     bs.cur ^= 1;
   }
@@ -339,15 +339,15 @@ __device__ __forceinline__ void down_block_t(const ExpertDownCombineArgs &a, con
 
 __device__ __forceinline__ void gemv_block_dispatch(int K, const GemvMat *smats, int nmats, long total_rows,
                                                     const StagedAct4 &act, BlockScratch &bs, int blk,
-                                                    int nblk) {
+                                                    int nblk, int m = 0) {
   switch (K) {
-    case 128: gemv_block_t<128>(smats, nmats, total_rows, act, bs, blk, nblk); break;
-    case 256: gemv_block_t<256>(smats, nmats, total_rows, act, bs, blk, nblk); break;
-    case 512: gemv_block_t<512>(smats, nmats, total_rows, act, bs, blk, nblk); break;
-    case 1024: gemv_block_t<1024>(smats, nmats, total_rows, act, bs, blk, nblk); break;
-    case 2048: gemv_block_t<2048>(smats, nmats, total_rows, act, bs, blk, nblk); break;
-    case 4096: gemv_block_t<4096>(smats, nmats, total_rows, act, bs, blk, nblk); break;
-    case 8192: gemv_block_t<8192>(smats, nmats, total_rows, act, bs, blk, nblk); break;
+    case 128: gemv_block_t<128>(smats, nmats, total_rows, act, bs, blk, nblk, m); break;
+    case 256: gemv_block_t<256>(smats, nmats, total_rows, act, bs, blk, nblk, m); break;
+    case 512: gemv_block_t<512>(smats, nmats, total_rows, act, bs, blk, nblk, m); break;
+    case 1024: gemv_block_t<1024>(smats, nmats, total_rows, act, bs, blk, nblk, m); break;
+    case 2048: gemv_block_t<2048>(smats, nmats, total_rows, act, bs, blk, nblk, m); break;
+    case 4096: gemv_block_t<4096>(smats, nmats, total_rows, act, bs, blk, nblk, m); break;
+    case 8192: gemv_block_t<8192>(smats, nmats, total_rows, act, bs, blk, nblk, m); break;
     default: break;  // rejected on the host before launch
   }
 }

@@ -51,69 +51,12 @@ __device__ __forceinline__ int warp_sum_int(int v) {
   return v;
 }
 
-// Streaming 16-byte load: weights are read once per token, keep them out of L1.
-__device__ __forceinline__ uint4 ldg_stream16(const void *p) {
-  uint4 v;
-  asm("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
-}
-__device__ __forceinline__ uint2 ldg_stream8(const void *p) {
-  uint2 v;
-  asm("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
-  return v;
-}
-
 // Activation quantiser element rule (tools/cmdlist/kernels.cpp:574-577):
 // q = trunc(x/s +- 0.5), clamped to +-127.
 __device__ __forceinline__ int quant_round(float x, float s) {
   float v = x / s;
   int qi = (int)(v >= 0 ? v + 0.5f : v - 0.5f);
   return qi < -127 ? -127 : (qi > 127 ? 127 : qi);
-}
-
-// Dot of one 16-byte chunk of packed INT4 (32 weights, low nibble = even k)
-// with 32 INT8 activations held de-interleaved: xe[i] = bytes (x0,x2,x4,x6) and
-// xo[i] = (x1,x3,x5,x7) of the i-th 8-weight word. Nibbles are biased by xor 8
-// to unsigned 0..15; the caller subtracts 8 * sum(x) per group.
-__device__ __forceinline__ int dot_chunk_biased(const uint4 w, const uint4 xa, const uint4 xb,
-                                                int acc) {
-  // xa = {e0, o0, e1, o1}, xb = {e2, o2, e3, o3}
-  uint32_t b;
-  b = w.x ^ 0x88888888u;
-  acc = __dp4a((int)(b & 0x0F0F0F0Fu), (int)xa.x, acc);
-  acc = __dp4a((int)((b >> 4) & 0x0F0F0F0Fu), (int)xa.y, acc);
-  b = w.y ^ 0x88888888u;
-  acc = __dp4a((int)(b & 0x0F0F0F0Fu), (int)xa.z, acc);
-  acc = __dp4a((int)((b >> 4) & 0x0F0F0F0Fu), (int)xa.w, acc);
-  b = w.z ^ 0x88888888u;
-  acc = __dp4a((int)(b & 0x0F0F0F0Fu), (int)xb.x, acc);
-  acc = __dp4a((int)((b >> 4) & 0x0F0F0F0Fu), (int)xb.y, acc);
-  b = w.w ^ 0x88888888u;
-  acc = __dp4a((int)(b & 0x0F0F0F0Fu), (int)xb.z, acc);
-  acc = __dp4a((int)((b >> 4) & 0x0F0F0F0Fu), (int)xb.w, acc);
-  return acc;
-}
-
-// Stages K INT8 activations into shared memory de-interleaved for
-// dot_chunk_biased, and the per-group sums of the activations.
-// xs_e_o: K bytes, laid out as K/8 pairs {even word, odd word}. gsum: K/128 ints.
-__device__ __forceinline__ void stage_activations(const int8_t *__restrict__ xq, int K,
-                                                  uint32_t *xs_e_o, int *gsum) {
-  const uint2 *src = reinterpret_cast<const uint2 *>(xq);
-  for (int i = threadIdx.x; i < K / 8; i += blockDim.x) {
-    uint2 v = src[i];
-    xs_e_o[2 * i] = __byte_perm(v.x, v.y, 0x6420);
-    xs_e_o[2 * i + 1] = __byte_perm(v.x, v.y, 0x7531);
-  }
-  __syncthreads();
-  for (int g = threadIdx.x; g < K / 128; g += blockDim.x) {
-    int s = 0;
-    for (int i = 0; i < 32; ++i) s = __dp4a((int)xs_e_o[g * 32 + i], 0x01010101, s);
-    gsum[g] = s;
-  }
-  __syncthreads();
 }
 
 }  // namespace ainfer

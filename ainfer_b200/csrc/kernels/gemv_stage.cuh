@@ -6,7 +6,7 @@
 // same quantised activation (e.g. in_proj_qkv, in_proj_z, in_proj_b, in_proj_a).
 #pragma once
 #include "../common/tables.h"
-#include "gemv_core.cuh"
+#include "common.cuh"
 
 namespace ainfer {
 
@@ -59,69 +59,4 @@ static __device__ __noinline__ void gemv_epilogue(const GemvMat *pmt, int n, int
 // Rows of one launch for this block. Each warp walks passes of RPW rows (grid
 // stride over blocks), keeps the next pass' loads in flight while it computes
 // the current one, and hands each finished row to the matrix's epilogue.
-template <int K, int M>
-__device__ __forceinline__ void gemv_rows(const Int4GemvA8Args &a, const StagedAct &act,
-                                          const GemvMat *smats, int blk, int nblk) {
-  using Gm = RowGeom<K>;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int warps = blockDim.x >> 5;
-  const long total = a.total_rows;
-  const long stride = (long)nblk * warps * Gm::RPW;
-  long wrow = ((long)blk * warps + warp) * Gm::RPW;  // first row of this warp's pass
-  if (wrow >= total) return;
-  const int rs = lane / Gm::LPR;
-  // row -> (matrix, local row); rows are global over the launch's table (nmats <= 8)
-  auto locate = [&](long r, int &mi, long &lr, bool &ok) {
-    int idx = 0;
-    for (int i = 1; i < a.nmats; ++i)
-      if (r >= smats[i].row_start) idx = i;
-    ok = r < total;
-    mi = idx;
-    lr = ok ? r - smats[idx].row_start : 0;
-  };
-  PassRegs<K> cur, nxt;
-  int mi_c, mi_n = 0;
-  long lr_c, lr_n = 0;
-  bool ok_c, ok_n = false;
-  locate(wrow + rs, mi_c, lr_c, ok_c);
-  pass_load<K>(cur, smats[mi_c].P + lr_c * (K / 2), smats[mi_c].S + lr_c * Gm::G, ok_c);
-#pragma unroll 1
-  for (; wrow < total; wrow += stride) {
-    const bool more = wrow + stride < total;  // warp-uniform
-    if (more) {
-      locate(wrow + stride + rs, mi_n, lr_n, ok_n);
-      pass_load<K>(nxt, smats[mi_n].P + lr_n * (K / 2), smats[mi_n].S + lr_n * Gm::G, ok_n);
-    }
-    float acc[M];
-    pass_dot<K, M>(cur, act, 0, acc);
-    if (ok_c && (lane % Gm::LPR) == 0) {
-#pragma unroll
-      for (int m = 0; m < M; ++m) gemv_epilogue(smats + mi_c, (int)lr_c, m, acc[m]);
-    }
-    cur = nxt;
-    mi_c = mi_n; lr_c = lr_n; ok_c = ok_n;
-  }
-}
-
-// act holds the staged activations, smats the launch's matrix table (shared memory).
-template <int M>
-__device__ __forceinline__ void gemv_dispatch_k(const Int4GemvA8Args &a, const StagedAct &act,
-                                                const GemvMat *smats, int blk, int nblk) {
-  switch (a.K) {
-    case 128: gemv_rows<128, M>(a, act, smats, blk, nblk); break;
-    case 256: gemv_rows<256, M>(a, act, smats, blk, nblk); break;
-    case 512: gemv_rows<512, M>(a, act, smats, blk, nblk); break;
-    case 1024: gemv_rows<1024, M>(a, act, smats, blk, nblk); break;
-    case 2048: gemv_rows<2048, M>(a, act, smats, blk, nblk); break;
-    case 4096: gemv_rows<4096, M>(a, act, smats, blk, nblk); break;
-    case 8192: gemv_rows<8192, M>(a, act, smats, blk, nblk); break;
-    default: break;  // rejected on the host before launch
-  }
-}
-// Rows one pass of a block (8 warps) covers, by K; the host mirrors this to size grids.
-__host__ __device__ inline int gemv_tile_rows(int K) {
-  int cpr = K / 32, lpr = cpr < 32 ? cpr : 32;
-  return 8 * (32 / lpr);
-}
-
 }  // namespace ainfer

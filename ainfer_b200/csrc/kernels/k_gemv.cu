@@ -1,27 +1,27 @@
-// Kernel entries of the INT4 x INT8 GEMV; row code in gemv_stage.cuh (shared
-// with the persistent decode kernel).
+// Kernel entries of the INT4 x INT8 GEMV (weight ring + block_dot, block_stages.cuh).
 #include "block_stages.cuh"
 
 namespace ainfer {
 
 extern __shared__ __align__(128) unsigned char gemv_smem[];
 
-template <int M>
-__device__ __forceinline__ void gemv_kernel(const Int4GemvA8Args &a) {
-  __shared__ GemvMat smats[8];
-  pdl_launch_dependents();
-  pdl_wait();
-  if (threadIdx.x < a.nmats) smats[threadIdx.x] = a.mats[threadIdx.x];  // synced by stage_act
-  StagedAct act = stage_act(gemv_smem, a.XQ, a.SQ, a.K, M, a.K, a.K / 128);
-  gemv_dispatch_k<M>(a, act, smats, blockIdx.x, gridDim.x);
-}
-
-// One entry point per batch width so that register allocation follows M.
-// M = 1: the block-flattened form (block_dot.cuh); wider batches keep the warp-pass form.
+// One body for every batch width: activation row m = 0..M-1 is one pass of the M = 1 pipeline
+// over the block's rows (the weights are streamed once per activation row: exact W4A8 batches
+// are a parity surface for the operator sweep, the batched operator is Int4GemmA16).
 constexpr int kGemvStages = 5;
 __host__ __device__ inline uint32_t round128(uint32_t v) { return (v + 127u) & ~127u; }
 
-__global__ void __launch_bounds__(256, 2) Int4GemvA8(const Int4GemvA8Args a) {
+// One activation row through the single-row pipeline, out of line: the batched kernels call it
+// M times and it keeps the register allocation of the single-row kernel.
+static __device__ __noinline__ void gemv_pass(const int8_t *xq, const float *sq, int K, const GemvMat *smats, int nmats,
+                                              int total_rows, Ring *ring, SegList *lists, float *T, int m) {
+  BlockScratch bs{ring, lists, T, nullptr, 0, false};
+  StagedAct4 act = stage4(gemv_smem, xq, sq, K, 1, K, K / 128);
+  gemv_block_dispatch(K, smats, nmats, total_rows, act, bs, blockIdx.x, gridDim.x, m);
+}
+
+template <bool kBatched>
+__device__ __forceinline__ void gemv_a8_body(const Int4GemvA8Args &a) {
   __shared__ GemvMat smats[8];
   __shared__ SegList lists[2];
   __shared__ float T[kTFloats];
@@ -38,29 +38,37 @@ __global__ void __launch_bounds__(256, 2) Int4GemvA8(const Int4GemvA8Args a) {
   }
   bs.primed = true;
   pdl_wait();  // the activations come from the previous kernel
-  StagedAct4 act = stage4(gemv_smem, a.XQ, a.SQ, a.K, 1, a.K, a.K / 128);
-  gemv_block_dispatch(a.K, smats, a.nmats, a.total_rows, act, bs, blockIdx.x, gridDim.x);
+  if (!kBatched) {  // the decode kernel: no loop, so that its code is exactly the single-row pipeline
+    StagedAct4 act = stage4(gemv_smem, a.XQ, a.SQ, a.K, 1, a.K, a.K / 128);
+    gemv_block_dispatch(a.K, smats, a.nmats, a.total_rows, act, bs, blockIdx.x, gridDim.x, 0);
+  } else {
+    // (the prefetch above is consumed by the first pass: the ring remembers what is in flight)
+#pragma unroll 1
+    for (int m = 0; m < a.M; ++m) {
+      if (m > 0) __syncthreads();  // the staged vector and t[][] of the previous pass are no longer read
+      gemv_pass(a.XQ + (size_t)m * a.K, a.SQ + (size_t)m * (a.K / 128), a.K, smats, a.nmats, a.total_rows, &ring,
+                lists, T, m);
+    }
+  }
   if (threadIdx.x == 0) ring_drain_after_fault(&ring);
 }
-__global__ void __launch_bounds__(256, 3) Int4GemvA8M2(const Int4GemvA8Args a) { gemv_kernel<2>(a); }
-__global__ void __launch_bounds__(256) Int4GemvA8M4(const Int4GemvA8Args a) { gemv_kernel<4>(a); }
-__global__ void __launch_bounds__(256) Int4GemvA8M8(const Int4GemvA8Args a) { gemv_kernel<8>(a); }
+
+__global__ void __launch_bounds__(256, 2) Int4GemvA8(const Int4GemvA8Args a) { gemv_a8_body<false>(a); }
+__global__ void __launch_bounds__(256, 2) Int4GemvA8M2(const Int4GemvA8Args a) { gemv_a8_body<true>(a); }
+__global__ void __launch_bounds__(256, 2) Int4GemvA8M4(const Int4GemvA8Args a) { gemv_a8_body<true>(a); }
+__global__ void __launch_bounds__(256, 2) Int4GemvA8M8(const Int4GemvA8Args a) { gemv_a8_body<true>(a); }
 
 static uint32_t gemv1_smem_fn(const void *args) {
   const Int4GemvA8Args *a = (const Int4GemvA8Args *)args;
   return round128(staged4_bytes(a->K, 1)) + kGemvStages * kStageStride;
 }
-static uint32_t gemv_smem_fn(const void *args) {
-  const Int4GemvA8Args *a = (const Int4GemvA8Args *)args;
-  return staged_act_bytes(a->K, a->M);
-}
 
 #define F(f) AINFER_ARG(Int4GemvA8Args, f)
 #define GEMV_FIELDS F(mats), F(nmats), F(total_rows), F(XQ), F(SQ), F(K), F(M)
 AINFER_REGISTER(Int4GemvA8, Int4GemvA8Args, 256, 0, 0, gemv1_smem_fn, GEMV_FIELDS);
-AINFER_REGISTER(Int4GemvA8M2, Int4GemvA8Args, 256, 0, 0, gemv_smem_fn, GEMV_FIELDS);
-AINFER_REGISTER(Int4GemvA8M4, Int4GemvA8Args, 256, 0, 0, gemv_smem_fn, GEMV_FIELDS);
-AINFER_REGISTER(Int4GemvA8M8, Int4GemvA8Args, 256, 0, 0, gemv_smem_fn, GEMV_FIELDS);
+AINFER_REGISTER(Int4GemvA8M2, Int4GemvA8Args, 256, 0, 0, gemv1_smem_fn, GEMV_FIELDS);
+AINFER_REGISTER(Int4GemvA8M4, Int4GemvA8Args, 256, 0, 0, gemv1_smem_fn, GEMV_FIELDS);
+AINFER_REGISTER(Int4GemvA8M8, Int4GemvA8Args, 256, 0, 0, gemv1_smem_fn, GEMV_FIELDS);
 #undef F
 
 AINFER_EARLY_LAUNCH(Int4GemvA8);

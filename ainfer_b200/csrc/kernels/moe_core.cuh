@@ -5,7 +5,7 @@
 // counterpart and follows the arithmetic stated with each kernel.
 #pragma once
 #include "../common/tables.h"
-#include "gemv_core.cuh"
+#include "common.cuh"
 
 namespace ainfer {
 
@@ -155,44 +155,6 @@ struct ExpertGateUpArgs {
   int32_t slots, I, H;
   int32_t slot_begin;      // first slot this launch handles (expert-parallel ranks)
 };
-// act: the staged quantised hidden vector; blk/nblk: this block's share of the rows.
-template <int K>
-__device__ __forceinline__ void gateup_rows(const ExpertGateUpArgs &a, const StagedAct &act, int blk,
-                                            int nblk) {
-  using Gm = RowGeom<K>;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-  const long total = (long)a.slots * a.I;
-  const long stride = (long)nblk * warps * Gm::RPW;
-  const int rs = lane / Gm::LPR;
-#pragma unroll 1
-  for (long wrow = ((long)blk * warps + warp) * Gm::RPW; wrow < total; wrow += stride) {
-    long r = wrow + rs;
-    bool ok = r < total;
-    int s = ok ? (int)(r / a.I) : 0, n = ok ? (int)(r % a.I) : 0;
-    const ExpertW &ew = a.Experts[a.SelIdx[a.slot_begin + s]];
-    PassRegs<K> rg, ru;  // the row of gate_proj and the same row of up_proj
-    pass_load<K>(rg, ew.gP + (long)n * (K / 2), ew.gS + (long)n * Gm::G, ok);
-    pass_load<K>(ru, ew.uP + (long)n * (K / 2), ew.uS + (long)n * Gm::G, ok);
-    float g[1], u[1];
-    pass_dot<K, 1>(rg, act, 0, g);
-    pass_dot<K, 1>(ru, act, 0, u);
-    if (ok && (lane % Gm::LPR) == 0)
-      a.Act[(size_t)(a.slot_begin + s) * a.I + n] = silu_mul(g[0], u[0]);
-  }
-}
-__device__ __forceinline__ void gateup_dispatch(const ExpertGateUpArgs &a, const StagedAct &act, int blk,
-                                                int nblk) {
-  switch (a.H) {
-    case 256: gateup_rows<256>(a, act, blk, nblk); break;
-    case 512: gateup_rows<512>(a, act, blk, nblk); break;
-    case 1024: gateup_rows<1024>(a, act, blk, nblk); break;
-    case 2048: gateup_rows<2048>(a, act, blk, nblk); break;
-    case 4096: gateup_rows<4096>(a, act, blk, nblk); break;
-    default: break;
-  }
-}
-
-
 // ---------------------------------------------------- ExpertDownCombine ---
 // Quantises each slot's activation (per-128 quantiser), y_s[n] = down_e[n].act_s,
 // then out[n] = Res[n] + (sum_s w_s * y_s[n] in rank order, + sg * y_shared[n]),
@@ -210,58 +172,4 @@ struct ExpertDownCombineArgs {
 // Output rows of the down projections: for row n every active slot's matrix is
 // dotted with that slot's quantised activation (slots in groups of four, so that
 // four loads are in flight), then combined in rank order.
-template <int K>
-__device__ __forceinline__ void down_rows(const ExpertDownCombineArgs &a, const StagedAct &act, int blk,
-                                          int nblk) {
-  using Gm = RowGeom<K>;
-  constexpr int SG = 4;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-  const long stride = (long)nblk * warps * Gm::RPW;
-  const int rs = lane / Gm::LPR;
-#pragma unroll 1
-  for (long wrow = ((long)blk * warps + warp) * Gm::RPW; wrow < a.H; wrow += stride) {
-    long n = wrow + rs;
-    bool ok = n < a.H;
-    long nn = ok ? n : 0;
-    float acc = 0.0f;
-#pragma unroll 1
-    for (int p0 = 0; p0 < a.slots; p0 += SG) {
-      PassRegs<K> r[SG];
-#pragma unroll
-      for (int j = 0; j < SG; ++j) {
-        int p = p0 + j < a.slots ? p0 + j : 0;
-        const ExpertW &ew = a.Experts[a.SelIdx[p]];
-        pass_load<K>(r[j], ew.dP + nn * (K / 2), ew.dS + nn * Gm::G, ok && p0 + j < a.slots);
-      }
-#pragma unroll
-      for (int j = 0; j < SG; ++j) {
-        int p = p0 + j < a.slots ? p0 + j : 0;
-        float y[1];
-        pass_dot<K, 1>(r[j], act, p, y);
-        if (p0 + j < a.slots) acc = acc + a.SelW[p] * y[0];
-      }
-    }
-    if (ok && (lane % Gm::LPR) == 0) {
-      if (a.Moe) a.Moe[n] = acc;
-      a.X[n] = __ldcg(a.Res + n) + acc;
-    }
-  }
-}
-template <int K>
-__device__ __forceinline__ void down_dispatch_k(const ExpertDownCombineArgs &a, const StagedAct &act,
-                                                int blk, int nblk) {
-  down_rows<K>(a, act, blk, nblk);
-}
-__device__ __forceinline__ void down_dispatch(const ExpertDownCombineArgs &a, const StagedAct &act, int blk,
-                                              int nblk) {
-  switch (a.I) {
-    case 128: down_dispatch_k<128>(a, act, blk, nblk); break;
-    case 256: down_dispatch_k<256>(a, act, blk, nblk); break;
-    case 512: down_dispatch_k<512>(a, act, blk, nblk); break;
-    case 1024: down_dispatch_k<1024>(a, act, blk, nblk); break;
-    default: break;
-  }
-}
-
-
 }  // namespace ainfer

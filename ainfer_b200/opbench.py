@@ -52,7 +52,7 @@ def gemv_once(dev, N, K, M=1, reps=20, flush=False, groups=None):
     xq = dev.upload(rng.integers(-127, 128, (M, K), dtype=np.int8))
     sq = dev.upload(np.full((M, K // 128), 0.01, np.float32))
     if not groups:
-        groups = stream_groups(N, K, sm) if M == 1 else max(1, min(-(-N // 32), sm * 8))
+        groups = stream_groups(N, K, sm)
     bufs, kernels = [], []
     for b in range(nbuf):
         dP, dS, dY = dev.alloc(N * K // 2), dev.alloc(N * K // 128 * 2), dev.zeros(M * N * 4)
@@ -148,6 +148,9 @@ def main(argv=None):
     g.add_argument("--flush", action="store_true", help="time single launches after an L2 rewrite")
     ll = sub.add_parser("listlat", help="device time per node of a recorded list of tiny dependent launches")
     ll.add_argument("--n", type=int, default=400)
+    pl = sub.add_parser("pairlat", help="device time per (norm, GEMV) pair of a recorded list")
+    pl.add_argument("--n", type=int, default=200)
+    pl.add_argument("--rows", type=int, default=8192)
     d = sub.add_parser("decode")
     d.add_argument("--model", default="small")
     d.add_argument("--prompt", type=int, default=4)
@@ -165,6 +168,36 @@ def main(argv=None):
         for (m, n, k) in shapes:
             r = gemm_a16_once(dev, n, k, m, args.reps) if args.a16 else gemv_once(dev, n, k, m, args.reps, args.flush, args.groups)
             print(json.dumps(r), flush=True)
+    elif args.cmd == "pairlat":
+        # a recorded list of (RmsNormQuant, Int4GemvA8 on a small matrix) pairs: the dependency chain
+        # of a decode layer in miniature; run with and without AINFER_NO_EARLY_LAUNCH=1
+        K, N = 2048, args.rows
+        rng = np.random.default_rng(0)
+        dX = dev.upload(rng.standard_normal(K).astype(np.float32)); dW = dev.zeros(K * 4)
+        dQ8, dSQ = dev.zeros(K), dev.zeros(K // 128 * 4)
+        dP, dS, dY = dev.alloc(N * K // 2), dev.alloc(N * K // 128 * 2), dev.zeros(N * 4)
+        k = dev.kernel("SynthInt4")
+        k.set_arg(0, dP); k.set_arg(1, dS); k.set_arg(2, synth_key(0, "pairlat"), "u64")
+        k.set_arg(3, N * K // 128, "u64"); k.set_arg(4, 0.02)
+        k.launch(dev.info().sm_count * 8)
+        tab = np.zeros(1, GEMV_MAT)
+        tab[0]["P"], tab[0]["S"], tab[0]["Y"], tab[0]["N"], tab[0]["ldy"] = dP, dS, dY, N, N
+        norm, gemv = dev.kernel("RmsNormQuant"), dev.kernel("Int4GemvA8")
+        norm.set_args(dX, 0, 0, dW, 0, dQ8, dSQ, K, 1e-6)
+        gemv.set_args(dev.upload(tab.view(np.uint8)), 1, N, dQ8, dSQ, K, 1)
+        groups = stream_groups(N, K, dev.info().sm_count)
+        cl = dev.new_list()
+        for _ in range(args.n):
+            cl.append(norm, 1)
+            cl.append(gemv, groups)
+        cl.close()
+        e0, e1 = dev.event(), dev.event()
+        cl.execute()
+        e0.record(); cl.execute(); e1.record()
+        dev.sync()
+        print(json.dumps({"op": "pairlat", "pairs": args.n, "rows": N, "groups": groups,
+                          "us_per_pair": e0.elapsed_ms(e1) * 1000.0 / args.n}), flush=True)
+        cl.destroy()
     elif args.cmd == "listlat":
         ctrl = dev.zeros(16); ids = dev.zeros(64)
         k = dev.kernel("ControlAdvance")
