@@ -253,6 +253,23 @@ AINFER_BLOCK_DOT_LINKAGE void block_dot(Ring *ring, const SegList *cur, const Se
         sqg = act.sq[vec * G + g];
       }
     }
+    // The issuing thread refills the stage of the previous tile BEFORE it waits for this tile's
+    // data: the stage has been free since every warp copied tile t-1 out, and a refill that
+    // waited for tile t to land would leave one stage of the ring idle all the time.
+    if (tid == 0) {
+      if (t >= 1) --in_flight;  // tile t-1 has been consumed by this thread; the wait below covers the others
+      if (more && t >= 1) {
+        if (kRegCursor) {
+          mbar_wait_a(ring, empty_a + pr.stage * 8, pr.phase ^ 1u);
+          more = pr.issue(ring, ring->data, nst);
+          if (more) ++issued_here;
+        } else {
+          mbar_wait_a(ring, empty_a + ring->p_stage * 8, ring->p_phase ^ 1u);
+          more = ring_issue_next(ring);
+        }
+        if (more) ++in_flight;
+      }
+    }
     const uint32_t st = data_a + cs * kStageStride;
     AINFER_STAMP(51);
     mbar_wait_a(ring, full_a + cs * 8, cph);
@@ -275,21 +292,6 @@ AINFER_BLOCK_DOT_LINKAGE void block_dot(Ring *ring, const SegList *cur, const Se
     }
     __syncwarp();
     if (warp_lead) mbar_arrive_a(empty_a + cs * 8);
-    // the issuing thread refills the stage of the previous tile
-    if (tid == 0) {
-      if (t >= 1) --in_flight;  // tile t-1 has been consumed by this thread; the wait below covers the others
-      if (more && t >= 1) {
-        if (kRegCursor) {
-          mbar_wait_a(ring, empty_a + pr.stage * 8, pr.phase ^ 1u);
-          more = pr.issue(ring, ring->data, nst);
-          if (more) ++issued_here;
-        } else {
-          mbar_wait_a(ring, empty_a + ring->p_stage * 8, ring->p_phase ^ 1u);
-          more = ring_issue_next(ring);
-        }
-        if (more) ++in_flight;
-      }
-    }
     int d0 = 0, d1 = 0;
     d0 = dot16_x16(w0, 0, x[0], d0);
     d1 = dot16_x16(w0, 1, x[1], d1);
