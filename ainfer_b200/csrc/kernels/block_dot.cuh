@@ -196,28 +196,36 @@ AINFER_BLOCK_DOT_LINKAGE void block_dot(Ring *ring, const SegList *cur, const Se
   const int rot = (tid >> 1) & 3;
   const uint32_t lane_off = (uint32_t)tid * 64u;
 
-  // ---- issuing thread: fill the ring ----
-  // kRegCursor: the cursor lives in registers and the issue code is inlined (streaming
-  // kernels, where the issue sits on the critical path of a consuming warp); otherwise it
-  // stays in the Ring and one out-of-line function issues (small code for the persistent
-  // step, whose stages are a few prefetched tiles each).
-  // in_flight = tiles issued and not yet consumed (this call's and, towards its end, the next list's)
-  Producer pr;
-  uint32_t in_flight = 0, issued_here = 0;
+  // ---- issuing: fill the ring ----
+  // kRegCursor (streaming kernels): the tiles of this call and, towards its end, of the next
+  // list form one sequence j = 0, 1, ...; tile j is issued by the leader of warp j % 8, so the
+  // cost of issuing (two bulk copies, ~1100 cycles) rotates over the warps instead of sitting
+  // on one warp's critical path for every tile. Otherwise (persistent step: a few prefetched
+  // tiles per stage, small code wanted) thread 0 issues through the cursor kept in the Ring.
+  // in_flight = tiles issued and not yet consumed (this call's and the next list's)
+  uint32_t in_flight = 0;
   bool more = false;  // the cursor may still have tiles to issue
-  if (tid == 0) {
-    in_flight = ring->pre;
+  const uint32_t warp = (uint32_t)tid >> 5;
+  const uint32_t pre0 = ring->pre;
+  const uint32_t ntot = (uint32_t)ntiles + (next ? (uint32_t)next->ntiles : 0u);
+  const uint32_t fill = ntot < nst ? ntot : nst;  // tiles in flight after the initial fill
+  if (kRegCursor) {
+    if (warp_lead) {
+      for (uint32_t j = pre0; j < fill; ++j) {
+        if ((j & 7u) != warp) continue;
+        uint32_t st = cs + j;
+        if (st >= nst) st -= nst;
+        if (j < (uint32_t)ntiles) ring_issue_tile(ring, cur, (int)j, st);
+        else ring_issue_tile(ring, next, (int)(j - (uint32_t)ntiles), st);
+      }
+    }
+  } else if (tid == 0) {
+    in_flight = pre0;
     if (in_flight == 0) ring_open(ring, cur);
     ring->p_next = next;
-    if (kRegCursor) pr.load(ring);
     more = true;
     while (more && in_flight < nst) {
-      if (kRegCursor) {
-        more = pr.issue(ring, ring->data, nst);
-        if (more) ++issued_here;
-      } else {
-        more = ring_issue_next(ring);
-      }
+      more = ring_issue_next(ring);
       if (more) ++in_flight;
     }
   }
@@ -253,20 +261,22 @@ AINFER_BLOCK_DOT_LINKAGE void block_dot(Ring *ring, const SegList *cur, const Se
         sqg = act.sq[vec * G + g];
       }
     }
-    // The issuing thread refills the stage of the previous tile BEFORE it waits for this tile's
-    // data: the stage has been free since every warp copied tile t-1 out, and a refill that
-    // waited for tile t to land would leave one stage of the ring idle all the time.
-    if (tid == 0) {
+    // The stage of the previous tile is refilled BEFORE this tile's data is waited for: it has
+    // been free since every warp copied tile t-1 out, and a refill that waited for tile t to
+    // land would leave one stage of the ring idle all the time.
+    if (kRegCursor) {
+      const uint32_t j = (uint32_t)t - 1u + nst;  // the tile that takes the stage of tile t-1
+      if (warp_lead && t >= 1 && j < ntot && (j & 7u) == warp) {
+        const uint32_t ps = cs == 0 ? nst - 1 : cs - 1, pph = cs == 0 ? cph ^ 1u : cph;
+        mbar_wait_a(ring, empty_a + ps * 8, pph);
+        if (j < (uint32_t)ntiles) ring_issue_tile(ring, cur, (int)j, ps);
+        else ring_issue_tile(ring, next, (int)(j - (uint32_t)ntiles), ps);
+      }
+    } else if (tid == 0) {
       if (t >= 1) --in_flight;  // tile t-1 has been consumed by this thread; the wait below covers the others
       if (more && t >= 1) {
-        if (kRegCursor) {
-          mbar_wait_a(ring, empty_a + pr.stage * 8, pr.phase ^ 1u);
-          more = pr.issue(ring, ring->data, nst);
-          if (more) ++issued_here;
-        } else {
-          mbar_wait_a(ring, empty_a + ring->p_stage * 8, ring->p_phase ^ 1u);
-          more = ring_issue_next(ring);
-        }
+        mbar_wait_a(ring, empty_a + ring->p_stage * 8, ring->p_phase ^ 1u);
+        more = ring_issue_next(ring);
         if (more) ++in_flight;
       }
     }
@@ -312,14 +322,19 @@ AINFER_BLOCK_DOT_LINKAGE void block_dot(Ring *ring, const SegList *cur, const Se
     AINFER_STAMP(53);
   }
   if (tid == 0) {
-    if (kRegCursor) {
-      pr.store(ring);
-      ring->issued += issued_here;
-    }
     ring->c_stage = cs;
     ring->c_phase = cph;
-    // what is still in flight belongs to the next list (the last tile of cur was consumed above)
-    ring->pre = ntiles > 0 ? in_flight - 1 : in_flight;
+    if (kRegCursor) {
+      // issued in total, counted from tile 0 of cur: the initial fill, then one per consumed tile but the last
+      uint32_t last = (ntiles >= 1 ? (uint32_t)ntiles - 1u : 0u) + nst;
+      if (last > ntot) last = ntot;
+      const uint32_t total_issued = last > fill ? last : fill;
+      ring->issued += total_issued - pre0;
+      ring->pre = total_issued > (uint32_t)ntiles ? total_issued - (uint32_t)ntiles : 0;
+    } else {
+      // what is still in flight belongs to the next list (the last tile of cur was consumed above)
+      ring->pre = ntiles > 0 ? in_flight - 1 : in_flight;
+    }
   }
   __syncthreads();
 }

@@ -32,10 +32,9 @@ __device__ __forceinline__ void gemv_a8_body(const Int4GemvA8Args &a) {
   ring_init(&ring, gemv_smem + round128(staged4_bytes(a.K, 1)), kGemvStages);  // syncs: smats visible
   BlockScratch bs{&ring, lists, T, nullptr, 0, false};
   // start the weight stream before the activations are staged
-  if (threadIdx.x == 0) {
-    gemv_first_list(&lists[0], smats, a.nmats, a.K, a.total_rows, blockIdx.x, gridDim.x);
-    ring_prefetch(&ring, &lists[0]);
-  }
+  if (threadIdx.x == 0) gemv_first_list(&lists[0], smats, a.nmats, a.K, a.total_rows, blockIdx.x, gridDim.x);
+  __syncthreads();
+  ring_prefetch_all(&ring, &lists[0]);  // the warp leaders issue the first tiles in parallel
   bs.primed = true;
   pdl_wait();  // the activations come from the previous kernel
   if (!kBatched) {  // the decode kernel: no loop, so that its code is exactly the single-row pipeline
