@@ -38,8 +38,18 @@ __global__ void __launch_bounds__(256, 2) ExpertGateUp(const ExpertGateUpArgs a)
   __shared__ Ring ring;
   __shared__ ExpertW sew[kMaxSegs];
   fetch_expert_rows(sew, a.Experts, a.SelIdx + a.slot_begin, a.slots);
-  ring_init(&ring, moe_smem + moe_round128(staged4_bytes(a.H, 1)), kMoeStages);
+  ring_init(&ring, moe_smem + moe_round128(staged4_bytes(a.H, 1)), kMoeStages);  // syncs: sew visible
   BlockScratch bs{&ring, lists, T, sew, 0, false};
+  // weight stream first (it needs only the routing), activations while the tiles are in flight
+  if (threadIdx.x == 0) {
+    long lo, hi;
+    block_range((long)a.slots * a.I, blockIdx.x, gridDim.x, lo, hi);
+    const int SB = gateup_sub_rows(a.H);
+    gateup_list(&lists[0], a, sew, (int)lo, (int)(lo + SB < hi ? lo + SB : hi));
+  }
+  __syncthreads();
+  ring_prefetch_all(&ring, &lists[0]);
+  bs.primed = true;
   StagedAct4 act = stage4(moe_smem, a.XQ, a.SQ, a.H, 1, a.H, a.H / 128);
   gateup_block_dispatch_t(a, act, bs, blockIdx.x, gridDim.x);
   if (threadIdx.x == 0) ring_drain_after_fault(&ring);
@@ -53,8 +63,19 @@ __global__ void __launch_bounds__(256, 2) ExpertDownCombine(const ExpertDownComb
   __shared__ Ring ring;
   __shared__ ExpertW sew[kMaxSegs];
   fetch_expert_rows(sew, a.Experts, a.SelIdx, a.slots);
-  ring_init(&ring, moe_smem + moe_round128(staged4_bytes(a.I, a.slots)), kMoeStages);
+  ring_init(&ring, moe_smem + moe_round128(staged4_bytes(a.I, a.slots)), kMoeStages);  // syncs: sew visible
   BlockScratch bs{&ring, lists, T, sew, 0, false};
+  // weight stream first (it needs only the routing), the slots' activations are quantised while
+  // the tiles are in flight
+  if (threadIdx.x == 0) {
+    long lo, hi;
+    block_range(a.H, blockIdx.x, gridDim.x, lo, hi);
+    const int SB = down_sub_rows(a.I, a.slots);
+    down_list(&lists[0], a, sew, (int)lo, (int)(lo + SB < hi ? lo + SB : hi));
+  }
+  __syncthreads();
+  ring_prefetch_all(&ring, &lists[0]);
+  bs.primed = true;
   StagedAct4 act = stage4_from_f32<true>(moe_smem, a.Act, a.I, a.slots, a.I);
   down_block_dispatch_t(a, act, bs, blockIdx.x, gridDim.x);
   if (threadIdx.x == 0) ring_drain_after_fault(&ring);

@@ -104,33 +104,43 @@ static __device__ __noinline__ void router_select(const float *lg, int E, int k,
   for (int e = tid; e < E; e += nthr) sp[e] = sp[e] / sum;
   __syncthreads();
   if (tid < 32) {
+    // Top-k by one warp, E/32 candidates per lane in registers. Probabilities are >= 0, so
+    // their bit patterns order like unsigned integers; key = bits + 1 keeps 0 free for "not a
+    // candidate" (beyond E, or already selected). The warp maximum and, among its holders, the
+    // lowest index are two hardware warp reductions per rank (same (value desc, index asc) rule
+    // as a comparison tournament).
+    constexpr int kPerLane = 32;  // E <= 1024
+    unsigned v[kPerLane];
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) {
+      const int e = lane + 32 * i;
+      v[i] = e < E ? __float_as_uint(sp[e]) + 1u : 0u;
+    }
+    const int per = (E + 31) / 32;
     float s = 0.0f, lastp = 0.0f;
     float wsel = 0.0f;  // lane j keeps the weight of rank j (k <= 32)
 #pragma unroll 1
     for (int j = 0; j <= k && j < E; ++j) {
-      float bv = -1.0f;
+      unsigned bv = 0u;
       int bi = 0x7FFFFFFF;
-#pragma unroll 4
-      for (int e = lane; e < E; e += 32) {
-        float p = sp[e];
-        if (p > bv) { bv = p; bi = e; }
-      }
 #pragma unroll
-      for (int off = 16; off > 0; off >>= 1) {
-        float ov = __shfl_xor_sync(kFull, bv, off);
-        int oi = __shfl_xor_sync(kFull, bi, off);
-        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
-      }
+      for (int i = 0; i < kPerLane; ++i)
+        if (i < per && v[i] > bv) { bv = v[i]; bi = lane + 32 * i; }
+      const unsigned wv = __reduce_max_sync(kFull, bv);
+      const int wi = (int)__reduce_min_sync(kFull, bv == wv ? (unsigned)bi : 0x7FFFFFFFu);
+      const float p = __uint_as_float(wv - 1u);
       if (j == k) {
-        if (lane == 0) *near_gap = lastp > 0.0f ? (lastp - bv) / lastp : 0.0f;
+        if (lane == 0) *near_gap = lastp > 0.0f ? (lastp - p) / lastp : 0.0f;
         break;
       }
-      if ((bi & 31) == lane) sp[bi] = -1.0f;  // probabilities are >= 0: never selected again
-      __syncwarp();
-      if (lane == j) wsel = bv;
-      if (lane == 0) sel_idx[j] = bi;
-      s = s + bv;
-      lastp = bv;
+      // never selected again: a selected entry is marked by an index test, not by its value
+#pragma unroll
+      for (int i = 0; i < kPerLane; ++i)
+        if (lane + 32 * i == wi) v[i] = 0u, sp[wi] = -1.0f;
+      if (lane == j) wsel = p;
+      if (lane == 0) sel_idx[j] = wi;
+      s = s + p;
+      lastp = p;
     }
     if (k >= E && lane == 0) *near_gap = 1.0f;
     if (lane < k) sel_w[lane] = wsel / s;
