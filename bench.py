@@ -277,7 +277,10 @@ def run_ours(args):
         top = sweep[0]
         roof = {"bound": "hbm", "kernel": f"Int4GemvA8 lm_head [{top['N']}x{top['K']}] M=1",
                 "achieved": top["gbs"], "peak": peak, "unit": "GB/s", "frac": top["frac"],
-                "peak_source": peak_src, "traffic": None,
+                "peak_source": peak_src,
+                # DRAM bytes of one launch of this kernel at this shape from the ncu capture summarised in
+                # profiles/int4_gemv_a8_lm_head_151936x2048.md (dram__bytes_read.sum + dram__bytes_write.sum)
+                "traffic": 164.45e6 if (top["N"], top["K"]) == (151936, 2048) else None,
                 "algorithmic_bytes_per_launch": top["N"] * top["K"] * 0.515625 + top["K"] + top["K"] // 128 * 4 + top["N"] * 4}
     except Exception as e:     # the probe must never take the decode number down with it
         roof = {"bound": "hbm", "error": str(e)}
