@@ -60,6 +60,10 @@ def _compile(cmd, out, src, hdr_time, verbose):
 
 
 def build_cuda(verbose=False, ptxas_v=False):
+    # AINFER_TIMELINE=1 in the environment builds the profiling variant (every kernel stamps the
+    # global timer around its dependency wait); its objects are cached apart from the product's.
+    timeline = os.environ.get("AINFER_TIMELINE") == "1"
+    OBJ = os.path.join(LIB, "obj_timeline" if timeline else "obj")
     os.makedirs(OBJ, exist_ok=True)
     srcs = sorted(glob.glob(os.path.join(CSRC, "kernels", "*.cu")) +
                   glob.glob(os.path.join(CSRC, "abi", "*.cu")))
@@ -68,15 +72,21 @@ def build_cuda(verbose=False, ptxas_v=False):
     with cf.ThreadPoolExecutor(max_workers=min(8, len(srcs))) as ex:
         for s in srcs:
             o = os.path.join(OBJ, os.path.basename(s) + ".o")
-            cmd = [_nvcc()] + NVCC_FLAGS + (["-Xptxas", "-v"] if ptxas_v else []) + ["-c", s, "-o", o]
+            cmd = ([_nvcc()] + NVCC_FLAGS + (["-DAINFER_TIMELINE"] if timeline else []) +
+                   (["-Xptxas", "-v"] if ptxas_v else []) + ["-c", s, "-o", o])
             jobs.append(ex.submit(_compile, cmd, o, s, ht, verbose))
         objs = [j.result() for j in jobs]
     out = os.path.join(LIB, "libainfer_cuda.so")
-    if not os.path.exists(out) or os.path.getmtime(out) < _newest(objs):
+    marker = os.path.join(LIB, "variant.txt")
+    want = "timeline" if timeline else "product"
+    have = open(marker).read().strip() if os.path.exists(marker) else ""
+    if not os.path.exists(out) or os.path.getmtime(out) < _newest(objs) or have != want:
         cmd = [_nvcc(), "-shared", "-o", out] + objs + ["-cudart", "static", "-Xcompiler", "-fPIC"]
         if verbose:
             print(" ".join(cmd), flush=True)
         subprocess.run(cmd, check=True)
+        with open(marker, "w") as f:
+            f.write(want + "\n")
     return out
 
 

@@ -43,6 +43,11 @@ static std::vector<FaultHook> &fault_hooks() {
 void register_fault_hook(FaultHook h) { fault_hooks().push_back(h); }
 int fault_hook_count() { return (int)fault_hooks().size(); }
 FaultHook fault_hook_at(int i) { return fault_hooks()[(size_t)i]; }
+static std::vector<TimelineHook> &timeline_hooks() {
+  static std::vector<TimelineHook> h;
+  return h;
+}
+void register_timeline_hook(TimelineHook h) { timeline_hooks().push_back(h); }
 int kernel_count() { return (int)registry().size(); }
 const KernelDesc *kernel_at(int i) {
   return i >= 0 && i < kernel_count() ? &registry()[i] : nullptr;
@@ -86,6 +91,43 @@ static int fault_word_setup(int ordinal, volatile unsigned int **out) {
   *out = g_fault_words[ordinal];
   return 0;
 }
+#ifdef AINFER_TIMELINE
+// Event buffer of the timeline build, one per GPU: 2 header words + kTimelineCap (enter, go) pairs.
+constexpr size_t kTimelineCap = 1u << 18;
+static unsigned long long *g_timeline_bufs[64];
+static int timeline_setup(int ordinal) {
+  if (ordinal < 0 || ordinal >= 64) return 1;
+  if (g_timeline_bufs[ordinal]) return 0;
+  unsigned long long *d = nullptr;
+  if (cudaMalloc((void **)&d, (2 + 2 * kTimelineCap) * 8) != cudaSuccess) return 1;
+  const unsigned long long hdr[2] = {0, kTimelineCap};
+  if (cudaMemcpy(d, hdr, sizeof hdr, cudaMemcpyHostToDevice) != cudaSuccess) return 1;
+  for (TimelineHook h : timeline_hooks())
+    if (h(d) != 0) return 1;
+  g_timeline_bufs[ordinal] = d;
+  return 0;
+}
+// Not part of the product ABI: exported by timeline builds for the profiling script.
+extern "C" int ainfer_timeline_read(int ordinal, unsigned long long *out_pairs, size_t cap_pairs, size_t *n_out,
+                                    int reset) {
+  if (ordinal < 0 || ordinal >= 64 || !g_timeline_bufs[ordinal]) return 1;
+  cudaSetDevice(ordinal);
+  cudaDeviceSynchronize();
+  unsigned long long hdr[2];
+  if (cudaMemcpy(hdr, g_timeline_bufs[ordinal], sizeof hdr, cudaMemcpyDeviceToHost) != cudaSuccess) return 1;
+  size_t n = (size_t)(hdr[0] < hdr[1] ? hdr[0] : hdr[1]);
+  if (n > cap_pairs) n = cap_pairs;
+  if (n && cudaMemcpy(out_pairs, g_timeline_bufs[ordinal] + 2, n * 16, cudaMemcpyDeviceToHost) != cudaSuccess)
+    return 1;
+  *n_out = n;
+  if (reset) {
+    const unsigned long long zero = 0;
+    cudaMemcpy(g_timeline_bufs[ordinal], &zero, 8, cudaMemcpyHostToDevice);
+  }
+  return 0;
+}
+#endif
+
 struct ainfer_kernel_s {
   ainfer_device_t dev;
   const KernelDesc *desc;
@@ -164,6 +206,14 @@ int ainfer_device_open(int ordinal, ainfer_device_t *out) {
     delete d;
     return fail(nullptr, AINFER_ERR_DEVICE, "could not set up the stream fault word");
   }
+#ifdef AINFER_TIMELINE
+  if (timeline_setup(ordinal) != 0) {
+    cudaGetLastError();
+    cudaStreamDestroy(d->stream);
+    delete d;
+    return fail(nullptr, AINFER_ERR_DEVICE, "could not set up the timeline buffer");
+  }
+#endif
   *out = d;
   return AINFER_OK;
 }

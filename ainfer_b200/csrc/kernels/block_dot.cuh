@@ -71,6 +71,39 @@ __device__ __forceinline__ StagedAct4 stage4(unsigned char *smem, const int8_t *
   return StagedAct4{reinterpret_cast<const uint4 *>(smem), sqs};
 }
 
+// stage4() of one vector (K <= 8 * 256 * kPer) with every global load issued before
+// `between()` runs and before the first shared-memory store: a caller puts a load
+// that depends on something fetched earlier into `between`, so that it is in flight
+// together with these instead of a round trip later (a warp issues in order).
+template <class F>
+__device__ __forceinline__ StagedAct4 stage4_issue_first(unsigned char *smem, const int8_t *xq, const float *sq,
+                                                        int K, F between) {
+  constexpr int kPer = 4;  // 8-byte pieces per thread: K <= 8192 with 256 threads
+  uint32_t *xw = reinterpret_cast<uint32_t *>(smem);
+  const int G = K / 128;
+  float *sqs = reinterpret_cast<float *>(smem + (size_t)K);
+  uint2 v[kPer];
+  float sc = 0.0f;
+#pragma unroll
+  for (int r = 0; r < kPer; ++r) {
+    const int pc = threadIdx.x + r * blockDim.x;
+    if (pc < K / 8) v[r] = __ldcg(reinterpret_cast<const uint2 *>(xq + (long)pc * 8));
+  }
+  if (threadIdx.x < G) sc = __ldcg(sq + threadIdx.x);
+  between();
+#pragma unroll
+  for (int r = 0; r < kPer; ++r) {
+    const int pc = threadIdx.x + r * blockDim.x;
+    if (pc < K / 8) {
+      xw[staged4_word(K, 0, pc, 0)] = __byte_perm(v[r].x, v[r].y, 0x6420);
+      xw[staged4_word(K, 0, pc, 1)] = __byte_perm(v[r].x, v[r].y, 0x7531);
+    }
+  }
+  if (threadIdx.x < G) sqs[threadIdx.x] = sc;
+  __syncthreads();
+  return StagedAct4{reinterpret_cast<const uint4 *>(smem), sqs};
+}
+
 // Quantises one group of 128 fp32 values held four per lane (per-128 activation
 // quantiser, tools/cmdlist/kernels.cpp:551-579) into the staged form. One warp;
 // one out-of-line copy of this code however many loops call it.

@@ -19,7 +19,52 @@ namespace ainfer {
 // and waits for its predecessor (completion and memory flush) before it reads or
 // writes anything the predecessor touches. Both are no-ops for an ordinary launch.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+#ifndef AINFER_TIMELINE
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#define AINFER_MARK(id)
+#else
+#define AINFER_MARK(id) ::ainfer::timeline_mark(id)
+// Timeline build (-DAINFER_TIMELINE): block 0 of every kernel records the global
+// timer when it reaches its dependency wait and when the wait returns (its
+// predecessor has completed), in launch order, into one device buffer:
+// word 0 = events so far, word 1 = capacity, then (enter, go) pairs. The time
+// between the `go` of consecutive kernels is what each costs on the chain.
+static __device__ unsigned long long *g_timeline;
+static int set_timeline_buffer(unsigned long long *device_ptr) {
+  return cudaMemcpyToSymbol(g_timeline, &device_ptr, sizeof device_ptr) == cudaSuccess ? 0 : 1;
+}
+static TimelineRegistrar g_timeline_registrar(set_timeline_buffer);
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void pdl_wait() {
+  const bool rec = blockIdx.x == 0 && threadIdx.x == 0 && g_timeline != nullptr;
+  unsigned long long t0 = 0;
+  if (rec) t0 = global_timer_ns();
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  if (rec) {
+    const unsigned long long t1 = global_timer_ns();
+    const unsigned long long slot = atomicAdd(g_timeline, 1ull);
+    if (slot < g_timeline[1]) {
+      g_timeline[2 + 2 * slot] = t0;
+      g_timeline[3 + 2 * slot] = t1;
+    }
+  }
+}
+// A point inside a kernel (block 0, thread 0): stored in the same buffer as (id | 1 << 63, time).
+__device__ __forceinline__ void timeline_mark(int id) {
+  if (blockIdx.x == 0 && threadIdx.x == 0 && g_timeline != nullptr) {
+    const unsigned long long t = global_timer_ns();
+    const unsigned long long slot = atomicAdd(g_timeline, 1ull);
+    if (slot < g_timeline[1]) {
+      g_timeline[2 + 2 * slot] = (1ull << 63) | (unsigned long long)id;
+      g_timeline[3 + 2 * slot] = t;
+    }
+  }
+}
+#endif
 
 
 constexpr unsigned kFull = 0xFFFFFFFFu;

@@ -1,7 +1,8 @@
 // Kernel entries of the mixture-of-experts block; bodies in moe_core.cuh
 // (shared with the persistent decode kernel).
 #define AINFER_BLOCK_DOT_INLINE 1
-#include "block_stages.cuh"
+
+#include "direct_dot.cuh"
 
 namespace ainfer {
 
@@ -9,10 +10,17 @@ extern __shared__ __align__(128) unsigned char moe_smem[];
 
 __global__ void __launch_bounds__(256) RouterTopK(const RouterTopKArgs a) {
   pdl_launch_dependents();
+  // the router's weights do not depend on the producer of Hn: fetch the first row's share first
+  RouterRowRegs first;
+  {
+    const int e = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (e < a.E + (a.Wsg ? 1 : 0)) router_row_load(first, router_row_ptr(a, e), 0, a.H / 256, threadIdx.x & 31);
+  }
   pdl_wait();
   __shared__ bool is_last;
   __shared__ float sp[1024 + 1];
-  router_logits_rows(a, blockIdx.x, gridDim.x);
+  router_logits_rows(a, blockIdx.x, gridDim.x, &first);
+  AINFER_MARK(1);
   // last block to arrive does the selection
   __threadfence();
   __syncthreads();
@@ -25,60 +33,112 @@ __global__ void __launch_bounds__(256) RouterTopK(const RouterTopKArgs a) {
   if (!is_last) return;
   __threadfence();
   router_select(a.Logits, a.E, a.k, a.Wsg != nullptr, sp, a.SelIdx, a.SelW, a.NearGap);
+  router_publish_rows(a);
 }
 
-constexpr int kMoeStages = 4;
 __host__ __device__ inline uint32_t moe_round128(uint32_t v) { return (v + 127u) & ~127u; }
+constexpr int kMoeTasks = 3;  // 64-byte weight groups a thread keeps in flight
 
+// The expert kernels stream only a few tens of KB per block (top-k experts of one token), so
+// they take the weights by direct loads (direct_dot.cuh), not through the shared-memory ring.
 __global__ void __launch_bounds__(256, 2) ExpertGateUp(const ExpertGateUpArgs a) {
   pdl_launch_dependents();
   pdl_wait();
-  __shared__ SegList lists[2];
+  __shared__ SegList list;
   __shared__ float T[kTFloats];
-  __shared__ Ring ring;
   __shared__ ExpertW sew[kMaxSegs];
-  fetch_expert_rows(sew, a.Experts, a.SelIdx + a.slot_begin, a.slots);
-  ring_init(&ring, moe_smem + moe_round128(staged4_bytes(a.H, 1)), kMoeStages);  // syncs: sew visible
-  BlockScratch bs{&ring, lists, T, sew, 0, false};
-  // weight stream first (it needs only the routing), activations while the tiles are in flight
-  if (threadIdx.x == 0) {
-    long lo, hi;
-    block_range((long)a.slots * a.I, blockIdx.x, gridDim.x, lo, hi);
-    const int SB = gateup_sub_rows(a.H);
-    gateup_list(&lists[0], a, sew, (int)lo, (int)(lo + SB < hi ? lo + SB : hi));
+  // the routing first, the hidden vector's loads next, then the dependent load of the selected
+  // experts' pointer records (a warp issues in order)
+  const int t = threadIdx.x;
+  const bool row_thread = t < a.slots * 3 && t < kMaxSegs * 3;
+  int sel = 0;
+  if (row_thread) sel = a.SelIdx ? __ldcg(a.SelIdx + a.slot_begin + t / 3) : a.slot_begin + t / 3;
+  StagedAct4 act = stage4_issue_first(moe_smem, a.XQ, a.SQ, a.H, [&] {
+    if (row_thread)
+      reinterpret_cast<uint4 *>(sew + t / 3)[t % 3] = __ldg(reinterpret_cast<const uint4 *>(a.Experts + sel) + t % 3);
+  });  // ends with a barrier: sew visible
+  AINFER_MARK(1);
+  if (a.prefetch_down) {
+    // the down projections of the same experts are read by the next kernel: start them towards L2
+    const int wl = a.H * (a.I / 2) / 128, sl = a.H * (a.I / 128) * 2 / 128;  // lines per slot: weights, scales
+    const int per = wl + sl, total = a.slots * per;
+    for (int i = blockIdx.x * blockDim.x + t; i < total; i += gridDim.x * blockDim.x) {
+      const int s = i / per, l = i - s * per;
+      prefetch_l2(l < wl ? sew[s].dP + (size_t)l * 128
+                         : reinterpret_cast<const uint8_t *>(sew[s].dS) + (size_t)(l - wl) * 128);
+    }
   }
-  __syncthreads();
-  ring_prefetch_all(&ring, &lists[0]);
-  bs.primed = true;
-  StagedAct4 act = stage4(moe_smem, a.XQ, a.SQ, a.H, 1, a.H, a.H / 128);
-  gateup_block_dispatch_t(a, act, bs, blockIdx.x, gridDim.x);
-  if (threadIdx.x == 0) ring_drain_after_fault(&ring);
+  const int SB = gateup_sub_rows(a.H);  // pair rows per sub-block
+  const int G = a.H / 128;
+  long lo, hi;
+  block_range((long)a.slots * a.I, blockIdx.x, gridDim.x, lo, hi);
+#pragma unroll 1
+  for (long sb = lo; sb < hi; sb += SB) {
+    const long se = sb + SB < hi ? sb + SB : hi;
+    gateup_list_par(&list, a, sew, (int)sb, (int)se);
+    __syncthreads();  // list complete; T of the previous sub-block is no longer read
+    AINFER_MARK(2);
+    direct_dot<kMoeTasks>(&list, act, T);
+    __syncthreads();
+    AINFER_MARK(3);
+    const long r = sb + threadIdx.x;
+    if (r < se) {
+      const float g = row_sum_rt(T, threadIdx.x, G), u = row_sum_rt(T, SB + threadIdx.x, G);
+      a.Act[(size_t)a.slot_begin * a.I + r] = silu_mul(g, u);
+    }
+  }
+  AINFER_MARK(9);
 }
 
 __global__ void __launch_bounds__(256, 2) ExpertDownCombine(const ExpertDownCombineArgs a) {
   pdl_launch_dependents();
   pdl_wait();
-  __shared__ SegList lists[2];
+  __shared__ SegList list;
   __shared__ float T[kTFloats];
-  __shared__ Ring ring;
   __shared__ ExpertW sew[kMaxSegs];
-  fetch_expert_rows(sew, a.Experts, a.SelIdx, a.slots);
-  ring_init(&ring, moe_smem + moe_round128(staged4_bytes(a.I, a.slots)), kMoeStages);  // syncs: sew visible
-  BlockScratch bs{&ring, lists, T, sew, 0, false};
-  // weight stream first (it needs only the routing), the slots' activations are quantised while
-  // the tiles are in flight
-  if (threadIdx.x == 0) {
-    long lo, hi;
-    block_range(a.H, blockIdx.x, gridDim.x, lo, hi);
-    const int SB = down_sub_rows(a.I, a.slots);
-    down_list(&lists[0], a, sew, (int)lo, (int)(lo + SB < hi ? lo + SB : hi));
+  __shared__ float sw[kMaxSegs];
+  // Every independent load first (routing, weights of the combine, the slots' activations),
+  // then the one dependent load (the selected experts' pointer records); the activation
+  // quantiser runs while that is in flight.
+  const int t = threadIdx.x;
+  const bool row_thread = t < a.slots * 3 && t < kMaxSegs * 3;
+  int sel = 0;
+  float selw = 0.0f;
+  if (row_thread) sel = a.SelIdx ? __ldcg(a.SelIdx + t / 3) : t / 3;
+  if (t < a.slots && t < kMaxSegs) selw = __ldcg(a.SelW + t);
+  QuantWide qw;
+  quant_wide_load(qw, a.Act, a.I, a.slots, a.I, 0);
+  uint4 row = make_uint4(0, 0, 0, 0);
+  if (row_thread) row = __ldg(reinterpret_cast<const uint4 *>(a.Experts + sel) + t % 3);
+  quant_wide_store(qw, moe_smem, a.I, a.slots);
+  if (row_thread) reinterpret_cast<uint4 *>(sew + t / 3)[t % 3] = row;
+  if (t < a.slots && t < kMaxSegs) sw[t] = selw;
+  StagedAct4 act = quant_wide_finish(moe_smem, a.Act, a.I, a.slots, a.I);  // ends with a barrier
+  AINFER_MARK(1);
+  const int SB = down_sub_rows(a.I, a.slots);
+  const int G = a.I / 128;
+  long lo, hi;
+  block_range(a.H, blockIdx.x, gridDim.x, lo, hi);
+#pragma unroll 1
+  for (long sb = lo; sb < hi; sb += SB) {
+    const long se = sb + SB < hi ? sb + SB : hi;
+    const int nr = (int)(se - sb);
+    down_list_par(&list, a, sew, (int)sb, (int)se);
+    const long n = sb + threadIdx.x;
+    const float res = n < se ? __ldcg(a.Res + n) : 0.0f;  // in flight while the weights are fetched
+    __syncthreads();
+    AINFER_MARK(2);
+    direct_dot<kMoeTasks>(&list, act, T);
+    __syncthreads();
+    AINFER_MARK(3);
+    if (n < se) {
+      float acc = 0.0f;
+      for (int s = 0; s < a.slots; ++s) acc = acc + sw[s] * row_sum_rt(T, s * nr + threadIdx.x, G);
+      if (a.Moe) a.Moe[n] = acc;
+      a.X[n] = res + acc;
+    }
   }
-  __syncthreads();
-  ring_prefetch_all(&ring, &lists[0]);
-  bs.primed = true;
-  StagedAct4 act = stage4_from_f32<true>(moe_smem, a.Act, a.I, a.slots, a.I);
-  down_block_dispatch_t(a, act, bs, blockIdx.x, gridDim.x);
-  if (threadIdx.x == 0) ring_drain_after_fault(&ring);
+  AINFER_MARK(9);
 }
 
 // ---- CombineSlots: the combine step of ExpertDownCombine on its own ----
@@ -161,20 +221,20 @@ AINFER_EARLY_LAUNCH(CombineSlots);
 
 #define F(f) AINFER_ARG(RouterTopKArgs, f)
 AINFER_REGISTER(RouterTopK, RouterTopKArgs, 256, 8, 0, nullptr, F(Wr), F(Wsg), F(Hn), F(Logits),
-                F(Counter), F(SelIdx), F(SelW), F(NearGap), F(E), F(H), F(k));
+                F(Counter), F(SelIdx), F(SelW), F(NearGap), F(E), F(H), F(k), F(Experts), F(SelRows));
 #undef F
 
 static uint32_t gateup_smem_fn(const void *args) {
-  return moe_round128(staged4_bytes(((const ExpertGateUpArgs *)args)->H, 1)) + kMoeStages * kStageStride;
+  return moe_round128(staged4_bytes(((const ExpertGateUpArgs *)args)->H, 1));
 }
 #define F(f) AINFER_ARG(ExpertGateUpArgs, f)
 AINFER_REGISTER(ExpertGateUp, ExpertGateUpArgs, 256, 0, 0, gateup_smem_fn, F(Experts), F(SelIdx),
-                F(XQ), F(SQ), F(Act), F(slots), F(I), F(H), F(slot_begin));
+                F(XQ), F(SQ), F(Act), F(slots), F(I), F(H), F(slot_begin), F(prefetch_down));
 #undef F
 
 static uint32_t down_smem_fn(const void *args) {
   const ExpertDownCombineArgs *a = (const ExpertDownCombineArgs *)args;
-  return moe_round128(staged4_bytes(a->I, a->slots)) + kMoeStages * kStageStride;
+  return moe_round128(staged4_bytes(a->I, a->slots));
 }
 #define F(f) AINFER_ARG(ExpertDownCombineArgs, f)
 AINFER_REGISTER(ExpertDownCombine, ExpertDownCombineArgs, 256, 0, 0, down_smem_fn, F(Experts),

@@ -35,30 +35,148 @@ struct RouterTopKArgs {
   float *SelW;           // [k+1]: renormalised weights, then sigmoid(shared gate)
   float *NearGap;        // [1] relative gap between the k-th and (k+1)-th probability
   int32_t E, H, k;
+  // Optional (null: skipped): the layer's expert table [E+1] and a buffer of k+1 records. The
+  // selecting block copies the selected experts' pointer records there in slot order (the expert
+  // kernels then read them with one load instead of chasing SelIdx through the table) and
+  // touches the first line of each selected matrix, so that the address translations of pages
+  // this token has not used yet are under way before the expert kernels ask for them.
+  const ExpertW *Experts;
+  ExpertW *SelRows;
 };
-// Router logits: one warp per row (experts, then the shared-expert gate row).
-__device__ __forceinline__ void router_logits_rows(const RouterTopKArgs &a, int blk, int nblk) {
+__device__ __forceinline__ void prefetch_l2(const void *p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+// Every thread of the selecting block calls, after router_select() returned.
+__device__ __forceinline__ void router_publish_rows(const RouterTopKArgs &a) {
+  if (!a.Experts || !a.SelRows) return;
+  const int t = threadIdx.x;
+  if (t < (a.k + 1) * 3) {
+    const int idx = __ldcg(a.SelIdx + t / 3);
+    const uint4 rec = __ldg(reinterpret_cast<const uint4 *>(a.Experts + idx) + t % 3);  // two pointers
+    reinterpret_cast<uint4 *>(a.SelRows + t / 3)[t % 3] = rec;
+    prefetch_l2(reinterpret_cast<const void *>(((unsigned long long)rec.y << 32) | rec.x));
+    prefetch_l2(reinterpret_cast<const void *>(((unsigned long long)rec.w << 32) | rec.z));
+  }
+}
+// Router logits: one warp per row (experts, then the shared-expert gate row). A lane's share of
+// a row is fetched eight 16-byte loads at a time so that the loads of a chunk are all in flight
+// together; the sums keep the order stated above. prefetch_router_row/consume split the first
+// chunk of a warp's first row so that a caller can issue its weight loads before it waits for
+// the producer of Hn.
+constexpr int kRouterChunk = 8;  // 16-byte loads in flight per lane
+struct RouterRowRegs { uint4 w[kRouterChunk]; };
+
+__device__ __forceinline__ const uint16_t *router_row_ptr(const RouterTopKArgs &a, int e) {
+  return e < a.E ? a.Wr + (size_t)e * a.H : a.Wsg;
+}
+__device__ __forceinline__ void router_row_load(RouterRowRegs &r, const uint16_t *w, int i0, int n, int lane) {
+#pragma unroll
+  for (int c = 0; c < kRouterChunk; ++c)
+    if (i0 + c < n) r.w[c] = __ldg(reinterpret_cast<const uint4 *>(w + ((i0 + c) * 32 + lane) * 8));
+}
+__device__ __forceinline__ float router_row_fma(const RouterRowRegs &r, const float *Hn, int i0, int n, int lane,
+                                                float acc) {
+  float4 x0[kRouterChunk], x1[kRouterChunk];
+#pragma unroll
+  for (int c = 0; c < kRouterChunk; ++c)
+    if (i0 + c < n) {
+      const int k0 = ((i0 + c) * 32 + lane) * 8;
+      x0[c] = __ldcg(reinterpret_cast<const float4 *>(Hn + k0));
+      x1[c] = __ldcg(reinterpret_cast<const float4 *>(Hn + k0 + 4));
+    }
+#pragma unroll
+  for (int c = 0; c < kRouterChunk; ++c)
+    if (i0 + c < n) {
+      const uint4 wv = r.w[c];
+      acc = fmaf(u2f(wv.x << 16), x0[c].x, acc);
+      acc = fmaf(u2f(wv.x & 0xFFFF0000u), x0[c].y, acc);
+      acc = fmaf(u2f(wv.y << 16), x0[c].z, acc);
+      acc = fmaf(u2f(wv.y & 0xFFFF0000u), x0[c].w, acc);
+      acc = fmaf(u2f(wv.z << 16), x1[c].x, acc);
+      acc = fmaf(u2f(wv.z & 0xFFFF0000u), x1[c].y, acc);
+      acc = fmaf(u2f(wv.w << 16), x1[c].z, acc);
+      acc = fmaf(u2f(wv.w & 0xFFFF0000u), x1[c].w, acc);
+    }
+  return acc;
+}
+// first: the chunk already loaded for row (blk*8 + warp), valid when that row exists
+__device__ __forceinline__ void router_logits_rows(const RouterTopKArgs &a, int blk, int nblk,
+                                                   RouterRowRegs *first = nullptr) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int rows = a.E + (a.Wsg ? 1 : 0);
+  const int n = a.H / 256;
   for (int e = blk * 8 + warp; e < rows; e += nblk * 8) {
-    const uint16_t *w = e < a.E ? a.Wr + (size_t)e * a.H : a.Wsg;
+    const uint16_t *w = router_row_ptr(a, e);
     float acc = 0.0f;
-    for (int i = 0; i < a.H / 256; ++i) {
-      int k0 = (i * 32 + lane) * 8;
-      uint4 wv = *reinterpret_cast<const uint4 *>(w + k0);
-      float4 x0 = __ldcg(reinterpret_cast<const float4 *>(a.Hn + k0));
-      float4 x1 = __ldcg(reinterpret_cast<const float4 *>(a.Hn + k0 + 4));
-      acc = fmaf(u2f(wv.x << 16), x0.x, acc);
-      acc = fmaf(u2f(wv.x & 0xFFFF0000u), x0.y, acc);
-      acc = fmaf(u2f(wv.y << 16), x0.z, acc);
-      acc = fmaf(u2f(wv.y & 0xFFFF0000u), x0.w, acc);
-      acc = fmaf(u2f(wv.z << 16), x1.x, acc);
-      acc = fmaf(u2f(wv.z & 0xFFFF0000u), x1.y, acc);
-      acc = fmaf(u2f(wv.w << 16), x1.z, acc);
-      acc = fmaf(u2f(wv.w & 0xFFFF0000u), x1.w, acc);
+    for (int i0 = 0; i0 < n; i0 += kRouterChunk) {
+      RouterRowRegs r;
+      if (first && i0 == 0 && e == blk * 8 + warp) r = *first;
+      else router_row_load(r, w, i0, n, lane);
+      acc = router_row_fma(r, a.Hn, i0, n, lane, acc);
     }
     acc = warp_tree_sum(acc);
     if (lane == 0) a.Logits[e] = acc;
+  }
+}
+
+// Top-k by one warp (all 32 lanes call), kPerLane candidates per lane in registers
+// (E <= 32 * kPerLane). Probabilities are >= 0, so their bit patterns order like unsigned
+// integers; key = bits + 1 keeps 0 free for "not a candidate" (beyond E, or already selected).
+// Per rank: the lane's best key and the lowest index holding it by two balanced trees
+// (depth log2 kPerLane, no long dependent chain), then the warp maximum and, among its
+// holders, the lowest index by two hardware warp reductions: the (value desc, index asc)
+// rule of a comparison tournament.
+template <int kPerLane>
+__device__ __forceinline__ void router_topk_warp(float *sp, int E, int k, bool has_shared, int32_t *sel_idx,
+                                                 float *sel_w, float *near_gap) {
+  const int lane = threadIdx.x & 31;
+  unsigned v[kPerLane];
+#pragma unroll
+  for (int i = 0; i < kPerLane; ++i) {
+    const int e = lane + 32 * i;
+    v[i] = e < E ? __float_as_uint(sp[e]) + 1u : 0u;
+  }
+  float s = 0.0f, lastp = 0.0f;
+  float wsel = 0.0f;  // lane j keeps the weight of rank j (k <= 32)
+#pragma unroll 1
+  for (int j = 0; j <= k && j < E; ++j) {
+    unsigned m[kPerLane];
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) m[i] = v[i];
+#pragma unroll
+    for (int w = kPerLane / 2; w >= 1; w >>= 1)
+#pragma unroll
+      for (int i = 0; i < w; ++i) m[i] = m[i] > m[i + w] ? m[i] : m[i + w];
+    const unsigned bv = m[0];
+    unsigned c[kPerLane];
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) c[i] = v[i] == bv ? (unsigned)i : 0xFFFFu;
+#pragma unroll
+    for (int w = kPerLane / 2; w >= 1; w >>= 1)
+#pragma unroll
+      for (int i = 0; i < w; ++i) c[i] = c[i] < c[i + w] ? c[i] : c[i + w];
+    const unsigned bi = bv ? (unsigned)lane + 32u * c[0] : 0x7FFFFFFFu;
+    const unsigned wv = __reduce_max_sync(kFull, bv);
+    const int wi = (int)__reduce_min_sync(kFull, bv == wv ? bi : 0x7FFFFFFFu);
+    const float p = __uint_as_float(wv - 1u);
+    if (j == k) {
+      if (lane == 0) *near_gap = lastp > 0.0f ? (lastp - p) / lastp : 0.0f;
+      break;
+    }
+    // never selected again: a selected entry is marked by an index test, not by its value
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i)
+      if (lane + 32 * i == wi) v[i] = 0u, sp[wi] = -1.0f;
+    if (lane == j) wsel = p;
+    if (lane == 0) sel_idx[j] = wi;
+    s = s + p;
+    lastp = p;
+  }
+  if (k >= E && lane == 0) *near_gap = 1.0f;
+  if (lane < k) sel_w[lane] = wsel / s;
+  if (lane == 0) {
+    sel_idx[k] = E;
+    sel_w[k] = has_shared ? 1.0f / (1.0f + det_expf(-sp[E])) : 0.0f;
   }
 }
 
@@ -104,50 +222,8 @@ static __device__ __noinline__ void router_select(const float *lg, int E, int k,
   for (int e = tid; e < E; e += nthr) sp[e] = sp[e] / sum;
   __syncthreads();
   if (tid < 32) {
-    // Top-k by one warp, E/32 candidates per lane in registers. Probabilities are >= 0, so
-    // their bit patterns order like unsigned integers; key = bits + 1 keeps 0 free for "not a
-    // candidate" (beyond E, or already selected). The warp maximum and, among its holders, the
-    // lowest index are two hardware warp reductions per rank (same (value desc, index asc) rule
-    // as a comparison tournament).
-    constexpr int kPerLane = 32;  // E <= 1024
-    unsigned v[kPerLane];
-#pragma unroll
-    for (int i = 0; i < kPerLane; ++i) {
-      const int e = lane + 32 * i;
-      v[i] = e < E ? __float_as_uint(sp[e]) + 1u : 0u;
-    }
-    const int per = (E + 31) / 32;
-    float s = 0.0f, lastp = 0.0f;
-    float wsel = 0.0f;  // lane j keeps the weight of rank j (k <= 32)
-#pragma unroll 1
-    for (int j = 0; j <= k && j < E; ++j) {
-      unsigned bv = 0u;
-      int bi = 0x7FFFFFFF;
-#pragma unroll
-      for (int i = 0; i < kPerLane; ++i)
-        if (i < per && v[i] > bv) { bv = v[i]; bi = lane + 32 * i; }
-      const unsigned wv = __reduce_max_sync(kFull, bv);
-      const int wi = (int)__reduce_min_sync(kFull, bv == wv ? (unsigned)bi : 0x7FFFFFFFu);
-      const float p = __uint_as_float(wv - 1u);
-      if (j == k) {
-        if (lane == 0) *near_gap = lastp > 0.0f ? (lastp - p) / lastp : 0.0f;
-        break;
-      }
-      // never selected again: a selected entry is marked by an index test, not by its value
-#pragma unroll
-      for (int i = 0; i < kPerLane; ++i)
-        if (lane + 32 * i == wi) v[i] = 0u, sp[wi] = -1.0f;
-      if (lane == j) wsel = p;
-      if (lane == 0) sel_idx[j] = wi;
-      s = s + p;
-      lastp = p;
-    }
-    if (k >= E && lane == 0) *near_gap = 1.0f;
-    if (lane < k) sel_w[lane] = wsel / s;
-    if (lane == 0) {
-      sel_idx[k] = E;
-      sel_w[k] = has_shared ? 1.0f / (1.0f + det_expf(-sp[E])) : 0.0f;
-    }
+    if (E <= 512) router_topk_warp<16>(sp, E, k, has_shared, sel_idx, sel_w, near_gap);
+    else router_topk_warp<32>(sp, E, k, has_shared, sel_idx, sel_w, near_gap);
   }
   __syncthreads();
 }
@@ -158,12 +234,13 @@ static __device__ __noinline__ void router_select(const float *lg, int E, int k,
 // GEMV), Act[s][n] = (g / (1 + exp(-g))) * u  (SiluMul, kernels.cpp:29-37).
 struct ExpertGateUpArgs {
   const ExpertW *Experts;  // [E+1]
-  const int32_t *SelIdx;   // [slots]
+  const int32_t *SelIdx;   // [slots]; null: Experts already holds the slots' records in slot order
   const int8_t *XQ;        // [H] quantised hidden
   const float *SQ;         // [H/128]
   float *Act;              // [slots][I]
   int32_t slots, I, H;
   int32_t slot_begin;      // first slot this launch handles (expert-parallel ranks)
+  int32_t prefetch_down;   // non-zero: also start these slots' down projections towards L2
 };
 // ---------------------------------------------------- ExpertDownCombine ---
 // Quantises each slot's activation (per-128 quantiser), y_s[n] = down_e[n].act_s,
@@ -171,7 +248,7 @@ struct ExpertGateUpArgs {
 // products and sums unfused. (Down GEMV + ResAddF, decode_l0.cpp:672-674.)
 struct ExpertDownCombineArgs {
   const ExpertW *Experts;
-  const int32_t *SelIdx;  // [slots]
+  const int32_t *SelIdx;  // [slots]; null: Experts already holds the slots' records in slot order
   const float *SelW;      // [slots] (last = shared-expert gate when has_shared)
   const float *Act;       // [slots][I]
   const float *Res;       // [H] residual input

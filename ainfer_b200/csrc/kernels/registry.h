@@ -48,6 +48,14 @@ struct FaultRegistrar {
   explicit FaultRegistrar(FaultHook h) { register_fault_hook(h); }
 };
 
+// Timeline builds only: every kernel translation unit registers a function that
+// stores the address of the shared event buffer in that unit's own pointer.
+typedef int (*TimelineHook)(unsigned long long *device_ptr);
+void register_timeline_hook(TimelineHook h);
+struct TimelineRegistrar {
+  explicit TimelineRegistrar(TimelineHook h) { register_timeline_hook(h); }
+};
+
 // Marks an already registered kernel as safe to launch early (see KernelDesc::early_launch).
 void mark_kernel_early_launch(const char *name);
 struct EarlyLaunchMark {

@@ -12,6 +12,7 @@
 #include <string>
 #include <vector>
 
+#include "../common/tables.h"
 #include "model.h"
 
 namespace ainfer {
@@ -49,7 +50,7 @@ struct Session {
   float *Mx = nullptr, *Z = nullptr, *Bt = nullptr, *Gt = nullptr, *O = nullptr;
   float *Q16 = nullptr, *K16 = nullptr, *V16 = nullptr, *Qn = nullptr;
   float *Pm = nullptr, *Pse = nullptr, *Pacc = nullptr;
-  float *RLogits = nullptr; uint32_t *Counter = nullptr; int32_t *SelIdx = nullptr;
+  float *RLogits = nullptr; uint32_t *Counter = nullptr; ExpertW *SelRows = nullptr; int32_t *SelIdx = nullptr;
   float *SelW = nullptr, *NearGap = nullptr, *Act = nullptr;
   float *Logits = nullptr, *PV = nullptr; int32_t *PI = nullptr;
   // MTP head (only when the model has one): its residual stream, chained hidden input,

@@ -225,7 +225,7 @@ class GpuMoeBackend:
         d.write(self.dRes, np.ascontiguousarray(res_row, np.float32))
         self.k_norm(1, self.dRes, 0, 0, self.norm_w, self.dHn, self.dQ8, self.dSQ, H, self.eps)
         self.k_router((E + 8) // 8, self.router, self.sgate, self.dHn, self.dLog, self.dCnt, self.dSelI, self.dSelW,
-                      self.dGap, E, H, k)
+                      self.dGap, E, H, k, 0, 0)
         d.sync()
         return (d.download(self.dQ8, H, np.int8), d.download(self.dSQ, H // 128, np.float32),
                 d.download(self.dSelI, k, np.int32), d.download(self.dSelW, k + 1, np.float32))
@@ -234,7 +234,7 @@ class GpuMoeBackend:
         d, H, I = self.dev, self.hidden, self.inter
         d.write(self.dQ8, np.ascontiguousarray(hq)); d.write(self.dSQ, np.ascontiguousarray(hs))
         d.write(self.dE1, np.array([e], np.int32))
-        self.k_up(min(2 * self.sm, max(1, 2 * I * H // 32768)), self.tab, self.dE1, self.dQ8, self.dSQ, self.dAct, 1, I, H, 0)
+        self.k_up(min(2 * self.sm, max(1, 2 * I * H // 32768)), self.tab, self.dE1, self.dQ8, self.dSQ, self.dAct, 1, I, H, 0, 0)
         self.k_down(min(2 * self.sm, max(1, H // 8)), self.tab, self.dE1, self.dOne, self.dAct, self.dZero, self.dX, self.dY, 1, I, H)
         d.sync()
         return d.download(self.dY, H, np.float32)
@@ -254,7 +254,7 @@ class GpuMoeBackend:
         slots = k + (1 if self.shared else 0)
         self.route(res_row)
         dAct = d.zeros(slots * I * 4)
-        self.k_up(2 * self.sm, self.tab, self.dSelI, self.dQ8, self.dSQ, dAct, slots, I, H, 0)
+        self.k_up(2 * self.sm, self.tab, self.dSelI, self.dQ8, self.dSQ, dAct, slots, I, H, 0, 0)
         self.k_down(self.sm, self.tab, self.dSelI, self.dSelW, dAct, self.dRes, self.dX, 0, slots, I, H)
         d.sync()
         out = d.download(self.dX, H, np.float32)

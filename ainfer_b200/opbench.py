@@ -15,6 +15,7 @@ Prints one JSON object per line. Timing uses device timestamps on the
 execution queue.
 """
 import argparse
+import ctypes as C
 import json
 import sys
 
@@ -134,6 +135,69 @@ def gemm_a16_once(dev, N, K, M, reps=20):
             "groups": groups, "buffers": nbuf, "flops": 2.0 * M * N * K, "tflops": 2.0 * M * N * K / ms / 1e9}
 
 
+def token_kernel_names(cfg):
+    """Kernel names of one token step of the recorded list, in launch order."""
+    lin = ["RmsNormQuant:in", "Int4GemvA8:in_proj", "DeltaNetStep", "GatedNormQuant", "Int4GemvA8:out_proj"]
+    att = ["RmsNormQuant:in", "Int4GemvA8:qkv", "AttnPrep", "AttnSplit", "AttnCombine", "Int4GemvA8:o_proj"]
+    moe = ["RmsNormQuant:post", "RouterTopK", "ExpertGateUp", "ExpertDownCombine"]
+    names = ["EmbedRow"]
+    for t in cfg["layer_types"]:
+        names += (att if t == "A" else lin) + moe
+    return names + ["RmsNormQuant:final", "Int4GemvA8:lm_head", "ArgmaxStage1", "ArgmaxStage2"]
+
+
+def timeline(dev, model, sess, prompt, steps):
+    """Cost of every kernel on the dependency chain of the recorded token step: the time from
+    the moment its dependency wait returned (its predecessor is complete) to the moment its
+    successor's wait returned, from global-timer stamps that block 0 of each kernel takes."""
+    lib = cuda_abi.load()
+    if not hasattr(lib, "ainfer_timeline_read"):
+        raise SystemExit("this library was not built with AINFER_TIMELINE=1")
+    rd = lib.ainfer_timeline_read
+    rd.argtypes = [C.c_int, C.c_void_p, C.c_size_t, C.POINTER(C.c_size_t), C.c_int]
+    names = token_kernel_names(model.config)
+    sess.generate(prompt, 2)                      # prompt steps + warm-up, stamps discarded below
+    cap = 1 << 18
+    buf = np.zeros((cap, 2), np.uint64)
+    n = C.c_size_t()
+    assert rd(0, buf.ctypes.data, cap, C.byref(n), 1) == 0
+    toks, ms = sess.generate(np.array([int(prompt[0])], np.int32), steps, start_pos=len(prompt) + 2, timed=True)
+    assert rd(0, buf.ctypes.data, cap, C.byref(n), 1) == 0
+    raw = buf[:n.value]
+    is_mark = (raw[:, 0] >> np.uint64(63)) != 0
+    # marks inside kernels (timeline builds may carry some): offset from the go of the kernel they follow
+    kernel_index = np.cumsum(~is_mark) - 1
+    marks_raw = [(int(kernel_index[i]), int(raw[i, 0] & np.uint64(0xFFFF)), int(raw[i, 1])) for i in np.nonzero(is_mark)[0]]
+    n_kernels = int((~is_mark).sum())
+    ev = raw[~is_mark].astype(np.int64)
+    per = len(names)
+    usable = (len(ev) // per) * per
+    ev = ev[len(ev) - usable:]                    # whole token steps, counted from the end
+    go = ev[:, 1]
+    cost = np.diff(go, append=go[-1]).reshape(-1, per)[:-1] / 1000.0   # us; the last step has no successor
+    early = ((ev[:, 1] - ev[:, 0]).reshape(-1, per)[:-1]) / 1000.0      # how long block 0 sat in its wait
+    agg = {}
+    for i, nm in enumerate(names):
+        a = agg.setdefault(nm, [0, 0.0, 0.0])
+        a[0] += 1; a[1] += float(cost[:, i].mean()); a[2] += float(early[:, i].mean())
+    total = sum(a[1] for a in agg.values())
+    rows = [{"kernel": k, "per_token": a[0], "us_per_token": round(a[1], 1), "share": round(a[1] / total, 4),
+             "mean_us": round(a[1] / a[0], 2), "mean_wait_us": round(a[2] / a[0], 2)}
+            for k, a in sorted(agg.items(), key=lambda kv: -kv[1][1])]
+    marks = {}
+    first = n_kernels - usable
+    for (ki, mid, t) in marks_raw:
+        if ki < first:
+            continue
+        pos = ki - first
+        a = marks.setdefault(f"{names[pos % per]}#{mid}", [0, 0.0])
+        a[0] += 1; a[1] += (t - int(go[pos])) / 1000.0
+    print(json.dumps({"op": "timeline", "tokens": int(cost.shape[0]), "launches_per_token": per,
+                      "chain_us_per_token": round(total, 1), "ms_per_token_events": ms / steps,
+                      "kernels": rows,
+                      "marks_us_after_go": {k: round(v[1] / v[0], 2) for k, v in sorted(marks.items())}}), flush=True)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -159,6 +223,9 @@ def main(argv=None):
     d.add_argument("--multi-kernel", action="store_true")
     d.add_argument("--persistent", action="store_true", help="one cooperative launch per token")
     d.add_argument("--stage-clock", action="store_true", help="print the time between grid barriers of the last token")
+    d.add_argument("--timeline", action="store_true",
+                   help="per-kernel cost on the dependency chain, measured inside the recorded list "
+                        "(needs a library built with AINFER_TIMELINE=1)")
     args = ap.parse_args(argv)
     dev = cuda_abi.Device(0)
     if args.cmd == "gemv":
@@ -214,12 +281,16 @@ def main(argv=None):
         cl.destroy()
     else:
         model = runtime.Model(dev, f"synth:{args.model}:seed=0")
-        sess = runtime.Session(model, args.prompt + args.steps + 8,
+        sess = runtime.Session(model, args.prompt + args.steps + 16,
                                runtime.Session.PER_LAYER_LISTS if args.per_layer else
                                (runtime.Session.MULTI_KERNEL if args.multi_kernel else
                                 runtime.Session.PERSISTENT if args.persistent else
                                 (runtime.Session.STAGE_CLOCK if args.stage_clock else 0)))
         prompt = (np.arange(args.prompt, dtype=np.int32) * 7919 + 13) % model.config["vocab"]
+        if args.timeline:
+            timeline(dev, model, sess, prompt, args.steps)
+            sess.close(); model.close(); dev.close()
+            return 0
         toks, ms = sess.generate(prompt, args.steps, timed=True)
         print(json.dumps({"op": "decode", "model": args.model, "prompt": args.prompt, "steps": args.steps,
                           "ms_per_token": ms / args.steps, "launches_per_token": sess.launches_per_token(),

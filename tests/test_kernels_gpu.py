@@ -312,9 +312,11 @@ def test_moe_block(dev, E, k, H, I):
     dLog, dCnt = dev.zeros((E + 1) * 4), dev.zeros(4)
     dSelI, dSelW, dGap = dev.zeros((k + 1) * 4), dev.zeros((k + 1) * 4), dev.zeros(4)
     dHn = dev.upload(hn)
+    dTab = dev.upload(tab.view(np.uint8))
+    dRows = dev.zeros((k + 1) * EXPERT_W.itemsize)   # the selected experts' records, slot order
     router = dev.kernel("RouterTopK")
     for _ in range(2):   # twice: the arrival counter must be left at zero
-        router((E + 8) // 8, dev.upload(Wr), dev.upload(Wsg), dHn, dLog, dCnt, dSelI, dSelW, dGap, E, H, k)
+        router((E + 8) // 8, dev.upload(Wr), dev.upload(Wsg), dHn, dLog, dCnt, dSelI, dSelW, dGap, E, H, k, dTab, dRows)
     dev.sync()
     assert np.array_equal(dev.download(dLog, E, np.float32), logits)
     selI = dev.download(dSelI, k + 1, np.int32); selW = dev.download(dSelW, k + 1, np.float32)
@@ -322,13 +324,15 @@ def test_moe_block(dev, E, k, H, I):
     assert np.array_equal(selW[:k], wt) and selW[k] == sg
     assert dev.download(dGap, 1, np.float32)[0] == np.float32(gap.value)
     slots = k + 1
-    dTab = dev.upload(tab.view(np.uint8))
+    rows = dev.download(dRows, k + 1, EXPERT_W)
+    assert all(rows[s_] == tab[int(selI[s_])] for s_ in range(k + 1))
     dAct = dev.zeros(slots * I * 4)
+    # gate/up through the index list; down through the records the router published (null index list)
     dev.kernel("ExpertGateUp")(dev.info().sm_count * 2, dTab, dSelI, dev.upload(hq), dev.upload(hs), dAct,
-                               slots, I, H, 0)
+                               slots, I, H, 0, 1)
     res = rng.standard_normal(H).astype(np.float32)
     dX, dMoe = dev.zeros(H * 4), dev.zeros(H * 4)
-    dev.kernel("ExpertDownCombine")(dev.info().sm_count, dTab, dSelI, dSelW, dAct, dev.upload(res), dX, dMoe,
+    dev.kernel("ExpertDownCombine")(dev.info().sm_count, dRows, 0, dSelW, dAct, dev.upload(res), dX, dMoe,
                                     slots, I, H)
     dev.sync()
     act_ref = np.zeros((slots, I), np.float32); y = np.zeros((slots, H), np.float32)

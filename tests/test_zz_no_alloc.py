@@ -26,7 +26,7 @@ def dev():
 def run_generic(dev, dWr, dWsg, dHn, E, H, k):
     dLog, dCnt = dev.zeros((E + 1) * 4), dev.zeros(4)
     dI, dW, dG = dev.zeros((k + 1) * 4), dev.zeros((k + 1) * 4), dev.zeros(4)
-    dev.kernel("RouterTopK")((E + 8) // 8, dWr, dWsg, dHn, dLog, dCnt, dI, dW, dG, E, H, k)
+    dev.kernel("RouterTopK")((E + 8) // 8, dWr, dWsg, dHn, dLog, dCnt, dI, dW, dG, E, H, k, 0, 0)
     dev.sync()
     return (dev.download(dI, k + 1, np.int32), dev.download(dW, k + 1, np.uint32), dev.download(dG, 1, np.uint32))
 
