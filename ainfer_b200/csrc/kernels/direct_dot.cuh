@@ -181,75 +181,72 @@ __device__ __forceinline__ void down_list_par(SegList *l, const ExpertDownCombin
 }
 
 // Quantises M fp32 vectors of K (global memory, per-128 activation quantiser,
-// tools/cmdlist/kernels.cpp:551-579) into the staged form with FOUR lanes per
-// group, 32 consecutive values each: 64 groups per pass of a 256-thread block.
-// Split in two so that a caller can issue the loads of the first pass together
-// with its other independent loads and do the arithmetic while dependent loads
-// are in flight (a warp issues in order: a load placed after the first use of an
-// earlier load's result waits a full round trip longer).
+// tools/cmdlist/kernels.cpp:551-579) into the staged form. One warp per group and
+// load instruction (32 lanes x 16 bytes = the group's 512 contiguous bytes), up to
+// eight groups per warp in flight at once (64 groups per pass of a 256-thread
+// block). Split in two so that a caller can issue the loads of the first pass
+// together with its other independent loads and do the arithmetic while
+// dependent loads are in flight (a warp issues in order: a load placed after the
+// first use of an earlier load's result waits a round trip longer).
 struct QuantWide {
-  float4 v[8];
-  int gi;  // group this lane works on in the current pass (may be >= M*G: idle)
+  float4 v[8];  // v[r]: this lane's four values of group (pass base) + warp + 8 r
 };
 __device__ __forceinline__ void quant_wide_load(QuantWide &q, const float *x, int K, int M, long x_stride, int gi0) {
   const int G = K >> 7, lg = 31 - __clz(G);
-  const int q4 = threadIdx.x & 3;
-  q.gi = gi0 + (threadIdx.x >> 2);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) q.v[j] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-  if (q.gi < M * G) {
-    const int m = q.gi >> lg, g = q.gi & (G - 1);
-    const float4 *src = reinterpret_cast<const float4 *>(x + (size_t)m * x_stride + (size_t)g * 128 + q4 * 32);
-#pragma unroll
-    for (int j = 0; j < 8; ++j) q.v[j] = __ldcg(src + j);
+  for (int r = 0; r < 8; ++r) {
+    const int gi = gi0 + warp + nw * r;
+    q.v[r] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (gi < M * G) {
+      const int m = gi >> lg, g = gi & (G - 1);
+      q.v[r] = __ldcg(reinterpret_cast<const float4 *>(x + (size_t)m * x_stride + (size_t)g * 128) + lane);
+    }
   }
 }
 // All 32 lanes of a warp call (shuffles inside).
-__device__ __forceinline__ void quant_wide_store(const QuantWide &q, unsigned char *smem, int K, int M) {
+__device__ __forceinline__ void quant_wide_store(const QuantWide &q, unsigned char *smem, int K, int M, int gi0) {
   uint32_t *xw = reinterpret_cast<uint32_t *>(smem);
   const int G = K >> 7, lg = 31 - __clz(G);
   float *sqs = reinterpret_cast<float *>(smem + (size_t)M * K);
-  const int q4 = threadIdx.x & 3;
-  float mx = 0.0f;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  float mx[8];
 #pragma unroll
-  for (int j = 0; j < 8; ++j)
-    mx = fmaxf(mx, fmaxf(fmaxf(fabsf(q.v[j].x), fabsf(q.v[j].y)), fmaxf(fabsf(q.v[j].z), fabsf(q.v[j].w))));
-  mx = fmaxf(mx, __shfl_xor_sync(kFull, mx, 1));
-  mx = fmaxf(mx, __shfl_xor_sync(kFull, mx, 2));
-  float s = mx / 127.0f;
-  if (s == 0.0f) s = 1.0f;
-  if (q.gi < M * G) {
-    const int m = q.gi >> lg, g = q.gi & (G - 1);
-#pragma unroll 1
-    for (int h = 0; h < 2; ++h) {  // half h: pieces 2h, 2h+1 of this lane = one 16-byte element
-      uint32_t wd[4];
+  for (int r = 0; r < 8; ++r)
+    mx[r] = fmaxf(fmaxf(fabsf(q.v[r].x), fabsf(q.v[r].y)), fmaxf(fabsf(q.v[r].z), fabsf(q.v[r].w)));
 #pragma unroll
-      for (int p = 0; p < 2; ++p) {
-        const float4 a0 = h ? q.v[4 + 2 * p] : q.v[2 * p], a1 = h ? q.v[5 + 2 * p] : q.v[2 * p + 1];
-        const int q0 = quant_round(a0.x, s), q1 = quant_round(a0.y, s), q2 = quant_round(a0.z, s),
-                  q3 = quant_round(a0.w, s), q4v = quant_round(a1.x, s), q5 = quant_round(a1.y, s),
-                  q6 = quant_round(a1.z, s), q7 = quant_round(a1.w, s);
-        wd[2 * p] = (uint32_t)(q0 & 0xFF) | ((uint32_t)(q2 & 0xFF) << 8) | ((uint32_t)(q4v & 0xFF) << 16) |
-                    ((uint32_t)(q6 & 0xFF) << 24);
-        wd[2 * p + 1] = (uint32_t)(q1 & 0xFF) | ((uint32_t)(q3 & 0xFF) << 8) | ((uint32_t)(q5 & 0xFF) << 16) |
-                        ((uint32_t)(q7 & 0xFF) << 24);
-      }
-      // pieces i = 4*q4 + 2h, +1 share (i >> 1) = 2*q4 + h: words 0..3 of one 16-byte element
-      uint4 *dst = reinterpret_cast<uint4 *>(xw + ((((size_t)m * 8 + 2 * q4 + h) * G + g) << 2));
-      *dst = make_uint4(wd[0], wd[1], wd[2], wd[3]);
+  for (int off = 16; off > 0; off >>= 1)
+#pragma unroll
+    for (int r = 0; r < 8; ++r) mx[r] = fmaxf(mx[r], __shfl_xor_sync(kFull, mx[r], off));
+#pragma unroll
+  for (int r = 0; r < 8; ++r) {
+    const int gi = gi0 + warp + nw * r;
+    float s = mx[r] / 127.0f;
+    if (s == 0.0f) s = 1.0f;
+    const float ri = quant_recip(s);
+    const int q0 = quant_round_r(q.v[r].x, s, ri), q1 = quant_round_r(q.v[r].y, s, ri),
+              q2 = quant_round_r(q.v[r].z, s, ri), q3 = quant_round_r(q.v[r].w, s, ri);
+    const uint32_t own = (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) | ((uint32_t)(q2 & 0xFF) << 16) |
+                         ((uint32_t)(q3 & 0xFF) << 24);
+    const uint32_t other = __shfl_xor_sync(kFull, own, 1);
+    if (gi < M * G) {
+      const int m = gi >> lg, g = gi & (G - 1);
+      const int pc = g * 16 + (lane >> 1);  // 8-value piece: two lanes of four values each
+      if (lane & 1) xw[staged4_word(K, m, pc, 1)] = __byte_perm(other, own, 0x7531);
+      else xw[staged4_word(K, m, pc, 0)] = __byte_perm(own, other, 0x6420);
+      if (lane == 0) sqs[gi] = s;
     }
-    if (q4 == 0) sqs[q.gi] = s;
   }
 }
 // The passes after the first (M*G > 64 groups), then the block barrier.
 __device__ __forceinline__ StagedAct4 quant_wide_finish(unsigned char *smem, const float *x, int K, int M,
                                                        long x_stride) {
-  const int G = K >> 7, per_pass = blockDim.x >> 2;
+  const int G = K >> 7, per_pass = (blockDim.x >> 5) * 8;
 #pragma unroll 1
   for (int gi0 = per_pass; gi0 < M * G; gi0 += per_pass) {
     QuantWide q;
     quant_wide_load(q, x, K, M, x_stride, gi0);
-    quant_wide_store(q, smem, K, M);
+    quant_wide_store(q, smem, K, M, gi0);
   }
   __syncthreads();
   return StagedAct4{reinterpret_cast<const uint4 *>(smem), reinterpret_cast<float *>(smem + (size_t)M * K)};

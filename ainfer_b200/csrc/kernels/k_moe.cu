@@ -39,6 +39,18 @@ __global__ void __launch_bounds__(256) RouterTopK(const RouterTopKArgs a) {
 __host__ __device__ inline uint32_t moe_round128(uint32_t v) { return (v + 127u) & ~127u; }
 constexpr int kMoeTasks = 3;  // 64-byte weight groups a thread keeps in flight
 
+// The down projections of the same experts are read by the next kernel: start them towards L2.
+// Every thread of every block calls; the lines are dealt over the whole grid.
+__device__ __forceinline__ void prefetch_down_rows(const ExpertGateUpArgs &a, const ExpertW *sew) {
+  const int wl = a.H * (a.I / 2) / 128, sl = a.H * (a.I / 128) * 2 / 128;  // lines per slot: weights, scales
+  const int per = wl + sl, total = a.slots * per;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+    const int s = i / per, l = i - s * per;
+    prefetch_l2(l < wl ? sew[s].dP + (size_t)l * 128
+                       : reinterpret_cast<const uint8_t *>(sew[s].dS) + (size_t)(l - wl) * 128);
+  }
+}
+
 // The expert kernels stream only a few tens of KB per block (top-k experts of one token), so
 // they take the weights by direct loads (direct_dot.cuh), not through the shared-memory ring.
 __global__ void __launch_bounds__(256, 2) ExpertGateUp(const ExpertGateUpArgs a) {
@@ -58,16 +70,6 @@ __global__ void __launch_bounds__(256, 2) ExpertGateUp(const ExpertGateUpArgs a)
       reinterpret_cast<uint4 *>(sew + t / 3)[t % 3] = __ldg(reinterpret_cast<const uint4 *>(a.Experts + sel) + t % 3);
   });  // ends with a barrier: sew visible
   AINFER_MARK(1);
-  if (a.prefetch_down) {
-    // the down projections of the same experts are read by the next kernel: start them towards L2
-    const int wl = a.H * (a.I / 2) / 128, sl = a.H * (a.I / 128) * 2 / 128;  // lines per slot: weights, scales
-    const int per = wl + sl, total = a.slots * per;
-    for (int i = blockIdx.x * blockDim.x + t; i < total; i += gridDim.x * blockDim.x) {
-      const int s = i / per, l = i - s * per;
-      prefetch_l2(l < wl ? sew[s].dP + (size_t)l * 128
-                         : reinterpret_cast<const uint8_t *>(sew[s].dS) + (size_t)(l - wl) * 128);
-    }
-  }
   const int SB = gateup_sub_rows(a.H);  // pair rows per sub-block
   const int G = a.H / 128;
   long lo, hi;
@@ -79,6 +81,7 @@ __global__ void __launch_bounds__(256, 2) ExpertGateUp(const ExpertGateUpArgs a)
     __syncthreads();  // list complete; T of the previous sub-block is no longer read
     AINFER_MARK(2);
     direct_dot<kMoeTasks>(&list, act, T);
+    if (a.prefetch_down && sb == lo) prefetch_down_rows(a, sew);
     __syncthreads();
     AINFER_MARK(3);
     const long r = sb + threadIdx.x;
@@ -110,7 +113,7 @@ __global__ void __launch_bounds__(256, 2) ExpertDownCombine(const ExpertDownComb
   quant_wide_load(qw, a.Act, a.I, a.slots, a.I, 0);
   uint4 row = make_uint4(0, 0, 0, 0);
   if (row_thread) row = __ldg(reinterpret_cast<const uint4 *>(a.Experts + sel) + t % 3);
-  quant_wide_store(qw, moe_smem, a.I, a.slots);
+  quant_wide_store(qw, moe_smem, a.I, a.slots, 0);
   if (row_thread) reinterpret_cast<uint4 *>(sew + t / 3)[t % 3] = row;
   if (t < a.slots && t < kMaxSegs) sw[t] = selw;
   StagedAct4 act = quant_wide_finish(moe_smem, a.Act, a.I, a.slots, a.I);  // ends with a barrier

@@ -51,6 +51,16 @@ struct RmsNormQuantArgs {
 };
 __global__ void __launch_bounds__(256) RmsNormQuant(const RmsNormQuantArgs a) {
   pdl_launch_dependents();
+  // the norm weight does not depend on the predecessor: fetch this lane's share of the first
+  // groups of its warp while waiting (groups warp, warp + 8, ...)
+  constexpr int kPre = 2;
+  float4 wpre[kPre];
+#pragma unroll
+  for (int i = 0; i < kPre; ++i) {
+    const int g = (threadIdx.x >> 5) + 8 * i;
+    wpre[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (g < a.N / 128) wpre[i] = __ldg(reinterpret_cast<const float4 *>(a.W + g * 128) + (threadIdx.x & 31));
+  }
   pdl_wait();
   extern __shared__ __align__(16) unsigned char norm_smem[];
   float *xs = reinterpret_cast<float *>(norm_smem);  // [N]
@@ -87,7 +97,8 @@ __global__ void __launch_bounds__(256) RmsNormQuant(const RmsNormQuantArgs a) {
   for (int g = warp; g < N / 128; g += 8) {
     int j = g * 128 + lane * 4;
     float4 x = *reinterpret_cast<const float4 *>(xs + j);
-    float4 w = *reinterpret_cast<const float4 *>(a.W + j);
+    const int it = (g - warp) >> 3;
+    float4 w = it == 0 ? wpre[0] : it == 1 ? wpre[1] : *reinterpret_cast<const float4 *>(a.W + j);
     float4 y;
     y.x = (x.x * inv) * (1.0f + w.x);
     y.y = (x.y * inv) * (1.0f + w.y);
