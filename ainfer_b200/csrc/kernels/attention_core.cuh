@@ -139,24 +139,42 @@ __device__ __forceinline__ void attn_split_body(const AttnSplitArgs &a, int blk,
       q[g][0] = v0.x; q[g][1] = v0.y; q[g][2] = v0.z; q[g][3] = v0.w;
       q[g][4] = v1.x; q[g][5] = v1.y; q[g][6] = v1.z; q[g][7] = v1.w;
     }
-    // phase 1: scores. warp w takes tokens t0+w, t0+w+8, ...
-    for (int tt = warp; tt < nt; tt += 8) {
-      const int t = t0 + tt;
-      uint2 kw = __ldcg(reinterpret_cast<const uint2 *>(a.Kc + ((size_t)t * a.nKV + kv) * D + lane * 8));
-      float ks = f16_to_f32(__ldcg(a.Ks + (size_t)t * a.nKV + kv));
-      float kf[8];
+    // phase 1: scores. warp w takes tokens t0+w, t0+w+8, ...; all its K rows (C/8 of them) are
+    // fetched before the first is used, so the warp pays one round trip, not one per token
+    constexpr int kTok = C / 8;
+    uint2 kwv[kTok];
+    uint16_t ksv[kTok];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        kf[j] = (float)(int)(int8_t)((kw.x >> (8 * j)) & 0xFF);
-        kf[4 + j] = (float)(int)(int8_t)((kw.y >> (8 * j)) & 0xFF);
+    for (int i = 0; i < kTok; ++i) {
+      const int tt = warp + 8 * i;
+      kwv[i] = make_uint2(0, 0);
+      ksv[i] = 0;
+      if (tt < nt) {
+        const int t = t0 + tt;
+        kwv[i] = __ldcg(reinterpret_cast<const uint2 *>(a.Kc + ((size_t)t * a.nKV + kv) * D + lane * 8));
+        ksv[i] = __ldcg(a.Ks + (size_t)t * a.nKV + kv);
       }
+    }
 #pragma unroll
-      for (int g = 0; g < GQ; ++g) {
-        float acc = 0.0f;
+    for (int i = 0; i < kTok; ++i) {
+      const int tt = warp + 8 * i;
+      if (tt < nt) {
+        const uint2 kw = kwv[i];
+        const float ks = f16_to_f32(ksv[i]);
+        float kf[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) acc = fmaf(q[g][j], kf[j], acc);
-        acc = warp_tree_sum(acc);
-        if (lane == 0) sc[g][tt] = (acc * ks) * scale;
+        for (int j = 0; j < 4; ++j) {
+          kf[j] = (float)(int)(int8_t)((kw.x >> (8 * j)) & 0xFF);
+          kf[4 + j] = (float)(int)(int8_t)((kw.y >> (8 * j)) & 0xFF);
+        }
+#pragma unroll
+        for (int g = 0; g < GQ; ++g) {
+          float acc = 0.0f;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc = fmaf(q[g][j], kf[j], acc);
+          acc = warp_tree_sum(acc);
+          if (lane == 0) sc[g][tt] = (acc * ks) * scale;
+        }
       }
     }
     __syncthreads();
@@ -188,6 +206,7 @@ __device__ __forceinline__ void attn_split_body(const AttnSplitArgs &a, int blk,
 #pragma unroll
     for (int g = 0; g < GQ; ++g) acc[g] = 0.0f;
     const int8_t *vp = a.Vc + ((size_t)t0 * a.nKV + kv) * D + tid;
+#pragma unroll 8
     for (int tt = 0; tt < nt; ++tt) {
       float v = (float)(int)__ldcg(vp + (size_t)tt * a.nKV * D);
 #pragma unroll

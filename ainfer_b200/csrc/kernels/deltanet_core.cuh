@@ -31,9 +31,23 @@ struct DeltaNetStepArgs {
 
 constexpr int kDnSlices = 4;  // column slices per head (32 columns each)
 
+constexpr int kDnSeg = 16;  // state rows per warp
+// This thread's state values of item `item` (rows warp*16 .. +15, its column). The state is written
+// only by this kernel, so a caller may fetch the first item's values before it waits for its
+// predecessor.
+__device__ __forceinline__ void deltanet_load_state(const DeltaNetStepArgs &a, int item, float (&s)[kDnSeg]) {
+  const int h = item / kDnSlices, slice = item % kDnSlices;
+  const int warp = threadIdx.x >> 5, col = slice * 32 + (threadIdx.x & 31);
+  const float *Sh = a.S + (size_t)h * 128 * 128;
+#pragma unroll
+  for (int r = 0; r < kDnSeg; ++r) s[r] = __ldcg(Sh + (size_t)(warp * kDnSeg + r) * 128 + col);
+}
+
 // Body for a 256-thread block; blk/nblk give the block its share of the (head, slice) items.
-__device__ __forceinline__ void deltanet_step_body(const DeltaNetStepArgs &a, int blk, int nblk) {
-  constexpr int D = 128, SEG = 16;
+// first: state values of item `blk` already loaded (or null).
+__device__ __forceinline__ void deltanet_step_body(const DeltaNetStepArgs &a, int blk, int nblk,
+                                                   const float (*first)[kDnSeg] = nullptr) {
+  constexpr int D = 128, SEG = kDnSeg;
   __shared__ float qs[D], ks[D];
   __shared__ float part[8][32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -44,8 +58,12 @@ __device__ __forceinline__ void deltanet_step_body(const DeltaNetStepArgs &a, in
     // issue the state loads first: 16 rows per warp, one column per lane
     float *Sh = a.S + (size_t)h * D * D;
     float s[SEG];
+    if (first && item == blk) {
 #pragma unroll
-    for (int r = 0; r < SEG; ++r) s[r] = __ldcg(Sh + (size_t)(warp * SEG + r) * D + col);
+      for (int r = 0; r < SEG; ++r) s[r] = (*first)[r];
+    } else {
+      deltanet_load_state(a, item, s);
+    }
     // l2norm of q (warp 0) and k (warp 1)
     if (warp < 2) {
       const float *src = a.Mx + (warp == 0 ? (size_t)kh * D : (size_t)a.nK * D + (size_t)kh * D);

@@ -142,8 +142,11 @@ struct GatedNormQuantArgs {
 };
 __global__ void __launch_bounds__(128) GatedNormQuant(const GatedNormQuantArgs a) {
   pdl_launch_dependents();
-  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float wn[4];  // the norm weight does not depend on the predecessor
+#pragma unroll
+  for (int i = 0; i < 4; ++i) wn[i] = __ldg(a.W + lane + 32 * i);
+  pdl_wait();
   for (int h = blockIdx.x * 4 + warp; h < a.heads; h += gridDim.x * 4) {
     const float *o = a.O + (size_t)h * 128;
     const float *z = a.Z + (size_t)h * 128;
@@ -161,7 +164,7 @@ __global__ void __launch_bounds__(128) GatedNormQuant(const GatedNormQuantArgs a
     for (int i = 0; i < 4; ++i) {
       int d = lane + 32 * i;
       float zv = z[d];
-      y[i] = ((a.W[d] * ov[i]) * inv) * (zv / (1.0f + det_expf(-zv)));
+      y[i] = ((wn[i] * ov[i]) * inv) * (zv / (1.0f + det_expf(-zv)));
       m = fmaxf(m, fabsf(y[i]));
     }
     m = warp_max(m);
