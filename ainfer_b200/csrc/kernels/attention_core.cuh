@@ -206,7 +206,7 @@ __device__ __forceinline__ void attn_split_body(const AttnSplitArgs &a, int blk,
 #pragma unroll
     for (int g = 0; g < GQ; ++g) acc[g] = 0.0f;
     const int8_t *vp = a.Vc + ((size_t)t0 * a.nKV + kv) * D + tid;
-#pragma unroll 8
+#pragma unroll 16
     for (int tt = 0; tt < nt; ++tt) {
       float v = (float)(int)__ldcg(vp + (size_t)tt * a.nKV * D);
 #pragma unroll
@@ -248,7 +248,9 @@ struct AttnCombineArgs {
 };
 __device__ __forceinline__ void attn_combine_body(const AttnCombineArgs &a, int blk, int nblk) {
   constexpr int D = kHeadDim, C = kAttnChunk;
+  constexpr int kCombineChunks = 1024;  // contexts up to 65536 tokens take the shared-memory path
   __shared__ float wmax[8];
+  __shared__ float s_pm[kCombineChunks], s_pf[kCombineChunks];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   int T = __ldcg(a.Ctrl + CTRL_LEN);
   if (T > a.max_ctx) T = a.max_ctx;
@@ -257,16 +259,36 @@ __device__ __forceinline__ void attn_combine_body(const AttnCombineArgs &a, int 
     const float *pm = a.Pm + (size_t)h * a.max_chunks;
     const float *pse = a.Pse + (size_t)h * a.max_chunks;
     const float *pacc = a.Pacc + (size_t)h * a.max_chunks * D;
-    float M = -INFINITY;
-    for (int c = 0; c < nch; ++c) M = fmaxf(M, __ldcg(pm + c));
-    float se = 0.0f, acc = 0.0f;
-    for (int c = 0; c < nch; ++c) {
-      float f = det_expf(__ldcg(pm + c) - M);
-      se = fmaf(__ldcg(pse + c), f, se);
-      acc = fmaf(__ldcg(pacc + (size_t)c * D + tid), f, acc);
+    const float gate = __ldcg(a.Q16 + (size_t)h * 2 * D + D + tid);  // in flight during the sums below
+    float M = -INFINITY, se = 0.0f, acc = 0.0f;
+    if (nch <= kCombineChunks) {
+      // The chunk maxima and sums are fetched once by the block (thread c takes chunk c) and the
+      // rescale factors exp(m_c - M) are computed once; every thread then runs the same sums in
+      // ascending chunk order from shared memory, with its partial-output loads 16 in flight.
+      __syncthreads();  // s_pm/s_pf of the previous head are no longer read
+      for (int c = tid; c < nch; c += 256) {
+        s_pm[c] = __ldcg(pm + c);
+        s_pf[c] = __ldcg(pse + c);
+      }
+      __syncthreads();
+      for (int c = 0; c < nch; ++c) M = fmaxf(M, s_pm[c]);
+      __syncthreads();  // every thread has M: s_pm may be overwritten with the factors
+      for (int c = tid; c < nch; c += 256) s_pm[c] = det_expf(s_pm[c] - M);
+      __syncthreads();
+      for (int c = 0; c < nch; ++c) se = fmaf(s_pf[c], s_pm[c], se);
+#pragma unroll 16
+      for (int c = 0; c < nch; ++c) acc = fmaf(__ldcg(pacc + (size_t)c * D + tid), s_pm[c], acc);
+    } else {
+#pragma unroll 8
+      for (int c = 0; c < nch; ++c) M = fmaxf(M, __ldcg(pm + c));
+#pragma unroll 8
+      for (int c = 0; c < nch; ++c) {
+        float f = det_expf(__ldcg(pm + c) - M);
+        se = fmaf(__ldcg(pse + c), f, se);
+        acc = fmaf(__ldcg(pacc + (size_t)c * D + tid), f, acc);
+      }
     }
     float o = acc / se;
-    float gate = __ldcg(a.Q16 + (size_t)h * 2 * D + D + tid);
     float y = o / (1.0f + det_expf(-gate));
     if (a.Att) a.Att[(size_t)h * D + tid] = y;
     // activation quantiser: groups of 128 = 4 warps

@@ -5,7 +5,33 @@
 namespace ainfer {
 
 __global__ void __launch_bounds__(256) AttnPrep(const AttnPrepArgs a) { pdl_launch_dependents(); pdl_wait(); attn_prep_body(a, blockIdx.x, gridDim.x); }
-__global__ void __launch_bounds__(256) AttnSplit(const AttnSplitArgs a) { pdl_launch_dependents(); pdl_wait(); attn_split_dispatch(a, blockIdx.x, gridDim.x); }
+__global__ void __launch_bounds__(256) AttnSplit(const AttnSplitArgs a) {
+  pdl_launch_dependents();
+  // While the predecessor (which only appends the newest token) runs: start this block's first
+  // chunk of the KV cache towards L2, one 128-byte line per thread. The context length is in
+  // the control block since the end of the previous step; a stale value would only change what
+  // is prefetched (rows stay below max_ctx).
+  {
+    int T = __ldcg(a.Ctrl + CTRL_LEN);
+    if (T > a.max_ctx) T = a.max_ctx;
+    const int nch = (T + kAttnChunk - 1) / kAttnChunk, item = blockIdx.x;
+    if (item < nch * a.nKV) {
+      const int c = item / a.nKV, kv = item % a.nKV, tid = threadIdx.x;
+      const int row = (tid & 127) >> 1, t = c * kAttnChunk + row;
+      if (t < T) {
+        const int8_t *base = (tid < 128 ? a.Kc : a.Vc) + ((size_t)t * a.nKV + kv) * kHeadDim + (tid & 1) * 128;
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(base));
+      }
+      if (tid < 2) {
+        const uint16_t *sc = (tid == 0 ? a.Ks : a.Vs) + (size_t)c * kAttnChunk * a.nKV;
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(sc));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(sc + 64));
+      }
+    }
+  }
+  pdl_wait();
+  attn_split_dispatch(a, blockIdx.x, gridDim.x);
+}
 __global__ void __launch_bounds__(256) AttnCombine(const AttnCombineArgs a) { pdl_launch_dependents(); pdl_wait(); attn_combine_body(a, blockIdx.x, gridDim.x); }
 
 #define F(f) AINFER_ARG(AttnPrepArgs, f)
