@@ -117,8 +117,15 @@ struct AttnSplitArgs {
   int32_t nQ, nKV, max_ctx, max_chunks;
 };
 
-template <int GQ>  // query heads per KV head
-__device__ __forceinline__ void attn_split_body(const AttnSplitArgs &a, int blk, int nblk) {
+// kStage: the chunk's K and V rows and their scales are first copied to shared memory by the
+// whole block (every global load of the item in flight at once: one round trip), and the token
+// loops run rolled over shared memory. A kernel of this chain runs once per layer with a cold
+// instruction cache, so its time follows the amount of distinct code it executes: the rolled
+// loops are several times faster here than the same work unrolled over registers.
+// kvs: 2*C*D bytes (K rows, then V rows), kss/vss: C scales each; shared memory of the caller.
+template <int GQ, bool kStage>  // query heads per KV head
+__device__ __forceinline__ void attn_split_body(const AttnSplitArgs &a, int blk, int nblk, unsigned char *kvs,
+                                                uint16_t *kss, uint16_t *vss) {
   constexpr int D = kHeadDim, C = kAttnChunk;
   __shared__ float sc[GQ][C];   // scores, then p = w * v_scale
   __shared__ float hmax[GQ], hse[GQ];
@@ -139,28 +146,41 @@ __device__ __forceinline__ void attn_split_body(const AttnSplitArgs &a, int blk,
       q[g][0] = v0.x; q[g][1] = v0.y; q[g][2] = v0.z; q[g][3] = v0.w;
       q[g][4] = v1.x; q[g][5] = v1.y; q[g][6] = v1.z; q[g][7] = v1.w;
     }
-    // phase 1: scores. warp w takes tokens t0+w, t0+w+8, ...; all its K rows (C/8 of them) are
-    // fetched before the first is used, so the warp pays one round trip, not one per token
-    constexpr int kTok = C / 8;
-    uint2 kwv[kTok];
-    uint16_t ksv[kTok];
+    if (kStage) {
+      const uint4 *kg = reinterpret_cast<const uint4 *>(a.Kc + ((size_t)t0 * a.nKV + kv) * D);
+      const uint4 *vg = reinterpret_cast<const uint4 *>(a.Vc + ((size_t)t0 * a.nKV + kv) * D);
+      const size_t rs = (size_t)a.nKV * (D / 16);  // 16-byte pieces between consecutive tokens' rows
+      uint4 kr[C * D / 16 / 256], vr[C * D / 16 / 256];
 #pragma unroll
-    for (int i = 0; i < kTok; ++i) {
-      const int tt = warp + 8 * i;
-      kwv[i] = make_uint2(0, 0);
-      ksv[i] = 0;
-      if (tt < nt) {
-        const int t = t0 + tt;
-        kwv[i] = __ldcg(reinterpret_cast<const uint2 *>(a.Kc + ((size_t)t * a.nKV + kv) * D + lane * 8));
-        ksv[i] = __ldcg(a.Ks + (size_t)t * a.nKV + kv);
+      for (int u = 0; u < C * D / 16 / 256; ++u) {
+        const int i = tid + 256 * u, row = i / (D / 16), pc = i % (D / 16);
+        kr[u] = make_uint4(0, 0, 0, 0);
+        vr[u] = make_uint4(0, 0, 0, 0);
+        if (row < nt) {
+          kr[u] = __ldcg(kg + row * rs + pc);
+          vr[u] = __ldcg(vg + row * rs + pc);
+        }
       }
-    }
+      uint16_t ksc = 0, vsc = 0;
+      if (tid < nt) {
+        ksc = __ldcg(a.Ks + (size_t)(t0 + tid) * a.nKV + kv);
+        vsc = __ldcg(a.Vs + (size_t)(t0 + tid) * a.nKV + kv);
+      }
 #pragma unroll
-    for (int i = 0; i < kTok; ++i) {
-      const int tt = warp + 8 * i;
-      if (tt < nt) {
-        const uint2 kw = kwv[i];
-        const float ks = f16_to_f32(ksv[i]);
+      for (int u = 0; u < C * D / 16 / 256; ++u) {
+        reinterpret_cast<uint4 *>(kvs)[tid + 256 * u] = kr[u];
+        reinterpret_cast<uint4 *>(kvs + C * D)[tid + 256 * u] = vr[u];
+      }
+      if (tid < C) {
+        kss[tid] = ksc;
+        vss[tid] = vsc;
+      }
+      __syncthreads();
+      // phase 1: scores. warp w takes tokens t0+w, t0+w+8, ...
+#pragma unroll 1
+      for (int tt = warp; tt < nt; tt += 8) {
+        const uint2 kw = reinterpret_cast<const uint2 *>(kvs)[tt * (D / 8) + lane];
+        const float ks = f16_to_f32(kss[tt]);
         float kf[8];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -176,8 +196,48 @@ __device__ __forceinline__ void attn_split_body(const AttnSplitArgs &a, int blk,
           if (lane == 0) sc[g][tt] = (acc * ks) * scale;
         }
       }
+    } else {
+    // phase 1: scores. warp w takes tokens t0+w, t0+w+8, ...; all its K rows (C/8 of them) are
+      // fetched before the first is used, so the warp pays one round trip, not one per token
+      constexpr int kTok = C / 8;
+      uint2 kwv[kTok];
+      uint16_t ksv[kTok];
+#pragma unroll
+      for (int i = 0; i < kTok; ++i) {
+        const int tt = warp + 8 * i;
+        kwv[i] = make_uint2(0, 0);
+        ksv[i] = 0;
+        if (tt < nt) {
+          const int t = t0 + tt;
+          kwv[i] = __ldcg(reinterpret_cast<const uint2 *>(a.Kc + ((size_t)t * a.nKV + kv) * D + lane * 8));
+          ksv[i] = __ldcg(a.Ks + (size_t)t * a.nKV + kv);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < kTok; ++i) {
+        const int tt = warp + 8 * i;
+        if (tt < nt) {
+          const uint2 kw = kwv[i];
+          const float ks = f16_to_f32(ksv[i]);
+          float kf[8];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            kf[j] = (float)(int)(int8_t)((kw.x >> (8 * j)) & 0xFF);
+            kf[4 + j] = (float)(int)(int8_t)((kw.y >> (8 * j)) & 0xFF);
+          }
+#pragma unroll
+          for (int g = 0; g < GQ; ++g) {
+            float acc = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc = fmaf(q[g][j], kf[j], acc);
+            acc = warp_tree_sum(acc);
+            if (lane == 0) sc[g][tt] = (acc * ks) * scale;
+          }
+        }
+      }
     }
     __syncthreads();
+    AINFER_MARK(1);
     // phase 2: per head max, weights, sum of exp (ascending t)
     if (tid < GQ) {
       float mx = -INFINITY;
@@ -198,19 +258,30 @@ __device__ __forceinline__ void attn_split_body(const AttnSplitArgs &a, int blk,
     __syncthreads();
     for (int i = tid; i < GQ * nt; i += 256) {
       int g = i / nt, tt = i % nt;
-      sc[g][tt] = sc[g][tt] * f16_to_f32(__ldcg(a.Vs + (size_t)(t0 + tt) * a.nKV + kv));
+      sc[g][tt] = sc[g][tt] * f16_to_f32(kStage ? vss[tt] : __ldcg(a.Vs + (size_t)(t0 + tt) * a.nKV + kv));
     }
     __syncthreads();
+    AINFER_MARK(2);
     // phase 3: thread d accumulates dim d for all heads of the group, ascending t
     float acc[GQ];
 #pragma unroll
     for (int g = 0; g < GQ; ++g) acc[g] = 0.0f;
-    const int8_t *vp = a.Vc + ((size_t)t0 * a.nKV + kv) * D + tid;
-#pragma unroll 16
-    for (int tt = 0; tt < nt; ++tt) {
-      float v = (float)(int)__ldcg(vp + (size_t)tt * a.nKV * D);
+    if (kStage) {
+      const int8_t *vs = reinterpret_cast<const int8_t *>(kvs + C * D) + tid;
+#pragma unroll 2
+      for (int tt = 0; tt < nt; ++tt) {
+        const float v = (float)(int)vs[tt * D];
 #pragma unroll
-      for (int g = 0; g < GQ; ++g) acc[g] = fmaf(sc[g][tt], v, acc[g]);
+        for (int g = 0; g < GQ; ++g) acc[g] = fmaf(sc[g][tt], v, acc[g]);
+      }
+    } else {
+      const int8_t *vp = a.Vc + ((size_t)t0 * a.nKV + kv) * D + tid;
+#pragma unroll 16
+      for (int tt = 0; tt < nt; ++tt) {
+        float v = (float)(int)__ldcg(vp + (size_t)tt * a.nKV * D);
+#pragma unroll
+        for (int g = 0; g < GQ; ++g) acc[g] = fmaf(sc[g][tt], v, acc[g]);
+      }
     }
 #pragma unroll
     for (int g = 0; g < GQ; ++g) {
@@ -221,17 +292,21 @@ __device__ __forceinline__ void attn_split_body(const AttnSplitArgs &a, int blk,
         a.Pse[slot] = hse[g];
       }
     }
+    AINFER_MARK(3);
     __syncthreads();
   }
 }
 
+template <bool kStage>
 __device__ __forceinline__ void attn_split_dispatch(const AttnSplitArgs &a, int blk, int nblk) {
+  __shared__ __align__(16) unsigned char kvs[kStage ? 2 * kAttnChunk * kHeadDim : 16];
+  __shared__ uint16_t kss[kStage ? kAttnChunk : 1], vss[kStage ? kAttnChunk : 1];
   switch (a.nQ / a.nKV) {
-    case 1: attn_split_body<1>(a, blk, nblk); break;
-    case 2: attn_split_body<2>(a, blk, nblk); break;
-    case 4: attn_split_body<4>(a, blk, nblk); break;
-    case 6: attn_split_body<6>(a, blk, nblk); break;
-    case 8: attn_split_body<8>(a, blk, nblk); break;
+    case 1: attn_split_body<1, kStage>(a, blk, nblk, kvs, kss, vss); break;
+    case 2: attn_split_body<2, kStage>(a, blk, nblk, kvs, kss, vss); break;
+    case 4: attn_split_body<4, kStage>(a, blk, nblk, kvs, kss, vss); break;
+    case 6: attn_split_body<6, kStage>(a, blk, nblk, kvs, kss, vss); break;
+    case 8: attn_split_body<8, kStage>(a, blk, nblk, kvs, kss, vss); break;
     default: break;  // rejected on the host
   }
 }

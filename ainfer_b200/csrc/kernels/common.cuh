@@ -22,7 +22,9 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 #ifndef AINFER_TIMELINE
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 #define AINFER_MARK(id)
+#define AINFER_MARK_ANY(id)
 #else
+#define AINFER_MARK_ANY(id) ::ainfer::timeline_mark(id, true)
 #define AINFER_MARK(id) ::ainfer::timeline_mark(id)
 // Timeline build (-DAINFER_TIMELINE): block 0 of every kernel records the global
 // timer when it reaches its dependency wait and when the wait returns (its
@@ -54,8 +56,9 @@ __device__ __forceinline__ void pdl_wait() {
   }
 }
 // A point inside a kernel (block 0, thread 0): stored in the same buffer as (id | 1 << 63, time).
-__device__ __forceinline__ void timeline_mark(int id) {
-  if (blockIdx.x == 0 && threadIdx.x == 0 && g_timeline != nullptr) {
+// any_block: for code that only one block of the grid runs (a last-block section).
+__device__ __forceinline__ void timeline_mark(int id, bool any_block = false) {
+  if ((blockIdx.x == 0 || any_block) && threadIdx.x == 0 && g_timeline != nullptr) {
     const unsigned long long t = global_timer_ns();
     const unsigned long long slot = atomicAdd(g_timeline, 1ull);
     if (slot < g_timeline[1]) {

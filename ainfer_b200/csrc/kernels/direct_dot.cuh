@@ -238,6 +238,57 @@ __device__ __forceinline__ void quant_wide_store(const QuantWide &q, unsigned ch
     }
   }
 }
+// Rolled form for a contiguous [M][K] fp32 source of at most 8192 values: the block copies the
+// values to shared memory (`raw`, M*K floats; all loads of a thread in flight at once), then
+// each warp walks its groups in a rolled loop. Far less distinct code than the register form
+// above, which matters for a kernel that runs once per layer with a cold instruction cache.
+struct RawCopy {
+  float4 v[8];
+};
+__device__ __forceinline__ void raw_copy_load(RawCopy &c, const float *x, int count4) {
+#pragma unroll
+  for (int u = 0; u < 8; ++u) {
+    const int i = threadIdx.x + u * 256;
+    c.v[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (i < count4) c.v[u] = __ldcg(reinterpret_cast<const float4 *>(x) + i);
+  }
+}
+__device__ __forceinline__ void raw_copy_store(const RawCopy &c, float *raw, int count4) {
+#pragma unroll
+  for (int u = 0; u < 8; ++u) {
+    const int i = threadIdx.x + u * 256;
+    if (i < count4) reinterpret_cast<float4 *>(raw)[i] = c.v[u];
+  }
+}
+// After raw_copy_store and a block barrier; ends with a block barrier.
+__device__ __forceinline__ StagedAct4 quant_rolled(unsigned char *smem, const float *raw, int K, int M) {
+  uint32_t *xw = reinterpret_cast<uint32_t *>(smem);
+  const int G = K >> 7, lg = 31 - __clz(G);
+  float *sqs = reinterpret_cast<float *>(smem + (size_t)M * K);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+#pragma unroll 1
+  for (int gi = warp; gi < M * G; gi += nw) {
+    const float4 v = reinterpret_cast<const float4 *>(raw + (size_t)gi * 128)[lane];
+    float mx = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+    mx = warp_max(mx);
+    float s = mx / 127.0f;
+    if (s == 0.0f) s = 1.0f;
+    const float ri = quant_recip(s);
+    const int q0 = quant_round_r(v.x, s, ri), q1 = quant_round_r(v.y, s, ri), q2 = quant_round_r(v.z, s, ri),
+              q3 = quant_round_r(v.w, s, ri);
+    const uint32_t own = (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) | ((uint32_t)(q2 & 0xFF) << 16) |
+                         ((uint32_t)(q3 & 0xFF) << 24);
+    const uint32_t other = __shfl_xor_sync(kFull, own, 1);
+    const int m = gi >> lg, g = gi & (G - 1);
+    const int pc = g * 16 + (lane >> 1);
+    if (lane & 1) xw[staged4_word(K, m, pc, 1)] = __byte_perm(other, own, 0x7531);
+    else xw[staged4_word(K, m, pc, 0)] = __byte_perm(own, other, 0x6420);
+    if (lane == 0) sqs[gi] = s;
+  }
+  __syncthreads();
+  return StagedAct4{reinterpret_cast<const uint4 *>(smem), sqs};
+}
+
 // The passes after the first (M*G > 64 groups), then the block barrier.
 __device__ __forceinline__ StagedAct4 quant_wide_finish(unsigned char *smem, const float *x, int K, int M,
                                                        long x_stride) {

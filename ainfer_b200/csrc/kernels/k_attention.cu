@@ -30,7 +30,7 @@ __global__ void __launch_bounds__(256) AttnSplit(const AttnSplitArgs a) {
     }
   }
   pdl_wait();
-  attn_split_dispatch(a, blockIdx.x, gridDim.x);
+  attn_split_dispatch<true>(a, blockIdx.x, gridDim.x);
 }
 __global__ void __launch_bounds__(256) AttnCombine(const AttnCombineArgs a) { pdl_launch_dependents(); pdl_wait(); attn_combine_body(a, blockIdx.x, gridDim.x); }
 

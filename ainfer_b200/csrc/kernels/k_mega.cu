@@ -227,7 +227,7 @@ static __device__ __noinline__ void mega_attn_prep(const AttnPrepArgs &a, int bl
   attn_prep_body(a, blk, nblk);
 }
 static __device__ __noinline__ void mega_attn_split(const AttnSplitArgs &a, int blk, int nblk) {
-  attn_split_dispatch(a, blk, nblk);
+  attn_split_dispatch<false>(a, blk, nblk);
 }
 static __device__ __noinline__ void mega_attn_combine(const AttnCombineArgs &a, int blk, int nblk) {
   attn_combine_body(a, blk, nblk);

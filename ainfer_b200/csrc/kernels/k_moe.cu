@@ -109,14 +109,31 @@ __global__ void __launch_bounds__(256, 2) ExpertDownCombine(const ExpertDownComb
   float selw = 0.0f;
   if (row_thread) sel = a.SelIdx ? __ldcg(a.SelIdx + t / 3) : t / 3;
   if (t < a.slots && t < kMaxSegs) selw = __ldcg(a.SelW + t);
-  QuantWide qw;
-  quant_wide_load(qw, a.Act, a.I, a.slots, a.I, 0);
-  uint4 row = make_uint4(0, 0, 0, 0);
-  if (row_thread) row = __ldg(reinterpret_cast<const uint4 *>(a.Experts + sel) + t % 3);
-  quant_wide_store(qw, moe_smem, a.I, a.slots, 0);
-  if (row_thread) reinterpret_cast<uint4 *>(sew + t / 3)[t % 3] = row;
-  if (t < a.slots && t < kMaxSegs) sw[t] = selw;
-  StagedAct4 act = quant_wide_finish(moe_smem, a.Act, a.I, a.slots, a.I);  // ends with a barrier
+  // activations: rolled shared-memory quantiser when they fit its copy (slots * I <= 8192)
+  const int count4 = a.slots * a.I / 4;
+  const bool rolled = count4 <= 8 * 256;
+  float *raw = reinterpret_cast<float *>(moe_smem + moe_round128(staged4_bytes(a.I, a.slots)));
+  StagedAct4 act;
+  if (rolled) {
+    RawCopy rc;
+    raw_copy_load(rc, a.Act, count4);
+    uint4 row = make_uint4(0, 0, 0, 0);
+    if (row_thread) row = __ldg(reinterpret_cast<const uint4 *>(a.Experts + sel) + t % 3);
+    raw_copy_store(rc, raw, count4);
+    if (row_thread) reinterpret_cast<uint4 *>(sew + t / 3)[t % 3] = row;
+    if (t < a.slots && t < kMaxSegs) sw[t] = selw;
+    __syncthreads();
+    act = quant_rolled(moe_smem, raw, a.I, a.slots);  // ends with a barrier
+  } else {
+    QuantWide qw;
+    quant_wide_load(qw, a.Act, a.I, a.slots, a.I, 0);
+    uint4 row = make_uint4(0, 0, 0, 0);
+    if (row_thread) row = __ldg(reinterpret_cast<const uint4 *>(a.Experts + sel) + t % 3);
+    quant_wide_store(qw, moe_smem, a.I, a.slots, 0);
+    if (row_thread) reinterpret_cast<uint4 *>(sew + t / 3)[t % 3] = row;
+    if (t < a.slots && t < kMaxSegs) sw[t] = selw;
+    act = quant_wide_finish(moe_smem, a.Act, a.I, a.slots, a.I);  // ends with a barrier
+  }
   AINFER_MARK(1);
   const int SB = down_sub_rows(a.I, a.slots);
   const int G = a.I / 128;
@@ -237,7 +254,8 @@ AINFER_REGISTER(ExpertGateUp, ExpertGateUpArgs, 256, 0, 0, gateup_smem_fn, F(Exp
 
 static uint32_t down_smem_fn(const void *args) {
   const ExpertDownCombineArgs *a = (const ExpertDownCombineArgs *)args;
-  return moe_round128(staged4_bytes(a->I, a->slots));
+  const uint32_t raw = (uint32_t)a->slots * (uint32_t)a->I * 4u;  // fp32 copy for the rolled quantiser
+  return moe_round128(staged4_bytes(a->I, a->slots)) + (raw <= 8192u * 4u ? raw : 0u);
 }
 #define F(f) AINFER_ARG(ExpertDownCombineArgs, f)
 AINFER_REGISTER(ExpertDownCombine, ExpertDownCombineArgs, 256, 0, 0, down_smem_fn, F(Experts),

@@ -119,56 +119,59 @@ __device__ __forceinline__ void router_logits_rows(const RouterTopKArgs &a, int 
   }
 }
 
-// Top-k by one warp (all 32 lanes call), kPerLane candidates per lane in registers
-// (E <= 32 * kPerLane). Probabilities are >= 0, so their bit patterns order like unsigned
-// integers; key = bits + 1 keeps 0 free for "not a candidate" (beyond E, or already selected).
-// Per rank: the lane's best key and the lowest index holding it by two balanced trees
-// (depth log2 kPerLane, no long dependent chain), then the warp maximum and, among its
-// holders, the lowest index by two hardware warp reductions: the (value desc, index asc)
-// rule of a comparison tournament.
+// Top-k of the block's probabilities sp[0..E) in two levels. Probabilities are >= 0, so their
+// bit patterns order like unsigned integers; key = bits + 1 keeps 0 free for "no candidate".
+// Level 1: each of eight warps takes an eighth of the experts (four per lane) and extracts its
+// own best k+1 in (value desc, index asc) order: every expert of the global top k+1 is among
+// them. Level 2: warp 0 extracts the global order from those 8 (k+1) candidates by the same
+// rule. One extraction = the lane's best key and the lowest index holding it, then the warp
+// maximum and, among its holders, the lowest index by two hardware warp reductions. The
+// result is that of a comparison tournament over all E; only the work per step is small.
+constexpr int kTopkWarps = 8, kTopkMaxSel = 33;  // k <= 32
 template <int kPerLane>
-__device__ __forceinline__ void router_topk_warp(float *sp, int E, int k, bool has_shared, int32_t *sel_idx,
-                                                 float *sel_w, float *near_gap) {
-  const int lane = threadIdx.x & 31;
-  unsigned v[kPerLane];
+__device__ __forceinline__ void topk_extract(unsigned (&key)[kPerLane], const unsigned (&idx)[kPerLane],
+                                             unsigned &wv, unsigned &wi) {
+  unsigned m = key[0];
 #pragma unroll
-  for (int i = 0; i < kPerLane; ++i) {
-    const int e = lane + 32 * i;
-    v[i] = e < E ? __float_as_uint(sp[e]) + 1u : 0u;
+  for (int i = 1; i < kPerLane; ++i) m = key[i] > m ? key[i] : m;
+  unsigned bi = 0x7FFFFFFFu;
+#pragma unroll
+  for (int i = 0; i < kPerLane; ++i)
+    if (key[i] == m && m != 0u && idx[i] < bi) bi = idx[i];
+  wv = __reduce_max_sync(kFull, m);
+  wi = __reduce_min_sync(kFull, m == wv ? bi : 0x7FFFFFFFu);
+#pragma unroll
+  for (int i = 0; i < kPerLane; ++i)
+    if (key[i] == wv && idx[i] == wi) key[i] = 0u;  // never extracted again
+}
+template <int kPerLane2>
+__device__ __forceinline__ void topk_level2(const unsigned *ck, const unsigned *ci, int ncand, float *sp, int E,
+                                            int k, bool has_shared, int32_t *sel_idx, float *sel_w,
+                                            float *near_gap) {
+  const int lane = threadIdx.x & 31;
+  unsigned key[kPerLane2], idx[kPerLane2];
+#pragma unroll
+  for (int i = 0; i < kPerLane2; ++i) {
+    const int c = lane + 32 * i;
+    key[i] = c < ncand ? ck[c] : 0u;
+    idx[i] = c < ncand ? ci[c] : 0x7FFFFFFFu;
   }
   float s = 0.0f, lastp = 0.0f;
   float wsel = 0.0f;  // lane j keeps the weight of rank j (k <= 32)
 #pragma unroll 1
   for (int j = 0; j <= k && j < E; ++j) {
-    unsigned m[kPerLane];
-#pragma unroll
-    for (int i = 0; i < kPerLane; ++i) m[i] = v[i];
-#pragma unroll
-    for (int w = kPerLane / 2; w >= 1; w >>= 1)
-#pragma unroll
-      for (int i = 0; i < w; ++i) m[i] = m[i] > m[i + w] ? m[i] : m[i + w];
-    const unsigned bv = m[0];
-    unsigned c[kPerLane];
-#pragma unroll
-    for (int i = 0; i < kPerLane; ++i) c[i] = v[i] == bv ? (unsigned)i : 0xFFFFu;
-#pragma unroll
-    for (int w = kPerLane / 2; w >= 1; w >>= 1)
-#pragma unroll
-      for (int i = 0; i < w; ++i) c[i] = c[i] < c[i + w] ? c[i] : c[i + w];
-    const unsigned bi = bv ? (unsigned)lane + 32u * c[0] : 0x7FFFFFFFu;
-    const unsigned wv = __reduce_max_sync(kFull, bv);
-    const int wi = (int)__reduce_min_sync(kFull, bv == wv ? bi : 0x7FFFFFFFu);
+    unsigned wv, wi;
+    topk_extract<kPerLane2>(key, idx, wv, wi);
     const float p = __uint_as_float(wv - 1u);
     if (j == k) {
       if (lane == 0) *near_gap = lastp > 0.0f ? (lastp - p) / lastp : 0.0f;
       break;
     }
-    // never selected again: a selected entry is marked by an index test, not by its value
-#pragma unroll
-    for (int i = 0; i < kPerLane; ++i)
-      if (lane + 32 * i == wi) v[i] = 0u, sp[wi] = -1.0f;
+    if (lane == 0) {
+      sp[wi] = -1.0f;  // a selected entry is marked in the probability array
+      sel_idx[j] = (int32_t)wi;
+    }
     if (lane == j) wsel = p;
-    if (lane == 0) sel_idx[j] = wi;
     s = s + p;
     lastp = p;
   }
@@ -177,6 +180,39 @@ __device__ __forceinline__ void router_topk_warp(float *sp, int E, int k, bool h
   if (lane == 0) {
     sel_idx[k] = E;
     sel_w[k] = has_shared ? 1.0f / (1.0f + det_expf(-sp[E])) : 0.0f;
+  }
+}
+// Every thread of a block of at least 256 threads calls (one __syncthreads inside); E <= 1024.
+__device__ __forceinline__ void router_topk_block(float *sp, int E, int k, bool has_shared, int32_t *sel_idx,
+                                                  float *sel_w, float *near_gap) {
+  __shared__ unsigned ck[kTopkWarps * kTopkMaxSel], ci[kTopkWarps * kTopkMaxSel];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nsel = k + 1 < kTopkMaxSel ? k + 1 : kTopkMaxSel;
+  if (warp < kTopkWarps) {
+    const int per = (E + kTopkWarps - 1) / kTopkWarps;  // experts of this warp: [warp*per, +per)
+    unsigned key[4], idx[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int o = lane + 32 * i, e = warp * per + o;
+      const bool ok = o < per && e < E;
+      key[i] = ok ? __float_as_uint(sp[e]) + 1u : 0u;
+      idx[i] = ok ? (unsigned)e : 0x7FFFFFFFu;
+    }
+#pragma unroll 1
+    for (int j = 0; j < nsel; ++j) {
+      unsigned wv, wi;
+      topk_extract<4>(key, idx, wv, wi);
+      if (lane == 0) {
+        ck[warp * nsel + j] = wv;
+        ci[warp * nsel + j] = wi;
+      }
+    }
+  }
+  __syncthreads();
+  if (warp == 0) {
+    const int ncand = kTopkWarps * nsel;
+    if (ncand <= 128) topk_level2<4>(ck, ci, ncand, sp, E, k, has_shared, sel_idx, sel_w, near_gap);
+    else topk_level2<9>(ck, ci, ncand, sp, E, k, has_shared, sel_idx, sel_w, near_gap);
   }
 }
 
@@ -221,10 +257,7 @@ static __device__ __noinline__ void router_select(const float *lg, int E, int k,
 #pragma unroll 1
   for (int e = tid; e < E; e += nthr) sp[e] = sp[e] / sum;
   __syncthreads();
-  if (tid < 32) {
-    if (E <= 512) router_topk_warp<16>(sp, E, k, has_shared, sel_idx, sel_w, near_gap);
-    else router_topk_warp<32>(sp, E, k, has_shared, sel_idx, sel_w, near_gap);
-  }
+  router_topk_block(sp, E, k, has_shared, sel_idx, sel_w, near_gap);
   __syncthreads();
 }
 
