@@ -267,16 +267,19 @@ __device__ __forceinline__ void gemv_block_t(const GemvMat *smats, int nmats, lo
     const long se = sb + SB < hi ? sb + SB : hi;
     const bool more = se < hi;
     if (threadIdx.x == 0 && more) gemv_list(&bs.lists[bs.cur ^ 1], smats, nmats, K, (int)se, (int)( se + SB < hi ? se + SB : hi));
-    __syncthreads();  // lists built; T of the previous sub-block is no longer read
-    block_dot<K, true>(bs.ring, &bs.lists[bs.cur], more ? &bs.lists[bs.cur ^ 1] : nullptr, act, bs.T);
-    // one thread per row: ordered sum, then the matrix's epilogue
+    // one thread per row: its epilogue's operands are fetched now, under the dot
     const long r = sb + threadIdx.x;
+    int mi = 0;
+    EpiOperands eo;
     if (r < se) {
-      int mi = 0;
       for (int i = 1; i < nmats; ++i)
         if (r >= smats[i].row_start) mi = i;
-      gemv_epilogue(smats + mi, (int)(r - smats[mi].row_start), m, row_sum<K>(bs.T, threadIdx.x));
+      gemv_epilogue_fetch(smats + mi, (int)(r - smats[mi].row_start), m, eo);
     }
+    __syncthreads();  // lists built; T of the previous sub-block is no longer read
+    block_dot<K, true>(bs.ring, &bs.lists[bs.cur], more ? &bs.lists[bs.cur ^ 1] : nullptr, act, bs.T);
+    // ordered sum, then the matrix's epilogue
+    if (r < se) gemv_epilogue_with(smats + mi, (int)(r - smats[mi].row_start), m, row_sum<K>(bs.T, threadIdx.x), eo);
     bs.cur ^= 1;
   }
 }
