@@ -1,4 +1,4 @@
-// Device-resident plan of the persistent decode kernel (DecodeStepMega): every
+// Device-resident plan of the persistent decode kernel (DecodeStep): every
 // pointer and dimension one token step needs, built once by the runtime when
 // the session is created. Plain C layout shared by host (g++) and device code.
 #pragma once
@@ -8,7 +8,7 @@
 
 namespace ainfer {
 
-struct MegaLayer {
+struct StepLayer {
   int32_t type;            // 0 = Gated DeltaNet, 1 = gated GQA attention
   int32_t pad0;
   const float *in_norm;    // [H]
@@ -26,7 +26,7 @@ struct MegaLayer {
   const ExpertW *experts;       // [E+1]
 };
 
-struct MegaPlan {
+struct StepPlan {
   int32_t H, layers, vocab;
   int32_t nQ, nKV, rot;
   int32_t nK, nV;
@@ -35,7 +35,7 @@ struct MegaPlan {
   int32_t history_cap, argmax_parts;
   float eps;
   int32_t pad0;
-  const MegaLayer *L;
+  const StepLayer *L;
   const uint16_t *emb;      // [vocab][H] bf16
   const float *final_norm;  // [H]
   GemvMat lm_head;          // Y = logits

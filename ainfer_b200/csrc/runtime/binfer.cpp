@@ -233,6 +233,10 @@ int container_open(const char *path, int level, Container &c, std::string &err) 
       uint64_t ng = (t.numel() + 127) / 128;
       if (t.group != 128 || t.sc_bytes != ng * 2) { err = "bad quant params " + t.name; return 2; }
       if (t.d_bytes != ng * 64) { err = "bad packed size " + t.name; return 2; }
+    } else if (t.storage == DT_BF16 || t.storage == DT_FP16 || t.storage == DT_FP32) {
+      // a payload shorter than its shape would make every reader of the tensor run past it
+      const uint64_t elem = t.storage == DT_FP32 ? 4 : 2;
+      if (t.d_bytes != t.numel() * elem) { err = "payload size does not match shape: " + t.name; return 2; }
     }
   }
   compute_spans(c);

@@ -5,7 +5,7 @@
 #include <algorithm>
 #include <cstring>
 
-#include "../common/mega_plan.h"
+#include "../common/step_plan.h"
 #include "../common/tables.h"
 
 namespace ainfer {
@@ -334,17 +334,18 @@ GemvMat make_mat(Session *s, int &status, const std::string &name, int K, float 
   return g;
 }
 
-// Builds the device plan of the persistent decode kernel and records the two
-// one-launch lists (token step with tail, prompt step).
-int build_mega(Session *s) {
+// Builds the device plan of the persistent decode kernel (DecodeStep, one block per SM) and
+// records the two one-launch lists (token step with tail, prompt step). Fails with a message
+// when a stage's share per block would not fit the kernel's shared-memory scratch.
+int build_step(Session *s) {
   DeviceModel *m = s->m;
   const ModelConfig &c = m->cfg;
   const int H = c.hidden, D = c.head_dim, nQ = c.q_heads, nKV = c.kv_heads, nV = c.lin_v_heads;
   const int C = c.conv_dim(), VD = c.value_dim(), E = c.experts;
   int status = 0;
-  std::vector<MegaLayer> layers((size_t)c.layers);
+  std::vector<StepLayer> layers((size_t)c.layers);
   for (int L = 0; L < c.layers && !status; ++L) {
-    MegaLayer &ly = layers[(size_t)L];
+    StepLayer &ly = layers[(size_t)L];
     std::memset(&ly, 0, sizeof ly);
     const std::string p = layer_prefix(L);
     const int slot = m->slot[L];
@@ -380,7 +381,7 @@ int build_mega(Session *s) {
     ly.experts = (const ExpertW *)m->expert_tables + (size_t)L * (E + 1);
   }
   if (status) return status;
-  MegaPlan P;
+  StepPlan P;
   std::memset(&P, 0, sizeof P);
   P.H = H; P.layers = c.layers; P.vocab = c.vocab;
   P.nQ = nQ; P.nKV = nKV; P.rot = c.rotary_dim; P.nK = c.lin_k_heads; P.nV = nV;
@@ -401,40 +402,60 @@ int build_mega(Session *s) {
   P.Q8 = s->Q8; P.SQ = s->SQ; P.SelIdx = s->SelIdx; P.SelW = s->SelW; P.NearGap = s->NearGap;
   P.ctrl = s->ctrl; P.history = s->history; P.out_tok = s->out_tok; P.ids = s->ids;
   P.layer_out = s->layer_out; P.routed = s->routed; P.near_gap = s->near_gap;
-  if (salloc(s, 1, &s->bar_count) || salloc(s, 1, &s->mega_error)) return 1;
+  if (salloc(s, 1, &s->bar_count) || salloc(s, 1, &s->step_error)) return 1;
   if (s->flags & SESSION_STAGE_CLOCK) {
     s->stage_stamp_cap = 2 * (c.layers * 64 + 64);  // first half: barrier clock, second half: fine clock
     if (salloc(s, (size_t)s->stage_stamp_cap, &s->stage_stamps)) return 1;
     P.stage_stamps = s->stage_stamps;
     P.stage_stamp_cap = s->stage_stamp_cap;
   }
-  P.bar_count = s->bar_count; P.error = s->mega_error;
-  MegaLayer *dl = nullptr;
+  P.bar_count = s->bar_count; P.error = s->step_error;
+  StepLayer *dl = nullptr;
   if (salloc(s, layers.size(), &dl, false)) return 1;
-  s->mega_layers = dl;
+  s->step_layers = dl;
   P.L = dl;
-  MegaPlan *dp = nullptr;
+  StepPlan *dp = nullptr;
   if (salloc(s, 1, &dp, false)) return 1;
-  s->mega_plan = dp;
-  if (ainfer_memcpy_h2d(s->dev, dl, layers.data(), layers.size() * sizeof(MegaLayer)) != AINFER_OK ||
+  s->step_plan = dp;
+  if (ainfer_memcpy_h2d(s->dev, dl, layers.data(), layers.size() * sizeof(StepLayer)) != AINFER_OK ||
       ainfer_memcpy_h2d(s->dev, dp, &P, sizeof P) != AINFER_OK) {
     s->err = ainfer_last_error(s->dev);
     return 1;
   }
   ainfer_kernel_t k = nullptr;
-  if (ainfer_kernel_get(s->dev, "DecodeStepMega", &k) != AINFER_OK) { s->err = "entry DecodeStepMega not found"; return 1; }
-  s->kernels["DecodeStepMega"] = k;
-  const MegaPlan *cdp = dp;
+  if (ainfer_kernel_get(s->dev, "DecodeStep", &k) != AINFER_OK) { s->err = "entry DecodeStep not found"; return 1; }
+  s->kernels["DecodeStep"] = k;
+  const StepPlan *cdp = dp;
   int32_t mode = 1;
   ainfer_kernel_set_arg(k, 0, sizeof cdp, &cdp);
   ainfer_kernel_set_arg(k, 1, sizeof mode, &mode);
   uint32_t groups = 0;
   if (ainfer_kernel_max_groups(k, &groups) != AINFER_OK || groups == 0) {
-    s->err = std::string("DecodeStepMega cannot be made resident: ") + ainfer_last_error(s->dev);
+    s->err = std::string("DecodeStep cannot be made resident: ") + ainfer_last_error(s->dev);
     return 1;
   }
-  groups = std::min<uint32_t>(groups, (uint32_t)s->sm_count * 2);
+  groups = std::min<uint32_t>(groups, (uint32_t)s->sm_count);
   if ((int)groups > s->argmax_parts) { s->err = "internal: argmax partial buffers too small"; return 3; }
+  {
+    // what one block must hold per stage: (rows x K/128) group terms <= 4096, staged activations
+    // <= 8192 bytes, fp32 scratch <= 8192 values
+    const long nb = groups;
+    auto share = [&](long total, long unit) { return ((total / unit + nb - 1) / nb + 1) * unit; };
+    auto unit = [](int K) { int G = K / 128; return G >= 8 ? 1 : 8 / G; };
+    const int slots = P.slots;
+    const long in_rows = (c.n_lin() ? C + VD + 2L * nV : 0), qkv_rows = (long)nQ * 2 * D + 2L * nKV * D;
+    bool ok = share(std::max(in_rows, qkv_rows), unit(H)) * (H / 128) <= 4096;
+    ok = ok && share(H, unit(std::max(VD, nQ * D))) * (std::max(VD, nQ * D) / 128) <= 4096;
+    ok = ok && 2 * share((long)slots * P.I, unit(H)) * (H / 128) <= 4096;
+    ok = ok && slots * share(H, unit(P.I)) * (P.I / 128) <= 4096;
+    ok = ok && (long)slots * P.I <= 8192 && std::max(VD, nQ * D) <= 4096 && H <= 4096 && slots <= 12 && E + 1 <= 8192;
+    ok = ok && (c.n_attn() == 0 || nQ / nKV <= 8);
+    if (!ok) {
+      s->err = "usage: this model's shapes do not fit the persistent decode kernel on " + std::to_string(groups) +
+               " blocks; use the recorded list";
+      return 2;
+    }
+  }
   for (int md = 1; md >= 0; --md) {
     ainfer_list_t *l = md ? &s->gen_list : &s->body_list;
     if (ainfer_list_create(s->dev, l) != AINFER_OK) { s->err = "list create failed"; return 1; }
@@ -447,7 +468,7 @@ int build_mega(Session *s) {
     }
   }
   s->launches_per_token = 1;
-  s->mega = true;
+  s->persistent = true;
   return 0;
 }
 
@@ -563,7 +584,7 @@ int session_create(DeviceModel *m, int max_ctx, int flags, Session **out, std::s
     rec.list = *l;
   };
   if ((flags & (SESSION_PERSISTENT | SESSION_STAGE_CLOCK)) && !(flags & SESSION_PER_LAYER_LISTS)) {
-    rec.status = build_mega(s);
+    rec.status = build_step(s);
   } else if (flags & SESSION_PER_LAYER_LISTS) {
     new_list(&s->embed_list);
     record_embed(rec);
@@ -670,12 +691,12 @@ static int run_token(Session *s, bool with_tail) {
 
 // The persistent kernel reports a barrier that ran out of polls through a sticky
 // error word instead of hanging; surface it as a device error.
-static int check_mega_error(Session *s) {
-  if (!s->mega) return 0;
+static int check_step_error(Session *s) {
+  if (!s->persistent) return 0;
   int32_t e = 0;
-  S_CHECK(ainfer_memcpy_d2h(s->dev, &e, s->mega_error, 4));
+  S_CHECK(ainfer_memcpy_d2h(s->dev, &e, s->step_error, 4));
   if (e != 0) {
-    s->err = "device error: a grid barrier of the persistent decode kernel timed out (status " +
+    s->err = "device error: a bounded wait of the persistent decode kernel ran out (status " +
              std::to_string(e) + ")";
     return 1;
   }
@@ -693,7 +714,7 @@ int session_step(Session *s, int token, int pos, int *out_token) {
   if (r) return r;
   S_CHECK(ainfer_memcpy_d2h(s->dev, s->host_tok, s->out_tok, 4));
   if (out_token) *out_token = s->host_tok[0];
-  return check_mega_error(s);
+  return check_step_error(s);
 }
 
 int session_mtp_draft(Session *s, int next_token, int pos, int from_trunk, int *draft_token) {
@@ -797,7 +818,7 @@ int session_generate(Session *s, const int *prompt, int P, int G, int start_pos,
   } else {
     S_CHECK(ainfer_sync(s->dev, UINT64_MAX));
   }
-  return check_mega_error(s);
+  return check_step_error(s);
 }
 
 }  // namespace ainfer

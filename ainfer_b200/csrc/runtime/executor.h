@@ -22,7 +22,7 @@ enum SessionFlags {
   SESSION_PER_LAYER_LISTS = 2,  // one list per layer + embed + tail, executed and fenced one by one
   SESSION_MULTI_KERNEL = 4,     // one list per token of ~450 stand-alone launches (the default; flag kept for callers)
   SESSION_STAGE_CLOCK = 8,      // persistent step (implies it): keep a device timestamp after every grid barrier
-  SESSION_PERSISTENT = 16       // one persistent cooperative launch per token (DecodeStepMega)
+  SESSION_PERSISTENT = 16       // one persistent cooperative launch per token (DecodeStep)
 };
 
 struct Session {
@@ -72,10 +72,10 @@ struct Session {
   std::vector<ainfer_list_t> layer_lists;  // per-layer mode
   ainfer_list_t embed_list = nullptr, tail_list = nullptr, advance_list = nullptr;
   // persistent-kernel path: device plan, barrier counter, sticky error word
-  void *mega_plan = nullptr, *mega_layers = nullptr;
+  void *step_plan = nullptr, *step_layers = nullptr;
   uint32_t *bar_count = nullptr;
-  int32_t *mega_error = nullptr;
-  bool mega = false;
+  int32_t *step_error = nullptr;
+  bool persistent = false;
   unsigned long long *stage_stamps = nullptr;  // [stage_stamp_cap] of the last launch
   int stage_stamp_cap = 0;
   std::map<std::string, ainfer_kernel_t> kernels;

@@ -361,6 +361,53 @@ static int mirror_small(DeviceModel *m, const std::string &name, float *dst, uin
   return launch_simple(dev, "WidenBf16", {{&dst, 8}, {&in, 8}, {&count, 8}}, groups, err);
 }
 
+int check_directory_shapes(const Container &dir, const ModelConfig &c, std::string &err) {
+  const uint64_t H = c.hidden, D = c.head_dim, I = c.expert_inter, V = c.vocab;
+  auto need = [&](const std::string &name, uint64_t rows, uint64_t cols, int storage) -> int {
+    const TensorEntry *e = dir.find(name);
+    if (!e) { err = "missing " + name; return 1; }
+    if (e->storage != storage) { err = "unexpected storage of " + name; return 2; }
+    // [rows][cols]; a leading dimension of 1 may be dropped (a [1][H] gate row stored as [H])
+    const bool two = e->ndim == 2 && e->shape[0] == rows && e->shape[1] == cols;
+    const bool one = rows == 1 && e->ndim == 1 && e->shape[0] == cols;
+    if (!two && !one) { err = "unexpected shape of " + name; return 2; }
+    return 0;
+  };
+  int r;
+  if ((r = need("model.language_model.embed_tokens.weight", V, H, DT_BF16))) return r;
+  if ((r = need("lm_head.weight", V, H, DT_INT4_SYM_G128))) return r;
+  const int nl = c.layers + c.mtp_layers;
+  for (int L = 0; L < nl; ++L) {
+    const bool mtp = L >= c.layers;
+    const bool attn = mtp || c.layer_types[L] == 'A';
+    const std::string p = mtp ? "mtp.layers.0." : layer_prefix(L);
+    if (attn) {
+      if ((r = need(p + "self_attn.q_proj.weight", (uint64_t)c.q_heads * 2 * D, H, DT_INT4_SYM_G128))) return r;
+      if ((r = need(p + "self_attn.k_proj.weight", (uint64_t)c.kv_heads * D, H, DT_INT4_SYM_G128))) return r;
+      if ((r = need(p + "self_attn.v_proj.weight", (uint64_t)c.kv_heads * D, H, DT_INT4_SYM_G128))) return r;
+      if ((r = need(p + "self_attn.o_proj.weight", H, (uint64_t)c.q_heads * D, DT_INT4_SYM_G128))) return r;
+    } else {
+      const uint64_t C = c.conv_dim(), VD = c.value_dim(), NV = c.lin_v_heads;
+      if ((r = need(p + "linear_attn.in_proj_qkv.weight", C, H, DT_INT4_SYM_G128))) return r;
+      if ((r = need(p + "linear_attn.in_proj_z.weight", VD, H, DT_INT4_SYM_G128))) return r;
+      if ((r = need(p + "linear_attn.in_proj_b.weight", NV, H, DT_INT4_SYM_G128))) return r;
+      if ((r = need(p + "linear_attn.in_proj_a.weight", NV, H, DT_INT4_SYM_G128))) return r;
+      if ((r = need(p + "linear_attn.out_proj.weight", H, VD, DT_INT4_SYM_G128))) return r;
+    }
+    if ((r = need(p + "mlp.gate.weight", (uint64_t)c.experts, H, DT_BF16))) return r;
+    if (c.shared_experts && (r = need(p + "mlp.shared_expert_gate.weight", 1, H, DT_BF16))) return r;
+    for (int e = 0; e <= c.experts; ++e) {
+      if (e == c.experts && !c.shared_experts) break;
+      const std::string ep = e < c.experts ? p + "mlp.experts." + std::to_string(e) + "." : p + "mlp.shared.";
+      if ((r = need(ep + "gate_proj.weight", I, H, DT_INT4_SYM_G128))) return r;
+      if ((r = need(ep + "up_proj.weight", I, H, DT_INT4_SYM_G128))) return r;
+      if ((r = need(ep + "down_proj.weight", H, I, DT_INT4_SYM_G128))) return r;
+    }
+  }
+  if (c.mtp_layers && (r = need("mtp.fc.weight", H, 2 * H, DT_INT4_SYM_G128))) return r;
+  return 0;
+}
+
 static int build_mirrors(DeviceModel *m, std::string &err) {
   const ModelConfig &c = m->cfg;
   ainfer_device_t dev = m->dev;
@@ -547,6 +594,10 @@ int model_open(ainfer_device_t dev, const char *spec, int validate_level, Device
     r = container_open(s.c_str(), validate_level, m->dir, err);
     if (r) { delete m; return r; }
     if (!ModelConfig::from_json(m->dir.arch_json, m->cfg, err)) { delete m; return 2; }
+    // before anything is uploaded or launched: the directory must describe the model the
+    // architecture section names
+    r = check_directory_shapes(m->dir, m->cfg, err);
+    if (r) { delete m; return r; }
   }
   m->pay_bytes = m->dir.pay_hi - m->dir.pay_lo;
   m->sc_bytes = m->dir.sc_hi - m->dir.sc_lo;

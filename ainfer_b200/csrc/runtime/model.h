@@ -48,6 +48,13 @@ struct SynthSpec {
 // order the writer lays them out, and how each is filled when synthetic.
 void build_plan(const ModelConfig &cfg, Container &c, std::vector<SynthSpec> &specs);
 
+// Checks every tensor the decode kernels read against the architecture: presence, shape and
+// storage of the projection matrices, every expert's gate/up/down, router, shared-expert gate,
+// embedding and LM head. The kernels take their loop bounds from the architecture, so a
+// directory that disagrees with it would make them read past the weight arenas. Host only.
+// Returns 0, 1 (missing tensor) or 2 (wrong shape or storage) with the first violation in err.
+int check_directory_shapes(const Container &dir, const ModelConfig &cfg, std::string &err);
+
 // Writes a synthetic model file on the host (no GPU involved).
 int synth_write_file(const char *path, const ModelConfig &cfg, uint64_t seed, std::string &err);
 

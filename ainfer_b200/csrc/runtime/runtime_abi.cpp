@@ -28,9 +28,10 @@ int ainfer_binfer_validate(const char *path, int level) {
   int r = container_open(path, level, c, err);
   if (r == 0) {
     ModelConfig cfg;
-    if (!c.arch_json.empty() && c.arch_json.find("\"text_layers\"") != std::string::npos &&
-        !ModelConfig::from_json(c.arch_json, cfg, err))
-      r = 2;
+    if (!c.arch_json.empty() && c.arch_json.find("\"text_layers\"") != std::string::npos) {
+      if (!ModelConfig::from_json(c.arch_json, cfg, err)) r = 2;
+      else r = check_directory_shapes(c, cfg, err);
+    }
   }
   return set_err(r, err);
 }

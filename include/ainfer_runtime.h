@@ -71,7 +71,7 @@ enum {
                                          programmatic dependencies: the default (flag kept for callers) */
   AINFER_SESSION_STAGE_CLOCK = 8,     /* persistent step (implies it): device timestamp after every grid
                                          barrier, read back through the "stage_stamps" buffer (u64 ns) */
-  AINFER_SESSION_PERSISTENT = 16      /* ONE persistent cooperative launch per token (DecodeStepMega) */
+  AINFER_SESSION_PERSISTENT = 16      /* ONE persistent cooperative launch per token (DecodeStep) */
 };
 int ainfer_session_create(ainfer_model_t m, int max_ctx, int flags, ainfer_session_t *out);
 int ainfer_session_destroy(ainfer_session_t s);

@@ -424,22 +424,27 @@ static void moe_block(const Model &M, const std::string &pfx, const float *hn, c
   for (int j = 0; j < k; ++j) routed[j] = idx[j];
   int slots = k + (c.shared_experts ? 1 : 0);
   std::vector<float> y((size_t)slots * H);
-  parallel_for((int64_t)(slots), [&](int64_t s_) {
-    int s = (int)s_;
+  // the slots' tensors once, then every (slot, row) as its own work item
+  std::vector<const Tensor *> wg(slots), wu(slots), wd(slots);
+  for (int s = 0; s < slots; ++s) {
     std::string ep = s < k ? pfx + "mlp.experts." + std::to_string(idx[s]) + "."
                            : pfx + "mlp.shared.";
-    const Tensor &wg = M.get(ep + "gate_proj.weight"), &wu = M.get(ep + "up_proj.weight"),
-                 &wd = M.get(ep + "down_proj.weight");
-    std::vector<float> g(I), u(I);
-    for (int n = 0; n < I; ++n) {
-      g[n] = gemv_a8_row(wg.data, wg.scales, n, H, hq.q.data(), hq.s.data());
-      u[n] = gemv_a8_row(wu.data, wu.scales, n, H, hq.q.data(), hq.s.data());
-    }
-    for (int n = 0; n < I; ++n) g[n] = (g[n] / (1.0f + det_expf(-g[n]))) * u[n];
-    Quant aq;
-    aq.run(g.data(), I);
-    for (int n = 0; n < H; ++n)
-      y[(size_t)s * H + n] = gemv_a8_row(wd.data, wd.scales, n, I, aq.q.data(), aq.s.data());
+    wg[s] = &M.get(ep + "gate_proj.weight");
+    wu[s] = &M.get(ep + "up_proj.weight");
+    wd[s] = &M.get(ep + "down_proj.weight");
+  }
+  std::vector<float> act((size_t)slots * I);
+  parallel_for((int64_t)slots * I, [&](int64_t i_) {
+    int s = (int)(i_ / I), n = (int)(i_ % I);
+    float g = gemv_a8_row(wg[s]->data, wg[s]->scales, n, H, hq.q.data(), hq.s.data());
+    float u = gemv_a8_row(wu[s]->data, wu[s]->scales, n, H, hq.q.data(), hq.s.data());
+    act[(size_t)s * I + n] = (g / (1.0f + det_expf(-g))) * u;
+  });
+  std::vector<Quant> aq(slots);
+  for (int s = 0; s < slots; ++s) aq[s].run(&act[(size_t)s * I], I);
+  parallel_for((int64_t)slots * H, [&](int64_t i_) {
+    int s = (int)(i_ / H), n = (int)(i_ % H);
+    y[i_] = gemv_a8_row(wd[s]->data, wd[s]->scales, n, I, aq[s].q.data(), aq[s].s.data());
   });
   float sg = 0.0f;
   if (c.shared_experts) {
@@ -700,6 +705,16 @@ int orc_step(void *sess, int token, int pos, int want_logits) {
 }
 int orc_mtp_step(void *sess, int next_token, int pos, float *h_io, float *logits) {
   return mtp_step(*(Session *)sess, next_token, pos, h_io, logits);
+}
+// The MoE block of one layer on its own (for cross-checks against third-party
+// implementations): hn = the normalised fp32 activations, which are also quantised here the way
+// decoder_layer does before calling the block. out[H], routed[top_k], near_gap[1].
+void orc_moe_block(void *model, const char *prefix, const float *hn, float *out, int *routed,
+                   float *near_gap) {
+  const Model &M = *(Model *)model;
+  Quant hq;
+  hq.run(hn, M.cfg.hidden);
+  moe_block(M, prefix, hn, hq, out, routed, near_gap);
 }
 // Greedy token loop: prompt of P ids, then G generated tokens; as
 // tools/decode/decode_l0.cpp:742-825 (logits only from step P-1 on).

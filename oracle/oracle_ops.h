@@ -81,14 +81,17 @@ static inline float gemv_a8_row(const uint8_t *P, const uint16_t *S, size_t row,
   float acc = 0.0f;
   for (int g = 0; g < G; ++g) {
     float sc = bf16_to_f32(S[row * G + g]);
-    int gs = 0;
     const uint8_t *p = P + (row * (size_t)K + (size_t)g * 128) / 2;
+    const int8_t *x = xq + g * 128;
+    // two's-complement nibbles widened without a branch ((v ^ 8) - 8), then the exact
+    // int32 sum of the 128 products; two loops so that the compiler vectorises both
+    int8_t w[128];
     for (int j = 0; j < 64; ++j) {
-      int lo = p[j] & 0xF, hi = p[j] >> 4;
-      lo = lo >= 8 ? lo - 16 : lo;
-      hi = hi >= 8 ? hi - 16 : hi;
-      gs += lo * (int)xq[g * 128 + 2 * j] + hi * (int)xq[g * 128 + 2 * j + 1];
+      w[2 * j] = (int8_t)(((p[j] & 0xF) ^ 8) - 8);
+      w[2 * j + 1] = (int8_t)(((p[j] >> 4) ^ 8) - 8);
     }
+    int gs = 0;
+    for (int j = 0; j < 128; ++j) gs += (int)w[j] * (int)x[j];
     float t = (float)gs * sc;
     t = t * sq[g];
     acc = acc + t;

@@ -54,6 +54,7 @@ def lib():
         "orc_step": (i, [vp, i, i, i]),
         "orc_mtp_step": (i, [vp, i, i, f32p, f32p]),
         "orc_decode_loop": (d, [vp, i32p, i, i, i, i32p]),
+        "orc_moe_block": (None, [vp, C.c_char_p, f32p, f32p, i32p, f32p]),
         "orc_threads": (i, []),
         "orc_quantize_int4": (None, [f32p, u64, u8p, u16p]),
         "orc_aquant": (None, [f32p, i, i8p, f32p]),

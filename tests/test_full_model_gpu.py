@@ -1,0 +1,97 @@
+"""Full 80B-A3B-shaped model, batch 1: greedy decode of 256 tokens after a 512-token seeded
+prompt, GPU runtime against the CPU oracle. Compared bit for bit: every generated token, the
+routed experts of every layer at every generated step, the near-tie gaps, the final logits and
+the recurrent state at the end.
+
+Both sides work on the same weight bytes: the runtime fills the model on the device with the
+seeded generator (the same bytes as the host writer and the oracle's own generator produce,
+which the small-model tests check), the test copies the two weight arenas to host memory once
+and registers every tensor with the oracle. The oracle's own lazy generator would produce the
+same 41.6 GB, but takes minutes of host time per hundred tokens to do so.
+"""
+import json
+import time
+
+import numpy as np
+import pytest
+
+import oracle_lib as O
+
+pytestmark = pytest.mark.gpu
+
+PROMPT, GEN = 512, 256
+
+
+def oracle_model_from_device(dev, model):
+    """Oracle model whose tensors are host copies of the device model's arenas."""
+    n = model.tensor_count()
+    infos = [model.tensor_at(i) for i in range(n)]
+    spans = {}
+    for kind, ptr_of, len_of in (("data", lambda t: t.data, lambda t: t.data_bytes),
+                                 ("scales", lambda t: t.scales, lambda t: t.scale_bytes)):
+        live = [(ptr_of(t), len_of(t)) for t in infos if len_of(t)]
+        lo = min(p for p, _ in live)
+        hi = max(p + b for p, b in live)
+        host = np.empty(hi - lo, np.uint8)
+        step = 1 << 30
+        for off in range(0, hi - lo, step):
+            nb = min(step, hi - lo - off)
+            host[off:off + nb] = dev.download(lo + off, nb, np.uint8)
+        spans[kind] = (lo, host)
+    om = O.Model(arch_json=model.config_json)
+    for t in infos:
+        lo, host = spans["data"]
+        data = host[t.data - lo:t.data - lo + t.data_bytes]
+        scales = None
+        if t.scale_bytes:
+            slo, shost = spans["scales"]
+            scales = shost[t.scales - slo:t.scales - slo + t.scale_bytes].view(np.uint16)
+        om.add_tensor(t.name.decode(), t.storage, list(t.shape)[:t.ndim], data, scales)
+    return om
+
+
+def test_full_model_256_greedy_tokens_routing_logits_state():
+    from ainfer_b200 import cuda_abi, runtime
+    dev = cuda_abi.Device(0)
+    info = dev.info()
+    if info.total_mem < 90 * (1 << 30):
+        pytest.skip("needs a GPU with room for the 41.6 GB model")
+    model = runtime.Model(dev, "synth:full:seed=0")
+    cfg = model.config
+    V, k = cfg["vocab"], cfg["top_k"]
+    om = oracle_model_from_device(dev, model)
+    max_ctx = PROMPT + GEN + 8
+    prompt = np.array([O.lib().orc_draw_u32(b"input.prompt", 0, i) % V for i in range(PROMPT)], np.int32)
+
+    sess = runtime.Session(model, max_ctx, runtime.Session.DIAG)
+    osess = O.Session(om, max_ctx)
+    t0 = time.time()
+    tok = int(sess.generate(prompt, 1)[0])              # the prompt by loop-decode + the first token
+    t_gpu = time.time() - t0
+    t0 = time.time()
+    for i in range(PROMPT - 1):
+        osess.step(int(prompt[i]), i, want_logits=False)
+    otok = osess.step(int(prompt[-1]), PROMPT - 1)
+    assert tok == otok
+    toks, otoks = [tok], [otok]
+    for g in range(1, GEN):
+        pos = PROMPT - 1 + g
+        tok = sess.step(tok, pos)
+        otok = osess.step(otok, pos)
+        routed = sess.read("routed", np.int32).reshape(-1, k + 1)[:, :k]
+        assert np.array_equal(routed, osess.buf("routed").reshape(-1, k)), f"routing differs at step {g}"
+        assert np.array_equal(sess.read("near_gap", np.float32), osess.buf("near_gap")), f"gaps differ at step {g}"
+        assert tok == otok, f"token differs at step {g}"
+        toks.append(tok)
+        otoks.append(otok)
+    t_cpu = time.time() - t0
+    assert len(set(toks)) > 8
+    assert np.array_equal(sess.logits(), osess.buf("logits"))
+    assert np.array_equal(sess.read("layer_out", np.float32), osess.buf("layer_out"))
+    for b, dt in (("S", np.float32), ("conv", np.float32), ("Kc", np.int8), ("Vc", np.int8),
+                  ("Ks", np.uint16), ("Vs", np.uint16)):
+        assert np.array_equal(sess.read(b, dt), osess.buf(b)), b
+    print(json.dumps({"full_model_parity": {"prompt": PROMPT, "generated": GEN, "tokens_equal": True,
+                                            "gpu_prompt_s": round(t_gpu, 2), "cpu_total_s": round(t_cpu, 1),
+                                            "cpu_threads": O.lib().orc_threads()}}))
+    sess.close(); model.close(); osess.close(); om.close(); dev.close()
