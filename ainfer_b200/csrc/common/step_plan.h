@@ -62,7 +62,9 @@ struct StepPlan {
   int32_t pad1;
   // grid barrier state: count is zeroed before every launch; error is sticky
   uint32_t *bar_count;
-  int32_t *error;           // 0 ok, 1 a barrier wait ran out of spins
+  int32_t *error;           // 0 ok, otherwise the code of the bounded wait that ran out
+  int64_t pad2;             // size a multiple of 16 bytes: the kernel copies the plan as 16-byte words
 };
+static_assert(sizeof(StepPlan) % 16 == 0, "StepPlan is copied 16 bytes at a time");
 
 }  // namespace ainfer

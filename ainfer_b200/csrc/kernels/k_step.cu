@@ -44,7 +44,7 @@
 namespace ainfer {
 
 struct DecodeStepArgs {
-  const StepPlan *plan;
+  const StepPlan *plan;  // device copy of the plan (the kernel keeps its own copy in shared memory)
   int32_t mode;  // 1: final norm + lm_head + argmax, control advances to the selected token
                  // 0: prompt step, control advances to ids[position + 1]
 };
@@ -52,13 +52,16 @@ struct DecodeStepArgs {
 constexpr int kCons = 512;          // consumer threads (16 warps)
 constexpr int kStepThreads = 544;   // consumers + the producer warp
 constexpr int kNT = 10;             // ring tiles
-constexpr int kMaxPieces = 8;       // contiguous row ranges a tile may be assembled from
+constexpr int kMaxPieces = 12;      // contiguous row ranges a tile may be assembled from (>= expert slots)
 constexpr int kTileStride = kTileBytes + kTileScaleBytes;
-constexpr unsigned long long kWaitNs = 2000000000ull;  // limit of any single wait
+// Limit of any single wait, in SM clock cycles (about two seconds). The waits are timed with the
+// SM's own cycle counter: reading the global nanosecond timer takes about a microsecond, far too
+// long for a poll loop that usually succeeds within a few hundred nanoseconds.
+constexpr long long kWaitCycles = 4000000000ll;
 
 // ---- shared-memory map (all dynamic) ----
-constexpr int kHdrBytes = 4096;                 // StepShared
-constexpr int kActBytes = 9216;                 // staged INT8 activations (<= 8192) + group scales
+constexpr int kHdrBytes = 5120;                 // StepShared
+constexpr int kActBytes = 8704;                 // staged INT8 activations (<= 8192) + group scales (<= 512)
 constexpr int kFbufFloats = 8192;               // fp32 scratch: norm input, O|Z, Act, KV chunk
 constexpr int kActOff = kHdrBytes;
 constexpr int kFbufOff = kActOff + kActBytes;
@@ -70,17 +73,26 @@ static_assert(kStepSmemBytes <= 232448, "shared memory of one SM");
 struct Piece {
   const uint16_t *S;   // scales of the piece's first row in global memory (when not copied)
   int32_t trow;        // first row of the piece in the stage's t[][] numbering
-  int32_t nrows;
-  int32_t vec;         // staged activation vector the rows are dotted with
-  int32_t sc_in_tile;  // the scales travelled with the tile
+  int16_t nrows;
+  uint8_t vec;         // staged activation vector the rows are dotted with
+  uint8_t sc_in_tile;  // the scales travelled with the tile
 };
 struct TileDesc {
   int32_t npieces, nrows, last, pad;
   Piece pc[kMaxPieces];
 };
+// Contiguous rows of one matrix, as the producer streams them.
+struct Seg {
+  const uint8_t *P;   // first row's bytes
+  const uint8_t *S;   // first row's scales (null: none)
+  int32_t nrows, vec, trow, pad;
+};
+constexpr int kMaxSegs2 = 24;
+
 struct StepShared {
-  // the two members that are copied 16 bytes at a time come first (the struct sits at a
-  // 128-byte aligned address and both sizes are multiples of 16)
+  // the members that are copied 16 bytes at a time come first (the struct sits at a
+  // 128-byte aligned address and the sizes are multiples of 16)
+  StepPlan plan;                // the plan: read from here, not from global memory, by every stage
   StepLayer ly;                 // the current layer's record
   ExpertW sew[12];              // weight pointers of the selected expert slots
   unsigned long long full[kNT], empty[kNT];
@@ -93,10 +105,21 @@ struct StepShared {
   float av[16];
   int32_t ai[16];
   volatile int32_t fail;
+  int32_t nstamp[2];            // stage clock: records written so far (consumer, producer)
+  Seg segs[kMaxSegs2];          // the producer warp's current segment list
+  int32_t nseg;
 };
 static_assert(sizeof(StepShared) <= kHdrBytes, "header area");
-static_assert(sizeof(StepLayer) % 16 == 0 && sizeof(ExpertW) % 16 == 0 && offsetof(StepShared, sew) % 16 == 0,
+static_assert(sizeof(StepPlan) % 16 == 0 && sizeof(StepLayer) % 16 == 0 && sizeof(ExpertW) % 16 == 0 &&
+                  offsetof(StepShared, ly) % 16 == 0 && offsetof(StepShared, sew) % 16 == 0,
               "records copied as 16-byte words");
+
+// The block's shared memory and the two things every stage needs from it. (Kept out of the
+// per-thread context on purpose: that lives in local memory, and with 544 threads and a
+// 24 KB L1 every access to it was a trip to L2.)
+extern __shared__ __align__(128) unsigned char step_smem[];
+#define SH (reinterpret_cast<StepShared *>(step_smem))
+#define PL (reinterpret_cast<StepShared *>(step_smem)->plan)
 
 __device__ __forceinline__ void csync() { asm volatile("bar.sync 1, 512;" ::: "memory"); }
 __device__ __forceinline__ void hsync() { asm volatile("bar.sync 2, 256;" ::: "memory"); }  // threads 0..255
@@ -111,36 +134,37 @@ __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned *p) {
   return v;
 }
 
-// Everything a thread needs to find its way around (registers / local memory of each thread).
-struct Ctx {
-  const StepPlan *P;
-  StepShared *sh;
-  unsigned char *smem;
-  uint32_t tile;    // running tile index (consumers: next to consume; producer: next to issue)
-  unsigned epoch;   // grid barriers passed
-  int blk, nblk;
-  int nstamp;
-};
-
-__device__ __forceinline__ void step_fail(Ctx &c, int code) {
-  c.sh->fail = code;
-  atomicExch(c.P->error, code);
+__device__ __forceinline__ void step_fail(int code) {
+  SH->fail = code;
+  atomicExch(PL.error, code);
 }
 // Bounded wait on an mbarrier phase; false when it gave up (now or earlier).
-__device__ __forceinline__ bool mbar_wait_b(Ctx &c, uint32_t addr, uint32_t parity, int code) {
+__device__ __forceinline__ bool mbar_wait_b(uint32_t addr, uint32_t parity, int code) {
   if (mbar_try_a(addr, parity)) return true;
-  if (c.sh->fail) return false;
-  const unsigned long long t0 = gtime_ns();
+  if (SH->fail) return false;
+  const long long t0 = clock64();
 #pragma unroll 1
   for (unsigned i = 1;; ++i) {
     if (mbar_try_a(addr, parity)) return true;
     if ((i & 63u) == 0u) {
-      if (c.sh->fail) return false;
-      if (gtime_ns() - t0 > kWaitNs) {
-        step_fail(c, code);
+      if (SH->fail) return false;
+      if (clock64() - t0 > kWaitCycles) {
+        step_fail(code);
         return false;
       }
     }
+  }
+}
+
+// Optional stage clock (plan->stage_stamps non-null): block 0 appends (id << 48 | %globaltimer)
+// records, consumer thread 0 to the first half of the buffer, the producer thread to the second.
+static __device__ __noinline__ void stamp(int id) {
+  if (PL.stage_stamps && blockIdx.x == 0 && (threadIdx.x == 0 || threadIdx.x == kCons)) {
+    const int who = threadIdx.x == 0 ? 0 : 1, half = PL.stage_stamp_cap / 2;
+    const int n = SH->nstamp[who];
+    if (n < half)
+      PL.stage_stamps[who * half + n] = ((unsigned long long)id << 48) | (gtime_ns() & 0xFFFFFFFFFFFFull);
+    SH->nstamp[who] = n + 1;
   }
 }
 
@@ -161,209 +185,238 @@ __device__ __forceinline__ int row_unit(int K) {
 // ------------------------------------------------------------------ grid barrier ---
 // Two halves, so that loads which do not depend on other blocks (recurrent state, KV rows of
 // earlier tokens, epilogue operands) can be issued between arriving and waiting.
-__device__ __forceinline__ void grid_arrive(Ctx &c) {
+static __device__ __noinline__ void grid_arrive() {
   csync();
-  c.epoch += 1;
   if (threadIdx.x == 0) {
     __threadfence();
-    atomicAdd(c.P->bar_count, 1u);
+    atomicAdd(PL.bar_count, 1u);
   }
 }
-__device__ __forceinline__ void grid_wait(Ctx &c) {
-  if (threadIdx.x == 0 && !c.sh->fail) {
-    const unsigned target = c.epoch * (unsigned)c.nblk;
-    unsigned long long t0 = 0;
+// epoch: how many barriers this block has arrived at, this one included
+static __device__ __noinline__ void grid_wait(unsigned epoch) {
+  if (threadIdx.x == 0 && !SH->fail) {
+    const unsigned target = epoch * gridDim.x;
+    const long long t0 = clock64();
 #pragma unroll 1
     for (unsigned i = 0;; ++i) {
-      if (ld_acquire_u32(c.P->bar_count) >= target) break;
-      if ((i & 31u) == 31u) {
-        if (t0 == 0) t0 = gtime_ns();
-        if (*(volatile int *)c.P->error != 0) { c.sh->fail = 1; break; }
-        if (gtime_ns() - t0 > kWaitNs) { step_fail(c, 1); break; }
+      if (ld_acquire_u32(PL.bar_count) >= target) break;
+      if ((i & 63u) == 63u) {
+        if (*(volatile int *)PL.error != 0) { SH->fail = 1; break; }
+        if (clock64() - t0 > kWaitCycles) { step_fail(1); break; }
       }
     }
   }
   csync();
-  if (c.P->stage_stamps && c.blk == 0 && threadIdx.x == 0) {
-    if (c.nstamp < c.P->stage_stamp_cap) c.P->stage_stamps[c.nstamp] = gtime_ns();
-    c.nstamp += 1;
-  }
+  stamp(1);
 }
 
 // ====================================================================== producer ===
-struct Seg {
-  const uint8_t *P;   // first row's bytes
-  const uint8_t *S;   // first row's scales (null: none)
-  int32_t nrows, vec, trow;
-};
 
-// Streams the rows of `segs`, laid end to end, through the ring in tiles of 16 KB.
-static __device__ __noinline__ void prod_emit(Ctx &c, const Seg *segs, int nseg, int row_bytes, int sc_row_bytes) {
+// Streams the rows of the segment list in shared memory (SH->segs), laid end to end, through
+// the ring in tiles of 16 KB. Called by the whole producer warp: lane l (l < kNT) owns ring slot
+// l and issues the tiles whose running index is l modulo kNT, so up to kNT tiles are prepared and
+// issued at once. Tile j of the call holds rows [j * rpt, (j + 1) * rpt) of the list. `tile` is
+// the running index of the call's first tile; returns the index after its last.
+static __device__ __noinline__ uint32_t prod_emit(uint32_t tile, int row_bytes, int sc_row_bytes) {
+  const Seg *segs = SH->segs;
+  const int nseg = SH->nseg;
   const int rpt = kTileBytes / row_bytes;
   int total = 0;
   for (int i = 0; i < nseg; ++i) total += segs[i].nrows;
-  int si = 0, sr = 0, done = 0;
-  unsigned char *ring = c.smem + kRingOff;
-  while (done < total) {
-    const uint32_t slot = c.tile % kNT, use = c.tile / kNT;
-    if (use > 0 && !mbar_wait_b(c, smem_addr(&c.sh->empty[slot]), (use - 1u) & 1u, 3)) return;
-    TileDesc &d = c.sh->desc[slot];
-    unsigned char *dst = ring + slot * kTileStride;
-    unsigned long long *bar = &c.sh->full[slot];
-    int rows = 0, np = 0;
-    while (rows < rpt && np < kMaxPieces && si < nseg) {
-      const Seg &s = segs[si];
-      const int left = s.nrows - sr;
-      const int take = rpt - rows < left ? rpt - rows : left;
-      if (take > 0) {
-        const uint8_t *src = s.P + (size_t)sr * row_bytes;
-        const uint8_t *ssrc = s.S ? s.S + (size_t)sr * sc_row_bytes : nullptr;
-        const uint32_t wb = (uint32_t)(take * row_bytes), sb = (uint32_t)(take * sc_row_bytes);
-        const bool sc_bulk = ssrc != nullptr &&
-                             ((reinterpret_cast<uintptr_t>(ssrc) | sb | (uint32_t)(rows * sc_row_bytes)) & 15u) == 0;
-        Piece &pc = d.pc[np];
-        pc.S = reinterpret_cast<const uint16_t *>(ssrc);
-        pc.trow = s.trow + sr;
-        pc.nrows = take;
-        pc.vec = s.vec;
-        pc.sc_in_tile = sc_bulk ? 1 : 0;
-        if (reinterpret_cast<uintptr_t>(src) & 15u) {  // cannot be copied in bulk: report, skip
-          if (g_stream_fault_word) *reinterpret_cast<volatile unsigned int *>(g_stream_fault_word) = 2;
-        } else {
-          mbar_expect_tx(bar, wb + (sc_bulk ? sb : 0u));
-          bulk_g2s(dst + (size_t)rows * row_bytes, src, wb, bar);
-          if (sc_bulk) bulk_g2s(dst + kTileBytes + (size_t)rows * sc_row_bytes, ssrc, sb, bar);
+  const int ntiles = (total + rpt - 1) / rpt;
+  const uint32_t base = tile;
+  const int lane = threadIdx.x & 31;
+  if (lane < kNT && ntiles > 0) {
+    unsigned char *ring = step_smem + kRingOff;
+    int j = (int)(((uint32_t)lane + kNT - base % kNT) % kNT);  // first tile of this call that lands in slot `lane`
+#pragma unroll 1
+    for (; j < ntiles; j += kNT) {
+      const uint32_t g = base + (uint32_t)j, slot = (uint32_t)lane, use = g / kNT;
+      if (use > 0 && !mbar_wait_b(smem_addr(&SH->empty[slot]), (use - 1u) & 1u, 3)) break;
+      TileDesc &d = SH->desc[slot];
+      unsigned char *dst = ring + slot * kTileStride;
+      unsigned long long *bar = &SH->full[slot];
+      const int f0 = j * rpt, f1 = f0 + rpt < total ? f0 + rpt : total;
+      int np = 0, row0 = 0;  // row0: flat row of the current segment's first row
+#pragma unroll 1
+      for (int si = 0; si < nseg && row0 < f1; ++si) {
+        const Seg sg = segs[si];
+        const int a = row0 > f0 ? row0 : f0, b = row0 + sg.nrows < f1 ? row0 + sg.nrows : f1;
+        if (a < b && np < kMaxPieces) {
+          const int sr = a - row0, take = b - a, rows = a - f0;
+          const uint8_t *src = sg.P + (size_t)sr * row_bytes;
+          const uint8_t *ssrc = sg.S ? sg.S + (size_t)sr * sc_row_bytes : nullptr;
+          const uint32_t wb = (uint32_t)(take * row_bytes), sb = (uint32_t)(take * sc_row_bytes);
+          const bool sc_bulk = ssrc != nullptr &&
+                               ((reinterpret_cast<uintptr_t>(ssrc) | sb | (uint32_t)(rows * sc_row_bytes)) & 15u) == 0;
+          Piece &pc = d.pc[np];
+          pc.S = reinterpret_cast<const uint16_t *>(ssrc);
+          pc.trow = sg.trow + sr;
+          pc.nrows = (int16_t)take;
+          pc.vec = (uint8_t)sg.vec;
+          pc.sc_in_tile = sc_bulk ? 1 : 0;
+          if (reinterpret_cast<uintptr_t>(src) & 15u) {  // cannot be copied in bulk: report, skip
+            if (g_stream_fault_word) *reinterpret_cast<volatile unsigned int *>(g_stream_fault_word) = 2;
+          } else {
+            mbar_expect_tx(bar, wb + (sc_bulk ? sb : 0u));
+            bulk_g2s(dst + (size_t)rows * row_bytes, src, wb, bar);
+            if (sc_bulk) bulk_g2s(dst + kTileBytes + (size_t)rows * sc_row_bytes, ssrc, sb, bar);
+          }
+          ++np;
         }
-        rows += take;
-        sr += take;
-        ++np;
+        row0 += sg.nrows;
       }
-      if (sr >= s.nrows) {
-        ++si;
-        sr = 0;
-      }
+      d.npieces = np;
+      d.nrows = f1 - f0;
+      d.last = j == ntiles - 1 ? 1 : 0;
+      mbar_arrive(bar);  // releases the descriptor and completes the phase once the bytes have landed
     }
-    done += rows;
-    d.npieces = np;
-    d.nrows = rows;
-    d.last = done >= total ? 1 : 0;
-    mbar_arrive(bar);  // releases the descriptor and completes the phase once the bytes have landed
-    c.tile += 1;
   }
+  __syncwarp();  // the list may be rewritten once every lane is done with it
+  return base + (uint32_t)ntiles;
 }
 
-// Rows [lo, hi) of a table of matrices whose rows are numbered end to end.
-__device__ __forceinline__ int segs_gemv(Seg *out, const GemvMat *m, int nm, int K, int lo, int hi) {
-  int n = 0, rs = 0;
-  for (int i = 0; i < nm; ++i) {
-    const int N = m[i].N;
-    const int a = lo > rs ? lo : rs, b = hi < rs + N ? hi : rs + N;
-    if (a < b) {
-      out[n].P = m[i].P + (size_t)(a - rs) * (K >> 1);
-      out[n].S = reinterpret_cast<const uint8_t *>(m[i].S + (size_t)(a - rs) * (K >> 7));
-      out[n].nrows = b - a;
-      out[n].vec = 0;
-      out[n].trow = a - lo;
-      ++n;
-    }
-    rs += N;
-  }
-  return n;
-}
 __device__ __forceinline__ int mats_rows(const GemvMat *m, int nm) {
   int t = 0;
   for (int i = 0; i < nm; ++i) t += m[i].N;
   return t;
 }
 
-static __device__ __noinline__ void prod_gemv(Ctx &c, const GemvMat *m, int nm, int K) {
-  Seg segs[4];
-  int lo, hi;
-  deal(mats_rows(m, nm), row_unit(K), c.blk, c.nblk, lo, hi);
-  const int n = segs_gemv(segs, m, nm, K, lo, hi);
-  prod_emit(c, segs, n, K >> 1, (K >> 7) * 2);
+// Segment list of rows [lo, hi) of a table of matrices whose rows are numbered end to end
+// (written by lane 0 of the producer warp).
+__device__ __forceinline__ void segs_gemv(const GemvMat *m, int nm, int K, int lo, int hi) {
+  if ((threadIdx.x & 31) == 0) {
+    Seg *out = SH->segs;
+    int n = 0, rs = 0;
+    for (int i = 0; i < nm; ++i) {
+      const int N = m[i].N;
+      const int a = lo > rs ? lo : rs, b = hi < rs + N ? hi : rs + N;
+      if (a < b) {
+        out[n].P = m[i].P + (size_t)(a - rs) * (K >> 1);
+        out[n].S = reinterpret_cast<const uint8_t *>(m[i].S + (size_t)(a - rs) * (K >> 7));
+        out[n].nrows = b - a;
+        out[n].vec = 0;
+        out[n].trow = a - lo;
+        ++n;
+      }
+      rs += N;
+    }
+    SH->nseg = n;
+  }
+  __syncwarp();
 }
 
-static __device__ __noinline__ void producer_main(Ctx &c, int mode) {
-  const StepPlan &P = *c.P;
-  const int H = P.H;
+static __device__ __noinline__ uint32_t prod_gemv(uint32_t tile, const GemvMat *m, int nm, int K) {
+  int lo, hi;
+  deal(mats_rows(m, nm), row_unit(K), (int)blockIdx.x, (int)gridDim.x, lo, hi);
+  segs_gemv(m, nm, K, lo, hi);
+  return prod_emit(tile, K >> 1, (K >> 7) * 2);
+}
+
+// The producer warp's whole token. Returns the number of tiles issued.
+static __device__ __noinline__ uint32_t producer_main(int mode) {
+  const StepPlan &P = PL;
+  const int H = P.H, blk = (int)blockIdx.x, nblk = (int)gridDim.x;
+  const bool lead = (threadIdx.x & 31) == 0;
+  uint32_t tile = 0;
   for (int L = 0; L < P.layers; ++L) {
     const StepLayer &ly = P.L[L];
     const bool lin = ly.type == 0;
-    prod_gemv(c, &ly.m[0], lin ? 4 : 3, H);
-    prod_gemv(c, &ly.m[4], 1, lin ? P.nV * 128 : P.nQ * 256);
+    tile = prod_gemv(tile, &ly.m[0], lin ? 4 : 3, H);
+    stamp(10);
+    tile = prod_gemv(tile, &ly.m[4], 1, lin ? P.nV * 128 : P.nQ * 256);
+    stamp(11);
     {  // router rows (bf16) and the shared-expert gate row
       const int rows = P.E + (ly.shared_gate ? 1 : 0);
       int lo, hi;
-      deal(rows, 1, c.blk, c.nblk, lo, hi);
-      Seg segs[2];
-      int n = 0;
-      const int b = hi < P.E ? hi : P.E;
-      if (lo < b) segs[n++] = Seg{reinterpret_cast<const uint8_t *>(ly.router + (size_t)lo * H), nullptr, b - lo, 0, 0};
-      if (hi > P.E) segs[n++] = Seg{reinterpret_cast<const uint8_t *>(ly.shared_gate), nullptr, 1, 0, P.E - lo};
-      prod_emit(c, segs, n, H * 2, 0);
+      deal(rows, 1, blk, nblk, lo, hi);
+      if (lead) {
+        Seg *segs = SH->segs;
+        int n = 0;
+        const int b = hi < P.E ? hi : P.E;
+        if (lo < b) segs[n++] = Seg{reinterpret_cast<const uint8_t *>(ly.router + (size_t)lo * H), nullptr, b - lo, 0, 0, 0};
+        if (hi > P.E) segs[n++] = Seg{reinterpret_cast<const uint8_t *>(ly.shared_gate), nullptr, 1, 0, P.E - lo, 0};
+        SH->nseg = n;
+      }
+      __syncwarp();
+      tile = prod_emit(tile, H * 2, 0);
     }
     // the expert weights depend on the routing: wait for the consumers' selection
-    if (!mbar_wait_b(c, smem_addr(&c.sh->sel_bar), (uint32_t)L & 1u, 4)) return;
+    stamp(12);
+    if (!mbar_wait_b(smem_addr(&SH->sel_bar), (uint32_t)L & 1u, 4)) return tile;
+    stamp(13);
     {  // gate and up rows of pair rows [lo, hi) over slots x I
       int lo, hi;
-      deal(P.slots * P.I, row_unit(H), c.blk, c.nblk, lo, hi);
-      if (lo < hi) {
-        Seg segs[24];
+      deal(P.slots * P.I, row_unit(H), blk, nblk, lo, hi);
+      if (lead) {
+        Seg *segs = SH->segs;
         int n = 0;
-        const int s0 = lo / P.I, s1 = (hi - 1) / P.I;
-        for (int s = s0; s <= s1 && n + 2 <= 24; ++s) {
-          const int a = lo > s * P.I ? lo : s * P.I, b = hi < (s + 1) * P.I ? hi : (s + 1) * P.I;
-          const ExpertW &ew = c.sh->sew[s];
-          const size_t r0 = (size_t)(a - s * P.I);
-          segs[n++] = Seg{ew.gP + r0 * (H >> 1), reinterpret_cast<const uint8_t *>(ew.gS + r0 * (H >> 7)), b - a, 0, a - lo};
-          segs[n++] = Seg{ew.uP + r0 * (H >> 1), reinterpret_cast<const uint8_t *>(ew.uS + r0 * (H >> 7)), b - a, 0,
-                          (hi - lo) + (a - lo)};
+        if (lo < hi) {
+          const int s0 = lo / P.I, s1 = (hi - 1) / P.I;
+          for (int s = s0; s <= s1 && n + 2 <= kMaxSegs2; ++s) {
+            const int a = lo > s * P.I ? lo : s * P.I, b = hi < (s + 1) * P.I ? hi : (s + 1) * P.I;
+            const ExpertW &ew = SH->sew[s];
+            const size_t r0 = (size_t)(a - s * P.I);
+            segs[n++] = Seg{ew.gP + r0 * (H >> 1), reinterpret_cast<const uint8_t *>(ew.gS + r0 * (H >> 7)), b - a, 0, a - lo, 0};
+            segs[n++] = Seg{ew.uP + r0 * (H >> 1), reinterpret_cast<const uint8_t *>(ew.uS + r0 * (H >> 7)), b - a, 0,
+                            (hi - lo) + (a - lo), 0};
+          }
         }
-        prod_emit(c, segs, n, H >> 1, (H >> 7) * 2);
+        SH->nseg = n;
       }
+      __syncwarp();
+      tile = prod_emit(tile, H >> 1, (H >> 7) * 2);
     }
+    stamp(14);
     {  // down rows [lo, hi) of every slot
       int lo, hi;
-      deal(H, row_unit(P.I), c.blk, c.nblk, lo, hi);
-      if (lo < hi) {
-        Seg segs[12];
-        const int nr = hi - lo;
-        for (int s = 0; s < P.slots; ++s) {
-          const ExpertW &ew = c.sh->sew[s];
-          segs[s] = Seg{ew.dP + (size_t)lo * (P.I >> 1), reinterpret_cast<const uint8_t *>(ew.dS + (size_t)lo * (P.I >> 7)),
-                        nr, s, s * nr};
+      deal(H, row_unit(P.I), blk, nblk, lo, hi);
+      if (lead) {
+        Seg *segs = SH->segs;
+        int n = 0;
+        if (lo < hi) {
+          const int nr = hi - lo;
+          for (int s = 0; s < P.slots; ++s) {
+            const ExpertW &ew = SH->sew[s];
+            segs[n++] = Seg{ew.dP + (size_t)lo * (P.I >> 1), reinterpret_cast<const uint8_t *>(ew.dS + (size_t)lo * (P.I >> 7)),
+                            nr, s, s * nr, 0};
+          }
         }
-        prod_emit(c, segs, P.slots, P.I >> 1, (P.I >> 7) * 2);
+        SH->nseg = n;
       }
+      __syncwarp();
+      tile = prod_emit(tile, P.I >> 1, (P.I >> 7) * 2);
     }
+    stamp(15);
   }
-  if (mode != 0) prod_gemv(c, &P.lm_head, 1, H);
+  if (mode != 0) tile = prod_gemv(tile, &P.lm_head, 1, H);
+  return tile;
 }
 
 // ====================================================================== consumers ===
 // Dots the tiles of one stage with staged activations: t[g][trow - trow_base] for every
-// (row, group) of every tile, until the tile flagged `last` (or max_tiles tiles). A tile is
+// (row, group) of every tile, from running tile index `tile` until the tile flagged `last` (or
+// max_tiles tiles); returns the running index after the last tile consumed. A tile is
 // 256 (row, group) tasks of 64 bytes; two adjacent lanes share a task (32 bytes each) and add
 // their exact integer sums with one shuffle.
-static __device__ __noinline__ bool dot_tiles(Ctx &c, int K, const uint4 *xa, const float *sq, float *T, int max_tiles,
-                                              int trow_base) {
+static __device__ __noinline__ uint32_t dot_tiles(uint32_t tile, int K, const uint4 *xa, const float *sq, float *T,
+                                                  int max_tiles, int trow_base) {
   const int G = K >> 7, lg = 31 - __clz(G);
   const int TS = (kTCap >> lg) + 1;
   const int task = threadIdx.x >> 1, half = threadIdx.x & 1, lane = threadIdx.x & 31;
   const int r = task >> lg, g = task & (G - 1);
   const uint32_t rot = (uint32_t)(lane >> 2) & 1u;
-  const uint32_t ring_a = smem_addr(c.smem + kRingOff);
+  const uint32_t ring_a = smem_addr(step_smem + kRingOff);
   int cvec = -1;
   uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0, x2 = x0, x3 = x0;
   float sqg = 0.0f;
   bool last = false;
 #pragma unroll 1
   for (int n = 0; n < max_tiles && !last; ++n) {
-    const uint32_t slot = c.tile % kNT, use = c.tile / kNT;
+    const uint32_t slot = tile % kNT, use = tile / kNT;
     // a wait that gave up ends the stage for the whole warp (the results are lost anyway)
-    if (!__all_sync(kFull, mbar_wait_b(c, smem_addr(&c.sh->full[slot]), use & 1u, 5))) return true;
-    const TileDesc &d = c.sh->desc[slot];
+    if (!__all_sync(kFull, mbar_wait_b(smem_addr(&SH->full[slot]), use & 1u, 5))) return tile;
+    const TileDesc &d = SH->desc[slot];
     last = d.last != 0;
     const int nr = d.nrows;
     const uint32_t tb = ring_a + slot * kTileStride;
@@ -387,7 +440,7 @@ static __device__ __noinline__ bool dot_tiles(Ctx &c, int K, const uint4 *xa, co
       }
     }
     __syncwarp();
-    if (lane == 0) mbar_arrive_a(smem_addr(&c.sh->empty[slot]));
+    if (lane == 0) mbar_arrive_a(smem_addr(&SH->empty[slot]));
     int dsum = 0;
     if (trow >= 0) {
       if (vec != cvec) {
@@ -410,44 +463,60 @@ static __device__ __noinline__ bool dot_tiles(Ctx &c, int K, const uint4 *xa, co
       const float v = (float)(dsum >> 4) * __uint_as_float(sraw << 16);
       T[g * TS + (trow - trow_base)] = v * sqg;
     }
-    c.tile += 1;
+    tile += 1;
   }
-  return last;
+  return tile;
 }
 
 // (1+w) RMSNorm + per-128 quantiser of one H-vector into the staged form, by the whole
-// consumer group (RMSNormW + ScalesMax + Quantize, tools/cmdlist/kernels.cpp:73-114,551-579):
-// fp64 sum of squares over 256 strided lanes, stride-halving tree, then one warp per group.
-// src: fp32 vector in global memory, or (emb != null) a bf16 embedding row. hn (optional):
-// the normalised fp32 vector, shared memory. xout (optional): copy of the input, global.
-static __device__ __noinline__ void norm_quant(Ctx &c, const float *src, const uint16_t *emb, const float *w, int H,
-                                               float *hn, float *xout) {
-  float *xs = reinterpret_cast<float *>(c.smem + kFbufOff);
-  double *ps = reinterpret_cast<double *>(c.smem + kTOff);
-  unsigned char *act = c.smem + kActOff;
+// consumer group (RMSNormW + ScalesMax + Quantize, tools/cmdlist/kernels.cpp:73-114,551-579).
+// Sum of squares: fp64 over 256 strided lanes (thread j < 256 adds x[j], x[j+256], ... in
+// order), then the stride-halving tree, whose levels 128, 64 and 32 every warp evaluates for
+// itself from the 256 partial sums in shared memory (lane l: ((p[l]+p[l+128]) + (p[l+64]+
+// p[l+192])) + ((p[l+32]+p[l+160]) + (p[l+96]+p[l+224]))) and whose last five levels are the xor
+// butterfly. Double-precision arithmetic is slow on this GPU (a few lanes per cycle and SM), so
+// the element-wise part is done once, not once per warp.
+// src: fp32 vector in global memory, or (emb != null) a bf16 embedding row. hn (optional): the
+// normalised fp32 vector, shared memory. xout (optional): copy of the input, global.
+static __device__ __noinline__ void norm_quant(const float *src, const uint16_t *emb, const float *w, int H, float *hn,
+                                               float *xout) {
+  float *xs = reinterpret_cast<float *>(step_smem + kFbufOff);
+  double *ps = reinterpret_cast<double *>(step_smem + kTOff);
+  unsigned char *act = step_smem + kActOff;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  for (int j = tid * 4; j < H; j += kCons * 4) {
-    float4 v;
-    if (emb) {
-      const uint2 e = __ldg(reinterpret_cast<const uint2 *>(emb + j));
-      v = make_float4(u2f(e.x << 16), u2f(e.x & 0xFFFF0000u), u2f(e.y << 16), u2f(e.y & 0xFFFF0000u));
-    } else {
-      v = __ldcg(reinterpret_cast<const float4 *>(src + j));
+  float4 v[2];  // H <= 4096: at most two float4 per thread
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const int j = (tid + kCons * u) * 4;
+    v[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (j < H) {
+      if (emb) {
+        const uint2 e = __ldg(reinterpret_cast<const uint2 *>(emb + j));
+        v[u] = make_float4(u2f(e.x << 16), u2f(e.x & 0xFFFF0000u), u2f(e.y << 16), u2f(e.y & 0xFFFF0000u));
+      } else {
+        v[u] = __ldcg(reinterpret_cast<const float4 *>(src + j));
+      }
     }
-    *reinterpret_cast<float4 *>(xs + j) = v;
-    if (xout) *reinterpret_cast<float4 *>(xout + j) = v;
   }
-  // the weights of this lane's groups, in flight during the reduction
-  float4 wv[2];
+  float4 wv[2];  // the weights of this warp's groups, in flight during the reduction
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
     const int g = warp + 16 * i;
     wv[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     if (g < H / 128) wv[i] = __ldg(reinterpret_cast<const float4 *>(w + g * 128) + lane);
   }
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const int j = (tid + kCons * u) * 4;
+    if (j < H) {
+      *reinterpret_cast<float4 *>(xs + j) = v[u];
+      if (xout) *reinterpret_cast<float4 *>(xout + j) = v[u];
+    }
+  }
   csync();
   if (tid < 256) {
     double ss = 0;
+#pragma unroll 1
     for (int j = tid; j < H; j += 256) {
       const double dv = (double)xs[j];
       ss = ss + dv * dv;
@@ -455,18 +524,11 @@ static __device__ __noinline__ void norm_quant(Ctx &c, const float *src, const u
     ps[tid] = ss;
   }
   csync();
-  if (tid < 128) ps[tid] = ps[tid] + ps[tid + 128];
-  csync();
-  if (tid < 64) ps[tid] = ps[tid] + ps[tid + 64];
-  csync();
-  if (tid < 32) {
-    double v = ps[tid] + ps[tid + 32];
+  double t = ((ps[lane] + ps[lane + 128]) + (ps[lane + 64] + ps[lane + 192])) +
+             ((ps[lane + 32] + ps[lane + 160]) + (ps[lane + 96] + ps[lane + 224]));
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) v = v + __shfl_xor_sync(kFull, v, off);
-    if (tid == 0) c.sh->s_inv = 1.0f / sqrtf((float)(v / (double)H) + c.P->eps);
-  }
-  csync();
-  const float inv = c.sh->s_inv;
+  for (int off = 16; off > 0; off >>= 1) t = t + __shfl_xor_sync(kFull, t, off);
+  const float inv = 1.0f / sqrtf((float)(t / (double)H) + PL.eps);
   uint32_t *xw = reinterpret_cast<uint32_t *>(act);
   float *sqs = reinterpret_cast<float *>(act + H);
 #pragma unroll
@@ -488,8 +550,8 @@ static __device__ __noinline__ void norm_quant(Ctx &c, const float *src, const u
 }
 
 // Stages an already quantised vector (INT8 + group scales in global memory).
-static __device__ __noinline__ void stage_q8(Ctx &c, const int8_t *xq, const float *sqg, int K) {
-  unsigned char *act = c.smem + kActOff;
+static __device__ __noinline__ void stage_q8(const int8_t *xq, const float *sqg, int K) {
+  unsigned char *act = step_smem + kActOff;
   uint32_t *xw = reinterpret_cast<uint32_t *>(act);
   float *sqs = reinterpret_cast<float *>(act + K);
   for (int pc = threadIdx.x; pc < K / 8; pc += kCons) {
@@ -501,35 +563,60 @@ static __device__ __noinline__ void stage_q8(Ctx &c, const int8_t *xq, const flo
   csync();
 }
 
-// Quantises M contiguous fp32 vectors of K (global memory) into the staged form.
-static __device__ __noinline__ void quant_rows(Ctx &c, const float *x, int K, int M) {
-  float *raw = reinterpret_cast<float *>(c.smem + kFbufOff);
-  unsigned char *act = c.smem + kActOff;
+// Quantises M contiguous fp32 vectors of K (global memory, M * K <= 8192) into the staged form.
+static __device__ __noinline__ void quant_rows(const float *x, int K, int M) {
+  float *raw = reinterpret_cast<float *>(step_smem + kFbufOff);
+  unsigned char *act = step_smem + kActOff;
   const int n4 = M * K / 4;
-  for (int i = threadIdx.x; i < n4; i += kCons)
-    reinterpret_cast<float4 *>(raw)[i] = __ldcg(reinterpret_cast<const float4 *>(x) + i);
+  float4 v[4];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int i = threadIdx.x + kCons * u;
+    v[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (i < n4) v[u] = __ldcg(reinterpret_cast<const float4 *>(x) + i);
+  }
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int i = threadIdx.x + kCons * u;
+    if (i < n4) reinterpret_cast<float4 *>(raw)[i] = v[u];
+  }
   csync();
   uint32_t *xw = reinterpret_cast<uint32_t *>(act);
   float *sqs = reinterpret_cast<float *>(act + (size_t)M * K);
   const int G = K >> 7, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #pragma unroll 1
   for (int gi = warp; gi < M * G; gi += 16) {
-    const float4 v = reinterpret_cast<const float4 *>(raw + (size_t)gi * 128)[lane];
-    quant_group_staged(xw, sqs, K, gi / G, gi % G, v);
+    const float4 q = reinterpret_cast<const float4 *>(raw + (size_t)gi * 128)[lane];
+    quant_group_staged(xw, sqs, K, gi / G, gi % G, q);
   }
   csync();
 }
 
 // Gated per-head norm + quantiser (RmsInv + NormGated + ScalesMax + Quantize,
 // kernels.cpp:619-644,551-579), one warp per head, into the staged form (K = nV * 128).
-static __device__ __noinline__ void gated_norm_quant(Ctx &c, const float *O, const float *Z, const float *W, int nV) {
-  float *os = reinterpret_cast<float *>(c.smem + kFbufOff), *zs = os + 4096;
-  unsigned char *act = c.smem + kActOff;
+static __device__ __noinline__ void gated_norm_quant(const float *O, const float *Z, const float *W, int nV) {
+  float *os = reinterpret_cast<float *>(step_smem + kFbufOff), *zs = os + 4096;
+  unsigned char *act = step_smem + kActOff;
   const int n4 = nV * 32, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const float4 wn = __ldg(reinterpret_cast<const float4 *>(W) + lane);
-  for (int i = threadIdx.x; i < n4; i += kCons) {
-    reinterpret_cast<float4 *>(os)[i] = __ldcg(reinterpret_cast<const float4 *>(O) + i);
-    reinterpret_cast<float4 *>(zs)[i] = __ldcg(reinterpret_cast<const float4 *>(Z) + i);
+  float4 vo[2], vz[2];  // nV * 128 <= 4096 values: at most two float4 of each per thread
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const int i = threadIdx.x + kCons * u;
+    vo[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    vz[u] = vo[u];
+    if (i < n4) {
+      vo[u] = __ldcg(reinterpret_cast<const float4 *>(O) + i);
+      vz[u] = __ldcg(reinterpret_cast<const float4 *>(Z) + i);
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const int i = threadIdx.x + kCons * u;
+    if (i < n4) {
+      reinterpret_cast<float4 *>(os)[i] = vo[u];
+      reinterpret_cast<float4 *>(zs)[i] = vz[u];
+    }
   }
   csync();
   const int K = nV * 128;
@@ -545,7 +632,7 @@ static __device__ __noinline__ void gated_norm_quant(Ctx &c, const float *O, con
       ss = fmaf(ov, ov, ss);
     }
     ss = warp_tree_sum(ss);
-    const float inv = 1.0f / sqrtf(ss / 128.0f + c.P->eps);
+    const float inv = 1.0f / sqrtf(ss / 128.0f + PL.eps);
     const float4 ov = reinterpret_cast<const float4 *>(o)[lane], zv = reinterpret_cast<const float4 *>(z)[lane];
     float4 y;
     y.x = ((wn.x * ov.x) * inv) * (zv.x / (1.0f + det_expf(-zv.x)));
@@ -570,12 +657,12 @@ __device__ __forceinline__ int mat_of_row(const GemvMat *m, int nm, int flat, in
 
 // One GEMV stage: this block's rows of the matrices, activations already staged. The operands
 // of the rows' epilogues (residual, conv state, decay constants) are fetched before the dot.
-static __device__ __noinline__ void gemv_stage_run(Ctx &c, const GemvMat *m, int nm, int K) {
+static __device__ __noinline__ uint32_t gemv_stage_run(uint32_t tile, const GemvMat *m, int nm, int K) {
   int lo, hi;
-  deal(mats_rows(m, nm), row_unit(K), c.blk, c.nblk, lo, hi);
-  if (lo >= hi) return;
-  float *T = reinterpret_cast<float *>(c.smem + kTOff);
-  unsigned char *act = c.smem + kActOff;
+  deal(mats_rows(m, nm), row_unit(K), (int)blockIdx.x, (int)gridDim.x, lo, hi);
+  if (lo >= hi) return tile;
+  float *T = reinterpret_cast<float *>(step_smem + kTOff);
+  unsigned char *act = step_smem + kActOff;
   const int G = K >> 7, nr = hi - lo;
   EpiOperands eo;
   int mi = 0, n = 0;
@@ -583,30 +670,31 @@ static __device__ __noinline__ void gemv_stage_run(Ctx &c, const GemvMat *m, int
     mi = mat_of_row(m, nm, lo + threadIdx.x, n);
     gemv_epilogue_fetch(&m[mi], n, 0, eo);
   }
-  dot_tiles(c, K, reinterpret_cast<const uint4 *>(act), reinterpret_cast<const float *>(act + K), T, 1 << 30, 0);
+  tile = dot_tiles(tile, K, reinterpret_cast<const uint4 *>(act), reinterpret_cast<const float *>(act + K), T, 1 << 30, 0);
   csync();
   if ((int)threadIdx.x < nr) gemv_epilogue_with(&m[mi], n, 0, row_sum_rt(T, threadIdx.x, G), eo);
   for (int r = threadIdx.x + kCons; r < nr; r += kCons) {
     mi = mat_of_row(m, nm, lo + r, n);
     gemv_epilogue(&m[mi], n, 0, row_sum_rt(T, r, G));
   }
+  return tile;
 }
 
 // Router logits of this block's rows from the ring (bf16 rows), activations hn in shared memory.
 // logits[e] = sum_k bf16(W[e][k]) * hn[k]: lane l takes k = (i*32+l)*8+j, fma chain in (i, j)
 // order, then the lane tree (as RouterTopK).
-static __device__ __noinline__ void router_stage(Ctx &c, const float *hn, int H, int rows_total) {
+static __device__ __noinline__ uint32_t router_stage(uint32_t tile, const float *hn, int H, int rows_total) {
   int lo, hi;
-  deal(rows_total, 1, c.blk, c.nblk, lo, hi);
-  if (lo >= hi) return;
+  deal(rows_total, 1, (int)blockIdx.x, (int)gridDim.x, lo, hi);
+  if (lo >= hi) return tile;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n = H / 256;
-  const uint32_t ring_a = smem_addr(c.smem + kRingOff);
+  const uint32_t ring_a = smem_addr(step_smem + kRingOff);
   bool last = false;
 #pragma unroll 1
   while (!last) {
-    const uint32_t slot = c.tile % kNT, use = c.tile / kNT;
-    if (!__all_sync(kFull, mbar_wait_b(c, smem_addr(&c.sh->full[slot]), use & 1u, 5))) return;
-    const TileDesc &d = c.sh->desc[slot];
+    const uint32_t slot = tile % kNT, use = tile / kNT;
+    if (!__all_sync(kFull, mbar_wait_b(smem_addr(&SH->full[slot]), use & 1u, 5))) return tile;
+    const TileDesc &d = SH->desc[slot];
     last = d.last != 0;
     const uint32_t tb = ring_a + slot * kTileStride;
     for (int r = warp; r < d.nrows; r += 16) {
@@ -633,23 +721,24 @@ static __device__ __noinline__ void router_stage(Ctx &c, const float *hn, int H,
         acc = fmaf(u2f(wv.w & 0xFFFF0000u), a1.w, acc);
       }
       acc = warp_tree_sum(acc);
-      if (lane == 0) c.P->RLogits[lo + trow] = acc;
+      if (lane == 0) PL.RLogits[lo + trow] = acc;
     }
     __syncwarp();
-    if (lane == 0) mbar_arrive_a(smem_addr(&c.sh->empty[slot]));
-    c.tile += 1;
+    if (lane == 0) mbar_arrive_a(smem_addr(&SH->empty[slot]));
+    tile += 1;
   }
+  return tile;
 }
 
 // Softmax over the E router logits, top-k by (probability desc, index asc), renormalised
 // weights, shared-expert gate: the selection of RouterTopK, run by every block for itself.
-static __device__ __noinline__ void router_select_cons(Ctx &c, int E, int k, bool has_shared) {
-  float *sp = reinterpret_cast<float *>(c.smem + kFbufOff);
-  unsigned *ck = reinterpret_cast<unsigned *>(c.smem + kTOff), *ci = ck + kTopkWarps * kTopkMaxSel;
-  StepShared *sh = c.sh;
+static __device__ __noinline__ void router_select_cons(int E, int k, bool has_shared) {
+  float *sp = reinterpret_cast<float *>(step_smem + kFbufOff);
+  unsigned *ck = reinterpret_cast<unsigned *>(step_smem + kTOff), *ci = ck + kTopkWarps * kTopkMaxSel;
+  StepShared *sh = SH;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   for (int e = tid; e <= E; e += kCons)
-    if (e < E || has_shared) sp[e] = __ldcg(c.P->RLogits + e);
+    if (e < E || has_shared) sp[e] = __ldcg(PL.RLogits + e);
   csync();
   if (tid < 32) {
     float m = -INFINITY;
@@ -705,26 +794,26 @@ static __device__ __noinline__ void router_select_cons(Ctx &c, int E, int k, boo
 // One (head, column slice) item per block, 256 threads, state in registers; the arithmetic is
 // DeltaNetStep's (deltanet_core.cuh). The state of the block's first item is loaded before the
 // grid barrier is waited for: it was last written one token ago by this same block.
-static __device__ __noinline__ void deltanet_stage(Ctx &c, const StepLayer &ly) {
-  const StepPlan &P = *c.P;
+static __device__ __noinline__ void deltanet_stage(unsigned epoch, const StepLayer &ly) {
+  const StepPlan &P = PL;
   constexpr int D = 128, SEG = kDnSeg;
   DeltaNetStepArgs a{P.O, P.Mx, ly.S, P.Bt, P.Gt, P.nK, P.nV};
   const int nitems = P.nV * kDnSlices;
   const bool worker = threadIdx.x < 256;
   float s[SEG];
-  if (worker && c.blk < nitems) deltanet_load_state(a, c.blk, s);
-  grid_wait(c);
+  if (worker && (int)blockIdx.x < nitems) deltanet_load_state(a, (int)blockIdx.x, s);
+  grid_wait(epoch);
   if (!worker) return;
-  float *qs = reinterpret_cast<float *>(c.smem + kFbufOff), *ks = qs + D;
+  float *qs = reinterpret_cast<float *>(step_smem + kFbufOff), *ks = qs + D;
   float(*part)[32] = reinterpret_cast<float(*)[32]>(ks + D);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 #pragma unroll 1
-  for (int item = c.blk; item < nitems; item += c.nblk) {
+  for (int item = (int)blockIdx.x; item < nitems; item += (int)gridDim.x) {
     const int h = item / kDnSlices, slice = item % kDnSlices;
     const int kh = h / (a.nV / a.nK);
     const int col = slice * 32 + lane;
     float *Sh = a.S + (size_t)h * D * D;
-    if (item != c.blk) deltanet_load_state(a, item, s);
+    if (item != (int)blockIdx.x) deltanet_load_state(a, item, s);
     if (warp < 2) {
       const float *src = a.Mx + (warp == 0 ? (size_t)kh * D : (size_t)a.nK * D + (size_t)kh * D);
       float x[4];
@@ -782,18 +871,18 @@ static __device__ __noinline__ void deltanet_stage(Ctx &c, const StepLayer &ly) 
 // (attention_core.cuh). K/V rows of earlier tokens are fetched before the grid barrier is
 // waited for (they were written by earlier steps).
 template <int GQ>
-static __device__ __noinline__ void attn_stage_t(Ctx &c, const StepLayer &ly, int pos, int T) {
-  const StepPlan &P = *c.P;
+static __device__ __noinline__ void attn_stage_t(unsigned epoch, const StepLayer &ly, int pos, int T) {
+  const StepPlan &P = PL;
   constexpr int D = kHeadDim, C = kAttnChunk;
   constexpr int GH = (GQ + 1) / 2;  // query heads per half of the block in the value pass
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int nKV = P.nKV;
   const int nch = (T + C - 1) / C, nitems = nch * nKV;
-  unsigned char *kvs = c.smem + kFbufOff;  // K rows [C][D], then V rows [C][D]
-  float *qs = reinterpret_cast<float *>(c.smem + kTOff);  // [GQ][D]
+  unsigned char *kvs = step_smem + kFbufOff;  // K rows [C][D], then V rows [C][D]
+  float *qs = reinterpret_cast<float *>(step_smem + kTOff);  // [GQ][D]
   float *sc = qs + GQ * D;                                // [GQ][C]
   uint16_t *kss = reinterpret_cast<uint16_t *>(sc + GQ * C), *vss = kss + C;
-  StepShared *sh = c.sh;
+  StepShared *sh = SH;
   const int p = pos < P.max_ctx ? pos : P.max_ctx - 1;  // clamp, kernels.cpp:456
   const float scale = 1.0f / sqrtf((float)D);
 
@@ -818,13 +907,13 @@ static __device__ __noinline__ void attn_stage_t(Ctx &c, const StepLayer &ly, in
       if (row < nt && t0 + row != p) scr = __ldcg((tid < C ? ly.Ks : ly.Vs) + (size_t)(t0 + row) * nKV + kv);
     }
   };
-  if (c.blk < nitems) load_chunk(c.blk);
-  grid_wait(c);
+  if ((int)blockIdx.x < nitems) load_chunk((int)blockIdx.x);
+  grid_wait(epoch);
 #pragma unroll 1
-  for (int item = c.blk; item < nitems; item += c.nblk) {
+  for (int item = (int)blockIdx.x; item < nitems; item += (int)gridDim.x) {
     const int ch = item / nKV, kv = item % nKV, t0 = ch * C;
     const int nt = (T < t0 + C ? T : t0 + C) - t0;
-    if (item != c.blk) load_chunk(item);
+    if (item != (int)blockIdx.x) load_chunk(item);
 #pragma unroll
     for (int u = 0; u < 4; ++u) reinterpret_cast<uint4 *>(kvs)[tid + kCons * u] = kvr[u];
     if (tid < C) kss[tid] = scr;
@@ -954,29 +1043,29 @@ static __device__ __noinline__ void attn_stage_t(Ctx &c, const StepLayer &ly, in
     csync();
   }
 }
-static __device__ __noinline__ void attn_stage(Ctx &c, const StepLayer &ly, int pos, int T) {
-  switch (c.P->nQ / c.P->nKV) {
-    case 1: attn_stage_t<1>(c, ly, pos, T); break;
-    case 2: attn_stage_t<2>(c, ly, pos, T); break;
-    case 4: attn_stage_t<4>(c, ly, pos, T); break;
-    case 6: attn_stage_t<6>(c, ly, pos, T); break;
-    case 8: attn_stage_t<8>(c, ly, pos, T); break;
-    default: grid_wait(c); break;  // rejected on the host
+static __device__ __noinline__ void attn_stage(unsigned epoch, const StepLayer &ly, int pos, int T) {
+  switch (PL.nQ / PL.nKV) {
+    case 1: attn_stage_t<1>(epoch, ly, pos, T); break;
+    case 2: attn_stage_t<2>(epoch, ly, pos, T); break;
+    case 4: attn_stage_t<4>(epoch, ly, pos, T); break;
+    case 6: attn_stage_t<6>(epoch, ly, pos, T); break;
+    case 8: attn_stage_t<8>(epoch, ly, pos, T); break;
+    default: grid_wait(epoch); break;  // rejected on the host
   }
 }
 
 // Ordered merge of the chunk partials of one query head per block (256 threads), sigmoid
 // gate, quantiser: AttnCombine's arithmetic (attention_core.cuh).
-static __device__ __noinline__ void attn_combine_stage(Ctx &c, int T) {
-  const StepPlan &P = *c.P;
+static __device__ __noinline__ void attn_combine_stage(int T) {
+  const StepPlan &P = PL;
   constexpr int D = kHeadDim, C = kAttnChunk;
   if (threadIdx.x >= 256) return;
-  float *s_pm = reinterpret_cast<float *>(c.smem + kFbufOff), *s_pf = s_pm + 2048;
-  float *wmax = c.sh->wmax;
+  float *s_pm = reinterpret_cast<float *>(step_smem + kFbufOff), *s_pf = s_pm + 2048;
+  float *wmax = SH->wmax;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int nch = (T + C - 1) / C;
 #pragma unroll 1
-  for (int h = c.blk; h < P.nQ; h += c.nblk) {
+  for (int h = (int)blockIdx.x; h < P.nQ; h += (int)gridDim.x) {
     const float *pm = P.Pm + (size_t)h * P.max_chunks;
     const float *pse = P.Pse + (size_t)h * P.max_chunks;
     const float *pacc = P.Pacc + (size_t)h * P.max_chunks * D;
@@ -1020,65 +1109,65 @@ static __device__ __noinline__ void attn_combine_stage(Ctx &c, int T) {
 }
 
 // ------------------------------------------------------------------- MoE stages ---
-static __device__ __noinline__ void gateup_stage(Ctx &c) {
-  const StepPlan &P = *c.P;
+static __device__ __noinline__ uint32_t gateup_stage(uint32_t tile) {
+  const StepPlan &P = PL;
   const int H = P.H;
   int lo, hi;
-  deal(P.slots * P.I, row_unit(H), c.blk, c.nblk, lo, hi);
-  if (lo >= hi) return;
-  float *T = reinterpret_cast<float *>(c.smem + kTOff);
-  unsigned char *act = c.smem + kActOff;
-  dot_tiles(c, H, reinterpret_cast<const uint4 *>(act), reinterpret_cast<const float *>(act + H), T, 1 << 30, 0);
+  deal(P.slots * P.I, row_unit(H), (int)blockIdx.x, (int)gridDim.x, lo, hi);
+  if (lo >= hi) return tile;
+  float *T = reinterpret_cast<float *>(step_smem + kTOff);
+  unsigned char *act = step_smem + kActOff;
+  tile = dot_tiles(tile, H, reinterpret_cast<const uint4 *>(act), reinterpret_cast<const float *>(act + H), T, 1 << 30, 0);
   csync();
   const int np = hi - lo, G = H >> 7;
   for (int r = threadIdx.x; r < np; r += kCons) {
     const float g = row_sum_rt(T, r, G), u = row_sum_rt(T, np + r, G);
     P.Act[lo + r] = silu_mul(g, u);
   }
+  return tile;
 }
 
-static __device__ __noinline__ void down_stage(Ctx &c, int L) {
-  const StepPlan &P = *c.P;
+static __device__ __noinline__ uint32_t down_stage(uint32_t tile, int L) {
+  const StepPlan &P = PL;
   const int H = P.H, I = P.I;
   int lo, hi;
-  deal(H, row_unit(I), c.blk, c.nblk, lo, hi);
+  deal(H, row_unit(I), (int)blockIdx.x, (int)gridDim.x, lo, hi);
   // residual input of this block's rows: in flight while the activations are staged
   float res = 0.0f;
   if (lo + (int)threadIdx.x < hi) res = __ldcg(P.Tmp + lo + threadIdx.x);
-  quant_rows(c, P.Act, I, P.slots);
-  if (lo >= hi) return;
-  float *T = reinterpret_cast<float *>(c.smem + kTOff);
-  unsigned char *act = c.smem + kActOff;
-  dot_tiles(c, I, reinterpret_cast<const uint4 *>(act), reinterpret_cast<const float *>(act + (size_t)P.slots * I), T,
+  quant_rows(P.Act, I, P.slots);
+  stamp(2);
+  if (lo >= hi) return tile;
+  float *T = reinterpret_cast<float *>(step_smem + kTOff);
+  unsigned char *act = step_smem + kActOff;
+  tile = dot_tiles(tile, I, reinterpret_cast<const uint4 *>(act), reinterpret_cast<const float *>(act + (size_t)P.slots * I), T,
             1 << 30, 0);
   csync();
   const int nr = hi - lo, G = I >> 7;
   for (int r = threadIdx.x; r < nr; r += kCons) {
     if (r >= kCons) res = __ldcg(P.Tmp + lo + r);
     float acc = 0.0f;
-    for (int s = 0; s < P.slots; ++s) acc = acc + c.sh->sel_w[s] * row_sum_rt(T, s * nr + r, G);
+    for (int s = 0; s < P.slots; ++s) acc = acc + SH->sel_w[s] * row_sum_rt(T, s * nr + r, G);
     const float x = res + acc;
     P.X[lo + r] = x;
     if (P.layer_out) P.layer_out[(size_t)L * H + lo + r] = x;
   }
+  return tile;
 }
 
 // LM head in sub-blocks of 16 tiles (t[][] holds 256 rows of K = 2048), running argmax per thread.
-static __device__ __noinline__ void lm_head_stage(Ctx &c, float &bv, int &bi) {
-  const StepPlan &P = *c.P;
+static __device__ __noinline__ uint32_t lm_head_stage(uint32_t tile, float &bv, int &bi) {
+  const StepPlan &P = PL;
   const int K = P.H, G = K >> 7;
   int lo, hi;
-  deal(P.vocab, row_unit(K), c.blk, c.nblk, lo, hi);
-  if (lo >= hi) return;
-  float *T = reinterpret_cast<float *>(c.smem + kTOff);
-  unsigned char *act = c.smem + kActOff;
+  deal(P.vocab, row_unit(K), (int)blockIdx.x, (int)gridDim.x, lo, hi);
+  float *T = reinterpret_cast<float *>(step_smem + kTOff);
+  unsigned char *act = step_smem + kActOff;
   const int rpt = 2 * kTileBytes / K;
   const int sub_tiles = (kTCap / G) / rpt;  // tiles whose rows fit t[][]
-  int base = 0;
-  bool last = false;
 #pragma unroll 1
-  while (!last) {
-    last = dot_tiles(c, K, reinterpret_cast<const uint4 *>(act), reinterpret_cast<const float *>(act + K), T, sub_tiles,
+  for (int base = 0; base < hi - lo; base += sub_tiles * rpt) {
+    tile = dot_tiles(tile, K, reinterpret_cast<const uint4 *>(act), reinterpret_cast<const float *>(act + K), T, sub_tiles,
                      base);
     csync();
     const int nrows = (hi - lo) - base < sub_tiles * rpt ? (hi - lo) - base : sub_tiles * rpt;
@@ -1088,40 +1177,42 @@ static __device__ __noinline__ void lm_head_stage(Ctx &c, float &bv, int &bi) {
       P.Logits[n] = v;
       argmax_merge(bv, bi, v, n);
     }
-    base += nrows;
     csync();
   }
+  return tile;
 }
 
 // Block-wide first-max-wins argmax over the consumer threads; result valid in thread 0.
-__device__ __forceinline__ void cons_argmax(Ctx &c, float &bv, int &bi) {
+static __device__ __noinline__ void cons_argmax(float &bv, int &bi) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1)
     argmax_merge(bv, bi, __shfl_xor_sync(kFull, bv, off), __shfl_xor_sync(kFull, bi, off));
   if (lane == 0) {
-    c.sh->av[warp] = bv;
-    c.sh->ai[warp] = bi;
+    SH->av[warp] = bv;
+    SH->ai[warp] = bi;
   }
   csync();
   if (warp == 0) {
-    bv = lane < 16 ? c.sh->av[lane] : -INFINITY;
-    bi = lane < 16 ? c.sh->ai[lane] : 0x7FFFFFFF;
+    bv = lane < 16 ? SH->av[lane] : -INFINITY;
+    bi = lane < 16 ? SH->ai[lane] : 0x7FFFFFFF;
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1)
       argmax_merge(bv, bi, __shfl_xor_sync(kFull, bv, off), __shfl_xor_sync(kFull, bi, off));
   }
 }
 
-static __device__ __noinline__ void consumer_main(Ctx &c, int mode) {
-  const StepPlan &P = *c.P;
-  StepShared *sh = c.sh;
+static __device__ __noinline__ void consumer_main(int mode) {
+  const StepPlan &P = PL;
+  StepShared *sh = SH;
   const int H = P.H, tid = threadIdx.x;
+  uint32_t tile = 0;   // running index of the next ring tile to consume
+  unsigned epoch = 0;  // grid barriers this block has arrived at
   const int token = __ldcg(P.ctrl + CTRL_TOKEN), pos = __ldcg(P.ctrl + CTRL_POS);
   int T = __ldcg(P.ctrl + CTRL_LEN);
   if (T > P.max_ctx) T = P.max_ctx;
   const int tok = token < 0 ? 0 : (token >= P.vocab ? P.vocab - 1 : token);
-  float *hn = reinterpret_cast<float *>(c.smem + kFbufOff) + 4096;
+  float *hn = reinterpret_cast<float *>(step_smem + kFbufOff) + 4096;
 
   for (int L = 0; L < P.layers; ++L) {
     // the layer's record into shared memory (the previous layer's is no longer read: every
@@ -1134,44 +1225,59 @@ static __device__ __noinline__ void consumer_main(Ctx &c, int mode) {
     const StepLayer &ly = sh->ly;
     const bool lin = ly.type == 0;
     // ---- stage 1: input norm + quantiser, first projections ----
-    norm_quant(c, P.X, L == 0 ? P.emb + (size_t)tok * H : nullptr, ly.in_norm, H, nullptr,
-               (L == 0 && c.blk == 0) ? P.X : nullptr);
-    gemv_stage_run(c, &ly.m[0], lin ? 4 : 3, H);
-    grid_arrive(c);
+    norm_quant(P.X, L == 0 ? P.emb + (size_t)tok * H : nullptr, ly.in_norm, H, nullptr,
+               (L == 0 && (int)blockIdx.x == 0) ? P.X : nullptr);
+    stamp(2);
+    tile = gemv_stage_run(tile, &ly.m[0], lin ? 4 : 3, H);
+    stamp(3);
+    grid_arrive();
+    ++epoch;
     if (lin) {
       // ---- stage 2: gated delta rule ----
-      deltanet_stage(c, ly);  // waits for the barrier inside, after its state loads
-      grid_arrive(c);
-      grid_wait(c);
+      deltanet_stage(epoch, ly);  // waits for the barrier inside, after its state loads
+      grid_arrive();
+    ++epoch;
+      grid_wait(epoch);
       // ---- stage 3: gated norm, out_proj + residual ----
-      gated_norm_quant(c, P.O, P.Z, ly.lin_norm, P.nV);
-      gemv_stage_run(c, &ly.m[4], 1, P.nV * 128);
+      stamp(4);
+      gated_norm_quant(P.O, P.Z, ly.lin_norm, P.nV);
+      stamp(2);
+      tile = gemv_stage_run(tile, &ly.m[4], 1, P.nV * 128);
+      stamp(3);
     } else {
-      attn_stage(c, ly, pos, T);  // waits for the barrier inside, after its KV loads
-      grid_arrive(c);
-      grid_wait(c);
-      attn_combine_stage(c, T);
-      grid_arrive(c);
-      grid_wait(c);
-      stage_q8(c, P.Q8, P.SQ, P.nQ * 256);
-      gemv_stage_run(c, &ly.m[4], 1, P.nQ * 256);
+      attn_stage(epoch, ly, pos, T);  // waits for the barrier inside, after its KV loads
+      grid_arrive();
+    ++epoch;
+      grid_wait(epoch);
+      attn_combine_stage(T);
+      grid_arrive();
+    ++epoch;
+      grid_wait(epoch);
+      stage_q8(P.Q8, P.SQ, P.nQ * 256);
+      tile = gemv_stage_run(tile, &ly.m[4], 1, P.nQ * 256);
     }
-    grid_arrive(c);
-    grid_wait(c);
+    grid_arrive();
+    ++epoch;
+    grid_wait(epoch);
     // ---- stage 4: post norm + quantiser (kept staged for the experts), router logits ----
-    norm_quant(c, P.Tmp, nullptr, ly.post_norm, H, hn, nullptr);
-    router_stage(c, hn, H, P.E + (ly.shared_gate ? 1 : 0));
-    grid_arrive(c);
-    grid_wait(c);
+    norm_quant(P.Tmp, nullptr, ly.post_norm, H, hn, nullptr);
+    stamp(2);
+    tile = router_stage(tile, hn, H, P.E + (ly.shared_gate ? 1 : 0));
+    stamp(3);
+    grid_arrive();
+    ++epoch;
+    grid_wait(epoch);
     // ---- stage 5: selection, expert gate/up ----
-    router_select_cons(c, P.E, P.topk, ly.shared_gate != nullptr);
+    router_select_cons(P.E, P.topk, ly.shared_gate != nullptr);
+    stamp(5);
     if (tid < P.slots * 3) {
       const uint4 *src = reinterpret_cast<const uint4 *>(ly.experts + sh->sel_idx[tid / 3]) + tid % 3;
       reinterpret_cast<uint4 *>(sh->sew + tid / 3)[tid % 3] = __ldg(src);
     }
     csync();
     if (tid == 0) mbar_arrive(&sh->sel_bar);  // the producer may now stream the experts
-    if (c.blk == 0 && tid <= P.topk) {
+    stamp(6);
+    if ((int)blockIdx.x == 0 && tid <= P.topk) {
       P.SelIdx[tid] = sh->sel_idx[tid];
       P.SelW[tid] = sh->sel_w[tid];
       if (tid == 0) *P.NearGap = sh->gap;
@@ -1180,18 +1286,22 @@ static __device__ __noinline__ void consumer_main(Ctx &c, int mode) {
         if (tid == 0) P.near_gap[L] = sh->gap;
       }
     }
-    gateup_stage(c);
-    grid_arrive(c);
-    grid_wait(c);
+    tile = gateup_stage(tile);
+    stamp(3);
+    grid_arrive();
+    ++epoch;
+    grid_wait(epoch);
     // ---- stage 6: expert down, combine, residual ----
-    down_stage(c, L);
-    grid_arrive(c);
-    grid_wait(c);
+    tile = down_stage(tile, L);
+    stamp(3);
+    grid_arrive();
+    ++epoch;
+    grid_wait(epoch);
   }
 
   if (mode == 0) {
     // prompt step: no logits; move on to the next prompt id
-    if (c.blk == 0 && tid == 0) {
+    if ((int)blockIdx.x == 0 && tid == 0) {
       const int np = pos + 1;
       P.ctrl[CTRL_POS] = np;
       P.ctrl[CTRL_LEN] = P.ctrl[CTRL_LEN] + 1;
@@ -1201,23 +1311,24 @@ static __device__ __noinline__ void consumer_main(Ctx &c, int mode) {
     return;
   }
   // ---- tail: final norm, LM head, first-max-wins argmax, control update ----
-  norm_quant(c, P.X, nullptr, P.final_norm, H, nullptr, nullptr);
+  norm_quant(P.X, nullptr, P.final_norm, H, nullptr, nullptr);
   float bv = -INFINITY;
   int bi = 0x7FFFFFFF;
-  lm_head_stage(c, bv, bi);
-  cons_argmax(c, bv, bi);
+  tile = lm_head_stage(tile, bv, bi);
+  cons_argmax(bv, bi);
   if (tid == 0) {
-    P.PV[c.blk] = bv;
-    P.PI[c.blk] = bi;
+    P.PV[(int)blockIdx.x] = bv;
+    P.PI[(int)blockIdx.x] = bi;
   }
-  grid_arrive(c);
-  grid_wait(c);
-  if (c.blk == 0) {
+  grid_arrive();
+    ++epoch;
+  grid_wait(epoch);
+  if ((int)blockIdx.x == 0) {
     bv = -INFINITY;
     bi = 0x7FFFFFFF;
-    for (int i = tid; i < c.nblk; i += kCons) argmax_merge(bv, bi, __ldcg(P.PV + i), __ldcg(P.PI + i));
+    for (int i = tid; i < (int)gridDim.x; i += kCons) argmax_merge(bv, bi, __ldcg(P.PV + i), __ldcg(P.PI + i));
     csync();
-    cons_argmax(c, bv, bi);
+    cons_argmax(bv, bi);
     if (tid == 0) {
       P.out_tok[0] = bi;
       if (P.history && P.history_cap > 0) P.history[pos % P.history_cap] = bi;
@@ -1229,10 +1340,8 @@ static __device__ __noinline__ void consumer_main(Ctx &c, int mode) {
   }
 }
 
-extern __shared__ __align__(128) unsigned char step_smem[];
-
 __global__ void __launch_bounds__(kStepThreads, 1) DecodeStep(const DecodeStepArgs args) {
-  StepShared *sh = reinterpret_cast<StepShared *>(step_smem);
+  StepShared *sh = SH;
   if (threadIdx.x == 0) {
     for (int i = 0; i < kNT; ++i) {
       mbar_init(&sh->full[i], 1);
@@ -1240,28 +1349,30 @@ __global__ void __launch_bounds__(kStepThreads, 1) DecodeStep(const DecodeStepAr
     }
     mbar_init(&sh->sel_bar, 1);
     sh->fail = 0;
+    sh->nstamp[0] = 0;
+    sh->nstamp[1] = 0;
+    sh->nseg = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  if (threadIdx.x < sizeof(StepPlan) / 16)
+    reinterpret_cast<uint4 *>(&sh->plan)[threadIdx.x] = __ldg(reinterpret_cast<const uint4 *>(args.plan) + threadIdx.x);
   __syncthreads();
-  if (*(volatile int *)args.plan->error != 0) return;  // a previous launch failed: stay out
-  Ctx c{args.plan, sh, step_smem, 0u, 0u, (int)blockIdx.x, (int)gridDim.x, 0};
+  if (*(volatile int *)PL.error != 0) return;  // a previous launch failed: stay out
   if (threadIdx.x >= kCons) {
-    if (threadIdx.x == kCons) {
-      producer_main(c, args.mode);
-      // Nothing may still be landing in this block's shared memory when it retires: wait
-      // (bounded) for the last use of every ring slot. In a run without faults the consumers
-      // have waited for all of them already.
-      const uint32_t issued = c.tile;
-      for (uint32_t st = 0; st < (uint32_t)kNT && st < issued; ++st) {
-        const uint32_t t = issued - 1u - ((issued - 1u - st) % kNT);  // latest tile issued into slot st
-        const unsigned long long t0 = gtime_ns();
-        while (!mbar_try(&sh->full[st], (t / kNT) & 1u))
-          if (gtime_ns() - t0 > kWaitNs) break;
-      }
+    const uint32_t issued = producer_main(args.mode);
+    // Nothing may still be landing in this block's shared memory when it retires: every slot
+    // owner waits (bounded) for the last tile it issued. In a run without faults the consumers
+    // have waited for all of them already.
+    const uint32_t lane = threadIdx.x & 31;
+    if (lane < (uint32_t)kNT && issued > lane) {
+      const uint32_t t = issued - 1u - ((issued - 1u - lane) % kNT);  // latest tile issued into slot `lane`
+      const long long t0 = clock64();
+      while (!mbar_try(&sh->full[lane], (t / kNT) & 1u))
+        if (clock64() - t0 > kWaitCycles) break;
     }
     return;
   }
-  consumer_main(c, args.mode);
+  consumer_main(args.mode);
 }
 
 static uint32_t step_smem_fn(const void *) { return (uint32_t)kStepSmemBytes; }

@@ -296,29 +296,19 @@ def main(argv=None):
                           "ms_per_token": ms / args.steps, "launches_per_token": sess.launches_per_token(),
                           "tokens": [int(t) for t in toks]}), flush=True)
         if args.stage_clock:
+            # block 0's records of the last token: [id, microseconds since the previous record]; the
+            # consumers' list (id 1 = a grid barrier was passed) and the producer warp's list
             st = sess.read("stage_stamps", np.uint64)
             half = len(st) // 2
-            coarse = st[:half][st[:half] != 0].astype(np.int64)
-            d = np.diff(coarse) / 1000.0
-            print(json.dumps({"op": "stage_clock", "unit": "us", "stages": [round(float(x), 2) for x in d]}), flush=True)
-            fine = st[half:][st[half:] != 0]
-            if len(fine):
-                mask = (1 << 48) - 1
-                cyc = {int(t) >> 48: int(t) & mask for t in fine if (int(t) >> 48) in (61, 63)}
-                tim = {int(t) >> 48: int(t) & mask for t in fine if (int(t) >> 48) in (60, 62)}
-                if len(cyc) == 2 and len(tim) == 2:
-                    print(json.dumps({"op": "sm_clock", "mhz": round((cyc[63] - cyc[61]) / ((tim[62] - tim[60]) / 1000.0), 1)}), flush=True)
-                fine = np.array([t for t in fine if (int(t) >> 48) not in (61, 63)], dtype=np.uint64)
-                ev = [(int(t) & mask, 0) for t in coarse] + [(int(t) & mask, int(t) >> 48) for t in fine]
-                ev.sort()
-                t0 = ev[0][0]
-                # merged timeline of the last token: [id, microseconds since the previous event];
-                # id 0 = the barrier clock's own stamps, other ids = points inside the stages
-                tl, prev = [], t0
-                for (t, i) in ev:
-                    tl.append([i, round((t - prev) / 1000.0, 2)])
+            mask = (1 << 48) - 1
+            for name, part in (("consumer", st[:half]), ("producer", st[half:])):
+                part = part[part != 0]
+                ev = [(int(t) >> 48, int(t) & mask) for t in part]
+                out, prev = [], ev[0][1] if ev else 0
+                for (i, t) in ev:
+                    out.append([i, round((t - prev) / 1000.0, 2)])
                     prev = t
-                print(json.dumps({"op": "fine_clock", "unit": "us", "events": tl}), flush=True)
+                print(json.dumps({"op": "stage_clock", "who": name, "unit": "us", "events": out}), flush=True)
         sess.close(); model.close()
     dev.close()
     return 0

@@ -225,3 +225,41 @@ class Session:
         if self.h:
             lib().orc_session_free(self.h)
             self.h = None
+
+
+def preset_json(name):
+    """Architecture JSON of a named synthetic shape (oracle/presets.json; the same shapes as the
+    runtime's presets, which a test compares)."""
+    import json
+    with open(os.path.join(ORACLE_DIR, "presets.json")) as f:
+        return json.dumps(json.load(f)[name], separators=(",", ":"))
+
+
+def model_from_device(dev, model):
+    """Oracle model whose tensors are host copies of a device model's two weight arenas.
+    dev: ainfer_b200.cuda_abi.Device, model: ainfer_b200.runtime.Model (both passed in: this
+    module never imports the product)."""
+    n = model.tensor_count()
+    infos = [model.tensor_at(i) for i in range(n)]
+    spans = {}
+    for kind, ptr_of, len_of in (("data", lambda t: t.data, lambda t: t.data_bytes),
+                                 ("scales", lambda t: t.scales, lambda t: t.scale_bytes)):
+        live = [(ptr_of(t), len_of(t)) for t in infos if len_of(t)]
+        lo = min(p for p, _ in live)
+        hi = max(p + b for p, b in live)
+        host = np.empty(hi - lo, np.uint8)
+        step = 1 << 30
+        for off in range(0, hi - lo, step):
+            nb = min(step, hi - lo - off)
+            host[off:off + nb] = dev.download(lo + off, nb, np.uint8)
+        spans[kind] = (lo, host)
+    om = Model(arch_json=model.config_json)
+    for t in infos:
+        lo, host = spans["data"]
+        data = host[t.data - lo:t.data - lo + t.data_bytes]
+        scales = None
+        if t.scale_bytes:
+            slo, shost = spans["scales"]
+            scales = shost[t.scales - slo:t.scales - slo + t.scale_bytes].view(np.uint16)
+        om.add_tensor(t.name.decode(), t.storage, list(t.shape)[:t.ndim], data, scales)
+    return om

@@ -22,34 +22,6 @@ pytestmark = pytest.mark.gpu
 PROMPT, GEN = 512, 256
 
 
-def oracle_model_from_device(dev, model):
-    """Oracle model whose tensors are host copies of the device model's arenas."""
-    n = model.tensor_count()
-    infos = [model.tensor_at(i) for i in range(n)]
-    spans = {}
-    for kind, ptr_of, len_of in (("data", lambda t: t.data, lambda t: t.data_bytes),
-                                 ("scales", lambda t: t.scales, lambda t: t.scale_bytes)):
-        live = [(ptr_of(t), len_of(t)) for t in infos if len_of(t)]
-        lo = min(p for p, _ in live)
-        hi = max(p + b for p, b in live)
-        host = np.empty(hi - lo, np.uint8)
-        step = 1 << 30
-        for off in range(0, hi - lo, step):
-            nb = min(step, hi - lo - off)
-            host[off:off + nb] = dev.download(lo + off, nb, np.uint8)
-        spans[kind] = (lo, host)
-    om = O.Model(arch_json=model.config_json)
-    for t in infos:
-        lo, host = spans["data"]
-        data = host[t.data - lo:t.data - lo + t.data_bytes]
-        scales = None
-        if t.scale_bytes:
-            slo, shost = spans["scales"]
-            scales = shost[t.scales - slo:t.scales - slo + t.scale_bytes].view(np.uint16)
-        om.add_tensor(t.name.decode(), t.storage, list(t.shape)[:t.ndim], data, scales)
-    return om
-
-
 def test_full_model_256_greedy_tokens_routing_logits_state():
     from ainfer_b200 import cuda_abi, runtime
     dev = cuda_abi.Device(0)
@@ -59,7 +31,7 @@ def test_full_model_256_greedy_tokens_routing_logits_state():
     model = runtime.Model(dev, "synth:full:seed=0")
     cfg = model.config
     V, k = cfg["vocab"], cfg["top_k"]
-    om = oracle_model_from_device(dev, model)
+    om = O.model_from_device(dev, model)
     max_ctx = PROMPT + GEN + 8
     prompt = np.array([O.lib().orc_draw_u32(b"input.prompt", 0, i) % V for i in range(PROMPT)], np.int32)
 
