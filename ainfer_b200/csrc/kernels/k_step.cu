@@ -399,7 +399,7 @@ static __device__ __noinline__ uint32_t producer_main(int mode) {
 // max_tiles tiles); returns the running index after the last tile consumed. A tile is
 // 256 (row, group) tasks of 64 bytes; two adjacent lanes share a task (32 bytes each) and add
 // their exact integer sums with one shuffle.
-static __device__ __noinline__ uint32_t dot_tiles(uint32_t tile, int K, const uint4 *xa, const float *sq, float *T,
+__device__ __forceinline__ uint32_t dot_tiles(uint32_t tile, int K, const uint4 *xa, const float *sq, float *T,
                                                   int max_tiles, int trow_base) {
   const int G = K >> 7, lg = 31 - __clz(G);
   const int TS = (kTCap >> lg) + 1;
@@ -656,7 +656,9 @@ __device__ __forceinline__ int mat_of_row(const GemvMat *m, int nm, int flat, in
 }
 
 // One GEMV stage: this block's rows of the matrices, activations already staged. The operands
-// of the rows' epilogues (residual, conv state, decay constants) are fetched before the dot.
+// of the rows' epilogues (residual, conv state, decay constants) are fetched before the dot and
+// stay in flight during it: dot_tiles is inlined here, because across a real call the compiler
+// would have to spill the registers the loads land in, and the spill would wait for the loads.
 static __device__ __noinline__ uint32_t gemv_stage_run(uint32_t tile, const GemvMat *m, int nm, int K) {
   int lo, hi;
   deal(mats_rows(m, nm), row_unit(K), (int)blockIdx.x, (int)gridDim.x, lo, hi);
@@ -733,31 +735,26 @@ static __device__ __noinline__ uint32_t router_stage(uint32_t tile, const float 
 // Softmax over the E router logits, top-k by (probability desc, index asc), renormalised
 // weights, shared-expert gate: the selection of RouterTopK, run by every block for itself.
 static __device__ __noinline__ void router_select_cons(int E, int k, bool has_shared) {
-  float *sp = reinterpret_cast<float *>(step_smem + kFbufOff);
+  float *lg = reinterpret_cast<float *>(step_smem + kFbufOff), *sp = lg + 2048;  // logits, probabilities (E <= 1024)
   unsigned *ck = reinterpret_cast<unsigned *>(step_smem + kTOff), *ci = ck + kTopkWarps * kTopkMaxSel;
   StepShared *sh = SH;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   for (int e = tid; e <= E; e += kCons)
-    if (e < E || has_shared) sp[e] = __ldcg(PL.RLogits + e);
+    if (e < E || has_shared) lg[e] = __ldcg(PL.RLogits + e);
   csync();
-  if (tid < 32) {
-    float m = -INFINITY;
-    for (int e = lane; e < E; e += 32) m = fmaxf(m, sp[e]);
-    m = warp_max(m);
-    if (lane == 0) sh->s_m = m;
-  }
+  // maximum and sum keep the one-warp partition (lane l takes entries l, l+32, ... in ascending
+  // order, then the xor butterfly); every warp evaluates them for itself, which gives every warp
+  // the same bits and saves two block barriers and two one-warp sections
+  float m = -INFINITY;
+  for (int e = lane; e < E; e += 32) m = fmaxf(m, lg[e]);
+  m = warp_max(m);
+  for (int e = tid; e < E; e += kCons) sp[e] = det_expf(lg[e] - m);
+  if (tid == 0 && has_shared) sp[E] = lg[E];
   csync();
-  const float m = sh->s_m;
-  for (int e = tid; e < E; e += kCons) sp[e] = det_expf(sp[e] - m);
-  csync();
-  if (tid < 32) {
-    float sum = 0.0f;
-    for (int e = lane; e < E; e += 32) sum = sum + sp[e];
-    sum = warp_tree_sum(sum);
-    if (lane == 0) sh->s_sum = sum;
-  }
-  csync();
-  const float sum = sh->s_sum;
+  float sum = 0.0f;
+  for (int e = lane; e < E; e += 32) sum = sum + sp[e];
+  sum = warp_tree_sum(sum);
+  csync();  // every warp has read the exponentials
   for (int e = tid; e < E; e += kCons) sp[e] = sp[e] / sum;
   csync();
   const int nsel = k + 1 < kTopkMaxSel ? k + 1 : kTopkMaxSel;
@@ -1132,12 +1129,12 @@ static __device__ __noinline__ uint32_t down_stage(uint32_t tile, int L) {
   const int H = P.H, I = P.I;
   int lo, hi;
   deal(H, row_unit(I), (int)blockIdx.x, (int)gridDim.x, lo, hi);
-  // residual input of this block's rows: in flight while the activations are staged
-  float res = 0.0f;
-  if (lo + (int)threadIdx.x < hi) res = __ldcg(P.Tmp + lo + threadIdx.x);
   quant_rows(P.Act, I, P.slots);
   stamp(2);
   if (lo >= hi) return tile;
+  // residual input of this block's rows: in flight while the tiles are dotted (dot_tiles is inlined)
+  float res0 = 0.0f;
+  if (lo + (int)threadIdx.x < hi) res0 = __ldcg(P.Tmp + lo + threadIdx.x);
   float *T = reinterpret_cast<float *>(step_smem + kTOff);
   unsigned char *act = step_smem + kActOff;
   tile = dot_tiles(tile, I, reinterpret_cast<const uint4 *>(act), reinterpret_cast<const float *>(act + (size_t)P.slots * I), T,
@@ -1145,7 +1142,7 @@ static __device__ __noinline__ uint32_t down_stage(uint32_t tile, int L) {
   csync();
   const int nr = hi - lo, G = I >> 7;
   for (int r = threadIdx.x; r < nr; r += kCons) {
-    if (r >= kCons) res = __ldcg(P.Tmp + lo + r);
+    const float res = r < kCons ? res0 : __ldcg(P.Tmp + lo + r);
     float acc = 0.0f;
     for (int s = 0; s < P.slots; ++s) acc = acc + SH->sel_w[s] * row_sum_rt(T, s * nr + r, G);
     const float x = res + acc;
