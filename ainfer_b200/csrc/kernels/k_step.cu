@@ -52,7 +52,6 @@ struct DecodeStepArgs {
 constexpr int kCons = 512;          // consumer threads (16 warps)
 constexpr int kStepThreads = 544;   // consumers + the producer warp
 constexpr int kNT = 10;             // ring tiles
-constexpr int kMaxPieces = 12;      // contiguous row ranges a tile may be assembled from (>= expert slots)
 constexpr int kTileStride = kTileBytes + kTileScaleBytes;
 // Limit of any single wait, in SM clock cycles (about two seconds). The waits are timed with the
 // SM's own cycle counter: reading the global nanosecond timer takes about a microsecond, far too
@@ -70,17 +69,6 @@ constexpr int kRingOff = (kTOff + kTFloats * 4 + 127) / 128 * 128;
 constexpr int kStepSmemBytes = kRingOff + kNT * kTileStride;
 static_assert(kStepSmemBytes <= 232448, "shared memory of one SM");
 
-struct Piece {
-  const uint16_t *S;   // scales of the piece's first row in global memory (when not copied)
-  int32_t trow;        // first row of the piece in the stage's t[][] numbering
-  int16_t nrows;
-  uint8_t vec;         // staged activation vector the rows are dotted with
-  uint8_t sc_in_tile;  // the scales travelled with the tile
-};
-struct TileDesc {
-  int32_t npieces, nrows, last, pad;
-  Piece pc[kMaxPieces];
-};
 // Contiguous rows of one matrix, as the producer streams them.
 struct Seg {
   const uint8_t *P;   // first row's bytes
@@ -97,7 +85,6 @@ struct StepShared {
   ExpertW sew[12];              // weight pointers of the selected expert slots
   unsigned long long full[kNT], empty[kNT];
   unsigned long long sel_bar;   // consumers -> producer: this layer's routing is in sew[]
-  TileDesc desc[kNT];
   int32_t sel_idx[12];
   float sel_w[12];
   float gap, s_inv, s_m, s_sum;
@@ -215,8 +202,11 @@ static __device__ __noinline__ void grid_wait(unsigned epoch) {
 // Streams the rows of the segment list in shared memory (SH->segs), laid end to end, through
 // the ring in tiles of 16 KB. Called by the whole producer warp: lane l (l < kNT) owns ring slot
 // l and issues the tiles whose running index is l modulo kNT, so up to kNT tiles are prepared and
-// issued at once. Tile j of the call holds rows [j * rpt, (j + 1) * rpt) of the list. `tile` is
-// the running index of the call's first tile; returns the index after its last.
+// issued at once. Tile j of the call holds rows [j * rpt, (j + 1) * rpt) of the list, so the
+// consumers know what every tile holds without being told. The group scales of a piece travel
+// by bulk copy when source, size and offset are 16-byte aligned; otherwise (small matrices) the
+// lane copies them itself before it completes the tile. `tile` is the running index of the
+// call's first tile; returns the index after its last.
 static __device__ __noinline__ uint32_t prod_emit(uint32_t tile, int row_bytes, int sc_row_bytes) {
   const Seg *segs = SH->segs;
   const int nseg = SH->nseg;
@@ -233,28 +223,26 @@ static __device__ __noinline__ uint32_t prod_emit(uint32_t tile, int row_bytes, 
     for (; j < ntiles; j += kNT) {
       const uint32_t g = base + (uint32_t)j, slot = (uint32_t)lane, use = g / kNT;
       if (use > 0 && !mbar_wait_b(smem_addr(&SH->empty[slot]), (use - 1u) & 1u, 3)) break;
-      TileDesc &d = SH->desc[slot];
       unsigned char *dst = ring + slot * kTileStride;
       unsigned long long *bar = &SH->full[slot];
       const int f0 = j * rpt, f1 = f0 + rpt < total ? f0 + rpt : total;
-      int np = 0, row0 = 0;  // row0: flat row of the current segment's first row
+      int row0 = 0;  // flat row of the current segment's first row
 #pragma unroll 1
       for (int si = 0; si < nseg && row0 < f1; ++si) {
         const Seg sg = segs[si];
         const int a = row0 > f0 ? row0 : f0, b = row0 + sg.nrows < f1 ? row0 + sg.nrows : f1;
-        if (a < b && np < kMaxPieces) {
+        if (a < b) {
           const int sr = a - row0, take = b - a, rows = a - f0;
           const uint8_t *src = sg.P + (size_t)sr * row_bytes;
           const uint8_t *ssrc = sg.S ? sg.S + (size_t)sr * sc_row_bytes : nullptr;
           const uint32_t wb = (uint32_t)(take * row_bytes), sb = (uint32_t)(take * sc_row_bytes);
           const bool sc_bulk = ssrc != nullptr &&
                                ((reinterpret_cast<uintptr_t>(ssrc) | sb | (uint32_t)(rows * sc_row_bytes)) & 15u) == 0;
-          Piece &pc = d.pc[np];
-          pc.S = reinterpret_cast<const uint16_t *>(ssrc);
-          pc.trow = sg.trow + sr;
-          pc.nrows = (int16_t)take;
-          pc.vec = (uint8_t)sg.vec;
-          pc.sc_in_tile = sc_bulk ? 1 : 0;
+          if (ssrc != nullptr && !sc_bulk) {
+            const uint16_t *s16 = reinterpret_cast<const uint16_t *>(ssrc);
+            uint16_t *d16 = reinterpret_cast<uint16_t *>(dst + kTileBytes + (size_t)rows * sc_row_bytes);
+            for (uint32_t i = 0; i < sb / 2; ++i) d16[i] = __ldg(s16 + i);
+          }
           if (reinterpret_cast<uintptr_t>(src) & 15u) {  // cannot be copied in bulk: report, skip
             if (g_stream_fault_word) *reinterpret_cast<volatile unsigned int *>(g_stream_fault_word) = 2;
           } else {
@@ -262,14 +250,10 @@ static __device__ __noinline__ uint32_t prod_emit(uint32_t tile, int row_bytes, 
             bulk_g2s(dst + (size_t)rows * row_bytes, src, wb, bar);
             if (sc_bulk) bulk_g2s(dst + kTileBytes + (size_t)rows * sc_row_bytes, ssrc, sb, bar);
           }
-          ++np;
         }
         row0 += sg.nrows;
       }
-      d.npieces = np;
-      d.nrows = f1 - f0;
-      d.last = j == ntiles - 1 ? 1 : 0;
-      mbar_arrive(bar);  // releases the descriptor and completes the phase once the bytes have landed
+      mbar_arrive(bar);  // releases this lane's own stores and completes the phase once the bytes have landed
     }
   }
   __syncwarp();  // the list may be rewritten once every lane is done with it
@@ -394,55 +378,41 @@ static __device__ __noinline__ uint32_t producer_main(int mode) {
 }
 
 // ====================================================================== consumers ===
-// Dots the tiles of one stage with staged activations: t[g][trow - trow_base] for every
-// (row, group) of every tile, from running tile index `tile` until the tile flagged `last` (or
-// max_tiles tiles); returns the running index after the last tile consumed. A tile is
-// 256 (row, group) tasks of 64 bytes; two adjacent lanes share a task (32 bytes each) and add
-// their exact integer sums with one shuffle.
+// Dots the tiles of one stage with staged activations. The stage's rows are numbered 0..total-1
+// in the order the producer streams them (tile j holds rows [j * rpt, (j + 1) * rpt)); row f is
+// dotted with activation vector f / vec_rows (vec_rows = 0: always vector 0) and its group terms
+// go to t[g][f - row_base]. Rows [row_base, row_base + nrows) are done by this call, starting at
+// running tile index `tile`; returns the index after the last tile consumed. A tile is 256
+// (row, group) tasks of 64 bytes; two adjacent lanes share a task (32 bytes each) and add their
+// exact integer sums with one shuffle.
 __device__ __forceinline__ uint32_t dot_tiles(uint32_t tile, int K, const uint4 *xa, const float *sq, float *T,
-                                                  int max_tiles, int trow_base) {
+                                              int row_base, int nrows, int total, int vec_rows) {
   const int G = K >> 7, lg = 31 - __clz(G);
-  const int TS = (kTCap >> lg) + 1;
+  const int TS = (kTCap >> lg) + 1, rpt = 256 >> lg;
   const int task = threadIdx.x >> 1, half = threadIdx.x & 1, lane = threadIdx.x & 31;
   const int r = task >> lg, g = task & (G - 1);
   const uint32_t rot = (uint32_t)(lane >> 2) & 1u;
   const uint32_t ring_a = smem_addr(step_smem + kRingOff);
+  const int ntiles = (nrows + rpt - 1) / rpt;
   int cvec = -1;
   uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0, x2 = x0, x3 = x0;
   float sqg = 0.0f;
-  bool last = false;
 #pragma unroll 1
-  for (int n = 0; n < max_tiles && !last; ++n) {
+  for (int j = 0; j < ntiles; ++j) {
     const uint32_t slot = tile % kNT, use = tile / kNT;
     // a wait that gave up ends the stage for the whole warp (the results are lost anyway)
-    if (!__all_sync(kFull, mbar_wait_b(smem_addr(&SH->full[slot]), use & 1u, 5))) return tile;
-    const TileDesc &d = SH->desc[slot];
-    last = d.last != 0;
-    const int nr = d.nrows;
+    if (!__all_sync(kFull, mbar_wait_b(smem_addr(&SH->full[slot]), use & 1u, 5))) break;
     const uint32_t tb = ring_a + slot * kTileStride;
     const uint32_t wbase = tb + (uint32_t)task * 64u + (uint32_t)half * 32u;
     const uint4 wa = lds128(wbase + (rot << 4)), wb = lds128(wbase + ((rot ^ 1u) << 4));
-    int trow = -1, vec = 0;
-    uint32_t sraw = 0;
-    if (r < nr) {
-      int acc = 0;
-      const int np = d.npieces;
-      for (int i = 0; i < np; ++i) {
-        const int pn = d.pc[i].nrows;
-        if (r < acc + pn) {
-          trow = d.pc[i].trow + (r - acc);
-          vec = d.pc[i].vec;
-          sraw = d.pc[i].sc_in_tile ? lds_u16(tb + kTileBytes + (uint32_t)task * 2u)
-                                    : (uint32_t)__ldg(d.pc[i].S + (size_t)(r - acc) * G + g);
-          break;
-        }
-        acc += pn;
-      }
-    }
+    const uint32_t sraw = lds_u16(tb + kTileBytes + (uint32_t)task * 2u);
     __syncwarp();
     if (lane == 0) mbar_arrive_a(smem_addr(&SH->empty[slot]));
+    const int f = row_base + j * rpt + r;
+    const bool live = j * rpt + r < nrows && f < total;
     int dsum = 0;
-    if (trow >= 0) {
+    if (live) {
+      const int vec = vec_rows ? f / vec_rows : 0;
       if (vec != cvec) {
         cvec = vec;
         const uint4 *xv = xa + (size_t)vec * 8 * G + g;
@@ -459,9 +429,9 @@ __device__ __forceinline__ uint32_t dot_tiles(uint32_t tile, int K, const uint4 
       dsum = d0 + d1;
     }
     dsum += __shfl_xor_sync(kFull, dsum, 1);
-    if (trow >= 0 && half == 0) {
+    if (live && half == 0) {
       const float v = (float)(dsum >> 4) * __uint_as_float(sraw << 16);
-      T[g * TS + (trow - trow_base)] = v * sqg;
+      T[g * TS + (f - row_base)] = v * sqg;
     }
     tile += 1;
   }
@@ -672,7 +642,7 @@ static __device__ __noinline__ uint32_t gemv_stage_run(uint32_t tile, const Gemv
     mi = mat_of_row(m, nm, lo + threadIdx.x, n);
     gemv_epilogue_fetch(&m[mi], n, 0, eo);
   }
-  tile = dot_tiles(tile, K, reinterpret_cast<const uint4 *>(act), reinterpret_cast<const float *>(act + K), T, 1 << 30, 0);
+  tile = dot_tiles(tile, K, reinterpret_cast<const uint4 *>(act), reinterpret_cast<const float *>(act + K), T, 0, nr, nr, 0);
   csync();
   if ((int)threadIdx.x < nr) gemv_epilogue_with(&m[mi], n, 0, row_sum_rt(T, threadIdx.x, G), eo);
   for (int r = threadIdx.x + kCons; r < nr; r += kCons) {
@@ -690,24 +660,15 @@ static __device__ __noinline__ uint32_t router_stage(uint32_t tile, const float 
   deal(rows_total, 1, (int)blockIdx.x, (int)gridDim.x, lo, hi);
   if (lo >= hi) return tile;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n = H / 256;
+  const int rpt = kTileBytes / (H * 2), total = hi - lo, ntiles = (total + rpt - 1) / rpt;
   const uint32_t ring_a = smem_addr(step_smem + kRingOff);
-  bool last = false;
 #pragma unroll 1
-  while (!last) {
+  for (int j = 0; j < ntiles; ++j) {
     const uint32_t slot = tile % kNT, use = tile / kNT;
-    if (!__all_sync(kFull, mbar_wait_b(smem_addr(&SH->full[slot]), use & 1u, 5))) return tile;
-    const TileDesc &d = SH->desc[slot];
-    last = d.last != 0;
+    if (!__all_sync(kFull, mbar_wait_b(smem_addr(&SH->full[slot]), use & 1u, 5))) break;
     const uint32_t tb = ring_a + slot * kTileStride;
-    for (int r = warp; r < d.nrows; r += 16) {
-      int acc_rows = 0, trow = 0;
-      for (int i = 0; i < d.npieces; ++i) {
-        if (r < acc_rows + d.pc[i].nrows) {
-          trow = d.pc[i].trow + (r - acc_rows);
-          break;
-        }
-        acc_rows += d.pc[i].nrows;
-      }
+    const int nr = total - j * rpt < rpt ? total - j * rpt : rpt;
+    for (int r = warp; r < nr; r += 16) {
       float acc = 0.0f;
       for (int i = 0; i < n; ++i) {
         const int k0 = (i * 32 + lane) * 8;
@@ -723,7 +684,7 @@ static __device__ __noinline__ uint32_t router_stage(uint32_t tile, const float 
         acc = fmaf(u2f(wv.w & 0xFFFF0000u), a1.w, acc);
       }
       acc = warp_tree_sum(acc);
-      if (lane == 0) PL.RLogits[lo + trow] = acc;
+      if (lane == 0) PL.RLogits[lo + j * rpt + r] = acc;
     }
     __syncwarp();
     if (lane == 0) mbar_arrive_a(smem_addr(&SH->empty[slot]));
@@ -1108,17 +1069,24 @@ static __device__ __noinline__ void attn_combine_stage(int T) {
 // ------------------------------------------------------------------- MoE stages ---
 static __device__ __noinline__ uint32_t gateup_stage(uint32_t tile) {
   const StepPlan &P = PL;
-  const int H = P.H;
+  const int H = P.H, I = P.I;
   int lo, hi;
-  deal(P.slots * P.I, row_unit(H), (int)blockIdx.x, (int)gridDim.x, lo, hi);
+  deal(P.slots * I, row_unit(H), (int)blockIdx.x, (int)gridDim.x, lo, hi);
   if (lo >= hi) return tile;
   float *T = reinterpret_cast<float *>(step_smem + kTOff);
   unsigned char *act = step_smem + kActOff;
-  tile = dot_tiles(tile, H, reinterpret_cast<const uint4 *>(act), reinterpret_cast<const float *>(act + H), T, 1 << 30, 0);
-  csync();
   const int np = hi - lo, G = H >> 7;
+  tile = dot_tiles(tile, H, reinterpret_cast<const uint4 *>(act), reinterpret_cast<const float *>(act + H), T, 0, 2 * np,
+                   2 * np, 0);
+  csync();
+  // the producer streams, slot by slot, the slot's gate rows and then its up rows: the pair row
+  // lo + r of slot s (rows a .. a + n - 1 of the share belong to it) has its gate term at
+  // 2 (a - lo) + i and its up term n rows later
   for (int r = threadIdx.x; r < np; r += kCons) {
-    const float g = row_sum_rt(T, r, G), u = row_sum_rt(T, np + r, G);
+    const int s = (lo + r) / I;
+    const int a = lo > s * I ? lo : s * I, b = hi < (s + 1) * I ? hi : (s + 1) * I;
+    const int n = b - a, i = lo + r - a, fg = 2 * (a - lo) + i;
+    const float g = row_sum_rt(T, fg, G), u = row_sum_rt(T, fg + n, G);
     P.Act[lo + r] = silu_mul(g, u);
   }
   return tile;
@@ -1138,7 +1106,7 @@ static __device__ __noinline__ uint32_t down_stage(uint32_t tile, int L) {
   float *T = reinterpret_cast<float *>(step_smem + kTOff);
   unsigned char *act = step_smem + kActOff;
   tile = dot_tiles(tile, I, reinterpret_cast<const uint4 *>(act), reinterpret_cast<const float *>(act + (size_t)P.slots * I), T,
-            1 << 30, 0);
+                   0, P.slots * (hi - lo), P.slots * (hi - lo), hi - lo);
   csync();
   const int nr = hi - lo, G = I >> 7;
   for (int r = threadIdx.x; r < nr; r += kCons) {
@@ -1160,14 +1128,13 @@ static __device__ __noinline__ uint32_t lm_head_stage(uint32_t tile, float &bv, 
   deal(P.vocab, row_unit(K), (int)blockIdx.x, (int)gridDim.x, lo, hi);
   float *T = reinterpret_cast<float *>(step_smem + kTOff);
   unsigned char *act = step_smem + kActOff;
-  const int rpt = 2 * kTileBytes / K;
-  const int sub_tiles = (kTCap / G) / rpt;  // tiles whose rows fit t[][]
+  const int sub = kTCap / G;  // rows whose terms fit t[][]: a whole number of tiles
 #pragma unroll 1
-  for (int base = 0; base < hi - lo; base += sub_tiles * rpt) {
-    tile = dot_tiles(tile, K, reinterpret_cast<const uint4 *>(act), reinterpret_cast<const float *>(act + K), T, sub_tiles,
-                     base);
+  for (int base = 0; base < hi - lo; base += sub) {
+    const int nrows = (hi - lo) - base < sub ? (hi - lo) - base : sub;
+    tile = dot_tiles(tile, K, reinterpret_cast<const uint4 *>(act), reinterpret_cast<const float *>(act + K), T, base, nrows,
+                     hi - lo, 0);
     csync();
-    const int nrows = (hi - lo) - base < sub_tiles * rpt ? (hi - lo) - base : sub_tiles * rpt;
     for (int r = threadIdx.x; r < nrows; r += kCons) {
       const float v = row_sum_rt(T, r, G);
       const int n = lo + base + r;
