@@ -16,9 +16,10 @@
 
 #include "../kernels/registry.h"
 
+#include "../common/router_static.h"
+
 namespace ainfer {
 // defined beside the fixed scratch array (k_moe.cu)
-constexpr int kRouterStaticMaxExperts = 1024;
 cudaError_t router_static_scratch_address(void **ptr);
 cudaError_t router_static_launch(cudaStream_t stream, void *scratch, const void *Wr, const void *Wsg,
                                  const float *Hn, int32_t *SelIdx, float *SelW, float *NearGap, int E, int H,
@@ -264,6 +265,7 @@ int ainfer_mem_alloc(ainfer_device_t dev, size_t bytes, size_t align, void **out
 }
 int ainfer_mem_free(ainfer_device_t dev, void *ptr) {
   if (!dev) return AINFER_ERR_INVALID;
+  CU(dev, cudaSetDevice(dev->ordinal));
   CU(dev, cudaFree(ptr));
   return AINFER_OK;
 }
@@ -436,6 +438,7 @@ int ainfer_kernel_max_groups(ainfer_kernel_t k, uint32_t *groups) {
 int ainfer_kernel_launch(ainfer_device_t dev, ainfer_kernel_t k, uint32_t groups) {
   if (!dev || !k) return AINFER_ERR_INVALID;
   uint32_t smem = 0;
+  CU(dev, cudaSetDevice(dev->ordinal));  // function attributes and launches go to the current device
   int r = check_launch(k, groups, &smem);
   if (r) return r;
   void *params[1] = {k->args.data()};
@@ -465,6 +468,7 @@ int ainfer_list_append_launch(ainfer_list_t l, ainfer_kernel_t k, uint32_t group
   if (!l || !k) return AINFER_ERR_INVALID;
   if (l->closed) return fail(l->dev, AINFER_ERR_INVALID, "append to a closed list");
   uint32_t smem = 0;
+  CU(l->dev, cudaSetDevice(l->dev->ordinal));
   int r = check_launch(k, groups, &smem);
   if (r) return r;
   void *params[1] = {k->args.data()};
@@ -541,6 +545,7 @@ int ainfer_list_append_fill(ainfer_list_t l, void *dst, int byte_value, size_t b
 int ainfer_list_close(ainfer_list_t l) {
   if (!l) return AINFER_ERR_INVALID;
   if (l->closed) return fail(l->dev, AINFER_ERR_INVALID, "list already closed");
+  CU(l->dev, cudaSetDevice(l->dev->ordinal));
   CU(l->dev, cudaGraphInstantiate(&l->exec, l->graph, 0));
   l->closed = true;
   return AINFER_OK;
@@ -560,6 +565,7 @@ int ainfer_list_destroy(ainfer_list_t l) {
 int ainfer_list_execute(ainfer_list_t l) {
   if (!l) return AINFER_ERR_INVALID;
   if (!l->closed) return fail(l->dev, AINFER_ERR_INVALID, "execute of a list that is not closed");
+  CU(l->dev, cudaSetDevice(l->dev->ordinal));
   CU(l->dev, cudaGraphLaunch(l->exec, l->dev->stream));
   l->dev->launches += l->launches;
   return AINFER_OK;
@@ -672,11 +678,11 @@ int ainfer_router_topk_static(ainfer_device_t dev, const void *router, const voi
     return fail(dev, AINFER_ERR_INVALID, "ainfer_router_topk_static: hidden must be a positive multiple of 256");
   if (dev->ordinal < 0 || dev->ordinal >= 64) return fail(dev, AINFER_ERR_INVALID, "bad device ordinal");
   void *scratch = nullptr;
+  CU(dev, cudaSetDevice(dev->ordinal));  // the launch below goes to the current device
   {
     std::lock_guard<std::mutex> lock(g_router_static_mu);
     if (!g_router_static_ptr[dev->ordinal]) {
       // set-up, once per GPU, with that GPU current: where does this GPU keep the array?
-      CU(dev, cudaSetDevice(dev->ordinal));
       void *p = nullptr;
       cudaError_t e = router_static_scratch_address(&p);
       if (e != cudaSuccess || p == nullptr) {

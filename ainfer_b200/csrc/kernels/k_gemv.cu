@@ -57,6 +57,27 @@ __global__ void __launch_bounds__(256, 2) Int4GemvA8M2(const Int4GemvA8Args a) {
 __global__ void __launch_bounds__(256, 2) Int4GemvA8M4(const Int4GemvA8Args a) { gemv_a8_body<true>(a); }
 __global__ void __launch_bounds__(256, 2) Int4GemvA8M8(const Int4GemvA8Args a) { gemv_a8_body<true>(a); }
 
+// BoundedWaitProbe: one warp waits, with the ring's own bounded wait, for a shared-memory
+// barrier phase that nothing completes (no copy is issued). The wait runs out after
+// kRingSpinLimit polls (milliseconds), stores code 1 in the host-visible fault word and returns
+// false; the kernel then ends normally. It exists so that the error path every weight-streaming
+// kernel relies on (the wait gives up, control flow stays uniform, the next sync reports it) can
+// be exercised without any faulting access. Out[0] = 1 if the wait succeeded, 2 if it gave up.
+struct BoundedWaitProbeArgs {
+  int32_t *Out;
+};
+__global__ void __launch_bounds__(32) BoundedWaitProbe(const BoundedWaitProbeArgs a) {
+  __shared__ Ring ring;
+  __shared__ __align__(128) unsigned char dummy[128];
+  ring_init(&ring, dummy, 1);
+  const bool ok = mbar_wait(&ring, &ring.full[0], 0u);
+  __syncwarp();
+  if (threadIdx.x == 0) a.Out[0] = ok ? 1 : 2;
+}
+#define F(f) AINFER_ARG(BoundedWaitProbeArgs, f)
+AINFER_REGISTER(BoundedWaitProbe, BoundedWaitProbeArgs, 32, 0, 0, nullptr, F(Out));
+#undef F
+
 static uint32_t gemv1_smem_fn(const void *args) {
   const Int4GemvA8Args *a = (const Int4GemvA8Args *)args;
   return round128(staged4_bytes(a->K, 1)) + kGemvStages * kStageStride;

@@ -4,6 +4,7 @@
 // expert here is that same MLP, the routing around it has no reference
 // counterpart and follows the arithmetic stated with each kernel.
 #pragma once
+#include "../common/router_static.h"
 #include "../common/tables.h"
 #include "common.cuh"
 
@@ -20,11 +21,6 @@ static __device__ __noinline__ float silu_mul(float g, float u) { return (g / (1
 // weights in rank order, and evaluates the shared-expert gate sigmoid.
 // Scratch of the allocation-free router entry point: logits of up to 1024
 // experts plus the shared-expert gate, and a block counter.
-constexpr int kRouterStaticMaxExperts = 1024;
-constexpr int kRouterStaticScratchBytes = 8192;
-constexpr int kRouterStaticCounterOffset = 8128;
-static_assert((kRouterStaticMaxExperts + 1) * 4 <= kRouterStaticCounterOffset, "logits overlap the counter");
-
 struct RouterTopKArgs {
   const uint16_t *Wr;    // [E][H] bf16 router
   const uint16_t *Wsg;   // [H] bf16 shared-expert gate row (null: no shared expert)

@@ -7,6 +7,7 @@ computes in fp32 on the dequantised weights; the oracle quantises activations to
 of 128 (the decode policy), so routing must agree exactly away from near-ties, routing weights
 and the shared gate to fp32 rounding, and the block output to the activation-quantisation error.
 """
+import ctypes as C
 import json
 
 import numpy as np
@@ -75,7 +76,7 @@ def test_oracle_moe_block_agrees_with_hf_qwen3_next(seed):
     logits = np.array([O.lib().orc_dot_bf16(np.ascontiguousarray(router_row), hn, H) for router_row in
                        om.tensor(pfx + "mlp.gate.weight")["data"].view(np.uint16).reshape(E, H)], np.float32)
     idx = np.zeros(k, np.int32); wt = np.zeros(k, np.float32); g2 = np.zeros(1, np.float32)
-    O.lib().orc_router_topk(logits, E, k, idx, wt, g2)
+    O.lib().orc_router_topk(logits, E, k, idx, wt, g2.ctypes.data_as(C.POINTER(C.c_float)))
     assert idx.tolist() == routed.tolist()
     assert np.allclose(wt, w_hf.view(-1).numpy(), rtol=2e-5, atol=1e-7)
     sg_row = om.tensor(pfx + "mlp.shared_expert_gate.weight")["data"].view(np.uint16)
