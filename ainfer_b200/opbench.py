@@ -135,6 +135,45 @@ def gemm_a16_once(dev, N, K, M, reps=20):
             "groups": groups, "buffers": nbuf, "flops": 2.0 * M * N * K, "tflops": 2.0 * M * N * K / ms / 1e9}
 
 
+def gemm_tc_once(dev, N, K, M, reps=20, groups=0):
+    """Int4GemmA8Tc (W4A8 on tcgen05, 1 <= M <= 64, weights streamed once) on one shape: recorded list
+    rotating over enough weight buffers to exceed L2, timed as a whole on the device."""
+    wbytes = N * K // 2 + N * K // 128 * 2
+    nbuf = max(1, min(64, -(-(256 << 20) // wbytes)))
+    rng = np.random.default_rng(0)
+    xq = dev.upload(rng.integers(-127, 128, (M, K), dtype=np.int8))
+    sq = dev.upload(np.full((M, K // 128), 0.01, np.float32))
+    kernels, bufs = [], []
+    for b in range(nbuf):
+        dP, dS, dY = dev.alloc(N * K // 2), dev.alloc(N * K // 128 * 2), dev.zeros(M * N * 4)
+        k = dev.kernel("SynthInt4")
+        k.set_arg(0, dP); k.set_arg(1, dS); k.set_arg(2, synth_key(b, f"opbench.tc.{N}.{K}"), "u64")
+        k.set_arg(3, N * K // 128, "u64"); k.set_arg(4, 0.02)
+        k.launch(dev.info().sm_count * 8)
+        g = dev.kernel("Int4GemmA8Tc")
+        g.set_args(dP, dS, xq, sq, dY, N, K, M, N)
+        kernels.append(g); bufs.append((dP, dS, dY))
+    groups = groups or min((N + 127) // 128, dev.info().sm_count * 4)
+    for i in range(3):
+        kernels[i % nbuf].launch(groups)
+    cl = dev.new_list()
+    for i in range(reps):
+        cl.append(kernels[i % nbuf], groups)
+    cl.close()
+    e0, e1 = dev.event(), dev.event()
+    cl.execute()
+    e0.record(); cl.execute(); e1.record()
+    ms = e0.elapsed_ms(e1) / reps
+    cl.destroy()
+    dev.sync()
+    for t in bufs:
+        for p in t:
+            dev.free(p)
+    b = gemv_bytes(N, K, M)
+    return {"op": "int4_gemm_a8_tc", "M": M, "N": N, "K": K, "ms": ms, "gbs": b / ms / 1e6, "bytes": b,
+            "groups": groups, "buffers": nbuf, "flops": 2.0 * M * N * K, "tflops": 2.0 * M * N * K / ms / 1e9}
+
+
 def token_kernel_names(cfg):
     """Kernel names of one token step of the recorded list, in launch order."""
     lin = ["RmsNormQuant:in", "Int4GemvA8:in_proj", "DeltaNetStep", "GatedNormQuant", "Int4GemvA8:out_proj"]
@@ -208,6 +247,7 @@ def main(argv=None):
     g.add_argument("--reps", type=int, default=20)
     g.add_argument("--sweep", action="store_true")
     g.add_argument("--a16", action="store_true", help="bf16 activations (Int4GemmA16, M up to 64) instead of W4A8")
+    g.add_argument("--tc", action="store_true", help="W4A8 on the tcgen05 tensor cores (Int4GemmA8Tc, M up to 64)")
     g.add_argument("--groups", type=int, default=0, help="thread groups per launch (default: by shape)")
     g.add_argument("--flush", action="store_true", help="time single launches after an L2 rewrite")
     ll = sub.add_parser("listlat", help="device time per node of a recorded list of tiny dependent launches")
@@ -229,11 +269,16 @@ def main(argv=None):
     args = ap.parse_args(argv)
     dev = cuda_abi.Device(0)
     if args.cmd == "gemv":
-        ms_ = (1, 2, 4, 8, 64) if args.a16 else (1, 2, 4, 8)
+        ms_ = (1, 2, 4, 8, 64) if (args.a16 or args.tc) else (1, 2, 4, 8)
         shapes = ([(m, n, k) for (n, k) in [(512, 2048), (4096, 2048), (8192, 2048), (151936, 2048), (2048, 512)]
                    for m in ms_] if args.sweep else [(args.m, args.n, args.k)])
         for (m, n, k) in shapes:
-            r = gemm_a16_once(dev, n, k, m, args.reps) if args.a16 else gemv_once(dev, n, k, m, args.reps, args.flush, args.groups)
+            if args.tc:
+                r = gemm_tc_once(dev, n, k, m, args.reps, args.groups)
+            elif args.a16:
+                r = gemm_a16_once(dev, n, k, m, args.reps)
+            else:
+                r = gemv_once(dev, n, k, m, args.reps, args.flush, args.groups)
             print(json.dumps(r), flush=True)
     elif args.cmd == "pairlat":
         # a recorded list of (RmsNormQuant, Int4GemvA8 on a small matrix) pairs: the dependency chain
