@@ -736,30 +736,37 @@ int session_generate_mtp(Session *s, const int *prompt, int P, int G, int start_
                          int *out_tokens, int *stats) {
   if (!s->mtp_list) { s->err = "usage: the model has no MTP head"; return 2; }
   if (P < 1 || G < 1 || draft_k < 1 || draft_k > 8) { s->err = "usage: need a prompt, G >= 1 and 1 <= draft_k <= 8"; return 2; }
-  if (start_pos < 0 || start_pos + P + G - 1 + draft_k > s->max_ctx) {
+  if (start_pos < 0 || start_pos + P + G - 1 + draft_k >= s->max_ctx) {
     s->err = "context overflow: pos " + std::to_string(start_pos + P + G - 1 + draft_k) + " >= MAXCTX " +
              std::to_string(s->max_ctx);
     return 3;
   }
   int rounds = 0, drafted = 0, accepted = 0;
-  // prompt: every step but the last without tail
-  int y = -1;
+  // The MTP layer runs causally over every position, as the reference's offline measurement does
+  // (tools/t72/mtp_accept.py:142-151): after the trunk step at position q, whose successor token
+  // is known (the next prompt id, or the trunk's own prediction), the head runs on
+  // (token[q + 1], h[q]) and writes row q + 1 of its own KV slot. Its attention therefore always
+  // sees true rows below its position; rows that chained drafts wrote speculatively are
+  // rewritten by this call before any later position reads them. The head's output at the last
+  // trunk position is the first draft of the next round.
+  int y = -1, d = -1;
   for (int i = 0; i < P; ++i) {
-    int r = session_step(s, prompt[i], start_pos + i, &y);  // tail only matters for the last one
+    int r = session_step(s, prompt[i], start_pos + i, &y);
+    if (r) return r;
+    r = session_mtp_draft(s, i + 1 < P ? prompt[i + 1] : y, start_pos + i + 1, 1, &d);
     if (r) return r;
   }
   int p = start_pos + P - 1;  // position of the trunk step that produced y
   int g = 0;
   out_tokens[g++] = y;
   while (g < G) {
-    // draft chain from (y, h_p)
+    // d drafts the token after y; chain the rest of the round from the head's own hidden state
     int drafts[8];
-    int inp = y;
     const int k = std::min(draft_k, G - g);
-    for (int i = 0; i < k; ++i) {
-      int r = session_mtp_draft(s, inp, p + 1 + i, i == 0, &drafts[i]);
+    drafts[0] = d;
+    for (int i = 1; i < k; ++i) {
+      int r = session_mtp_draft(s, drafts[i - 1], p + 1 + i, 0, &drafts[i]);
       if (r) return r;
-      inp = drafts[i];
     }
     ++rounds;
     drafted += k;
@@ -769,6 +776,8 @@ int session_generate_mtp(Session *s, const int *prompt, int P, int G, int start_
       int r = session_step(s, y, p + 1, &y2);
       if (r) return r;
       ++p;
+      r = session_mtp_draft(s, y2, p + 1, 1, &d);
+      if (r) return r;
       const bool hit = y2 == drafts[i];
       y = y2;
       out_tokens[g++] = y;

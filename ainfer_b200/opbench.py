@@ -153,7 +153,7 @@ def gemm_tc_once(dev, N, K, M, reps=20, groups=0):
         g = dev.kernel("Int4GemmA8Tc")
         g.set_args(dP, dS, xq, sq, dY, N, K, M, N)
         kernels.append(g); bufs.append((dP, dS, dY))
-    groups = groups or min((N + 127) // 128, dev.info().sm_count * 4)
+    groups = groups or min((N + 127) // 128, dev.info().sm_count * 2)
     for i in range(3):
         kernels[i % nbuf].launch(groups)
     cl = dev.new_list()

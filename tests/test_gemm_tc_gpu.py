@@ -53,3 +53,47 @@ def test_gemm_a8_tc_several_tiles_per_block_and_extreme_values(dev):
     want = np.stack([O.gemv_a8(P, S, xq[m], sq[m]) for m in range(M)])
     got = run_tc(dev, P, S, xq, sq, N, K, M, groups=2)
     assert np.array_equal(got, want)
+
+
+TC_GROUP = np.dtype([("P", "<u8"), ("S", "<u8"), ("x_row0", "<i4"), ("M", "<i4"), ("y_col", "<i4"), ("pad", "<i4")])
+
+
+@pytest.mark.parametrize("N,K,blocks", [(512, 2048, 7), (2048, 512, 296), (300, 1024, 3)])
+def test_grouped_gemm_a8_tc_bit_exact(dev, N, K, blocks):
+    """A list of problems (own weights, own range of activation rows, own output column) in one
+    launch, the list and its length in device memory: every row equals the one-row GEMV; rows no
+    problem covers stay untouched; a second launch with an empty list writes nothing."""
+    rng = np.random.default_rng(N + K)
+    Ms = [1, 64, 3, 8, 17, 2, 40]
+    rows = sum(Ms) + 5
+    x = rng.standard_normal((rows, K)).astype(np.float32) * 2
+    q = [O.aquant(x[m]) for m in range(rows)]
+    xq = np.stack([a for a, _ in q]); sq = np.stack([b for _, b in q])
+    ldy = 2 * N + 8
+    want = np.full((rows, ldy), 7.0, np.float32)
+    tab = np.zeros(len(Ms), TC_GROUP)
+    keep = []
+    row0 = 2
+    for i, M in enumerate(Ms):
+        w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+        P, S = O.quantize_int4(w)
+        dP, dS = dev.upload(P), dev.upload(S)
+        keep.append((dP, dS))
+        col = (i % 2) * N + 4 * (i % 2)
+        tab[i] = (dP, dS, row0, M, col, 0)
+        for m in range(M):
+            want[row0 + m, col:col + N] = O.gemv_a8(P, S, xq[row0 + m], sq[row0 + m])
+        row0 += M
+    order = rng.permutation(len(Ms))          # the list need not be in row order
+    dTab, dN = dev.upload(tab[order].view(np.uint8)), dev.upload(np.array([len(Ms)], np.int32))
+    dY = dev.upload(np.full((rows, ldy), 7.0, np.float32))
+    k = dev.kernel("Int4GemmA8TcGrouped")
+    k(blocks, dTab, dN, dev.upload(xq), dev.upload(sq), dY, N, K, 64, ldy)
+    dev.sync()
+    got = dev.download(dY, rows * ldy, np.float32).reshape(rows, ldy)
+    assert np.array_equal(got, want)
+    dev.write(dN, np.zeros(1, np.int32))
+    dev.write(dY, np.full((rows, ldy), 3.0, np.float32))
+    k(blocks, dTab, dN, dev.upload(xq), dev.upload(sq), dY, N, K, 64, ldy)
+    dev.sync()
+    assert np.all(dev.download(dY, rows * ldy, np.float32) == 3.0)

@@ -73,22 +73,23 @@ def test_generate_mtp_equals_greedy_and_oracle_loop(dev, mtp_file):
     sess = runtime.Session(model, 64)
     got, st = sess.generate_mtp(prompt, G, draft_k=K)
     assert got.tolist() == want.tolist()
-    # the same loop on the oracle
+    # the same loop on the oracle: the head runs after every trunk step on (next token, h), so
+    # that its own cache holds a true row for every position
     om = O.Model(path=mtp_file)
     osess = O.Session(om, 64)
-    y = -1
+    y = d = -1
     for i, t in enumerate(prompt):
         y = osess.step(int(t), i)
+        h = osess.buf("hidden").copy()
+        d, _ = oracle_mtp(osess, int(prompt[i + 1]) if i + 1 < len(prompt) else y, i + 1, h, V)
     p, out = len(prompt) - 1, [y]
     rounds = drafted = accepted = 0
     while len(out) < G:
         k = min(K, G - len(out))
-        h = osess.buf("hidden").copy()
-        inp, drafts = y, []
-        for i in range(k):
-            d, _ = oracle_mtp(osess, inp, p + 1 + i, h, V)
-            drafts.append(d)
-            inp = d
+        drafts = [d]
+        for i in range(1, k):
+            dd, _ = oracle_mtp(osess, drafts[-1], p + 1 + i, h, V)   # h: the head's own chained state
+            drafts.append(dd)
         rounds += 1
         drafted += k
         for i in range(k):
@@ -96,6 +97,8 @@ def test_generate_mtp_equals_greedy_and_oracle_loop(dev, mtp_file):
                 break
             y2 = osess.step(y, p + 1)
             p += 1
+            h = osess.buf("hidden").copy()
+            d, _ = oracle_mtp(osess, y2, p + 1, h, V)
             hit = y2 == drafts[i]
             y = y2
             out.append(y)
@@ -104,6 +107,16 @@ def test_generate_mtp_equals_greedy_and_oracle_loop(dev, mtp_file):
             accepted += 1
     assert out == got.tolist()
     assert st == {"rounds": rounds, "drafted": drafted, "accepted": accepted}
+    # the head's own KV slot (the last one): every row up to the last position it ran at is a
+    # true row, non-empty and equal to the oracle's
+    cfg = model.config
+    n_slots = cfg["layer_types"].count("A") + cfg["mtp_layers"]
+    for name, dt in (("Kc", np.int8), ("Vc", np.int8), ("Ks", np.uint16), ("Vs", np.uint16)):
+        a = sess.read(name, dt).reshape(n_slots, 64, -1)[-1]
+        b = osess.buf(name).reshape(n_slots, 64, -1)[-1]
+        assert np.array_equal(a[:p + 2], b[:p + 2]), name
+        if name in ("Kc", "Vc"):
+            assert all(np.any(a[r] != 0) for r in range(1, p + 2)), f"{name}: empty row in the head's cache"
     sess.close(); model.close(); osess.close(); om.close()
 
 
