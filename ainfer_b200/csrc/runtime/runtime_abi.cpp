@@ -3,6 +3,7 @@
 #include <string>
 
 #include "../../../include/ainfer_runtime.h"
+#include "ep.h"
 #include "executor.h"
 #include "host_sampler.h"
 #include "model.h"
@@ -11,6 +12,7 @@ using namespace ainfer;
 
 struct ainfer_model_s { DeviceModel *m; std::string cfg_json; };
 struct ainfer_session_s { Session *s; };
+struct ainfer_ep_s { EpMoe e; };
 
 static thread_local std::string g_err;
 static int set_err(int code, const std::string &e) {
@@ -187,6 +189,57 @@ int ainfer_session_launches_per_token(ainfer_session_t s, uint64_t *launches) {
   if (!s || !launches) return 2;
   *launches = s->s->launches_per_token;
   return 0;
+}
+
+int ainfer_ep_unique_id(void *out128) {
+  if (!out128) return set_err(2, "usage: null argument");
+  std::string err;
+  int r = ep_unique_id(out128, err);
+  return set_err(r, err);
+}
+int ainfer_ep_create(ainfer_model_t m, const void *id128, int rank, int world, int batch, int flags, ainfer_ep_t *out) {
+  if (!m || !out) return set_err(2, "usage: null argument");
+  *out = nullptr;
+  ainfer_ep_s *h = new ainfer_ep_s;
+  int r = h->e.create(m->m, id128, rank, world, batch, flags);
+  if (r) {
+    set_err(r, h->e.err);
+    h->e.destroy();
+    delete h;
+    return r;
+  }
+  *out = h;
+  return 0;
+}
+int ainfer_ep_destroy(ainfer_ep_t ep) {
+  if (!ep) return 2;
+  ep->e.destroy();
+  delete ep;
+  return 0;
+}
+int ainfer_ep_buffer(ainfer_ep_t ep, const char *which, void **dptr, uint64_t *bytes) {
+  if (!ep || !which || !dptr || !bytes) return set_err(2, "usage: null argument");
+  EpMoe &e = ep->e;
+  const std::string w = which;
+  if (w == "res") { *dptr = e.Res; *bytes = (uint64_t)e.n * e.H * 4; }
+  else if (w == "x") { *dptr = e.X; *bytes = (uint64_t)e.n * e.H * 4; }
+  else if (w == "sel_idx") { *dptr = e.SelIdx; *bytes = (uint64_t)e.n * (e.k + 1) * 4; }
+  else if (w == "sel_w") { *dptr = e.SelW; *bytes = (uint64_t)e.n * (e.k + 1) * 4; }
+  else if (w == "near_gap") { *dptr = e.NearGap; *bytes = (uint64_t)e.n * 4; }
+  else if (w == "router_bias") { *dptr = e.Bias; *bytes = (uint64_t)e.E * 4; }
+  else if (w == "counts") { *dptr = e.Counts; *bytes = 16; }
+  else return set_err(2, "unknown buffer: " + w);
+  return 0;
+}
+int ainfer_ep_moe_layer(ainfer_ep_t ep, int layer) {
+  if (!ep) return 2;
+  int r = ep->e.run_layer(layer, false, nullptr);
+  return set_err(r, ep->e.err);
+}
+int ainfer_ep_moe_stack(ainfer_ep_t ep, int first, int count, float *seg_ms) {
+  if (!ep) return 2;
+  int r = ep->e.run_stack(first, count, seg_ms);
+  return set_err(r, ep->e.err);
 }
 
 int ainfer_apply_rep_penalty(float *logits, int V, const int *seen, int nseen, float penalty) {

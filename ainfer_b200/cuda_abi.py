@@ -99,6 +99,18 @@ def load():
     return _lib
 
 
+def device_count(limit=16):
+    """Number of GPUs the library can open (ordinals 0..n-1)."""
+    n = 0
+    while n < limit:
+        h = C.c_void_p()
+        if load().ainfer_device_open(n, C.byref(h)):
+            break
+        load().ainfer_device_close(h)
+        n += 1
+    return n
+
+
 class Device:
     def __init__(self, ordinal=0):
         self.L = load()

@@ -47,6 +47,12 @@ SIGNATURES = {
     "ainfer_session_mtp_draft": (_i, [_vp, _i, _i, _i, C.POINTER(_i)]),
     "ainfer_session_mtp_logits": (_i, [_vp, _vp]),
     "ainfer_session_generate_mtp": (_i, [_vp, _vp, _i, _i, _i, _i, _vp, _vp]),
+    "ainfer_ep_unique_id": (_i, [_vp]),
+    "ainfer_ep_create": (_i, [_vp, _vp, _i, _i, _i, _i, C.POINTER(_vp)]),
+    "ainfer_ep_destroy": (_i, [_vp]),
+    "ainfer_ep_buffer": (_i, [_vp, C.c_char_p, C.POINTER(_vp), C.POINTER(C.c_uint64)]),
+    "ainfer_ep_moe_layer": (_i, [_vp, _i]),
+    "ainfer_ep_moe_stack": (_i, [_vp, _i, _i, _vp]),
     "ainfer_apply_rep_penalty": (_i, [_vp, _i, _vp, _i, C.c_float]),
     "ainfer_sample_token": (_i, [_vp, _i, C.POINTER(SampleParams), C.POINTER(_u64), _vp]),
 }
@@ -234,3 +240,60 @@ def apply_rep_penalty(logits, seen, penalty):
     seen = np.ascontiguousarray(seen, dtype=np.int32)
     load().ainfer_apply_rep_penalty(logits.ctypes.data, logits.size, seen.ctypes.data, seen.size, penalty)
     return logits
+
+
+def ep_unique_id():
+    """128 bytes of a fresh NCCL id (one rank calls it and hands the bytes to the others)."""
+    buf = C.create_string_buffer(128)
+    _check(load().ainfer_ep_unique_id(buf))
+    return buf.raw
+
+
+class EpMoe:
+    """Expert-parallel MoE block of a loaded model for a decode batch (ainfer_ep_*): this rank
+    owns batch/world rows and experts/world experts. world == 1 needs no NCCL id."""
+    ROUTER_BIAS = 1
+
+    def __init__(self, model, batch, rank=0, world=1, nccl_id=None, flags=0):
+        self.model, self.dev = model, model.dev
+        self.batch, self.rank, self.world = batch, rank, world
+        h = C.c_void_p()
+        idb = C.create_string_buffer(nccl_id, 128) if nccl_id is not None else None
+        _check(load().ainfer_ep_create(model.h, idb, rank, world, batch, flags, C.byref(h)))
+        self.h = h
+        cfg = model.config
+        self.rows, self.hidden, self.top_k = batch // world, cfg["hidden"], cfg["top_k"]
+
+    def buffer(self, which):
+        p, n = C.c_void_p(), C.c_uint64()
+        _check(load().ainfer_ep_buffer(self.h, which.encode(), C.byref(p), C.byref(n)))
+        return p.value, n.value
+
+    def read(self, which, dtype):
+        p, n = self.buffer(which)
+        return self.dev.download(p, n // np.dtype(dtype).itemsize, dtype)
+
+    def write(self, which, arr):
+        p, n = self.buffer(which)
+        arr = np.ascontiguousarray(arr)
+        assert arr.nbytes == n, (which, arr.nbytes, n)
+        self.dev.write(p, arr)
+
+    def layer(self, layer, res):
+        """x = res + MoE(norm(res)) for this rank's rows [rows][H] (blocking)."""
+        self.write("res", np.asarray(res, np.float32))
+        _check(load().ainfer_ep_moe_layer(self.h, int(layer)))
+        self.dev.sync()
+        return self.read("x", np.float32).reshape(self.rows, self.hidden)
+
+    def stack(self, first, count, segments=False):
+        """`count` layers from `first`, chained through the "res" buffer; asynchronous unless
+        segments is set (then returns the summed ms of the five segments)."""
+        seg = (C.c_float * 5)() if segments else None
+        _check(load().ainfer_ep_moe_stack(self.h, int(first), int(count), seg))
+        return list(seg) if segments else None
+
+    def close(self):
+        if self.h:
+            load().ainfer_ep_destroy(self.h)
+            self.h = None

@@ -104,6 +104,30 @@ int ainfer_session_generate_mtp(ainfer_session_t s, const int *prompt, int P, in
 int ainfer_session_logits(ainfer_session_t s, float *host_out);
 int ainfer_session_launches_per_token(ainfer_session_t s, uint64_t *launches);
 
+/* ---- expert-parallel MoE block for a decode batch ----
+ * The reference decodes one token on one device (its MLP, tools/decode/decode_l0.cpp:666-674,
+ * is dense); this is the sharded form of this library's MoE block: experts split evenly over
+ * `world` ranks (one process per GPU), rank r owns batch rows [r*batch/world, (r+1)*batch/world),
+ * NCCL send/recv all-to-all for dispatch and return, every token's row bit-identical to the
+ * single-GPU decode kernels'. Return codes as above (1 device/NCCL error, 2 usage). */
+typedef struct ainfer_ep_s *ainfer_ep_t;
+enum { AINFER_EP_ROUTER_BIAS = 1 /* add the "router_bias" buffer to the routed logits (load generators) */ };
+/* 128 bytes of a fresh NCCL id: one rank calls it, the caller distributes the bytes. */
+int ainfer_ep_unique_id(void *out128);
+/* id128 may be NULL when world == 1 (no NCCL is loaded then). batch <= 64, batch % world == 0. */
+int ainfer_ep_create(ainfer_model_t m, const void *id128, int rank, int world, int batch, int flags, ainfer_ep_t *out);
+int ainfer_ep_destroy(ainfer_ep_t ep);
+/* Device buffers: "res" [n][H] f32 input rows of this rank, "x" [n][H] f32 output, "sel_idx"
+ * [n][k+1] i32, "sel_w" [n][k+1] f32, "near_gap" [n] f32, "router_bias" [E] f32, "counts" [4] i32
+ * (items received, gate/up problems, down problems of the last layer run). */
+int ainfer_ep_buffer(ainfer_ep_t ep, const char *which, void **dptr, uint64_t *bytes);
+/* x = res + MoE(post_attention_norm_L(res)) for the owned rows; asynchronous on the device's queue. */
+int ainfer_ep_moe_layer(ainfer_ep_t ep, int layer);
+/* `count` layers from `first`, each feeding the next (res <- x). seg_ms: NULL, or 5 floats that
+ * receive the summed device time of route+pack, dispatch exchange, experts, return exchange,
+ * shared expert+combine (the call then synchronises after every layer: not for timing the whole). */
+int ainfer_ep_moe_stack(ainfer_ep_t ep, int first, int count, float *seg_ms);
+
 /* ---- sampler (tools/sample/sampler.h:16-62) ---- */
 typedef struct ainfer_sample_params {
   float temp;

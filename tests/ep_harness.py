@@ -1,4 +1,8 @@
-"""Expert-parallel MoE block for a decode batch (the one place the decode path shards across GPUs).
+"""Host-side model of the expert-parallel MoE block's protocol (test infrastructure): ownership,
+dispatch plan, exchange and slot-ordered combine in numpy over torch.distributed, with the
+arithmetic supplied by a backend (the CPU oracle in the tests). The runtime's own implementation
+is csrc/runtime/ep.cpp with the kernels of csrc/kernels/k_ep.cu; this model states the same
+protocol in a form that runs as gloo ranks without a GPU.
 
 Experts are split evenly over the ranks (contiguous ids, E/R per rank); router, shared expert and
 everything outside the MoE block are replicated. Rank r OWNS tokens [r*B/R, (r+1)*B/R) of the batch:
@@ -13,9 +17,8 @@ everything outside the MoE block are replicated. Rank r OWNS tokens [r*B/R, (r+1
      in the same order as the single-GPU kernel, so the result is bit-identical to it;
   5. all-gather of the owners' rows, so that every replica holds the whole batch again.
 
-The exchange runs on torch.distributed (NCCL on GPUs, gloo in the CPU tests); the arithmetic is a
-backend object (`GpuMoeBackend` drives this package's kernels; the tests also plug in the CPU
-oracle to check the host logic without a GPU). Shapes follow the reference's conventions: one
+The exchange runs on torch.distributed (gloo in the CPU tests); the arithmetic is a backend
+object (the tests plug in the CPU oracle). Shapes follow the reference's conventions: one
 hidden row per token, experts addressed by global id.
 """
 import numpy as np
@@ -174,89 +177,3 @@ class EpMoeBlock:
                       "combine_bytes": n_items * (H * 4 + ITEM_META.itemsize)}
         # 5. every replica gets the whole batch back
         return comm.all_gather_rows(out, B)
-
-
-EXPERT_W = np.dtype([("gP", "<u8"), ("gS", "<u8"), ("uP", "<u8"), ("uS", "<u8"), ("dP", "<u8"), ("dS", "<u8")])
-
-
-def _bf16_to_f32(u16):
-    return (u16.astype(np.uint32) << 16).view(np.float32)
-
-
-class GpuMoeBackend:
-    """The MoE block of one layer of a loaded model, run with this package's kernels through the
-    C-ABI. Only the experts of this rank's shard are ever touched by `expert` calls that the
-    dispatch plan routes here (plus the replicated shared expert)."""
-
-    def __init__(self, dev, model, layer):
-        cfg = model.config
-        self.dev, self.hidden, self.experts = dev, cfg["hidden"], cfg["experts"]
-        self.top_k, self.shared, self.inter = cfg["top_k"], bool(cfg["shared_experts"]), cfg["expert_intermediate"]
-        self.eps = float(cfg["rms_eps"])
-        H, E, I, k = self.hidden, self.experts, self.inter, self.top_k
-        p = f"model.language_model.layers.{layer}."
-        t = model.tensor
-        self.router = t(p + "mlp.gate.weight").data
-        self.sgate = t(p + "mlp.shared_expert_gate.weight").data if self.shared else 0
-        nw = t(p + "post_attention_layernorm.weight")
-        self.norm_w = dev.upload(_bf16_to_f32(dev.download(nw.data, H, np.uint16)))
-        tab = np.zeros(E + 1, EXPERT_W)
-        for e in range(E + 1):
-            q = p + (f"mlp.experts.{e}." if e < E else "mlp.shared.")
-            if e == E and not self.shared:
-                continue
-            g, u, d = t(q + "gate_proj.weight"), t(q + "up_proj.weight"), t(q + "down_proj.weight")
-            tab[e] = (g.data, g.scales, u.data, u.scales, d.data, d.scales)
-        self.tab = dev.upload(tab.view(np.uint8))
-        # scratch (allocated once)
-        z = dev.zeros
-        self.dRes, self.dHn, self.dQ8, self.dSQ = z(H * 4), z(H * 4), z(H), z(H // 128 * 4)
-        self.dLog, self.dCnt = z((E + 1) * 4), z(4)
-        self.dSelI, self.dSelW, self.dGap = z((k + 1) * 4), z((k + 1) * 4), z(4)
-        self.dOne, self.dAct, self.dY, self.dX = dev.upload(np.ones(1, np.float32)), z(I * 4), z(H * 4), z(H * 4)
-        self.dZero, self.dE1 = z(H * 4), z(4)
-        self.dYs, self.dW = z((k + 1) * H * 4), z((k + 1) * 4)
-        self.sm = dev.info().sm_count
-        self.k_norm, self.k_router = dev.kernel("RmsNormQuant"), dev.kernel("RouterTopK")
-        self.k_up, self.k_down, self.k_comb = dev.kernel("ExpertGateUp"), dev.kernel("ExpertDownCombine"), dev.kernel("CombineSlots")
-
-    def route(self, res_row):
-        d, H, E, k = self.dev, self.hidden, self.experts, self.top_k
-        d.write(self.dRes, np.ascontiguousarray(res_row, np.float32))
-        self.k_norm(1, self.dRes, 0, 0, self.norm_w, self.dHn, self.dQ8, self.dSQ, H, self.eps)
-        self.k_router((E + 8) // 8, self.router, self.sgate, self.dHn, self.dLog, self.dCnt, self.dSelI, self.dSelW,
-                      self.dGap, E, H, k, 0, 0)
-        d.sync()
-        return (d.download(self.dQ8, H, np.int8), d.download(self.dSQ, H // 128, np.float32),
-                d.download(self.dSelI, k, np.int32), d.download(self.dSelW, k + 1, np.float32))
-
-    def expert(self, e, hq, hs):
-        d, H, I = self.dev, self.hidden, self.inter
-        d.write(self.dQ8, np.ascontiguousarray(hq)); d.write(self.dSQ, np.ascontiguousarray(hs))
-        d.write(self.dE1, np.array([e], np.int32))
-        self.k_up(min(2 * self.sm, max(1, 2 * I * H // 32768)), self.tab, self.dE1, self.dQ8, self.dSQ, self.dAct, 1, I, H, 0, 0)
-        self.k_down(min(2 * self.sm, max(1, H // 8)), self.tab, self.dE1, self.dOne, self.dAct, self.dZero, self.dX, self.dY, 1, I, H)
-        d.sync()
-        return d.download(self.dY, H, np.float32)
-
-    def combine(self, res_row, ys, w):
-        d, H = self.dev, self.hidden
-        slots = ys.shape[0]
-        d.write(self.dRes, np.ascontiguousarray(res_row, np.float32))
-        d.write(self.dYs, np.ascontiguousarray(ys)); d.write(self.dW, np.ascontiguousarray(w, np.float32))
-        self.k_comb(max(1, H // 256), self.dYs, self.dW, self.dRes, self.dX, slots, H)
-        d.sync()
-        return d.download(self.dX, H, np.float32)
-
-    def fused_reference(self, res_row):
-        """The same block through the single-GPU kernels (all slots in one launch each)."""
-        d, H, E, I, k = self.dev, self.hidden, self.experts, self.inter, self.top_k
-        slots = k + (1 if self.shared else 0)
-        self.route(res_row)
-        dAct = d.zeros(slots * I * 4)
-        self.k_up(2 * self.sm, self.tab, self.dSelI, self.dQ8, self.dSQ, dAct, slots, I, H, 0, 0)
-        self.k_down(self.sm, self.tab, self.dSelI, self.dSelW, dAct, self.dRes, self.dX, 0, slots, I, H)
-        d.sync()
-        out = d.download(self.dX, H, np.float32)
-        d.free(dAct)
-        return out

@@ -1,4 +1,4 @@
-"""MoE-block arithmetic on the CPU oracle, in the shape ainfer_b200.ep.EpMoeBlock expects from a
+"""MoE-block arithmetic on the CPU oracle, in the shape ep_harness.EpMoeBlock expects from a
 backend. Test infrastructure: lets the expert-parallel host logic (ownership, dispatch plan,
 exchange, slot-ordered combine, gather) run as gloo ranks without a GPU."""
 import ctypes as C

@@ -10,7 +10,7 @@ import pytest
 
 sys.path.insert(0, os.path.dirname(__file__))
 
-from ainfer_b200 import ep
+import ep_harness as ep
 
 
 def test_ownership_and_plan_edges():
