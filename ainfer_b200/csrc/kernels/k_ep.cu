@@ -30,16 +30,21 @@ struct RouterLogitsRowsArgs {
   const float *Bias;     // optional [E]: added to the routed experts' logits (load generators); null: none
   float *Logits;         // [rows][E+1]
   int32_t E, H, rows;
+  int32_t tokens_per_block;   // launched with ceil((E + 1) / 8) x ceil(rows / tokens_per_block) blocks
 };
-// One warp per router row (weights stay in L1 across the tokens); per token the sums of
-// RouterTopK (router_row_fma order, then the lane tree).
+// One warp per router row and block of tokens (the row's weights stay in L1 across the block's
+// tokens); per token the sums of RouterTopK (router_row_fma order, then the lane tree).
 __global__ void __launch_bounds__(256) RouterLogitsRows(const RouterLogitsRowsArgs a) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nrows = a.E + (a.Wsg ? 1 : 0), n = a.H / 256;
-  for (int e = blockIdx.x * 8 + warp; e < nrows; e += gridDim.x * 8) {
+  const int nrb = (a.E + 1 + 7) / 8, rb = blockIdx.x % nrb, tb = blockIdx.x / nrb;
+  const int t_end = (tb + 1) * a.tokens_per_block < a.rows ? (tb + 1) * a.tokens_per_block : a.rows;
+  {
+    const int e = rb * 8 + warp;
+    if (e >= nrows) return;
     const uint16_t *w = e < a.E ? a.Wr + (size_t)e * a.H : a.Wsg;
     const float bias = a.Bias && e < a.E ? __ldg(a.Bias + e) : 0.0f;
-    for (int t = 0; t < a.rows; ++t) {
+    for (int t = tb * a.tokens_per_block; t < t_end; ++t) {
       float acc = 0.0f;
       for (int i0 = 0; i0 < n; i0 += kRouterChunk) {
         RouterRowRegs r;
@@ -303,7 +308,8 @@ __global__ void __launch_bounds__(256) EpCombine(const EpCombineArgs a) {
 }
 
 #define F(f) AINFER_ARG(RouterLogitsRowsArgs, f)
-AINFER_REGISTER(RouterLogitsRows, RouterLogitsRowsArgs, 256, 8, 0, nullptr, F(Wr), F(Wsg), F(Hn), F(Bias), F(Logits), F(E), F(H), F(rows));
+AINFER_REGISTER(RouterLogitsRows, RouterLogitsRowsArgs, 256, 8, 0, nullptr, F(Wr), F(Wsg), F(Hn), F(Bias), F(Logits), F(E), F(H), F(rows),
+                F(tokens_per_block));
 #undef F
 #define F(f) AINFER_ARG(RouterSelectRowsArgs, f)
 AINFER_REGISTER(RouterSelectRows, RouterSelectRowsArgs, 256, 1, 0, nullptr, F(Logits), F(SelIdx), F(SelW), F(NearGap), F(E), F(k), F(has_shared));

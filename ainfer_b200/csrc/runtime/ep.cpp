@@ -238,9 +238,10 @@ int EpMoe::record_layer(int L) {
   // ---- A: route the owned rows and pack their items ----
   r.launch("RmsNormQuant", (uint32_t)n, (const float *)Res, (const float *)nullptr, (float *)nullptr,
            (const float *)(m->post_norm + (size_t)L * H), Hn, Q8, SQ, (int32_t)H, eps);
-  r.launch("RouterLogitsRows", (uint32_t)((E + 1 + 7) / 8), (const uint16_t *)router.data,
+  const int tpb = 4;   // tokens per block of the router: enough blocks to fill the device, weights re-read from L2
+  r.launch("RouterLogitsRows", (uint32_t)(((E + 1 + 7) / 8) * ((n + tpb - 1) / tpb)), (const uint16_t *)router.data,
            (const uint16_t *)(shared ? sgate.data : nullptr), (const float *)Hn,
-           (const float *)((flags & EP_ROUTER_BIAS) ? Bias : nullptr), Logits, (int32_t)E, (int32_t)H, (int32_t)n);
+           (const float *)((flags & EP_ROUTER_BIAS) ? Bias : nullptr), Logits, (int32_t)E, (int32_t)H, (int32_t)n, (int32_t)tpb);
   r.launch("RouterSelectRows", (uint32_t)n, (const float *)Logits, SelIdx, SelW, NearGap, (int32_t)E, (int32_t)k, (int32_t)(shared ? 1 : 0));
   r.launch("EpPlan", 1u, (const int32_t *)SelIdx, Send, ItemDest, (int32_t)n, (int32_t)k, (int32_t)epr, (int32_t)world, (int32_t)cap, slot_d);
   r.launch("EpPack", (uint32_t)cap, (const int8_t *)Q8, (const float *)SQ, (const int32_t *)ItemDest, Send, (int32_t)k, (int32_t)H, (int32_t)cap,

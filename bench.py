@@ -224,6 +224,79 @@ def step_traffic_note():
     return None
 
 
+def zipf_router_bias(experts, s=1.1, seed=0):
+    """log of a Zipf(s) popularity over a seeded permutation of the experts: added to the router
+    logits, it skews which experts the top-k picks the way a Zipf(s) load does."""
+    rng = np.random.default_rng(seed)
+    rank_of = rng.permutation(experts)
+    p = 1.0 / np.power(np.arange(1, experts + 1, dtype=np.float64), s)
+    p /= p.sum()
+    return np.log(p[rank_of]).astype(np.float32)
+
+
+def run_ep(args, dev, model, rank, world, dist):
+    """Batched decode of the MoE layers with the experts sharded over the ranks (expert parallelism):
+    a batch of EP_BATCH rows through the MoE block of every layer of the model (post-attention
+    norm, router with a Zipf(1.1) bias, top-k, dispatch all-to-all, grouped expert GEMMs, return
+    all-to-all, shared expert, combine), each layer feeding the next. Every rank owns batch/world
+    rows and experts/world experts. The timed region holds the whole stack, exchanges included;
+    device events, max over ranks."""
+    from ainfer_b200 import runtime
+    cfg = model.config
+    B, L = args.ep_batch, cfg["text_layers"]
+    if B % world or cfg["experts"] % world:
+        return {"skipped": f"batch {B} or {cfg['experts']} experts do not divide over {world} ranks"}
+    nid = None
+    if world > 1:
+        import torch
+        t = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            t = torch.frombuffer(bytearray(runtime.ep_unique_id()), dtype=torch.uint8).cuda()
+        dist.broadcast(t, 0)
+        nid = bytes(t.cpu().numpy().tobytes())
+    ep = runtime.EpMoe(model, B, rank=rank, world=world, nccl_id=nid, flags=runtime.EpMoe.ROUTER_BIAS)
+    ep.write("router_bias", zipf_router_bias(cfg["experts"]))
+    n, H = B // world, cfg["hidden"]
+    rows = np.random.default_rng(1234).standard_normal((B, H)).astype(np.float32)[rank * n:(rank + 1) * n]
+    ep.write("res", rows)
+    for _ in range(max(1, args.ep_warmup)):
+        ep.stack(0, L)
+    dev.sync()
+    if dist is not None:
+        dist.barrier()
+    passes, ms = [], 0.0
+    for _ in range(args.ep_steps):
+        e0, e1 = dev.event(), dev.event()
+        e0.record()
+        ep.stack(0, L)
+        e1.record()
+        dev.sync()
+        passes.append(e0.elapsed_ms(e1))
+    items = int(ep.read("counts", np.int32)[0])
+    seg = ep.stack(0, L, segments=True)
+    if dist is not None:
+        import torch
+        t = torch.tensor(passes + [float(items)], device="cuda", dtype=torch.float64)
+        tmax = t.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        passes, items_max, items_sum = [float(x) for x in tmax[:-1]], float(tmax[-1]), float(t[-1])
+    else:
+        items_max = items_sum = float(items)
+    ep.close()
+    med = float(np.median(passes))
+    I, k = cfg["expert_intermediate"], cfg["top_k"]
+    return {"workload": f"batch {B} through the MoE block of {L} layers, experts sharded over {world} rank(s), Zipf(1.1) router bias",
+            "tokens_per_s": B / (med / 1000.0), "ms_per_stack": med, "us_per_layer": med * 1000.0 / L,
+            "passes_ms": {"n": len(passes), "min": min(passes), "max": max(passes)},
+            "scaling": "strong", "batch": B, "layers": L, "world": world,
+            "exchange": "NCCL send/recv all-to-all, fixed-size slots" if world > 1 else "none (one rank)",
+            "segments_us_per_layer_rank0": dict(zip(("route_pack", "dispatch", "experts", "return", "shared_combine"),
+                                                    [round(x * 1000.0 / L, 2) for x in seg])),
+            "last_layer_items": {"max_rank": items_max, "mean_rank": items_sum / world, "total": B * k},
+            "expert_bytes_per_layer_all_ranks_upper": cfg["experts"] * 3 * H * I * (0.5 + 2.0 / 128)}
+
+
 def run_ours(args):
     rank, local_rank, world = dist_env()
     dist = None
@@ -238,7 +311,7 @@ def run_ours(args):
     from ainfer_b200 import cuda_abi, runtime
     dev = cuda_abi.Device(local_rank)
     t_load = time.time()
-    model = runtime.Model(dev, f"synth:{args.model}:seed={rank}")
+    model = runtime.Model(dev, f"synth:{args.model}:seed=0")   # same weights on every rank (the experts are sharded below)
     cfg = model.config
     t_load = time.time() - t_load
     P = args.prompt_len
@@ -287,6 +360,7 @@ def run_ours(args):
         t = torch.tensor([gen_ms, t_e2e], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         gen_ms, t_e2e = float(t[0]), float(t[1])
+    ep_line = None if args.no_ep else run_ep(args, dev, model, rank, world, dist)
     if rank != 0:
         model.close(); dev.close()
         dist.destroy_process_group()
@@ -365,7 +439,8 @@ def run_ours(args):
         "config": dict(workload_config(args.model, P, cfg),
                        mtp="off", step=("one persistent cooperative launch per token (DecodeStep)" if persistent else
                                         "one recorded list of stand-alone launches chained by programmatic dependencies"),
-                       parallelism="replicas" if world > 1 else "single GPU",
+                       parallelism=("batch-1 steps: one independent replica per GPU (the batch-1 path has no exchange); "
+                                    "the `ep` object times the sharded MoE layers") if world > 1 else "single GPU",
                        l2="inputs larger than L2: about 2.1 GB of weights and state streamed per step",
                        launches_per_token=launches),
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": 16, "d2h_bytes_per_step": 4,
@@ -374,7 +449,7 @@ def run_ours(args):
         "repeats": {"windows": len(win_ms), "ms_per_step_median": float(np.median(win_ms)), "ms_per_step_min": float(np.min(win_ms)),
                     "ms_per_step_max": float(np.max(win_ms))},
         "clocks": clk, "roofline": roof, "gemv_sweep": sweep,
-        "cpu_baseline": cpu, "parity": parity,
+        "cpu_baseline": cpu, "parity": parity, "ep": ep_line,
         "timing": {"model_fill_s": t_load, "prompt_s": t_prompt, "timed_wall_s": t_wall, "first_tokens": [int(t) for t in toks0[:8]]},
     }
     print(json.dumps(line))
@@ -395,6 +470,10 @@ def main():
     ap.add_argument("--cpu-steps", type=int, default=16)
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="skip the isolated GEMV probes")
+    ap.add_argument("--no-ep", action="store_true", help="skip the expert-parallel MoE stack")
+    ap.add_argument("--ep-batch", type=int, default=64)
+    ap.add_argument("--ep-steps", type=int, default=5)
+    ap.add_argument("--ep-warmup", type=int, default=2)
     ap.add_argument("--list", action="store_true", help="time the recorded list of stand-alone launches instead of the persistent step")
     args = ap.parse_args()
     if args.warmup < 3:
