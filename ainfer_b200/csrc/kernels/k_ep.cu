@@ -133,11 +133,15 @@ struct EpGroupArgs {
   const unsigned char *Recv;  // dispatch buffer received (R slots)
   const ExpertW *Experts;     // the layer's table [E+1]
   int32_t *Sorted;            // [R*cap]: src << 16 | index in the source's slot, grouped by expert
-  EpTcGroup *GroupsGateUp;    // [2 * experts_per_rank]: gate and up problem of every active expert
-  EpTcGroup *GroupsDown;      // [experts_per_rank]
+  EpTcGroup *GroupsGateUp;    // [2 * (experts_per_rank + 1)]: gate and up problem of every active expert
+  EpTcGroup *GroupsDown;      // [experts_per_rank + 1]
   int32_t *Counts;            // [4]: items in total, gate/up problems, down problems, 0
   int32_t world, rank, experts_per_rank, cap, I;
   uint32_t slot_bytes;
+  // The shared expert of this rank's own rows rides in the same launches as one more problem:
+  // its activations are rows [shared_row0, shared_row0 + shared_rows) of the grouped layout
+  // (the owner's quantiser writes them there). shared_rows == 0: none.
+  int32_t shared_row0, shared_rows, shared_expert;
 };
 // One block. Items are numbered (source rank, index) in ascending order; an item's row in the
 // grouped layout is the start of its expert's range plus the number of earlier items of the same
@@ -182,7 +186,16 @@ __global__ void __launch_bounds__(1024) EpGroup(const EpGroupArgs a) {
       run += __shfl_sync(kFull, sc, 31);
       nact += __shfl_sync(kFull, sf, 31);
     }
-    if (tid == 0) *reinterpret_cast<int4 *>(a.Counts) = make_int4(total, 2 * nact, nact, 0);
+    if (tid == 0) {
+      const int sh = a.shared_rows > 0 ? 1 : 0;
+      if (sh) {
+        const ExpertW w = a.Experts[a.shared_expert];
+        a.GroupsGateUp[2 * nact] = EpTcGroup{w.gP, w.gS, a.shared_row0, a.shared_rows, 0, 0};
+        a.GroupsGateUp[2 * nact + 1] = EpTcGroup{w.uP, w.uS, a.shared_row0, a.shared_rows, a.I, 0};
+        a.GroupsDown[nact] = EpTcGroup{w.dP, w.dS, a.shared_row0, a.shared_rows, 0, 0};
+      }
+      *reinterpret_cast<int4 *>(a.Counts) = make_int4(total, 2 * (nact + sh), nact + sh, 0);
+    }
   }
   __syncthreads();
   for (int e = tid; e < a.experts_per_rank; e += blockDim.x) {
@@ -231,14 +244,15 @@ __global__ void __launch_bounds__(128) EpGather(const EpGatherArgs a) {
 // 128, a lane holds four consecutive elements.
 struct SiluQuantRowsArgs {
   const float *GU;         // [rows][2*I]: gate outputs, then up outputs
-  const int32_t *Counts;   // optional device word: rows in use (null: every launched row)
+  const int32_t *Counts;   // optional device word: rows in use among the first always_from (null: every launched row)
   int8_t *AQ;              // [rows][I]
   float *ASQ;              // [rows][I/128]
   int32_t I;
+  int32_t always_from;     // rows from this one on are always in use
 };
 __global__ void __launch_bounds__(128) SiluQuantRows(const SiluQuantRowsArgs a) {
   const int row = blockIdx.x;
-  if (a.Counts && row >= __ldg(a.Counts)) return;
+  if (a.Counts && row < a.always_from && row >= __ldg(a.Counts)) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const float *g = a.GU + (size_t)row * 2 * a.I, *u = g + a.I;
   for (int grp = warp; grp < a.I / 128; grp += 4) {
@@ -323,13 +337,13 @@ AINFER_REGISTER(EpPack, EpPackArgs, 128, 1, 0, nullptr, F(Q8), F(SQ), F(ItemDest
 #undef F
 #define F(f) AINFER_ARG(EpGroupArgs, f)
 AINFER_REGISTER(EpGroup, EpGroupArgs, 1024, 0, 0, nullptr, F(Recv), F(Experts), F(Sorted), F(GroupsGateUp), F(GroupsDown), F(Counts), F(world),
-                F(rank), F(experts_per_rank), F(cap), F(I), F(slot_bytes));
+                F(rank), F(experts_per_rank), F(cap), F(I), F(slot_bytes), F(shared_row0), F(shared_rows), F(shared_expert));
 #undef F
 #define F(f) AINFER_ARG(EpGatherArgs, f)
 AINFER_REGISTER(EpGather, EpGatherArgs, 128, 1, 0, nullptr, F(Recv), F(Sorted), F(Counts), F(XQ), F(SQ), F(H), F(cap), F(slot_bytes));
 #undef F
 #define F(f) AINFER_ARG(SiluQuantRowsArgs, f)
-AINFER_REGISTER(SiluQuantRows, SiluQuantRowsArgs, 128, 1, 0, nullptr, F(GU), F(Counts), F(AQ), F(ASQ), F(I));
+AINFER_REGISTER(SiluQuantRows, SiluQuantRowsArgs, 128, 1, 0, nullptr, F(GU), F(Counts), F(AQ), F(ASQ), F(I), F(always_from));
 #undef F
 #define F(f) AINFER_ARG(EpScatterArgs, f)
 AINFER_REGISTER(EpScatter, EpScatterArgs, 128, 1, 0, nullptr, F(Y), F(Sorted), F(Counts), F(Ret), F(H), F(slot_bytes));

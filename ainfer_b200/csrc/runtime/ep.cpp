@@ -5,9 +5,10 @@
 //   A  owner:   post-attention RMSNorm + quantiser, router logits, top-k, dispatch plan, permute
 //      exchange of the dispatch buffer (one fixed-size slot per peer; NCCL send/recv in one group)
 //   B  experts: group received items by expert, gather, grouped tensor-core GEMM gate/up,
-//               SiLU-multiply + quantiser, grouped GEMM down, un-permute into the return buffer
+//               SiLU-multiply + quantiser, grouped GEMM down, un-permute into the return buffer;
+//               the shared expert of the owned rows is one more problem of the same launches
 //      exchange of the return buffer
-//   C  owner:   shared expert of the owned tokens, slot-ordered combine with the residual
+//   C  owner:   slot-ordered combine with the residual
 // Every piece keeps the single-token kernels' arithmetic, so each token's row is bit-identical
 // to the one-GPU decode kernels' whatever the batch and the number of ranks. The reference
 // decodes one token on one device (tools/decode/decode_l0.cpp:666-674 is its dense MLP) and has
@@ -58,11 +59,6 @@ struct Nccl {
 };
 Nccl g_nccl;
 constexpr int kNcclUint8 = 1;
-
-struct TcGroupRec {   // problem record of the grouped tensor-core GEMM
-  const void *P, *S;
-  int32_t x_row0, M, y_col, pad;
-};
 
 int item_bytes(int H) { return H + ((H / 128 * 4 + 15) & ~15); }
 
@@ -165,40 +161,24 @@ int EpMoe::create(DeviceModel *model, const void *id128, int rank_, int world_, 
   sm_count = info.sm_count;
   const int G = H / 128, rows = world * cap;   // rows: most items a rank can receive
   int r = 0;
+  const int shn = shared ? n : 0;   // the owned rows follow the received items in the grouped layout
   r |= alloc(&Res, (size_t)n * H * 4); r |= alloc(&X, (size_t)n * H * 4); r |= alloc(&Hn, (size_t)n * H * 4);
-  r |= alloc(&Q8, (size_t)n * H); r |= alloc(&SQ, (size_t)n * G * 4);
   r |= alloc(&Logits, (size_t)n * (E + 1) * 4); r |= alloc(&Bias, (size_t)E * 4);
   r |= alloc(&SelIdx, (size_t)n * (k + 1) * 4); r |= alloc(&SelW, (size_t)n * (k + 1) * 4); r |= alloc(&NearGap, (size_t)n * 4);
   r |= alloc(&ItemDest, (size_t)cap * 4);
   r |= alloc(&Send, (size_t)world * slot_d); r |= alloc(&Recv, (size_t)world * slot_d);
   r |= alloc(&Ret, (size_t)world * slot_r); r |= alloc(&Back, (size_t)world * slot_r);
   r |= alloc(&Sorted, (size_t)rows * 4); r |= alloc(&Counts, 16);
-  r |= alloc(&GroupsGU, (size_t)2 * epr * 32); r |= alloc(&GroupsD, (size_t)epr * 32);
-  r |= alloc(&XQs, (size_t)rows * H); r |= alloc(&SQs, (size_t)rows * G * 4);
-  r |= alloc(&GU, (size_t)rows * 2 * I * 4); r |= alloc(&AQ, (size_t)rows * I); r |= alloc(&ASQ, (size_t)rows * (I / 128) * 4);
-  r |= alloc(&Y2, (size_t)rows * H * 4);
-  if (shared) {
-    r |= alloc(&ShGU, (size_t)n * 2 * I * 4); r |= alloc(&ShAQ, (size_t)n * I); r |= alloc(&ShASQ, (size_t)n * (I / 128) * 4);
-    r |= alloc(&Ysh, (size_t)n * H * 4);
-    r |= alloc(&ShGroups, (size_t)(c.layers + c.mtp_layers) * 3 * 32); r |= alloc(&ShCounts, 16);
-  }
+  r |= alloc(&GroupsGU, (size_t)2 * (epr + 1) * 32); r |= alloc(&GroupsD, (size_t)(epr + 1) * 32);
+  r |= alloc(&XQs, (size_t)(rows + n) * H); r |= alloc(&SQs, (size_t)(rows + n) * G * 4);
+  r |= alloc(&GU, (size_t)(rows + shn) * 2 * I * 4); r |= alloc(&AQ, (size_t)(rows + shn) * I);
+  r |= alloc(&ASQ, (size_t)(rows + shn) * (I / 128) * 4);
+  r |= alloc(&Y2, (size_t)(rows + shn) * H * 4);
   if (r) return 1;
-  if (shared) {
-    // the shared expert's three problems per layer (gate, up, down over the n owned rows) and their counts
-    const int nl = c.layers + c.mtp_layers;
-    std::vector<ExpertW> tab((size_t)nl * (E + 1));
-    EP_CHECK(ainfer_memcpy_d2h(dev, tab.data(), m->expert_tables, tab.size() * sizeof(ExpertW)));
-    std::vector<TcGroupRec> g((size_t)nl * 3);
-    for (int L = 0; L < nl; ++L) {
-      const ExpertW &w = tab[(size_t)L * (E + 1) + E];
-      g[3 * L] = TcGroupRec{w.gP, w.gS, 0, n, 0, 0};
-      g[3 * L + 1] = TcGroupRec{w.uP, w.uS, 0, n, I, 0};
-      g[3 * L + 2] = TcGroupRec{w.dP, w.dS, 0, n, 0, 0};
-    }
-    EP_CHECK(ainfer_memcpy_h2d(dev, ShGroups, g.data(), g.size() * sizeof(TcGroupRec)));
-    const int32_t cnt[4] = {n, 2, 1, 0};
-    EP_CHECK(ainfer_memcpy_h2d(dev, ShCounts, cnt, 16));
-  }
+  // the owner's quantised rows live at the tail of the grouped layout: the shared expert reads them in place
+  Q8 = XQs + (size_t)rows * H;
+  SQ = SQs + (size_t)rows * G;
+  Ysh = shared ? Y2 + (size_t)rows * H : nullptr;
   if (world > 1) {
     if (!id128) { err = "usage: a world of several ranks needs the shared NCCL id"; return 2; }
     if (!g_nccl.load()) { err = g_nccl.err; return 1; }
@@ -254,12 +234,12 @@ int EpMoe::record_layer(int L) {
   }
   // ---- B: the experts of this rank on everything received ----
   r.launch("EpGroup", 1u, (const unsigned char *)Recv, tab, Sorted, GroupsGU, GroupsD, Counts, (int32_t)world, (int32_t)rank, (int32_t)epr,
-           (int32_t)cap, (int32_t)I, slot_d);
+           (int32_t)cap, (int32_t)I, slot_d, (int32_t)rows, (int32_t)(shared ? n : 0), (int32_t)E);
   r.launch("EpGather", (uint32_t)rows, (const unsigned char *)Recv, (const int32_t *)Sorted, (const int32_t *)Counts, XQs, SQs, (int32_t)H,
            (int32_t)cap, slot_d);
   r.launch("Int4GemmA8TcGrouped", tc_blocks, (const void *)GroupsGU, (const int32_t *)(Counts + 1), (const int8_t *)XQs, (const float *)SQs, GU,
            (int32_t)I, (int32_t)H, (int32_t)std::min(batch, 64), (int32_t)(2 * I));
-  r.launch("SiluQuantRows", (uint32_t)rows, (const float *)GU, (const int32_t *)Counts, AQ, ASQ, (int32_t)I);
+  r.launch("SiluQuantRows", (uint32_t)(rows + (shared ? n : 0)), (const float *)GU, (const int32_t *)Counts, AQ, ASQ, (int32_t)I, (int32_t)rows);
   r.launch("Int4GemmA8TcGrouped", tc_blocks, (const void *)GroupsD, (const int32_t *)(Counts + 2), (const int8_t *)AQ, (const float *)ASQ, Y2,
            (int32_t)H, (int32_t)I, (int32_t)std::min(batch, 64), (int32_t)H);
   r.launch("EpScatter", (uint32_t)rows, (const float *)Y2, (const int32_t *)Sorted, (const int32_t *)Counts, Ret, (int32_t)H, slot_r);
@@ -269,15 +249,7 @@ int EpMoe::record_layer(int L) {
   } else {
     r.copy(Back, Ret, slot_r);
   }
-  // ---- C: shared expert of the owned rows, combine ----
-  if (shared) {
-    const char *sg = (const char *)ShGroups + (size_t)L * 3 * 32;
-    r.launch("Int4GemmA8TcGrouped", tc_blocks, (const void *)sg, (const int32_t *)(ShCounts + 1), (const int8_t *)Q8, (const float *)SQ, ShGU,
-             (int32_t)I, (int32_t)H, (int32_t)n, (int32_t)(2 * I));
-    r.launch("SiluQuantRows", (uint32_t)n, (const float *)ShGU, (const int32_t *)nullptr, ShAQ, ShASQ, (int32_t)I);
-    r.launch("Int4GemmA8TcGrouped", tc_blocks, (const void *)(sg + 2 * 32), (const int32_t *)(ShCounts + 2), (const int8_t *)ShAQ,
-             (const float *)ShASQ, Ysh, (int32_t)H, (int32_t)I, (int32_t)n, (int32_t)H);
-  }
+  // ---- C: combine ----
   r.launch("EpCombine", (uint32_t)(n * ((H + 255) / 256)), (const float *)Res, (const unsigned char *)Back, (const int32_t *)ItemDest,
            (const float *)SelW, (const float *)(shared ? Ysh : nullptr), X, (int32_t)k, (int32_t)H, slot_r);
   (void)G;

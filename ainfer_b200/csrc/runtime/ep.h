@@ -39,11 +39,7 @@ struct EpMoe {
   void *GroupsGU = nullptr, *GroupsD = nullptr;
   int8_t *XQs = nullptr, *AQ = nullptr;
   float *SQs = nullptr, *GU = nullptr, *ASQ = nullptr, *Y2 = nullptr;
-  // shared expert of the owned rows
-  float *ShGU = nullptr, *ShASQ = nullptr, *Ysh = nullptr;
-  int8_t *ShAQ = nullptr;
-  void *ShGroups = nullptr;
-  int32_t *ShCounts = nullptr;
+  float *Ysh = nullptr;   // shared expert's outputs of the owned rows (tail of Y2)
   std::vector<int> layer_lists;   // per layer: index of its first list, -1 = not recorded yet
 
   // Returns 0, 1 (device / NCCL error) or 2 (usage); err holds the message.
