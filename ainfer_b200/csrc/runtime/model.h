@@ -57,6 +57,8 @@ int check_directory_shapes(const Container &dir, const ModelConfig &cfg, std::st
 
 // Writes a synthetic model file on the host (no GPU involved).
 int synth_write_file(const char *path, const ModelConfig &cfg, uint64_t seed, std::string &err);
+// SafeTensors file or directory (with model.safetensors.index.json) -> .binfer (ingest.cpp).
+int binfer_from_safetensors(const char *src, const char *arch_json, const char *out_path, std::string &err);
 
 struct DeviceTensor {
   const TensorEntry *entry = nullptr;

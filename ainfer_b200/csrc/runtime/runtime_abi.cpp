@@ -46,6 +46,12 @@ int ainfer_synth_write(const char *path, const char *preset, uint64_t seed) {
   return set_err(r, err);
 }
 
+int ainfer_binfer_from_safetensors(const char *src, const char *arch_json, const char *out_path) {
+  std::string err;
+  int r = binfer_from_safetensors(src, arch_json, out_path, err);
+  return set_err(r, err);
+}
+
 const char *ainfer_preset_config_json(const char *preset) {
   static thread_local std::string js;
   ModelConfig cfg;

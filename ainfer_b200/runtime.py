@@ -29,6 +29,7 @@ SIGNATURES = {
     "ainfer_binfer_validate": (_i, [C.c_char_p, _i]),
     "ainfer_synth_write": (_i, [C.c_char_p, C.c_char_p, _u64]),
     "ainfer_preset_config_json": (C.c_char_p, [C.c_char_p]),
+    "ainfer_binfer_from_safetensors": (_i, [C.c_char_p, C.c_char_p, C.c_char_p]),
     "ainfer_model_open": (_i, [_vp, C.c_char_p, _i, _pp]),
     "ainfer_model_close": (_i, [_vp]),
     "ainfer_model_config_json": (C.c_char_p, [_vp]),
@@ -240,6 +241,11 @@ def apply_rep_penalty(logits, seen, penalty):
     seen = np.ascontiguousarray(seen, dtype=np.int32)
     load().ainfer_apply_rep_penalty(logits.ctypes.data, logits.size, seen.ctypes.data, seen.size, penalty)
     return logits
+
+
+def from_safetensors(src, arch_json, out_path):
+    """SafeTensors file or sharded directory -> .binfer (ainfer_binfer_from_safetensors)."""
+    _check(load().ainfer_binfer_from_safetensors(str(src).encode(), arch_json.encode(), str(out_path).encode()))
 
 
 def ep_unique_id():

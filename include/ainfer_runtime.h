@@ -39,6 +39,13 @@ int ainfer_binfer_validate(const char *path, int level);
  * "small", "full") on the host. Counterpart of tools/binfer.py cmd_quantize
  * (:155-353) with seeded N(0, 0.02) weights in place of a checkpoint. */
 int ainfer_synth_write(const char *path, const char *preset, uint64_t seed);
+/* Checkpoint ingestion: a SafeTensors file, or a directory holding model.safetensors.index.json
+ * and its shards, to a .binfer container. Counterpart of tools/binfer.py cmd_quantize (:155-353)
+ * with its policy (:60-64: 2-D tensors to INT4 symmetric g128 with bf16 scales, token embedding
+ * and 1-D tensors bf16, vision tower left out) plus this runtime's two bf16 exceptions (router,
+ * shared-expert gate). arch_json: the architecture section (the keys ainfer_preset_config_json
+ * shows); the directory is checked against it before anything is written. Returns 0 or 2. */
+int ainfer_binfer_from_safetensors(const char *src, const char *arch_json, const char *out_path);
 /* Architecture JSON of a preset (pointer valid until the next call). */
 const char *ainfer_preset_config_json(const char *preset);
 
