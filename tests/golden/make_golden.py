@@ -1,7 +1,7 @@
 """Regenerates the committed golden fixtures from the reference checkout.
 
-Run in a container that has the reference at $REFERENCE (default
-/root/reference):   python tests/golden/make_golden.py
+Run where the reference checkout is at $REFERENCE (default: a directory named
+"reference" beside this repository):   python tests/golden/make_golden.py
 
 Outputs (committed, small):
   ref_vectors.npz   vectors extracted from the reference's own fixture files
@@ -24,7 +24,7 @@ import numpy as np
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = os.environ.get("REFERENCE", "/root/reference")
+REF = os.environ.get("REFERENCE") or os.path.join(os.path.dirname(ROOT), "reference")
 
 
 def ref_vectors():

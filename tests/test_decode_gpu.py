@@ -88,7 +88,7 @@ def test_device_fill_equals_file_upload(dev, mini_file):
 
 @pytest.mark.parametrize("flags", [16, 4], ids=["persistent", "multi_kernel"])
 def test_config1_mini_one_step_at_511_prior_tokens(dev, mini_file, flags):
-    """BASELINE config 1: mini model, one decode step at batch 1, seed 0, 511 cached tokens."""
+    """The reference's CPU-runnable case: mini model, one decode step at batch 1, seed 0, 511 cached tokens."""
     from ainfer_b200 import runtime
     model = runtime.Model(dev, mini_file)
     cfg = model.config
