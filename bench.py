@@ -211,14 +211,12 @@ def gemv_probe(dev, N, K, reps=20):
 
 
 def step_traffic_note():
-    """DRAM bytes of one launch of the persistent step from the committed ncu summary, if present:
-    a line 'dram_bytes_per_launch=<n> algorithmic_bytes_per_launch=<m>' measured on a smaller model."""
-    p = os.path.join(ROOT, "profiles", "decode_step_persistent_small_model.md")
+    """DRAM bytes and algorithmic bytes of one launch of the persistent step as an ncu capture on a
+    smaller preset measured them (a data file beside the package; the capture's command is in it)."""
+    p = os.path.join(ROOT, "ainfer_b200", "step_traffic.json")
     try:
-        for line in open(p):
-            if line.startswith("dram_bytes_per_launch="):
-                kv = dict(x.split("=") for x in line.split())
-                return float(kv["dram_bytes_per_launch"]), float(kv["algorithmic_bytes_per_launch"]), os.path.relpath(p, ROOT)
+        j = json.load(open(p))
+        return float(j["dram_bytes_per_launch"]), float(j["algorithmic_bytes_per_launch"]), f"ncu capture on the {j['preset']} preset"
     except Exception:
         pass
     return None
