@@ -35,6 +35,27 @@ __global__ void __launch_bounds__(256) ChunkConvSilu(const ChunkConvSiluArgs a) 
   a.CS[c * 3 + 0] = h0; a.CS[c * 3 + 1] = h1; a.CS[c * 3 + 2] = h2;
 }
 
+// ---- ChunkBetaDecay: beta = sigmoid(b), g = -exp(A_log) * softplus(a + dt_bias) for M rows ----
+// (BetaG, tools/cmdlist/kernels.cpp:606-617; the arithmetic of the decode GEMV's epilogues.)
+struct ChunkBetaDecayArgs {
+  const float *B;        // [M][nV] in_proj_b outputs
+  const float *A;        // [M][nV] in_proj_a outputs
+  const float *ALog;     // [nV]
+  const float *DtBias;   // [nV]
+  float *Bt;             // [M][nV]
+  float *Gt;             // [M][nV]
+  int32_t nV, count;     // count = M * nV
+};
+__global__ void __launch_bounds__(256) ChunkBetaDecay(const ChunkBetaDecayArgs a) {
+  const int i = blockIdx.x * 256 + threadIdx.x;
+  if (i >= a.count) return;
+  const int h = i % a.nV;
+  a.Bt[i] = 1.0f / (1.0f + det_expf(-a.B[i]));
+  const float sa = a.A[i] + a.DtBias[h];
+  const float soft = sa > 20.0f ? sa : det_logf(1.0f + det_expf(sa));
+  a.Gt[i] = (-det_expf(a.ALog[h])) * soft;
+}
+
 // ---- ChunkDeltaNet: the gated delta rule over M rows ----
 struct ChunkDeltaNetArgs {
   float *Out;        // [M][nV][128] head outputs
@@ -135,6 +156,9 @@ static uint32_t chunk_dn_smem_fn(const void *) { return 2u * kChunkRows * 128u *
 
 #define F(f) AINFER_ARG(ChunkConvSiluArgs, f)
 AINFER_REGISTER(ChunkConvSilu, ChunkConvSiluArgs, 256, 256, 0, nullptr, F(Mx), F(QKV), F(CS), F(CW), F(C), F(M));
+#undef F
+#define F(f) AINFER_ARG(ChunkBetaDecayArgs, f)
+AINFER_REGISTER(ChunkBetaDecay, ChunkBetaDecayArgs, 256, 256, 0, nullptr, F(B), F(A), F(ALog), F(DtBias), F(Bt), F(Gt), F(nV), F(count));
 #undef F
 #define F(f) AINFER_ARG(ChunkDeltaNetArgs, f)
 AINFER_REGISTER(ChunkDeltaNet, ChunkDeltaNetArgs, 256, 1, 0, chunk_dn_smem_fn, F(Out), F(Mx), F(S), F(Bt), F(Gt), F(nK), F(nV), F(M));

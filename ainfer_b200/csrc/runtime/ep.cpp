@@ -163,6 +163,7 @@ int EpMoe::create(DeviceModel *model, const void *id128, int rank_, int world_, 
   int r = 0;
   const int shn = shared ? n : 0;   // the owned rows follow the received items in the grouped layout
   r |= alloc(&Res, (size_t)n * H * 4); r |= alloc(&X, (size_t)n * H * 4); r |= alloc(&Hn, (size_t)n * H * 4);
+  if (flags & EP_RES_ADD) { r |= alloc(&Add, (size_t)n * H * 4); r |= alloc(&ResSum, (size_t)n * H * 4); }
   r |= alloc(&Logits, (size_t)n * (E + 1) * 4); r |= alloc(&Bias, (size_t)E * 4);
   r |= alloc(&SelIdx, (size_t)n * (k + 1) * 4); r |= alloc(&SelW, (size_t)n * (k + 1) * 4); r |= alloc(&NearGap, (size_t)n * 4);
   r |= alloc(&ItemDest, (size_t)cap * 4);
@@ -216,8 +217,10 @@ int EpMoe::record_layer(int L) {
   if (new_list(&la)) return 1;
   Rec r{this, la};
   // ---- A: route the owned rows and pack their items ----
-  r.launch("RmsNormQuant", (uint32_t)n, (const float *)Res, (const float *)nullptr, (float *)nullptr,
-           (const float *)(m->post_norm + (size_t)L * H), Hn, Q8, SQ, (int32_t)H, eps);
+  const float *res_in = (flags & EP_RES_ADD) ? ResSum : Res;   // what the combine adds the experts' outputs to
+  r.launch("RmsNormQuant", (uint32_t)n, (const float *)Res, (const float *)((flags & EP_RES_ADD) ? Add : nullptr),
+           (float *)((flags & EP_RES_ADD) ? ResSum : nullptr), (const float *)(m->post_norm + (size_t)L * H), Hn, Q8, SQ,
+           (int32_t)H, eps);
   const int tpb = 4;   // tokens per block of the router: enough blocks to fill the device, weights re-read from L2
   r.launch("RouterLogitsRows", (uint32_t)(((E + 1 + 7) / 8) * ((n + tpb - 1) / tpb)), (const uint16_t *)router.data,
            (const uint16_t *)(shared ? sgate.data : nullptr), (const float *)Hn,
@@ -250,7 +253,7 @@ int EpMoe::record_layer(int L) {
     r.copy(Back, Ret, slot_r);
   }
   // ---- C: combine ----
-  r.launch("EpCombine", (uint32_t)(n * ((H + 255) / 256)), (const float *)Res, (const unsigned char *)Back, (const int32_t *)ItemDest,
+  r.launch("EpCombine", (uint32_t)(n * ((H + 255) / 256)), res_in, (const unsigned char *)Back, (const int32_t *)ItemDest,
            (const float *)SelW, (const float *)(shared ? Ysh : nullptr), X, (int32_t)k, (int32_t)H, slot_r);
   (void)G;
   return close(r);

@@ -10,7 +10,8 @@
 namespace ainfer {
 
 enum EpFlags {
-  EP_ROUTER_BIAS = 1   // add the "router_bias" buffer to the routed experts' logits (load generators)
+  EP_ROUTER_BIAS = 1,  // add the "router_bias" buffer to the routed experts' logits (load generators)
+  EP_RES_ADD = 2       // the block's residual input is "res" + "add" (the mixer's output not yet added)
 };
 
 // Fills 128 bytes with a fresh NCCL id (rank 0 calls, the caller hands it to every rank).
@@ -29,6 +30,7 @@ struct EpMoe {
   bool shared = false;
   uint32_t slot_d = 0, slot_r = 0;   // bytes of one peer's slot in the dispatch / return buffers
   // owner side
+  float *Add = nullptr, *ResSum = nullptr;   // EP_RES_ADD: second addend, and the sum the block works on
   float *Res = nullptr, *X = nullptr, *Hn = nullptr, *SQ = nullptr, *Logits = nullptr, *Bias = nullptr;
   int8_t *Q8 = nullptr;
   int32_t *SelIdx = nullptr, *ItemDest = nullptr;

@@ -641,6 +641,7 @@ int session_create(DeviceModel *m, int max_ctx, int flags, Session **out, std::s
 }
 
 void session_destroy(Session *s) {
+  if (s && s->prefill) { prefill_destroy(s->prefill); s->prefill = nullptr; }
   if (!s) return;
   ainfer_sync(s->dev, UINT64_MAX);
   for (auto l : s->layer_lists) ainfer_list_destroy(l);

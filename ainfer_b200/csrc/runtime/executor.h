@@ -25,6 +25,8 @@ enum SessionFlags {
   SESSION_PERSISTENT = 16       // one persistent cooperative launch per token (DecodeStep)
 };
 
+struct Prefill;
+
 struct Session {
   DeviceModel *m = nullptr;
   ainfer_device_t dev = nullptr;
@@ -87,9 +89,16 @@ struct Session {
   std::map<std::string, std::vector<double>> buckets;
   int max_chunks = 0;
   int argmax_parts = 0;
+  Prefill *prefill = nullptr;   // created on the first ainfer_session_prefill
 };
 
 int session_create(DeviceModel *m, int max_ctx, int flags, Session **out, std::string &err);
+// Chunked prefill (prefill.cpp): advances the session's state over n tokens at positions start_pos..
+// without producing logits; bit-identical to n decode steps. The object holds the row buffers.
+struct Prefill;
+int prefill_create(Session *s, Prefill **out);
+void prefill_destroy(Prefill *p);
+int prefill_run(Prefill *p, const int *tokens, int n, int start_pos);
 void session_destroy(Session *s);
 // Zeroes conv history, DeltaNet state and the KV cache.
 int session_reset(Session *s);

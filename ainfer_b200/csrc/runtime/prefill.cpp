@@ -1,0 +1,214 @@
+// Chunked prefill: advances a session's state (DeltaNet state, conv history, INT8 KV cache) over a
+// run of prompt tokens, up to 64 rows at a time, instead of one decode step per token. The chunk
+// orchestration of the reference (tools/cmdlist/chunklayer_replay.cpp:366-443: ChunkGemm,
+// ChunkSsmConv, ChunkSsmRecur, ChunkAttn per layer, state persisting across chunk replays) with
+// this library's row-batched kernels:
+//   rows' RMSNorm + quantiser -> batched W4A8 GEMM on the tensor cores for every projection
+//   (weights cross HBM once per chunk, not once per token) -> DeltaNet: conv + SiLU over the rows,
+//   beta / decay, the recurrence with the state on the chip for the whole chunk, gated norm ->
+//   attention: per row, in order, the decode kernels (head norm + RoPE + INT8 append, chunked
+//   attention over the cache, merge) -> output projection -> the MoE block of the rows (router,
+//   device permute by expert, grouped tensor-core expert GEMMs, slot-ordered combine; ep.cpp with
+//   one rank), which also performs the residual add.
+// Every row's arithmetic is the decode path's, so a prefilled session is bit-identical to one that
+// decoded the same tokens one by one (tests/test_prefill_gpu.py). Launches are immediate (no
+// recorded list): the number of rows of the last chunk varies.
+#include <cstring>
+
+#include "ep.h"
+#include "executor.h"
+
+namespace ainfer {
+
+struct Prefill {
+  Session *s = nullptr;
+  EpMoe ep;
+  bool ep_ready = false;
+  int rows_cap = 64;
+  std::vector<void *> owned;
+  // row buffers
+  int32_t *Ctrl = nullptr;                       // [rows][4]
+  int8_t *Q8 = nullptr; float *SQ = nullptr;     // [rows][maxK], [rows][maxK/128]
+  float *Pq = nullptr, *Mx = nullptr, *Z = nullptr, *Br = nullptr, *Ar = nullptr, *Bt = nullptr, *Gt = nullptr, *O = nullptr;
+  float *Q16 = nullptr, *K16 = nullptr, *V16 = nullptr;
+  std::map<std::string, ainfer_kernel_t> kernels;
+};
+
+namespace {
+
+template <typename T>
+int palloc(Prefill *p, size_t count, T **out) {
+  Session *s = p->s;
+  void *q = nullptr;
+  const size_t bytes = std::max<size_t>(count * sizeof(T), 16);
+  if (ainfer_mem_alloc(s->dev, bytes, 256, &q) != AINFER_OK || ainfer_mem_fill(s->dev, q, 0, bytes) != AINFER_OK) {
+    s->err = std::string("prefill: alloc failed: ") + ainfer_last_error(s->dev);
+    return 1;
+  }
+  p->owned.push_back(q);
+  *out = (T *)q;
+  return 0;
+}
+
+struct Launcher {   // immediate launches; arguments by index in member order
+  Prefill *p;
+  int status = 0;
+  template <typename T>
+  void set(ainfer_kernel_t k, uint32_t &idx, const T &v) {
+    if (status) return;
+    if (ainfer_kernel_set_arg(k, idx, sizeof(T), &v) != AINFER_OK) { p->s->err = ainfer_last_error(p->s->dev); status = 1; }
+    ++idx;
+  }
+  template <typename... A>
+  void launch(const char *name, uint32_t groups, const A &...args) {
+    if (status) return;
+    Session *s = p->s;
+    auto it = p->kernels.find(name);
+    ainfer_kernel_t k = nullptr;
+    if (it != p->kernels.end()) k = it->second;
+    else {
+      if (ainfer_kernel_get(s->dev, name, &k) != AINFER_OK) { s->err = std::string("entry ") + name + " not found"; status = 1; return; }
+      p->kernels[name] = k;
+    }
+    uint32_t idx = 0;
+    (set(k, idx, args), ...);
+    if (status) return;
+    if (ainfer_kernel_launch(s->dev, k, groups ? groups : 1) != AINFER_OK) { s->err = std::string(name) + ": " + ainfer_last_error(s->dev); status = 1; }
+  }
+  // Y[rows][N] = X[rows][K] . W^T on the tensor cores
+  void gemm(const DeviceTensor &t, const int8_t *XQ, const float *SQ, float *Y, int K, int rows) {
+    if (status) return;
+    Session *s = p->s;
+    if (!t.entry || (int)t.entry->shape[1] != K || t.entry->storage != DT_INT4_SYM_G128) {
+      s->err = "prefill: missing tensor or unexpected shape/storage" + (t.entry ? " of " + t.entry->name : std::string());
+      status = 2;
+      return;
+    }
+    const int N = (int)t.entry->shape[0];
+    const uint32_t tiles = (uint32_t)((N + 127) / 128);
+    launch("Int4GemmA8Tc", std::min<uint32_t>(tiles, 2u * (uint32_t)s->sm_count), (const uint8_t *)t.data, (const uint16_t *)t.scales, XQ, SQ, Y,
+           (int32_t)N, (int32_t)K, (int32_t)rows, (int32_t)N);
+  }
+};
+
+}  // namespace
+
+int prefill_create(Session *s, Prefill **out) {
+  const ModelConfig &c = s->m->cfg;
+  Prefill *p = new Prefill;
+  p->s = s;
+  const int R = p->rows_cap, H = c.hidden, C = c.conv_dim(), VD = c.value_dim(), nV = c.lin_v_heads;
+  const int QN = c.q_heads * 2 * c.head_dim, KN = c.kv_heads * c.head_dim, AK = c.q_heads * c.head_dim;
+  const int maxK = std::max(H, std::max(VD, AK));
+  int r = 0;
+  r |= palloc(p, (size_t)R * 4, &p->Ctrl);
+  r |= palloc(p, (size_t)R * maxK, &p->Q8); r |= palloc(p, (size_t)R * (maxK / 128), &p->SQ);
+  r |= palloc(p, (size_t)R * C, &p->Pq); r |= palloc(p, (size_t)R * C, &p->Mx); r |= palloc(p, (size_t)R * VD, &p->Z);
+  r |= palloc(p, (size_t)R * nV, &p->Br); r |= palloc(p, (size_t)R * nV, &p->Ar);
+  r |= palloc(p, (size_t)R * nV, &p->Bt); r |= palloc(p, (size_t)R * nV, &p->Gt);
+  r |= palloc(p, (size_t)R * VD, &p->O);
+  r |= palloc(p, (size_t)R * QN, &p->Q16); r |= palloc(p, (size_t)R * KN, &p->K16); r |= palloc(p, (size_t)R * KN, &p->V16);
+  if (!r) {
+    int e = p->ep.create(s->m, nullptr, 0, 1, R, EP_RES_ADD);
+    if (e) { s->err = "prefill: " + p->ep.err; r = e; }
+    else p->ep_ready = true;
+  }
+  if (r) { prefill_destroy(p); return r; }
+  *out = p;
+  return 0;
+}
+
+void prefill_destroy(Prefill *p) {
+  if (!p) return;
+  ainfer_sync(p->s->dev, UINT64_MAX);
+  if (p->ep_ready || p->ep.impl) p->ep.destroy();
+  for (auto &kv : p->kernels) ainfer_kernel_release(kv.second);
+  for (void *q : p->owned) ainfer_mem_free(p->s->dev, q);
+  delete p;
+}
+
+// Advances the session over tokens[0..n) at positions start_pos.. (no logits, no sampling).
+int prefill_run(Prefill *p, const int *tokens, int n, int start_pos) {
+  Session *s = p->s;
+  DeviceModel *m = s->m;
+  const ModelConfig &c = m->cfg;
+  if (n < 0 || start_pos < 0 || start_pos + n > s->max_ctx) {
+    s->err = "context overflow: pos " + std::to_string(start_pos + n) + " >= MAXCTX " + std::to_string(s->max_ctx);
+    return 3;
+  }
+  const int H = c.hidden, C = c.conv_dim(), VD = c.value_dim(), nK = c.lin_k_heads, nV = c.lin_v_heads;
+  const int nQ = c.q_heads, nKV = c.kv_heads, D = c.head_dim;
+  const int QN = nQ * 2 * D, KN = nKV * D, AK = nQ * D;
+  const float eps = (float)c.rms_eps;
+  DeviceTensor emb = m->tensor("model.language_model.embed_tokens.weight");
+  if (!emb.entry) { s->err = "missing model.language_model.embed_tokens.weight"; return 1; }
+  EpMoe &ep = p->ep;
+  Launcher l{p};
+  std::vector<int32_t> ctrl((size_t)p->rows_cap * 4);
+  for (int t0 = 0; t0 < n && !l.status; t0 += p->rows_cap) {
+    const int rows = std::min(p->rows_cap, n - t0);
+    for (int i = 0; i < rows; ++i) {
+      ctrl[4 * i] = tokens[t0 + i];
+      ctrl[4 * i + 1] = start_pos + t0 + i;
+      ctrl[4 * i + 2] = start_pos + t0 + i + 1;
+      ctrl[4 * i + 3] = -1;
+    }
+    if (ainfer_memcpy_h2d(s->dev, p->Ctrl, ctrl.data(), (size_t)rows * 16) != AINFER_OK) { s->err = ainfer_last_error(s->dev); return 1; }
+    float *X = ep.Res;   // the rows' residual stream lives in the MoE block's input buffer
+    l.launch("EmbedRow", (uint32_t)rows, X, (const uint16_t *)emb.data, (const int32_t *)p->Ctrl, (int32_t)H, (int32_t)c.vocab, (int32_t)4);
+    for (int L = 0; L < c.layers && !l.status; ++L) {
+      const std::string pf = layer_prefix(L);
+      const int slot = m->slot[L];
+      l.launch("RmsNormQuant", (uint32_t)rows, (const float *)X, (const float *)nullptr, (float *)nullptr,
+               (const float *)(m->in_norm + (size_t)L * H), (float *)nullptr, p->Q8, p->SQ, (int32_t)H, eps);
+      if (c.layer_types[L] == 'A') {
+        l.gemm(m->tensor(pf + "self_attn.q_proj.weight"), p->Q8, p->SQ, p->Q16, H, rows);
+        l.gemm(m->tensor(pf + "self_attn.k_proj.weight"), p->Q8, p->SQ, p->K16, H, rows);
+        l.gemm(m->tensor(pf + "self_attn.v_proj.weight"), p->Q8, p->SQ, p->V16, H, rows);
+        const size_t kv_off = (size_t)slot * s->max_ctx * nKV;
+        int8_t *Kc = s->Kc + kv_off * D, *Vc = s->Vc + kv_off * D;
+        uint16_t *Ks = s->Ks + kv_off, *Vs = s->Vs + kv_off;
+        const uint32_t g_split = (uint32_t)std::min(s->max_chunks * nKV, s->sm_count * 8);
+        for (int i = 0; i < rows && !l.status; ++i) {   // rows in order: row i attends to the rows before it
+          const int32_t *ci = p->Ctrl + 4 * i;
+          const float *q16 = p->Q16 + (size_t)i * QN;
+          l.launch("AttnPrep", (uint32_t)((nQ + 2 * nKV + 7) / 8), q16, (const float *)(p->K16 + (size_t)i * KN),
+                   (const float *)(p->V16 + (size_t)i * KN), (const float *)(m->q_norm + (size_t)slot * D),
+                   (const float *)(m->k_norm + (size_t)slot * D), (const float *)m->rope_cos, (const float *)m->rope_sin, ci, s->Qn, Kc,
+                   Vc, Ks, Vs, (int32_t)nQ, (int32_t)nKV, (int32_t)c.rotary_dim, (int32_t)s->max_ctx, eps);
+          l.launch("AttnSplit", g_split, (const float *)s->Qn, (const int8_t *)Kc, (const int8_t *)Vc, (const uint16_t *)Ks,
+                   (const uint16_t *)Vs, ci, s->Pm, s->Pse, s->Pacc, (int32_t)nQ, (int32_t)nKV, (int32_t)s->max_ctx,
+                   (int32_t)s->max_chunks);
+          l.launch("AttnCombine", (uint32_t)nQ, (const float *)s->Pm, (const float *)s->Pse, (const float *)s->Pacc, q16, ci,
+                   p->Q8 + (size_t)i * AK, p->SQ + (size_t)i * (AK / 128), (float *)nullptr, (int32_t)nQ, (int32_t)s->max_ctx,
+                   (int32_t)s->max_chunks);
+        }
+        l.gemm(m->tensor(pf + "self_attn.o_proj.weight"), p->Q8, p->SQ, ep.Add, AK, rows);
+      } else {
+        l.gemm(m->tensor(pf + "linear_attn.in_proj_qkv.weight"), p->Q8, p->SQ, p->Pq, H, rows);
+        l.gemm(m->tensor(pf + "linear_attn.in_proj_z.weight"), p->Q8, p->SQ, p->Z, H, rows);
+        l.gemm(m->tensor(pf + "linear_attn.in_proj_b.weight"), p->Q8, p->SQ, p->Br, H, rows);
+        l.gemm(m->tensor(pf + "linear_attn.in_proj_a.weight"), p->Q8, p->SQ, p->Ar, H, rows);
+        l.launch("ChunkConvSilu", (uint32_t)((C + 255) / 256), p->Mx, (const float *)p->Pq, s->conv + (size_t)slot * C * 3,
+                 (const float *)(m->conv_w + (size_t)slot * C * 4), (int32_t)C, (int32_t)rows);
+        l.launch("ChunkBetaDecay", (uint32_t)((rows * nV + 255) / 256), (const float *)p->Br, (const float *)p->Ar,
+                 (const float *)(m->a_log + (size_t)slot * nV), (const float *)(m->dt_bias + (size_t)slot * nV), p->Bt, p->Gt, (int32_t)nV,
+                 (int32_t)(rows * nV));
+        l.launch("ChunkDeltaNet", (uint32_t)(nV * 4), p->O, (const float *)p->Mx, s->S + (size_t)slot * nV * 128 * 128, (const float *)p->Bt,
+                 (const float *)p->Gt, (int32_t)nK, (int32_t)nV, (int32_t)rows);
+        l.launch("GatedNormQuant", (uint32_t)((rows * nV + 3) / 4), (const float *)p->O, (const float *)p->Z,
+                 (const float *)(m->lin_norm + (size_t)slot * c.lin_head_dim), p->Q8, p->SQ, (float *)nullptr, (int32_t)(rows * nV), eps);
+        l.gemm(m->tensor(pf + "linear_attn.out_proj.weight"), p->Q8, p->SQ, ep.Add, VD, rows);
+      }
+      if (l.status) break;
+      // x = (x + mixer) + MoE(norm(x + mixer)) for the rows; rows past `rows` hold stale values and are ignored
+      int e = ep.run_layer(L, true, nullptr);
+      if (e) { s->err = "prefill: " + ep.err; return e; }
+    }
+  }
+  if (l.status) return l.status;
+  if (ainfer_sync(s->dev, UINT64_MAX) != AINFER_OK) { s->err = ainfer_last_error(s->dev); return 1; }
+  return 0;
+}
+
+}  // namespace ainfer

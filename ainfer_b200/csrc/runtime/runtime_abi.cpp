@@ -156,6 +156,16 @@ int ainfer_session_buffer(ainfer_session_t h, const char *which, void **dptr, ui
   else return set_err(2, "unknown session buffer: " + w);
   return 0;
 }
+int ainfer_session_prefill(ainfer_session_t h, const int *tokens, int n, int start_pos) {
+  if (!h || (!tokens && n > 0)) return set_err(2, "usage: null argument");
+  Session *s = h->s;
+  if (!s->prefill) {
+    int r = prefill_create(s, &s->prefill);
+    if (r) return set_err(r, s->err);
+  }
+  int r = prefill_run(s->prefill, tokens, n, start_pos);
+  return set_err(r, s->err);
+}
 int ainfer_session_step(ainfer_session_t s, int token, int pos, int *out_token) {
   if (!s) return 2;
   int r = session_step(s->s, token, pos, out_token);
@@ -229,6 +239,7 @@ int ainfer_ep_buffer(ainfer_ep_t ep, const char *which, void **dptr, uint64_t *b
   const std::string w = which;
   if (w == "res") { *dptr = e.Res; *bytes = (uint64_t)e.n * e.H * 4; }
   else if (w == "x") { *dptr = e.X; *bytes = (uint64_t)e.n * e.H * 4; }
+  else if (w == "add") { *dptr = e.Add; *bytes = e.Add ? (uint64_t)e.n * e.H * 4 : 0; }
   else if (w == "sel_idx") { *dptr = e.SelIdx; *bytes = (uint64_t)e.n * (e.k + 1) * 4; }
   else if (w == "sel_w") { *dptr = e.SelW; *bytes = (uint64_t)e.n * (e.k + 1) * 4; }
   else if (w == "near_gap") { *dptr = e.NearGap; *bytes = (uint64_t)e.n * 4; }

@@ -42,6 +42,7 @@ SIGNATURES = {
     "ainfer_session_reset": (_i, [_vp]),
     "ainfer_session_buffer": (_i, [_vp, C.c_char_p, _pp, C.POINTER(_u64)]),
     "ainfer_session_step": (_i, [_vp, _i, _i, C.POINTER(_i)]),
+    "ainfer_session_prefill": (_i, [_vp, C.POINTER(_i), _i, _i]),
     "ainfer_session_generate": (_i, [_vp, C.POINTER(_i), _i, _i, _i, C.POINTER(_i), C.POINTER(C.c_float)]),
     "ainfer_session_logits": (_i, [_vp, _vp]),
     "ainfer_session_launches_per_token": (_i, [_vp, C.POINTER(_u64)]),
@@ -194,6 +195,11 @@ class Session:
         out = np.zeros(V, np.float32)
         _check(load().ainfer_session_logits(self.h, out.ctypes.data))
         return out
+
+    def prefill(self, tokens, start_pos=0):
+        """Advances the state over the tokens in chunks of up to 64 rows (no logits)."""
+        t = np.ascontiguousarray(tokens, np.int32)
+        _check(load().ainfer_session_prefill(self.h, t.ctypes.data_as(C.POINTER(C.c_int)), len(t), int(start_pos)))
 
     def mtp_draft(self, next_token, pos, from_trunk=True):
         """One draft of the MTP head (hidden input: the trunk's last residual, or chained)."""

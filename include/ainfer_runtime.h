@@ -93,6 +93,11 @@ int ainfer_session_step(ainfer_session_t s, int token, int pos, int *out_token);
  * block, one readback at the end. gen_ms (optional): device time of the G steps. */
 int ainfer_session_generate(ainfer_session_t s, const int *prompt, int P, int G, int start_pos,
                             int *out_tokens, float *gen_ms);
+/* Chunked prefill: advances the session's state (DeltaNet state, conv history, INT8 KV cache) over
+ * n tokens at positions start_pos.. in chunks of up to 64 rows, without logits (chunk orchestration
+ * of tools/cmdlist/chunklayer_replay.cpp:366-443). The state afterwards is bit-identical to n calls
+ * of ainfer_session_step; follow with ainfer_session_generate(s, &last_prompt_id, 1, G, start_pos + n, ...). */
+int ainfer_session_prefill(ainfer_session_t s, const int *tokens, int n, int start_pos);
 /* ---- MTP head (multi-token prediction; dataflow of tools/t72/mtp_accept.py:11-16,142-151) ----
  * x = fc . quant([rms1w(embed(next_token)) ; rms1w(h)]) -> one full-attention decoder layer with
  * its own KV cache and MoE -> mtp.norm -> shared lm_head -> argmax. h is the trunk's final
