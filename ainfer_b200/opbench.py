@@ -266,9 +266,39 @@ def main(argv=None):
     d.add_argument("--timeline", action="store_true",
                    help="per-kernel cost on the dependency chain, measured inside the recorded list "
                         "(needs a library built with AINFER_TIMELINE=1)")
+    pf = sub.add_parser("prefill", help="chunked prefill of a seeded prompt against token-by-token decoding of it")
+    pf.add_argument("--model", default="small")
+    pf.add_argument("--prompt", type=int, default=512)
+    pf.add_argument("--steps", type=int, default=8)
+    pf.add_argument("--no-loop", action="store_true", help="skip the token-by-token run (no comparison)")
     args = ap.parse_args(argv)
     dev = cuda_abi.Device(0)
-    if args.cmd == "gemv":
+    if args.cmd == "prefill":
+        import time
+        model = runtime.Model(dev, f"synth:{args.model}:seed=0")
+        V, P = model.config["vocab"], args.prompt
+        prompt = np.random.default_rng(7).integers(0, V, P).astype(np.int32)
+        b = runtime.Session(model, P + args.steps + 8, runtime.Session.PERSISTENT)
+        b.prefill(prompt[:2])                       # creates the row buffers and records the MoE lists (untimed)
+        b.reset()
+        dev.sync()
+        t0 = time.time()
+        b.prefill(prompt[:P - 1])
+        t_pf = time.time() - t0
+        got = b.generate(prompt[P - 1:], args.steps, start_pos=P - 1)
+        out = {"op": "prefill", "model": args.model, "prompt": P, "prefill_s": t_pf, "prompt_tokens_per_s": (P - 1) / t_pf,
+               "tokens": [int(t) for t in got]}
+        if not args.no_loop:
+            a = runtime.Session(model, P + args.steps + 8, runtime.Session.PERSISTENT)
+            dev.sync()
+            t0 = time.time()
+            want = a.generate(prompt, args.steps)
+            t_loop = time.time() - t0
+            out.update({"loop_decode_s": t_loop, "same_tokens": got.tolist() == want.tolist()})
+            a.close()
+        print(json.dumps(out), flush=True)
+        b.close(); model.close()
+    elif args.cmd == "gemv":
         ms_ = (1, 2, 4, 8, 64) if (args.a16 or args.tc) else (1, 2, 4, 8)
         shapes = ([(m, n, k) for (n, k) in [(512, 2048), (4096, 2048), (8192, 2048), (151936, 2048), (2048, 512)]
                    for m in ms_] if args.sweep else [(args.m, args.n, args.k)])
