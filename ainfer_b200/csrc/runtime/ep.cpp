@@ -255,6 +255,7 @@ int EpMoe::record_layer(int L) {
   // ---- C: combine ----
   r.launch("EpCombine", (uint32_t)(n * ((H + 255) / 256)), res_in, (const unsigned char *)Back, (const int32_t *)ItemDest,
            (const float *)SelW, (const float *)(shared ? Ysh : nullptr), X, (int32_t)k, (int32_t)H, slot_r);
+  r.copy(Res, X, (size_t)n * H * 4);   // the next layer's input: layers chain through "res"
   (void)G;
   return close(r);
 }
@@ -312,7 +313,7 @@ int EpMoe::run_layer(int L, bool chain, float *seg_ms) {
     if (stamp(4)) return 1;
     EP_CHECK(ainfer_list_execute(impl->lists[i + 2]));
   }
-  if (chain) EP_CHECK(ainfer_memcpy_d2d(dev, Res, X, (size_t)n * H * 4));
+  (void)chain;   // the layer's last list already copies x to res
   if (stamp(5)) return 1;
   if (seg_ms) {
     EP_CHECK(ainfer_sync(dev, ~0ull));

@@ -46,7 +46,7 @@ struct EpMoe {
 
   // Returns 0, 1 (device / NCCL error) or 2 (usage); err holds the message.
   int create(DeviceModel *model, const void *id128, int rank, int world, int batch, int flags);
-  // X = Res + MoE(norm_L(Res)) for the owned rows; chain: Res <- X afterwards. seg_ms (optional,
+  // X = Res + MoE(norm_L(Res)) for the owned rows, and Res <- X afterwards (layers chain). seg_ms (optional,
   // 5 floats, accumulated): device time of route+pack, dispatch, experts, return, shared+combine;
   // asking for it synchronises after the layer.
   int run_layer(int L, bool chain, float *seg_ms);

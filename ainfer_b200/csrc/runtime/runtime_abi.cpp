@@ -3,6 +3,7 @@
 #include <string>
 
 #include "../../../include/ainfer_runtime.h"
+#include "batch.h"
 #include "ep.h"
 #include "executor.h"
 #include "host_sampler.h"
@@ -13,6 +14,7 @@ using namespace ainfer;
 struct ainfer_model_s { DeviceModel *m; std::string cfg_json; };
 struct ainfer_session_s { Session *s; };
 struct ainfer_ep_s { EpMoe e; };
+struct ainfer_batch_s { BatchDecode b; };
 
 static thread_local std::string g_err;
 static int set_err(int code, const std::string &e) {
@@ -257,6 +259,53 @@ int ainfer_ep_moe_stack(ainfer_ep_t ep, int first, int count, float *seg_ms) {
   if (!ep) return 2;
   int r = ep->e.run_stack(first, count, seg_ms);
   return set_err(r, ep->e.err);
+}
+
+int ainfer_batch_create(ainfer_model_t m, const void *id128, int rank, int world, int batch, int max_ctx, int flags,
+                        ainfer_batch_t *out) {
+  if (!m || !out) return set_err(2, "usage: null argument");
+  *out = nullptr;
+  ainfer_batch_s *h = new ainfer_batch_s;
+  int r = h->b.create(m->m, id128, rank, world, batch, max_ctx, flags);
+  if (r) {
+    set_err(r, h->b.err);
+    h->b.destroy();
+    delete h;
+    return r;
+  }
+  *out = h;
+  return 0;
+}
+int ainfer_batch_destroy(ainfer_batch_t h) {
+  if (!h) return 2;
+  h->b.destroy();
+  delete h;
+  return 0;
+}
+int ainfer_batch_buffer(ainfer_batch_t h, const char *which, void **dptr, uint64_t *bytes) {
+  if (!h || !which || !dptr || !bytes) return set_err(2, "usage: null argument");
+  BatchDecode &b = h->b;
+  const ModelConfig &c = b.m->cfg;
+  const std::string w = which;
+  const uint64_t n = (uint64_t)b.n;
+  if (w == "ctrl") { *dptr = b.Ctrl; *bytes = n * 16; }
+  else if (w == "out_tok") { *dptr = b.OutT; *bytes = n * 4; }
+  else if (w == "logits") { *dptr = b.Logits; *bytes = n * c.vocab * 4; }
+  else if (w == "x") { *dptr = b.ep.Res; *bytes = n * c.hidden * 4; }
+  else if (w == "S") { *dptr = b.S; *bytes = n * b.s_stride * 4; }
+  else if (w == "conv") { *dptr = b.conv; *bytes = n * b.conv_stride * 4; }
+  else if (w == "Kc") { *dptr = b.Kc; *bytes = n * b.kv_rows * c.kv_heads * c.head_dim; }
+  else if (w == "Vc") { *dptr = b.Vc; *bytes = n * b.kv_rows * c.kv_heads * c.head_dim; }
+  else if (w == "Ks") { *dptr = b.Ks; *bytes = n * b.kv_rows * c.kv_heads * 2; }
+  else if (w == "Vs") { *dptr = b.Vs; *bytes = n * b.kv_rows * c.kv_heads * 2; }
+  else if (w == "router_bias") { *dptr = b.ep.Bias; *bytes = (uint64_t)c.experts * 4; }
+  else return set_err(2, "unknown buffer: " + w);
+  return 0;
+}
+int ainfer_batch_step(ainfer_batch_t h) {
+  if (!h) return 2;
+  int r = h->b.step();
+  return set_err(r, h->b.err);
 }
 
 int ainfer_apply_rep_penalty(float *logits, int V, const int *seen, int nseen, float penalty) {

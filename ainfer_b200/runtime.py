@@ -55,6 +55,10 @@ SIGNATURES = {
     "ainfer_ep_buffer": (_i, [_vp, C.c_char_p, C.POINTER(_vp), C.POINTER(C.c_uint64)]),
     "ainfer_ep_moe_layer": (_i, [_vp, _i]),
     "ainfer_ep_moe_stack": (_i, [_vp, _i, _i, _vp]),
+    "ainfer_batch_create": (_i, [_vp, _vp, _i, _i, _i, _i, _i, C.POINTER(_vp)]),
+    "ainfer_batch_destroy": (_i, [_vp]),
+    "ainfer_batch_buffer": (_i, [_vp, C.c_char_p, C.POINTER(_vp), C.POINTER(C.c_uint64)]),
+    "ainfer_batch_step": (_i, [_vp]),
     "ainfer_apply_rep_penalty": (_i, [_vp, _i, _vp, _i, C.c_float]),
     "ainfer_sample_token": (_i, [_vp, _i, C.POINTER(SampleParams), C.POINTER(_u64), _vp]),
 }
@@ -308,4 +312,50 @@ class EpMoe:
     def close(self):
         if self.h:
             load().ainfer_ep_destroy(self.h)
+            self.h = None
+
+
+class BatchDecode:
+    """Batched decode (ainfer_batch_*): this rank owns batch/world sequences; every step advances
+    each of them by one greedy token on the device."""
+    ROUTER_BIAS = 1
+
+    def __init__(self, model, batch, max_ctx, rank=0, world=1, nccl_id=None, flags=0):
+        self.model, self.dev = model, model.dev
+        h = C.c_void_p()
+        idb = C.create_string_buffer(nccl_id, 128) if nccl_id is not None else None
+        _check(load().ainfer_batch_create(model.h, idb, rank, world, batch, max_ctx, flags, C.byref(h)))
+        self.h, self.rows = h, batch // world
+
+    def buffer(self, which):
+        p, n = C.c_void_p(), C.c_uint64()
+        _check(load().ainfer_batch_buffer(self.h, which.encode(), C.byref(p), C.byref(n)))
+        return p.value, n.value
+
+    def read(self, which, dtype):
+        p, n = self.buffer(which)
+        return self.dev.download(p, n // np.dtype(dtype).itemsize, dtype)
+
+    def write(self, which, arr):
+        p, n = self.buffer(which)
+        arr = np.ascontiguousarray(arr)
+        assert arr.nbytes == n, (which, arr.nbytes, n)
+        self.dev.write(p, arr)
+
+    def set_inputs(self, tokens, positions):
+        """Control block of every owned sequence: the token to feed and its position."""
+        c = np.zeros((self.rows, 4), np.int32)
+        c[:, 0], c[:, 1], c[:, 2], c[:, 3] = tokens, positions, np.asarray(positions) + 1, -1
+        self.write("ctrl", c)
+
+    def step(self):
+        _check(load().ainfer_batch_step(self.h))
+
+    def tokens(self):
+        self.dev.sync()
+        return self.read("out_tok", np.int32)
+
+    def close(self):
+        if self.h:
+            load().ainfer_batch_destroy(self.h)
             self.h = None

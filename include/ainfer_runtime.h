@@ -133,12 +133,31 @@ int ainfer_ep_destroy(ainfer_ep_t ep);
  * [n][k+1] i32, "sel_w" [n][k+1] f32, "near_gap" [n] f32, "router_bias" [E] f32, "counts" [4] i32
  * (items received, gate/up problems, down problems of the last layer run). */
 int ainfer_ep_buffer(ainfer_ep_t ep, const char *which, void **dptr, uint64_t *bytes);
-/* x = res + MoE(post_attention_norm_L(res)) for the owned rows; asynchronous on the device's queue. */
+/* x = res + MoE(post_attention_norm_L(res)) for the owned rows, then res <- x (so that layers
+ * chain); asynchronous on the device's queue. */
 int ainfer_ep_moe_layer(ainfer_ep_t ep, int layer);
 /* `count` layers from `first`, each feeding the next (res <- x). seg_ms: NULL, or 5 floats that
  * receive the summed device time of route+pack, dispatch exchange, experts, return exchange,
  * shared expert+combine (the call then synchronises after every layer: not for timing the whole). */
 int ainfer_ep_moe_stack(ainfer_ep_t ep, int first, int count, float *seg_ms);
+
+/* ---- batched decode ----
+ * `batch` sequences advance one token each per step; rank r of `world` owns sequences
+ * [r*batch/world, (r+1)*batch/world) with their state and INT8 KV caches (max_ctx tokens each);
+ * the MoE layers exchange tokens with the ranks that hold the routed experts (ainfer_ep_*), the
+ * rest runs on the owner. Per sequence the arithmetic is the single-sequence token loop's
+ * (tools/decode/decode_l0.cpp:742-825), so it decodes to the same tokens in a batch as alone. */
+typedef struct ainfer_batch_s *ainfer_batch_t;
+int ainfer_batch_create(ainfer_model_t m, const void *id128, int rank, int world, int batch, int max_ctx, int flags,
+                        ainfer_batch_t *out);
+int ainfer_batch_destroy(ainfer_batch_t b);
+/* Device buffers of this rank's n = batch/world sequences: "ctrl" [n][4] i32 {token, position,
+ * length, selected}, "out_tok" [n] i32, "logits" [n][V] f32, "x" [n][H] f32 (final residual),
+ * state "S", "conv", "Kc", "Vc", "Ks", "Vs" (sequence-major), "router_bias" [E] f32. */
+int ainfer_batch_buffer(ainfer_batch_t b, const char *which, void **dptr, uint64_t *bytes);
+/* One token for every owned sequence (asynchronous): reads each control block, writes the greedy
+ * token to "out_tok" and advances the block, so consecutive calls are a greedy loop. */
+int ainfer_batch_step(ainfer_batch_t b);
 
 /* ---- sampler (tools/sample/sampler.h:16-62) ---- */
 typedef struct ainfer_sample_params {
