@@ -154,6 +154,9 @@ class Device:
         self.check(self.L.ainfer_mem_fill(self.h, p, 0, max(nbytes, 16)))
         return p
 
+    def copy_d2d(self, dst, src, nbytes):
+        self.check(self.L.ainfer_memcpy_d2d(self.h, dst, src, nbytes))
+
     def write(self, ptr, arr):
         arr = np.ascontiguousarray(arr)
         self.check(self.L.ainfer_memcpy_h2d(self.h, ptr, arr.ctypes.data, arr.nbytes))

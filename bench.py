@@ -295,6 +295,82 @@ def run_ep(args, dev, model, rank, world, dist):
             "expert_bytes_per_layer_all_ranks_upper": cfg["experts"] * 3 * H * I * (0.5 + 2.0 / 128)}
 
 
+def run_batch(args, dev, model, rank, world, dist):
+    """Batched decode (the metric's batch-64 half): BATCH sequences, each at a long context with an
+    INT8 KV cache, advance one greedy token per step. Sequences are split over the ranks (state and
+    caches live with their owner); the MoE layers run expert-parallel with a Zipf(1.1) router bias.
+    The caches are filled with a seeded pattern (no 32 k-token prompt is decoded for each of 64
+    sequences); the timed region is whole steps: mixers, exchanges, LM head, argmax; device
+    events, max over ranks."""
+    from ainfer_b200 import runtime
+    cfg = model.config
+    B, ctx = args.batch, args.batch_ctx
+    if B % world or cfg["experts"] % world:
+        return {"skipped": f"batch {B} or {cfg['experts']} experts do not divide over {world} ranks"}
+    nid = None
+    if world > 1:
+        import torch
+        t = torch.zeros(128, dtype=torch.uint8, device="cuda")
+        if rank == 0:
+            t = torch.frombuffer(bytearray(runtime.ep_unique_id()), dtype=torch.uint8).cuda()
+        dist.broadcast(t, 0)
+        nid = bytes(t.cpu().numpy().tobytes())
+    steps, warm = args.batch_steps, max(1, args.batch_warmup)
+    max_ctx = ctx + steps + warm + 8
+    try:
+        bd = runtime.BatchDecode(model, B, max_ctx, rank=rank, world=world, nccl_id=nid, flags=runtime.BatchDecode.ROUTER_BIAS)
+    except Exception as e:
+        return {"skipped": f"cannot create the batch engine: {str(e)[:200]}"}
+    n = B // world
+    bd.write("router_bias", zipf_router_bias(cfg["experts"]))
+    rng = np.random.default_rng(4321 + rank)
+    # seeded cache contents: a 32 MB block of INT8 values, and fp16 scales near 0.02, repeated
+    block = rng.integers(-127, 128, 32 << 20, dtype=np.int8)
+    sblock = (0x2000 + rng.integers(0, 0x400, 1 << 20)).astype(np.uint16)     # fp16 in [0.0078, 0.0156)
+    for name, src in (("Kc", block), ("Vc", block[::-1].copy()), ("Ks", sblock), ("Vs", sblock[::-1].copy())):
+        p, nb = bd.buffer(name)
+        raw = src.view(np.uint8)
+        d0 = dev.upload(raw)
+        off = 0
+        while off < nb:
+            m = min(raw.nbytes, nb - off)
+            dev.copy_d2d(p + off, d0, m)
+            off += m
+        dev.free(d0)
+    bd.write("S", (rng.standard_normal(bd.buffer("S")[1] // 4) * 0.1).astype(np.float32))
+    bd.set_inputs(rng.integers(0, cfg["vocab"], n), np.full(n, ctx, np.int32))
+    for _ in range(warm):
+        bd.step()
+    dev.sync()
+    if dist is not None:
+        dist.barrier()
+    passes = []
+    for _ in range(steps):
+        e0, e1 = dev.event(), dev.event()
+        e0.record()
+        bd.step()
+        e1.record()
+        dev.sync()
+        passes.append(e0.elapsed_ms(e1))
+    toks = bd.tokens()
+    total_ms = float(sum(passes))
+    if dist is not None:
+        import torch
+        t = torch.tensor([total_ms] + passes, device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms, passes = float(t[0]), [float(x) for x in t[1:]]
+    bd.close()
+    nkv, D = cfg["kv_heads"], cfg["head_dim"]
+    n_attn = cfg["layer_types"].count("A")
+    kv_bytes = B * n_attn * ctx * nkv * (2 * D + 4)
+    return {"workload": f"batch {B} greedy decode, every sequence at context {ctx} (INT8 KV), sequences and experts split over {world} rank(s), Zipf(1.1) router bias",
+            "tokens_per_s": B * steps / (total_ms / 1000.0), "ms_per_step": total_ms / steps,
+            "passes_ms": {"n": len(passes), "median": float(np.median(passes)), "min": min(passes), "max": max(passes)},
+            "scaling": "strong", "batch": B, "context": ctx, "world": world, "steps": steps, "warmup": warm,
+            "kv_bytes_per_step_all_ranks": kv_bytes, "first_tokens_rank0": [int(x) for x in toks[:4]],
+            "cache_fill": "seeded INT8 pattern and fp16 scales (not decoded prompts)"}
+
+
 def run_ours(args):
     rank, local_rank, world = dist_env()
     dist = None
@@ -363,6 +439,7 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         gen_ms, t_e2e = float(t[0]), float(t[1])
     ep_line = None if args.no_ep else run_ep(args, dev, model, rank, world, dist)
+    batch_line = None if args.no_batch else run_batch(args, dev, model, rank, world, dist)
     if rank != 0:
         model.close(); dev.close()
         dist.destroy_process_group()
@@ -411,7 +488,8 @@ def run_ours(args):
             t_copy = time.time() - t0
             osess = O.Session(om, max_ctx)
             sess.reset()
-            first = int(sess.generate(prompt, 1)[0])
+            sess.prefill(prompt[:-1])
+            first = int(sess.generate(prompt[-1:], 1, start_pos=P - 1)[0])
             state = {n: sess.read(n, dt) for n, dt in STATE}
             n_cpu = args.cpu_steps
             gpu_toks = sess.generate(np.array([first], np.int32), n_cpu, start_pos=P)
@@ -451,7 +529,7 @@ def run_ours(args):
         "repeats": {"windows": len(win_ms), "ms_per_step_median": float(np.median(win_ms)), "ms_per_step_min": float(np.min(win_ms)),
                     "ms_per_step_max": float(np.max(win_ms))},
         "clocks": clk, "roofline": roof, "gemv_sweep": sweep,
-        "cpu_baseline": cpu, "parity": parity, "ep": ep_line,
+        "cpu_baseline": cpu, "parity": parity, "ep": ep_line, "batch_decode": batch_line,
         "timing": {"model_fill_s": t_load, "prompt_s": t_prompt, "prompt_by": "token-by-token decode" if args.loop_prompt else "chunked prefill (64 rows per pass)", "timed_wall_s": t_wall, "first_tokens": [int(t) for t in toks0[:8]]},
     }
     print(json.dumps(line))
@@ -473,6 +551,11 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="skip the isolated GEMV probes")
     ap.add_argument("--loop-prompt", action="store_true", help="run the prompt token by token instead of by chunked prefill")
+    ap.add_argument("--no-batch", action="store_true", help="skip the batched decode measurement")
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--batch-ctx", type=int, default=32768)
+    ap.add_argument("--batch-steps", type=int, default=8)
+    ap.add_argument("--batch-warmup", type=int, default=2)
     ap.add_argument("--no-ep", action="store_true", help="skip the expert-parallel MoE stack")
     ap.add_argument("--ep-batch", type=int, default=64)
     ap.add_argument("--ep-steps", type=int, default=5)
