@@ -17,6 +17,8 @@ struct ChunkConvSiluArgs {
   float *CS;          // [C][3] history, updated
   const float *CW;    // [C][4] taps
   int32_t C, M;
+  float *Snap;        // optional: the history [C][3] after row m at Snap + m * snap_stride (to roll a speculative chunk back); null: none
+  int64_t snap_stride;
 };
 __global__ void __launch_bounds__(256) ChunkConvSilu(const ChunkConvSiluArgs a) {
   const int c = blockIdx.x * 256 + threadIdx.x;
@@ -31,6 +33,10 @@ __global__ void __launch_bounds__(256) ChunkConvSilu(const ChunkConvSiluArgs a) 
     acc = acc + x * w.w;
     a.Mx[(size_t)m * a.C + c] = acc / (1.0f + det_expf(-acc));
     h0 = h1; h1 = h2; h2 = x;
+    if (a.Snap) {
+      float *sn = a.Snap + (size_t)m * a.snap_stride + (size_t)c * 3;
+      sn[0] = h0; sn[1] = h1; sn[2] = h2;
+    }
   }
   a.CS[c * 3 + 0] = h0; a.CS[c * 3 + 1] = h1; a.CS[c * 3 + 2] = h2;
 }
@@ -64,6 +70,8 @@ struct ChunkDeltaNetArgs {
   const float *Bt;   // [M][nV] beta
   const float *Gt;   // [M][nV] log decay
   int32_t nK, nV, M;
+  float *Snap;       // optional: the state [nV][128][128] after row m at Snap + m * snap_stride (to roll a speculative chunk back); null: none
+  int64_t snap_stride;
 };
 constexpr int kChunkRows = 64;   // rows whose normalised q / k are staged at a time
 
@@ -143,6 +151,11 @@ __global__ void __launch_bounds__(256) ChunkDeltaNet(const ChunkDeltaNetArgs a) 
                         ((part[1][4][lane] + part[1][5][lane]) + (part[1][6][lane] + part[1][7][lane]));
         a.Out[((size_t)(m0 + m) * a.nV + h) * D + col] = o;
       }
+      if (a.Snap) {
+        float *sn = a.Snap + (size_t)(m0 + m) * a.snap_stride + (size_t)h * D * D;
+#pragma unroll
+        for (int r = 0; r < SEG; ++r) sn[(size_t)(warp * SEG + r) * D + col] = s[r];
+      }
       val = val_next;
       // part[1] of this row is read by warp 0 only, before it writes part[1] of the next row
       // (it passes the next row's first barrier in between, as every writer of part[1] does)
@@ -155,13 +168,13 @@ __global__ void __launch_bounds__(256) ChunkDeltaNet(const ChunkDeltaNetArgs a) 
 static uint32_t chunk_dn_smem_fn(const void *) { return 2u * kChunkRows * 128u * 4u; }
 
 #define F(f) AINFER_ARG(ChunkConvSiluArgs, f)
-AINFER_REGISTER(ChunkConvSilu, ChunkConvSiluArgs, 256, 256, 0, nullptr, F(Mx), F(QKV), F(CS), F(CW), F(C), F(M));
+AINFER_REGISTER(ChunkConvSilu, ChunkConvSiluArgs, 256, 256, 0, nullptr, F(Mx), F(QKV), F(CS), F(CW), F(C), F(M), F(Snap), F(snap_stride));
 #undef F
 #define F(f) AINFER_ARG(ChunkBetaDecayArgs, f)
 AINFER_REGISTER(ChunkBetaDecay, ChunkBetaDecayArgs, 256, 256, 0, nullptr, F(B), F(A), F(ALog), F(DtBias), F(Bt), F(Gt), F(nV), F(count));
 #undef F
 #define F(f) AINFER_ARG(ChunkDeltaNetArgs, f)
-AINFER_REGISTER(ChunkDeltaNet, ChunkDeltaNetArgs, 256, 1, 0, chunk_dn_smem_fn, F(Out), F(Mx), F(S), F(Bt), F(Gt), F(nK), F(nV), F(M));
+AINFER_REGISTER(ChunkDeltaNet, ChunkDeltaNetArgs, 256, 1, 0, chunk_dn_smem_fn, F(Out), F(Mx), F(S), F(Bt), F(Gt), F(nK), F(nV), F(M), F(Snap), F(snap_stride));
 #undef F
 
 }  // namespace ainfer

@@ -642,6 +642,7 @@ int session_create(DeviceModel *m, int max_ctx, int flags, Session **out, std::s
 
 void session_destroy(Session *s) {
   if (s && s->prefill) { prefill_destroy(s->prefill); s->prefill = nullptr; }
+  if (s && s->verifier) { prefill_destroy(s->verifier); s->verifier = nullptr; }
   if (!s) return;
   ainfer_sync(s->dev, UINT64_MAX);
   for (auto l : s->layer_lists) ainfer_list_destroy(l);
@@ -760,31 +761,44 @@ int session_generate_mtp(Session *s, const int *prompt, int P, int G, int start_
   int p = start_pos + P - 1;  // position of the trunk step that produced y
   int g = 0;
   out_tokens[g++] = y;
+  // Batched verification: the accepted token and the round's drafts go through the trunk as ONE
+  // pass of up to draft_k + 1 rows (weights streamed once for all of them; prefill.cpp), which
+  // returns every row's greedy prediction and keeps the DeltaNet state after every row. Drafts
+  // are accepted while they equal the predictions; the state is rolled back to the last accepted
+  // row (tools/t72/mtp_accept.py:66-94,142-159 measures exactly this acceptance, offline).
+  if (s->verifier && prefill_rows_cap(s->verifier) < draft_k + 1) { prefill_destroy(s->verifier); s->verifier = nullptr; }
+  if (!s->verifier) {
+    int r = prefill_create(s, draft_k + 1, true, &s->verifier);
+    if (r) return r;
+  }
   while (g < G) {
-    // d drafts the token after y; chain the rest of the round from the head's own hidden state
-    int drafts[8];
-    const int k = std::min(draft_k, G - g);
-    drafts[0] = d;
-    for (int i = 1; i < k; ++i) {
-      int r = session_mtp_draft(s, drafts[i - 1], p + 1 + i, 0, &drafts[i]);
+    const int rows = std::min(draft_k + 1, G - g);   // tokens this round can emit
+    int feed[9], pred[9];
+    feed[0] = y;
+    if (rows > 1) feed[1] = d;                       // d drafts the token after y
+    for (int i = 2; i < rows; ++i) {                 // the rest chained from the head's own hidden state
+      int r = session_mtp_draft(s, feed[i - 1], p + i, 0, &feed[i]);
       if (r) return r;
     }
     ++rounds;
-    drafted += k;
-    // verify one by one with trunk steps; stop the round at the first miss
-    for (int i = 0; i < k && g < G; ++i) {
-      int y2 = -1;
-      int r = session_step(s, y, p + 1, &y2);
+    drafted += rows - 1;
+    int r = prefill_run(s->verifier, feed, rows, p + 1, pred);
+    if (r) return r;
+    int j = 0;
+    while (j < rows - 1 && feed[j + 1] == pred[j]) ++j;   // accepted drafts
+    accepted += j;
+    r = prefill_rollback(s->verifier, j + 1);
+    if (r) return r;
+    // the head's true rows for the accepted positions; the last one drafts the next round's first token
+    for (int i = 0; i <= j; ++i) {
+      r = prefill_row_hidden(s->verifier, i, s->X);
       if (r) return r;
-      ++p;
-      r = session_mtp_draft(s, y2, p + 1, 1, &d);
+      r = session_mtp_draft(s, pred[i], p + 2 + i, 1, &d);
       if (r) return r;
-      const bool hit = y2 == drafts[i];
-      y = y2;
-      out_tokens[g++] = y;
-      if (!hit) break;
-      ++accepted;
+      out_tokens[g++] = pred[i];
     }
+    p += j + 1;
+    y = pred[j];
   }
   if (stats) { stats[0] = rounds; stats[1] = drafted; stats[2] = accepted; }
   return 0;

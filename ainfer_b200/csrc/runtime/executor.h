@@ -90,15 +90,20 @@ struct Session {
   int max_chunks = 0;
   int argmax_parts = 0;
   Prefill *prefill = nullptr;   // created on the first ainfer_session_prefill
+  Prefill *verifier = nullptr;  // rows of the MTP loop's batched verification (created on first use)
 };
 
 int session_create(DeviceModel *m, int max_ctx, int flags, Session **out, std::string &err);
 // Chunked prefill (prefill.cpp): advances the session's state over n tokens at positions start_pos..
 // without producing logits; bit-identical to n decode steps. The object holds the row buffers.
 struct Prefill;
-int prefill_create(Session *s, Prefill **out);
+// rows_cap: rows per pass (1..64); verify: also allocate what per-row predictions and rollback need.
+int prefill_create(Session *s, int rows_cap, bool verify, Prefill **out);
 void prefill_destroy(Prefill *p);
-int prefill_run(Prefill *p, const int *tokens, int n, int start_pos);
+int prefill_run(Prefill *p, const int *tokens, int n, int start_pos, int *predictions);
+int prefill_rollback(Prefill *p, int keep);
+int prefill_row_hidden(Prefill *p, int row, float *dst);
+int prefill_rows_cap(const Prefill *p);
 void session_destroy(Session *s);
 // Zeroes conv history, DeltaNet state and the KV cache.
 int session_reset(Session *s);

@@ -13,6 +13,12 @@
 // Every row's arithmetic is the decode path's, so a prefilled session is bit-identical to one that
 // decoded the same tokens one by one (tests/test_prefill_gpu.py). Launches are immediate (no
 // recorded list): the number of rows of the last chunk varies.
+//
+// The same pass verifies speculative rows (the MTP loop's batched verification): it can return
+// every row's greedy prediction (final norm, LM head as one GEMM over the rows, argmax per row)
+// and keep a snapshot of the DeltaNet state and conv history after every row, so that the caller
+// rolls back to the last accepted row (the INT8 cache needs no rollback: rows beyond the accepted
+// ones are overwritten before any later position reads them).
 #include <cstring>
 
 #include "ep.h"
@@ -27,7 +33,11 @@ struct Prefill {
   int rows_cap = 64;
   std::vector<void *> owned;
   // row buffers
-  int32_t *Ctrl = nullptr;                       // [rows][4]
+  int32_t *Ctrl = nullptr, *OutT = nullptr;      // [rows][4], [rows]
+  float *Logits = nullptr;                       // [rows][V] (verification only)
+  float *SnapS = nullptr, *SnapC = nullptr;      // [rows][all DeltaNet layers' state / conv history] (verification only)
+  size_t snap_s_stride = 0, snap_c_stride = 0;
+  int last_rows = 0;
   int8_t *Q8 = nullptr; float *SQ = nullptr;     // [rows][maxK], [rows][maxK/128]
   float *Pq = nullptr, *Mx = nullptr, *Z = nullptr, *Br = nullptr, *Ar = nullptr, *Bt = nullptr, *Gt = nullptr, *O = nullptr;
   float *Q16 = nullptr, *K16 = nullptr, *V16 = nullptr;
@@ -93,10 +103,11 @@ struct Launcher {   // immediate launches; arguments by index in member order
 
 }  // namespace
 
-int prefill_create(Session *s, Prefill **out) {
+int prefill_create(Session *s, int rows_cap, bool verify, Prefill **out) {
   const ModelConfig &c = s->m->cfg;
   Prefill *p = new Prefill;
   p->s = s;
+  p->rows_cap = rows_cap;
   const int R = p->rows_cap, H = c.hidden, C = c.conv_dim(), VD = c.value_dim(), nV = c.lin_v_heads;
   const int QN = c.q_heads * 2 * c.head_dim, KN = c.kv_heads * c.head_dim, AK = c.q_heads * c.head_dim;
   const int maxK = std::max(H, std::max(VD, AK));
@@ -108,6 +119,12 @@ int prefill_create(Session *s, Prefill **out) {
   r |= palloc(p, (size_t)R * nV, &p->Bt); r |= palloc(p, (size_t)R * nV, &p->Gt);
   r |= palloc(p, (size_t)R * VD, &p->O);
   r |= palloc(p, (size_t)R * QN, &p->Q16); r |= palloc(p, (size_t)R * KN, &p->K16); r |= palloc(p, (size_t)R * KN, &p->V16);
+  if (verify) {
+    p->snap_s_stride = (size_t)c.n_lin() * nV * 128 * 128;
+    p->snap_c_stride = (size_t)c.n_lin() * C * 3;
+    r |= palloc(p, (size_t)R, &p->OutT); r |= palloc(p, (size_t)R * c.vocab, &p->Logits);
+    r |= palloc(p, (size_t)R * p->snap_s_stride, &p->SnapS); r |= palloc(p, (size_t)R * p->snap_c_stride, &p->SnapC);
+  }
   if (!r) {
     int e = p->ep.create(s->m, nullptr, 0, 1, R, EP_RES_ADD);
     if (e) { s->err = "prefill: " + p->ep.err; r = e; }
@@ -118,6 +135,8 @@ int prefill_create(Session *s, Prefill **out) {
   return 0;
 }
 
+int prefill_rows_cap(const Prefill *p) { return p->rows_cap; }
+
 void prefill_destroy(Prefill *p) {
   if (!p) return;
   ainfer_sync(p->s->dev, UINT64_MAX);
@@ -127,8 +146,10 @@ void prefill_destroy(Prefill *p) {
   delete p;
 }
 
-// Advances the session over tokens[0..n) at positions start_pos.. (no logits, no sampling).
-int prefill_run(Prefill *p, const int *tokens, int n, int start_pos) {
+// Advances the session over tokens[0..n) at positions start_pos... predictions (optional, needs a
+// verification object and n <= its rows): every row's greedy next token; the state after every
+// row is then also kept for prefill_rollback.
+int prefill_run(Prefill *p, const int *tokens, int n, int start_pos, int *predictions) {
   Session *s = p->s;
   DeviceModel *m = s->m;
   const ModelConfig &c = m->cfg;
@@ -144,6 +165,9 @@ int prefill_run(Prefill *p, const int *tokens, int n, int start_pos) {
   if (!emb.entry) { s->err = "missing model.language_model.embed_tokens.weight"; return 1; }
   EpMoe &ep = p->ep;
   Launcher l{p};
+  const bool verify = predictions != nullptr;
+  if (verify && (!p->SnapS || n > p->rows_cap)) { s->err = "usage: predictions need a verification object and at most its rows"; return 2; }
+  p->last_rows = verify ? n : 0;
   std::vector<int32_t> ctrl((size_t)p->rows_cap * 4);
   for (int t0 = 0; t0 < n && !l.status; t0 += p->rows_cap) {
     const int rows = std::min(p->rows_cap, n - t0);
@@ -190,12 +214,14 @@ int prefill_run(Prefill *p, const int *tokens, int n, int start_pos) {
         l.gemm(m->tensor(pf + "linear_attn.in_proj_b.weight"), p->Q8, p->SQ, p->Br, H, rows);
         l.gemm(m->tensor(pf + "linear_attn.in_proj_a.weight"), p->Q8, p->SQ, p->Ar, H, rows);
         l.launch("ChunkConvSilu", (uint32_t)((C + 255) / 256), p->Mx, (const float *)p->Pq, s->conv + (size_t)slot * C * 3,
-                 (const float *)(m->conv_w + (size_t)slot * C * 4), (int32_t)C, (int32_t)rows);
+                 (const float *)(m->conv_w + (size_t)slot * C * 4), (int32_t)C, (int32_t)rows,
+                 (float *)(verify ? p->SnapC + (size_t)slot * C * 3 : nullptr), (int64_t)p->snap_c_stride);
         l.launch("ChunkBetaDecay", (uint32_t)((rows * nV + 255) / 256), (const float *)p->Br, (const float *)p->Ar,
                  (const float *)(m->a_log + (size_t)slot * nV), (const float *)(m->dt_bias + (size_t)slot * nV), p->Bt, p->Gt, (int32_t)nV,
                  (int32_t)(rows * nV));
         l.launch("ChunkDeltaNet", (uint32_t)(nV * 4), p->O, (const float *)p->Mx, s->S + (size_t)slot * nV * 128 * 128, (const float *)p->Bt,
-                 (const float *)p->Gt, (int32_t)nK, (int32_t)nV, (int32_t)rows);
+                 (const float *)p->Gt, (int32_t)nK, (int32_t)nV, (int32_t)rows,
+                 (float *)(verify ? p->SnapS + (size_t)slot * nV * 128 * 128 : nullptr), (int64_t)p->snap_s_stride);
         l.launch("GatedNormQuant", (uint32_t)((rows * nV + 3) / 4), (const float *)p->O, (const float *)p->Z,
                  (const float *)(m->lin_norm + (size_t)slot * c.lin_head_dim), p->Q8, p->SQ, (float *)nullptr, (int32_t)(rows * nV), eps);
         l.gemm(m->tensor(pf + "linear_attn.out_proj.weight"), p->Q8, p->SQ, ep.Add, VD, rows);
@@ -206,8 +232,41 @@ int prefill_run(Prefill *p, const int *tokens, int n, int start_pos) {
       if (e) { s->err = "prefill: " + ep.err; return e; }
     }
   }
+  if (verify && !l.status) {
+    // every row's greedy prediction: final norm, LM head over the rows, argmax per row (no control advance)
+    l.launch("RmsNormQuant", (uint32_t)n, (const float *)ep.Res, (const float *)nullptr, (float *)nullptr, (const float *)m->final_norm,
+             (float *)nullptr, p->Q8, p->SQ, (int32_t)H, eps);
+    l.gemm(m->tensor("lm_head.weight"), p->Q8, p->SQ, p->Logits, H, n);
+    l.launch("BatchArgmax", (uint32_t)n, (const float *)p->Logits, p->OutT, p->Ctrl, (int32_t)c.vocab, (int32_t)0);
+  }
   if (l.status) return l.status;
-  if (ainfer_sync(s->dev, UINT64_MAX) != AINFER_OK) { s->err = ainfer_last_error(s->dev); return 1; }
+  if (verify) {
+    if (ainfer_memcpy_d2h(s->dev, predictions, p->OutT, (size_t)n * 4) != AINFER_OK) { s->err = ainfer_last_error(s->dev); return 1; }
+  } else if (ainfer_sync(s->dev, UINT64_MAX) != AINFER_OK) { s->err = ainfer_last_error(s->dev); return 1; }
+  return 0;
+}
+
+// Copies row `row`'s final residual of the last verifying pass to dst (H floats, device).
+int prefill_row_hidden(Prefill *p, int row, float *dst) {
+  Session *s = p->s;
+  const int H = s->m->cfg.hidden;
+  if (row < 0 || row >= p->last_rows) { s->err = "usage: no such row"; return 2; }
+  if (ainfer_memcpy_d2d(s->dev, dst, p->ep.Res + (size_t)row * H, (size_t)H * 4) != AINFER_OK) { s->err = ainfer_last_error(s->dev); return 1; }
+  return 0;
+}
+
+// After a verifying prefill_run of r rows: makes the session's DeltaNet state and conv history those
+// after the first `keep` rows (1 <= keep <= r).
+int prefill_rollback(Prefill *p, int keep) {
+  Session *s = p->s;
+  if (!p->SnapS || keep < 1 || keep > p->last_rows) { s->err = "usage: nothing to roll back to"; return 2; }
+  if (keep < p->last_rows) {
+    if (ainfer_memcpy_d2d(s->dev, s->S, p->SnapS + (size_t)(keep - 1) * p->snap_s_stride, p->snap_s_stride * 4) != AINFER_OK ||
+        ainfer_memcpy_d2d(s->dev, s->conv, p->SnapC + (size_t)(keep - 1) * p->snap_c_stride, p->snap_c_stride * 4) != AINFER_OK) {
+      s->err = ainfer_last_error(s->dev);
+      return 1;
+    }
+  }
   return 0;
 }
 

@@ -162,10 +162,10 @@ int ainfer_session_prefill(ainfer_session_t h, const int *tokens, int n, int sta
   if (!h || (!tokens && n > 0)) return set_err(2, "usage: null argument");
   Session *s = h->s;
   if (!s->prefill) {
-    int r = prefill_create(s, &s->prefill);
+    int r = prefill_create(s, 64, false, &s->prefill);
     if (r) return set_err(r, s->err);
   }
-  int r = prefill_run(s->prefill, tokens, n, start_pos);
+  int r = prefill_run(s->prefill, tokens, n, start_pos, nullptr);
   return set_err(r, s->err);
 }
 int ainfer_session_step(ainfer_session_t s, int token, int pos, int *out_token) {

@@ -1,6 +1,7 @@
 """MTP head on the GPU against the CPU oracle: single drafts (token and logits, bit for bit),
 chained drafts, and the draft/verify generation loop (tokens identical to plain greedy decoding,
-statistics identical to the same loop run on the oracle)."""
+statistics identical to the same loop run on the oracle; the trunk verifies a round's rows in one
+batched pass and rolls its recurrent state back to the last accepted row)."""
 import ctypes as C
 
 import numpy as np
@@ -85,26 +86,30 @@ def test_generate_mtp_equals_greedy_and_oracle_loop(dev, mtp_file):
     p, out = len(prompt) - 1, [y]
     rounds = drafted = accepted = 0
     while len(out) < G:
-        k = min(K, G - len(out))
-        drafts = [d]
-        for i in range(1, k):
-            dd, _ = oracle_mtp(osess, drafts[-1], p + 1 + i, h, V)   # h: the head's own chained state
-            drafts.append(dd)
+        # a round: the accepted token and up to K drafts are verified together; the oracle (which
+        # never speculates) feeds the same rows one by one and stops at the first rejected draft
+        rows = min(K + 1, G - len(out))
+        feed = [y] + ([d] if rows > 1 else [])
+        for i in range(2, rows):
+            dd, _ = oracle_mtp(osess, feed[i - 1], p + i, h, V)   # h: the head's own chained state
+            feed.append(dd)
         rounds += 1
-        drafted += k
-        for i in range(k):
-            if len(out) >= G:
+        drafted += rows - 1
+        preds, j = [], 0
+        for i in range(rows):
+            t = osess.step(feed[i], p + 1 + i)
+            preds.append((t, osess.buf("hidden").copy()))
+            if i < rows - 1 and feed[i + 1] == t:
+                j += 1
+            else:
                 break
-            y2 = osess.step(y, p + 1)
-            p += 1
-            h = osess.buf("hidden").copy()
-            d, _ = oracle_mtp(osess, y2, p + 1, h, V)
-            hit = y2 == drafts[i]
-            y = y2
-            out.append(y)
-            if not hit:
-                break
-            accepted += 1
+        accepted += j
+        for i in range(j + 1):
+            h = preds[i][1].copy()
+            d, _ = oracle_mtp(osess, preds[i][0], p + 2 + i, h, V)
+            out.append(preds[i][0])
+        p += j + 1
+        y = preds[j][0]
     assert out == got.tolist()
     assert st == {"rounds": rounds, "drafted": drafted, "accepted": accepted}
     # the head's own KV slot (the last one): every row up to the last position it ran at is a
