@@ -38,6 +38,9 @@ struct Prefill {
   float *SnapS = nullptr, *SnapC = nullptr;      // [rows][all DeltaNet layers' state / conv history] (verification only)
   size_t snap_s_stride = 0, snap_c_stride = 0;
   int last_rows = 0;
+  // a full verification pass recorded once: vlists[L] = everything between the MoE blocks of layers
+  // L - 1 and L (vlists[0] starts with the embedding), vlists[layers] = the rows' predictions
+  std::vector<ainfer_list_t> vlists;
   int8_t *Q8 = nullptr; float *SQ = nullptr;     // [rows][maxK], [rows][maxK/128]
   float *Pq = nullptr, *Mx = nullptr, *Z = nullptr, *Br = nullptr, *Ar = nullptr, *Bt = nullptr, *Gt = nullptr, *O = nullptr;
   float *Q16 = nullptr, *K16 = nullptr, *V16 = nullptr;
@@ -60,9 +63,22 @@ int palloc(Prefill *p, size_t count, T **out) {
   return 0;
 }
 
-struct Launcher {   // immediate launches; arguments by index in member order
+struct Launcher {   // immediate launches, or appended to recorded lists; arguments by index in member order
   Prefill *p;
   int status = 0;
+  bool recording = false;
+  ainfer_list_t list = nullptr;
+  // recording: closes the current list (if any) into p->vlists and opens the next one
+  void cut(bool open_next) {
+    if (status) return;
+    Session *s = p->s;
+    if (list) {
+      if (ainfer_list_close(list) != AINFER_OK) { s->err = ainfer_last_error(s->dev); status = 1; return; }
+      p->vlists.push_back(list);
+      list = nullptr;
+    }
+    if (open_next && ainfer_list_create(s->dev, &list) != AINFER_OK) { s->err = ainfer_last_error(s->dev); status = 1; }
+  }
   template <typename T>
   void set(ainfer_kernel_t k, uint32_t &idx, const T &v) {
     if (status) return;
@@ -83,7 +99,8 @@ struct Launcher {   // immediate launches; arguments by index in member order
     uint32_t idx = 0;
     (set(k, idx, args), ...);
     if (status) return;
-    if (ainfer_kernel_launch(s->dev, k, groups ? groups : 1) != AINFER_OK) { s->err = std::string(name) + ": " + ainfer_last_error(s->dev); status = 1; }
+    const int rc = recording ? ainfer_list_append_launch(list, k, groups ? groups : 1) : ainfer_kernel_launch(s->dev, k, groups ? groups : 1);
+    if (rc != AINFER_OK) { s->err = std::string(name) + ": " + ainfer_last_error(s->dev); status = 1; }
   }
   // Y[rows][N] = X[rows][K] . W^T on the tensor cores
   void gemm(const DeviceTensor &t, const int8_t *XQ, const float *SQ, float *Y, int K, int rows) {
@@ -141,6 +158,7 @@ void prefill_destroy(Prefill *p) {
   if (!p) return;
   ainfer_sync(p->s->dev, UINT64_MAX);
   if (p->ep_ready || p->ep.impl) p->ep.destroy();
+  for (ainfer_list_t l : p->vlists) ainfer_list_destroy(l);
   for (auto &kv : p->kernels) ainfer_kernel_release(kv.second);
   for (void *q : p->owned) ainfer_mem_free(p->s->dev, q);
   delete p;
@@ -164,20 +182,11 @@ int prefill_run(Prefill *p, const int *tokens, int n, int start_pos, int *predic
   DeviceTensor emb = m->tensor("model.language_model.embed_tokens.weight");
   if (!emb.entry) { s->err = "missing model.language_model.embed_tokens.weight"; return 1; }
   EpMoe &ep = p->ep;
-  Launcher l{p};
   const bool verify = predictions != nullptr;
   if (verify && (!p->SnapS || n > p->rows_cap)) { s->err = "usage: predictions need a verification object and at most its rows"; return 2; }
   p->last_rows = verify ? n : 0;
-  std::vector<int32_t> ctrl((size_t)p->rows_cap * 4);
-  for (int t0 = 0; t0 < n && !l.status; t0 += p->rows_cap) {
-    const int rows = std::min(p->rows_cap, n - t0);
-    for (int i = 0; i < rows; ++i) {
-      ctrl[4 * i] = tokens[t0 + i];
-      ctrl[4 * i + 1] = start_pos + t0 + i;
-      ctrl[4 * i + 2] = start_pos + t0 + i + 1;
-      ctrl[4 * i + 3] = -1;
-    }
-    if (ainfer_memcpy_h2d(s->dev, p->Ctrl, ctrl.data(), (size_t)rows * 16) != AINFER_OK) { s->err = ainfer_last_error(s->dev); return 1; }
+  // One pass over `rows` rows whose control blocks are in p->Ctrl: immediate, or recorded into p->vlists.
+  auto pass = [&](Launcher &l, int rows) -> int {
     float *X = ep.Res;   // the rows' residual stream lives in the MoE block's input buffer
     l.launch("EmbedRow", (uint32_t)rows, X, (const uint16_t *)emb.data, (const int32_t *)p->Ctrl, (int32_t)H, (int32_t)c.vocab, (int32_t)4);
     for (int L = 0; L < c.layers && !l.status; ++L) {
@@ -227,19 +236,60 @@ int prefill_run(Prefill *p, const int *tokens, int n, int start_pos, int *predic
         l.gemm(m->tensor(pf + "linear_attn.out_proj.weight"), p->Q8, p->SQ, ep.Add, VD, rows);
       }
       if (l.status) break;
-      // x = (x + mixer) + MoE(norm(x + mixer)) for the rows; rows past `rows` hold stale values and are ignored
-      int e = ep.run_layer(L, true, nullptr);
-      if (e) { s->err = "prefill: " + ep.err; return e; }
+      if (l.recording) {
+        l.cut(true);
+      } else {
+        // x = (x + mixer) + MoE(norm(x + mixer)) for the rows; rows past `rows` hold stale values and are ignored
+        int e = ep.run_layer(L, true, nullptr);
+        if (e) { s->err = "prefill: " + ep.err; return e; }
+      }
+    }
+    if (verify && !l.status) {
+      // every row's greedy prediction: final norm, LM head over the rows, argmax per row (no control advance)
+      l.launch("RmsNormQuant", (uint32_t)rows, (const float *)ep.Res, (const float *)nullptr, (float *)nullptr,
+               (const float *)m->final_norm, (float *)nullptr, p->Q8, p->SQ, (int32_t)H, eps);
+      l.gemm(m->tensor("lm_head.weight"), p->Q8, p->SQ, p->Logits, H, rows);
+      l.launch("BatchArgmax", (uint32_t)rows, (const float *)p->Logits, p->OutT, p->Ctrl, (int32_t)c.vocab, (int32_t)0);
+    }
+    if (l.recording) l.cut(false);
+    return l.status;
+  };
+  std::vector<int32_t> ctrl((size_t)p->rows_cap * 4);
+  const bool use_lists = verify && n == p->rows_cap;
+  if (use_lists && p->vlists.empty()) {
+    Launcher rec{p};
+    rec.recording = true;
+    rec.cut(true);
+    int e = pass(rec, n);
+    if (e || (int)p->vlists.size() != c.layers + 1) {
+      if (!e) { s->err = "internal: verification lists"; e = 3; }
+      for (ainfer_list_t q : p->vlists) ainfer_list_destroy(q);
+      p->vlists.clear();
+      return e;
     }
   }
-  if (verify && !l.status) {
-    // every row's greedy prediction: final norm, LM head over the rows, argmax per row (no control advance)
-    l.launch("RmsNormQuant", (uint32_t)n, (const float *)ep.Res, (const float *)nullptr, (float *)nullptr, (const float *)m->final_norm,
-             (float *)nullptr, p->Q8, p->SQ, (int32_t)H, eps);
-    l.gemm(m->tensor("lm_head.weight"), p->Q8, p->SQ, p->Logits, H, n);
-    l.launch("BatchArgmax", (uint32_t)n, (const float *)p->Logits, p->OutT, p->Ctrl, (int32_t)c.vocab, (int32_t)0);
+  for (int t0 = 0; t0 < n; t0 += p->rows_cap) {
+    const int rows = std::min(p->rows_cap, n - t0);
+    for (int i = 0; i < rows; ++i) {
+      ctrl[4 * i] = tokens[t0 + i];
+      ctrl[4 * i + 1] = start_pos + t0 + i;
+      ctrl[4 * i + 2] = start_pos + t0 + i + 1;
+      ctrl[4 * i + 3] = -1;
+    }
+    if (ainfer_memcpy_h2d(s->dev, p->Ctrl, ctrl.data(), (size_t)rows * 16) != AINFER_OK) { s->err = ainfer_last_error(s->dev); return 1; }
+    if (use_lists) {
+      for (int L = 0; L < c.layers; ++L) {
+        if (ainfer_list_execute(p->vlists[L]) != AINFER_OK) { s->err = ainfer_last_error(s->dev); return 1; }
+        int e = ep.run_layer(L, true, nullptr);
+        if (e) { s->err = "prefill: " + ep.err; return e; }
+      }
+      if (ainfer_list_execute(p->vlists[c.layers]) != AINFER_OK) { s->err = ainfer_last_error(s->dev); return 1; }
+    } else {
+      Launcher l{p};
+      int e = pass(l, rows);
+      if (e) return e;
+    }
   }
-  if (l.status) return l.status;
   if (verify) {
     if (ainfer_memcpy_d2h(s->dev, predictions, p->OutT, (size_t)n * 4) != AINFER_OK) { s->err = ainfer_last_error(s->dev); return 1; }
   } else if (ainfer_sync(s->dev, UINT64_MAX) != AINFER_OK) { s->err = ainfer_last_error(s->dev); return 1; }

@@ -271,9 +271,38 @@ def main(argv=None):
     pf.add_argument("--prompt", type=int, default=512)
     pf.add_argument("--steps", type=int, default=8)
     pf.add_argument("--no-loop", action="store_true", help="skip the token-by-token run (no comparison)")
+    mt = sub.add_parser("mtp", help="draft / batched-verify rounds against plain greedy decoding")
+    mt.add_argument("--model", default="mini-mtp")
+    mt.add_argument("--prompt", type=int, default=32)
+    mt.add_argument("--gen", type=int, default=32)
+    mt.add_argument("--draft-k", type=int, default=3)
     args = ap.parse_args(argv)
     dev = cuda_abi.Device(0)
-    if args.cmd == "prefill":
+    if args.cmd == "mtp":
+        import time
+        model = runtime.Model(dev, f"synth:{args.model}:seed=0")
+        V, P, G = model.config["vocab"], args.prompt, args.gen
+        prompt = np.random.default_rng(11).integers(0, V, P).astype(np.int32)
+        a = runtime.Session(model, P + G + 16, runtime.Session.PERSISTENT)
+        a.generate(prompt, 2)
+        a.reset(); dev.sync()
+        t0 = time.time(); want = a.generate(prompt, G); t_plain = time.time() - t0
+        t0 = time.time(); a.reset(); a.generate(prompt, 1); t_prompt = time.time() - t0
+        b = runtime.Session(model, P + G + 16, runtime.Session.PERSISTENT)
+        b.generate_mtp(prompt, 2 * args.draft_k + 4, draft_k=args.draft_k)   # creates the verifier and records its lists (untimed)
+        b.reset(); dev.sync()
+        t0 = time.time(); got, st = b.generate_mtp(prompt, G, draft_k=args.draft_k); t_mtp = time.time() - t0
+        t0 = time.time(); b.reset(); b.generate_mtp(prompt, 1, draft_k=args.draft_k); t_mprompt = time.time() - t0
+        gen_plain, gen_mtp = t_plain - t_prompt, t_mtp - t_mprompt
+        print(json.dumps({"op": "mtp", "model": args.model, "prompt": P, "generated": G, "draft_k": args.draft_k,
+                          "same_tokens": got.tolist() == want.tolist(), "stats": st,
+                          "plain_ms_per_token": gen_plain * 1000 / max(G - 1, 1),
+                          "round_ms": gen_mtp * 1000 / max(st["rounds"], 1),
+                          "rows_per_round": args.draft_k + 1,
+                          "plain_ms_for_the_same_rows": gen_plain * 1000 / max(G - 1, 1) * (args.draft_k + 1),
+                          "mtp_tokens_per_s": (G - 1) / gen_mtp, "plain_tokens_per_s": (G - 1) / gen_plain}), flush=True)
+        a.close(); b.close(); model.close()
+    elif args.cmd == "prefill":
         import time
         model = runtime.Model(dev, f"synth:{args.model}:seed=0")
         V, P = model.config["vocab"], args.prompt
