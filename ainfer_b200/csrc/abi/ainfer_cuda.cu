@@ -73,6 +73,8 @@ struct ainfer_device_s {
   int sm_count = 0;
   volatile unsigned int *fault_word = nullptr;  // host view of the stream fault word of this GPU
   bool early_launch = true;  // recorded lists use programmatic dependencies (AINFER_NO_EARLY_LAUNCH=1 turns it off)
+  std::map<void *, void *> over_aligned;  // blocks handed out above cudaMalloc's 256-byte alignment -> the block to free
+  std::mutex alloc_mu;
 };
 
 // One host-mapped fault word per GPU for the life of the process: kernels that
@@ -255,17 +257,32 @@ int ainfer_mem_alloc(ainfer_device_t dev, size_t bytes, size_t align, void **out
   if (!dev || !out) return AINFER_ERR_INVALID;
   if (align > 4096 || (align & (align - 1))) return fail(dev, AINFER_ERR_INVALID, "bad alignment");
   CU(dev, cudaSetDevice(dev->ordinal));
-  CU(dev, cudaMalloc(out, bytes ? bytes : 1));  // cudaMalloc returns >= 256-byte aligned blocks
-  if (align > 256 && ((uintptr_t)*out & (align - 1))) {
-    cudaFree(*out);
-    *out = nullptr;
-    return fail(dev, AINFER_ERR_INVALID, "allocator returned a block below the asked alignment");
+  if (align <= 256) {
+    CU(dev, cudaMalloc(out, bytes ? bytes : 1));  // cudaMalloc returns >= 256-byte aligned blocks
+    return AINFER_OK;
   }
+  // a larger alignment: allocate with slack and hand out the aligned address inside the block
+  void *raw = nullptr;
+  CU(dev, cudaMalloc(&raw, (bytes ? bytes : 1) + align));
+  void *al = (void *)(((uintptr_t)raw + align - 1) & ~(uintptr_t)(align - 1));
+  if (al != raw) {
+    std::lock_guard<std::mutex> g(dev->alloc_mu);
+    dev->over_aligned[al] = raw;
+  }
+  *out = al;
   return AINFER_OK;
 }
 int ainfer_mem_free(ainfer_device_t dev, void *ptr) {
   if (!dev) return AINFER_ERR_INVALID;
   CU(dev, cudaSetDevice(dev->ordinal));
+  {
+    std::lock_guard<std::mutex> g(dev->alloc_mu);
+    auto it = dev->over_aligned.find(ptr);
+    if (it != dev->over_aligned.end()) {
+      ptr = it->second;
+      dev->over_aligned.erase(it);
+    }
+  }
   CU(dev, cudaFree(ptr));
   return AINFER_OK;
 }

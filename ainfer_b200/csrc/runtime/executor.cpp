@@ -719,6 +719,45 @@ int session_step(Session *s, int token, int pos, int *out_token) {
   return check_step_error(s);
 }
 
+int session_sample(Session *s, float temp, int top_k, float top_p, float rep_penalty, const int *seen, int nseen,
+                   uint64_t *rng, int *out_token) {
+  const int V = s->m->cfg.vocab;
+  if (nseen < 0 || nseen > s->max_ctx) { s->err = "usage: more seen ids than the context holds"; return 2; }
+  if (!s->samp_work) {
+    if (salloc(s, (size_t)V, &s->samp_work) || salloc(s, (size_t)V, &s->samp_mark) || salloc(s, (size_t)s->max_ctx, &s->samp_seen) ||
+        salloc(s, (size_t)2, &s->samp_io))
+      return 1;
+  }
+  if (nseen > 0) S_CHECK(ainfer_memcpy_h2d(s->dev, s->samp_seen, seen, (size_t)nseen * 4));
+  S_CHECK(ainfer_memcpy_h2d(s->dev, s->samp_io, rng, 8));
+  auto it = s->kernels.find("SampleToken");
+  ainfer_kernel_t k = nullptr;
+  if (it != s->kernels.end()) k = it->second;
+  else {
+    if (ainfer_kernel_get(s->dev, "SampleToken", &k) != AINFER_OK) { s->err = "entry SampleToken not found"; return 1; }
+    s->kernels["SampleToken"] = k;
+  }
+  const float *logits = s->Logits;
+  const int32_t *dseen = s->samp_seen;
+  unsigned long long *drng = (unsigned long long *)s->samp_io;
+  int32_t *dtok = (int32_t *)(s->samp_io + 1);
+  float *probs = nullptr;
+  int32_t *ctrl = nullptr;
+  int32_t v = V, ns = nseen, tk = top_k;
+  uint32_t i = 0;
+  auto set = [&](size_t size, const void *p) { return ainfer_kernel_set_arg(k, i++, size, p); };
+  S_CHECK(set(sizeof logits, &logits)); S_CHECK(set(sizeof dseen, &dseen)); S_CHECK(set(sizeof s->samp_work, &s->samp_work));
+  S_CHECK(set(sizeof s->samp_mark, &s->samp_mark)); S_CHECK(set(sizeof drng, &drng)); S_CHECK(set(sizeof dtok, &dtok));
+  S_CHECK(set(sizeof probs, &probs)); S_CHECK(set(sizeof ctrl, &ctrl)); S_CHECK(set(4, &v)); S_CHECK(set(4, &ns));
+  S_CHECK(set(4, &temp)); S_CHECK(set(4, &tk)); S_CHECK(set(4, &top_p)); S_CHECK(set(4, &rep_penalty));
+  S_CHECK(ainfer_kernel_launch(s->dev, k, 1));
+  uint64_t back[2];
+  S_CHECK(ainfer_memcpy_d2h(s->dev, back, s->samp_io, 16));
+  *rng = back[0];
+  *out_token = (int)(int32_t)(back[1] & 0xFFFFFFFFu);
+  return 0;
+}
+
 int session_mtp_draft(Session *s, int next_token, int pos, int from_trunk, int *draft_token) {
   if (!s->mtp_list) { s->err = "usage: the model has no MTP head"; return 2; }
   if (pos < 0 || pos >= s->max_ctx) {

@@ -90,6 +90,8 @@ struct Session {
   int max_chunks = 0;
   int argmax_parts = 0;
   Prefill *prefill = nullptr;   // created on the first ainfer_session_prefill
+  // device sampler scratch (created on first use): probabilities, marks, seen ids, {rng state, token}
+  double *samp_work = nullptr; unsigned char *samp_mark = nullptr; int32_t *samp_seen = nullptr; uint64_t *samp_io = nullptr;
   Prefill *verifier = nullptr;  // rows of the MTP loop's batched verification (created on first use)
 };
 
@@ -110,6 +112,10 @@ int session_reset(Session *s);
 // One token: control = {token, pos, pos+1, -1}, replay, read the selected
 // token back (4 bytes). Returns 0 or a reference exit code (3 = context overflow).
 int session_step(Session *s, int token, int pos, int *out_token);
+// Samples from the last step's logits on the device (kernel SampleToken); reads back the token and
+// the advanced xorshift64* state.
+int session_sample(Session *s, float temp, int top_k, float top_p, float rep_penalty, const int *seen, int nseen,
+                   uint64_t *rng, int *out_token);
 // Greedy loop: P prompt ids starting at start_pos (no logits until the last
 // prompt token, decode_l0.cpp:771), then G generated tokens; control advances
 // on the device, tokens are read back once at the end. elapsed_ms (optional)

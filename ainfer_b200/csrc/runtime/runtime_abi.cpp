@@ -185,6 +185,13 @@ int ainfer_session_logits(ainfer_session_t s, float *host_out) {
     return set_err(1, ainfer_last_error(s->s->dev));
   return 0;
 }
+int ainfer_session_sample(ainfer_session_t h, const ainfer_sample_params *p, const int *seen, int nseen, uint64_t *rng,
+                          int *out_token) {
+  if (!h || !p || !rng || !out_token || (nseen > 0 && !seen)) return set_err(2, "usage: null argument");
+  Session *s = h->s;
+  int r = session_sample(s, p->temp, p->top_k, p->top_p, p->rep_penalty, seen, nseen, rng, out_token);
+  return set_err(r, s->err);
+}
 int ainfer_session_mtp_draft(ainfer_session_t s, int next_token, int pos, int from_trunk, int *draft_token) {
   if (!s) return 2;
   int r = session_mtp_draft(s->s, next_token, pos, from_trunk, draft_token);

@@ -45,6 +45,7 @@ SIGNATURES = {
     "ainfer_session_prefill": (_i, [_vp, C.POINTER(_i), _i, _i]),
     "ainfer_session_generate": (_i, [_vp, C.POINTER(_i), _i, _i, _i, C.POINTER(_i), C.POINTER(C.c_float)]),
     "ainfer_session_logits": (_i, [_vp, _vp]),
+    "ainfer_session_sample": (_i, [_vp, C.POINTER(SampleParams), _vp, _i, C.POINTER(_u64), C.POINTER(_i)]),
     "ainfer_session_launches_per_token": (_i, [_vp, C.POINTER(_u64)]),
     "ainfer_session_mtp_draft": (_i, [_vp, _i, _i, _i, C.POINTER(_i)]),
     "ainfer_session_mtp_logits": (_i, [_vp, _vp]),
@@ -199,6 +200,15 @@ class Session:
         out = np.zeros(V, np.float32)
         _check(load().ainfer_session_logits(self.h, out.ctypes.data))
         return out
+
+    def sample(self, temp, top_k=0, top_p=1.0, rep_penalty=1.0, seen=(), rng=1):
+        """Samples from the last step's logits on the device. Returns (token, new rng state)."""
+        p = SampleParams(temp, top_k, top_p, rep_penalty, 0)
+        seen = np.ascontiguousarray(seen, np.int32)
+        state, tok = C.c_uint64(rng), C.c_int()
+        _check(load().ainfer_session_sample(self.h, C.byref(p), seen.ctypes.data if seen.size else None, seen.size,
+                                            C.byref(state), C.byref(tok)))
+        return tok.value, state.value
 
     def prefill(self, tokens, start_pos=0):
         """Advances the state over the tokens in chunks of up to 64 rows (no logits)."""

@@ -25,6 +25,7 @@
 extern "C" {
 #endif
 
+struct ainfer_sample_params;
 typedef struct ainfer_model_s *ainfer_model_t;
 typedef struct ainfer_session_s *ainfer_session_t;
 
@@ -112,6 +113,12 @@ int ainfer_session_mtp_logits(ainfer_session_t s, float *host_out);
  * exactly ainfer_session_generate's. stats[3] = {rounds, drafted, accepted}. */
 int ainfer_session_generate_mtp(ainfer_session_t s, const int *prompt, int P, int G, int start_pos, int draft_k,
                                 int *out_tokens, int *stats);
+/* Samples from the last step's logits ON THE DEVICE (kernel SampleToken: the semantics of
+ * tools/sample/sampler.h:60-158, see ainfer_sample_token below) and reads back the token and the
+ * advanced RNG state (12 bytes instead of 4 V). seen / nseen: ids for the repetition penalty
+ * (host array, may be NULL). *rng is the caller's xorshift64* state, as for ainfer_sample_token. */
+int ainfer_session_sample(ainfer_session_t s, const struct ainfer_sample_params *p, const int *seen, int nseen,
+                          uint64_t *rng, int *out_token);
 /* Copies the last step's logits to the host (V floats). */
 int ainfer_session_logits(ainfer_session_t s, float *host_out);
 int ainfer_session_launches_per_token(ainfer_session_t s, uint64_t *launches);
