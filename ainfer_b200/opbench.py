@@ -135,7 +135,12 @@ def gemm_a16_once(dev, N, K, M, reps=20):
             "groups": groups, "buffers": nbuf, "flops": 2.0 * M * N * K, "tflops": 2.0 * M * N * K / ms / 1e9}
 
 
-def gemm_tc_once(dev, N, K, M, reps=20, groups=0):
+def gemv_multi_once(dev, N, K, M, reps=20, groups=0):
+    """Int4GemvA8Multi (W4A8, 1 <= M <= 8, weights streamed once, dp4a) on one shape; same protocol as gemm_tc_once."""
+    return gemm_tc_once(dev, N, K, M, reps, groups, kernel="Int4GemvA8Multi")
+
+
+def gemm_tc_once(dev, N, K, M, reps=20, groups=0, kernel="Int4GemmA8Tc"):
     """Int4GemmA8Tc (W4A8 on tcgen05, 1 <= M <= 64, weights streamed once) on one shape: recorded list
     rotating over enough weight buffers to exceed L2, timed as a whole on the device."""
     wbytes = N * K // 2 + N * K // 128 * 2
@@ -150,9 +155,11 @@ def gemm_tc_once(dev, N, K, M, reps=20, groups=0):
         k.set_arg(0, dP); k.set_arg(1, dS); k.set_arg(2, synth_key(b, f"opbench.tc.{N}.{K}"), "u64")
         k.set_arg(3, N * K // 128, "u64"); k.set_arg(4, 0.02)
         k.launch(dev.info().sm_count * 8)
-        g = dev.kernel("Int4GemmA8Tc")
+        g = dev.kernel(kernel)
         g.set_args(dP, dS, xq, sq, dY, N, K, M, N)
         kernels.append(g); bufs.append((dP, dS, dY))
+    if kernel == "Int4GemvA8Multi":
+        groups = groups or min(-(-N // (256 // (K // 128))), dev.info().sm_count * 2)
     groups = groups or min((N + 127) // 128, dev.info().sm_count * 2)
     for i in range(3):
         kernels[i % nbuf].launch(groups)
@@ -170,7 +177,7 @@ def gemm_tc_once(dev, N, K, M, reps=20, groups=0):
         for p in t:
             dev.free(p)
     b = gemv_bytes(N, K, M)
-    return {"op": "int4_gemm_a8_tc", "M": M, "N": N, "K": K, "ms": ms, "gbs": b / ms / 1e6, "bytes": b,
+    return {"op": "int4_gemm_a8_tc" if kernel == "Int4GemmA8Tc" else "int4_gemv_a8_multi", "M": M, "N": N, "K": K, "ms": ms, "gbs": b / ms / 1e6, "bytes": b,
             "groups": groups, "buffers": nbuf, "flops": 2.0 * M * N * K, "tflops": 2.0 * M * N * K / ms / 1e9}
 
 
@@ -247,6 +254,7 @@ def main(argv=None):
     g.add_argument("--reps", type=int, default=20)
     g.add_argument("--sweep", action="store_true")
     g.add_argument("--a16", action="store_true", help="bf16 activations (Int4GemmA16, M up to 64) instead of W4A8")
+    g.add_argument("--multi", action="store_true", help="W4A8 for M up to 8 with the weights streamed once (Int4GemvA8Multi, dp4a)")
     g.add_argument("--tc", action="store_true", help="W4A8 on the tcgen05 tensor cores (Int4GemmA8Tc, M up to 64)")
     g.add_argument("--groups", type=int, default=0, help="thread groups per launch (default: by shape)")
     g.add_argument("--flush", action="store_true", help="time single launches after an L2 rewrite")
@@ -329,11 +337,15 @@ def main(argv=None):
         b.close(); model.close()
     elif args.cmd == "gemv":
         ms_ = (1, 2, 4, 8, 64) if (args.a16 or args.tc) else (1, 2, 4, 8)
+        if args.multi and not args.sweep and args.m > 8:
+            raise SystemExit("--multi takes M up to 8")
         shapes = ([(m, n, k) for (n, k) in [(512, 2048), (4096, 2048), (8192, 2048), (151936, 2048), (2048, 512)]
                    for m in ms_] if args.sweep else [(args.m, args.n, args.k)])
         for (m, n, k) in shapes:
             if args.tc:
                 r = gemm_tc_once(dev, n, k, m, args.reps, args.groups)
+            elif args.multi:
+                r = gemv_multi_once(dev, n, k, m, args.reps, args.groups)
             elif args.a16:
                 r = gemm_a16_once(dev, n, k, m, args.reps)
             else:
