@@ -133,15 +133,20 @@ struct EpGroupArgs {
   const unsigned char *Recv;  // dispatch buffer received (R slots)
   const ExpertW *Experts;     // the layer's table [E+1]
   int32_t *Sorted;            // [R*cap]: src << 16 | index in the source's slot, grouped by expert
-  EpTcGroup *GroupsGateUp;    // [2 * (experts_per_rank + 1)]: gate and up problem of every active expert
+  // Problems are listed by size: up to small_rows rows for the dp4a kernel that streams weights
+  // once (Int4GemvA8MultiGrouped), more for the tensor-core kernel (Int4GemmA8TcGrouped).
+  EpTcGroup *GroupsGateUp;    // [2 * (experts_per_rank + 1)]: gate and up problem of every active expert with few rows
   EpTcGroup *GroupsDown;      // [experts_per_rank + 1]
-  int32_t *Counts;            // [4]: items in total, gate/up problems, down problems, 0
+  EpTcGroup *GroupsGateUpL;   // the same for experts with many rows
+  EpTcGroup *GroupsDownL;
+  int32_t *Counts;            // [8]: items in total, gate/up and down problems (few rows), gate/up and down problems (many rows)
   int32_t world, rank, experts_per_rank, cap, I;
   uint32_t slot_bytes;
   // The shared expert of this rank's own rows rides in the same launches as one more problem:
   // its activations are rows [shared_row0, shared_row0 + shared_rows) of the grouped layout
   // (the owner's quantiser writes them there). shared_rows == 0: none.
   int32_t shared_row0, shared_rows, shared_expert;
+  int32_t small_rows;   // problems up to this many rows go to the first pair of lists (a large value: all of them)
 };
 // One block. Items are numbered (source rank, index) in ascending order; an item's row in the
 // grouped layout is the start of its expert's range plus the number of earlier items of the same
@@ -149,7 +154,7 @@ struct EpGroupArgs {
 __global__ void __launch_bounds__(1024) EpGroup(const EpGroupArgs a) {
   __shared__ short le[kEpMaxItems];          // local expert of every received item
   __shared__ int base[65];                   // first item number of every source
-  __shared__ int hist[1024], start[1024], active[1024];
+  __shared__ int hist[1024], start[1024], active[1024];   // active: index in its list, many-row experts offset by 1 << 20
   const int tid = threadIdx.x;
   if (tid == 0) {
     int s = 0;
@@ -172,29 +177,32 @@ __global__ void __launch_bounds__(1024) EpGroup(const EpGroupArgs a) {
   }
   __syncthreads();
   if (tid < 32) {   // exclusive scans over the experts (counts, and "has items" flags): one warp, chunks of 32
-    int run = 0, nact = 0;
+    int run = 0, nact = 0, nactl = 0;
     for (int e0 = 0; e0 < a.experts_per_rank; e0 += 32) {
       const int e = e0 + tid;
-      const int c = e < a.experts_per_rank ? hist[e] : 0, f = c > 0;
-      int sc = c, sf = f;
+      const int c = e < a.experts_per_rank ? hist[e] : 0, f = c > 0 && c <= a.small_rows, fl = c > a.small_rows;
+      int sc = c, sf = f, sl = fl;
 #pragma unroll
       for (int off = 1; off < 32; off <<= 1) {
-        const int vc = __shfl_up_sync(kFull, sc, off), vf = __shfl_up_sync(kFull, sf, off);
-        if (tid >= off) { sc += vc; sf += vf; }
+        const int vc = __shfl_up_sync(kFull, sc, off), vf = __shfl_up_sync(kFull, sf, off), vl = __shfl_up_sync(kFull, sl, off);
+        if (tid >= off) { sc += vc; sf += vf; sl += vl; }
       }
-      if (e < a.experts_per_rank) { start[e] = run + sc - c; active[e] = nact + sf - f; }
+      if (e < a.experts_per_rank) { start[e] = run + sc - c; active[e] = fl ? (1 << 20) + nactl + sl - fl : nact + sf - f; }
       run += __shfl_sync(kFull, sc, 31);
       nact += __shfl_sync(kFull, sf, 31);
+      nactl += __shfl_sync(kFull, sl, 31);
     }
     if (tid == 0) {
-      const int sh = a.shared_rows > 0 ? 1 : 0;
-      if (sh) {
+      const int sh = a.shared_rows > 0 && a.shared_rows <= a.small_rows ? 1 : 0, shl = a.shared_rows > a.small_rows ? 1 : 0;
+      if (sh || shl) {
         const ExpertW w = a.Experts[a.shared_expert];
-        a.GroupsGateUp[2 * nact] = EpTcGroup{w.gP, w.gS, a.shared_row0, a.shared_rows, 0, 0};
-        a.GroupsGateUp[2 * nact + 1] = EpTcGroup{w.uP, w.uS, a.shared_row0, a.shared_rows, a.I, 0};
-        a.GroupsDown[nact] = EpTcGroup{w.dP, w.dS, a.shared_row0, a.shared_rows, 0, 0};
+        EpTcGroup *gu = sh ? a.GroupsGateUp + 2 * nact : a.GroupsGateUpL + 2 * nactl, *gd = sh ? a.GroupsDown + nact : a.GroupsDownL + nactl;
+        gu[0] = EpTcGroup{w.gP, w.gS, a.shared_row0, a.shared_rows, 0, 0};
+        gu[1] = EpTcGroup{w.uP, w.uS, a.shared_row0, a.shared_rows, a.I, 0};
+        gd[0] = EpTcGroup{w.dP, w.dS, a.shared_row0, a.shared_rows, 0, 0};
       }
-      *reinterpret_cast<int4 *>(a.Counts) = make_int4(total, 2 * (nact + sh), nact + sh, 0);
+      *reinterpret_cast<int4 *>(a.Counts) = make_int4(total, 2 * (nact + sh), nact + sh, 2 * (nactl + shl));
+      *reinterpret_cast<int4 *>(a.Counts + 4) = make_int4(nactl + shl, 0, 0, 0);
     }
   }
   __syncthreads();
@@ -202,10 +210,12 @@ __global__ void __launch_bounds__(1024) EpGroup(const EpGroupArgs a) {
     const int c = hist[e];
     if (c > 0) {
       const ExpertW w = a.Experts[a.rank * a.experts_per_rank + e];
-      const int g = active[e];
-      a.GroupsGateUp[2 * g] = EpTcGroup{w.gP, w.gS, start[e], c, 0, 0};
-      a.GroupsGateUp[2 * g + 1] = EpTcGroup{w.uP, w.uS, start[e], c, a.I, 0};
-      a.GroupsDown[g] = EpTcGroup{w.dP, w.dS, start[e], c, 0, 0};
+      const bool large = active[e] >= (1 << 20);
+      const int g = active[e] & ((1 << 20) - 1);
+      EpTcGroup *gu = (large ? a.GroupsGateUpL : a.GroupsGateUp) + 2 * g, *gd = (large ? a.GroupsDownL : a.GroupsDown) + g;
+      gu[0] = EpTcGroup{w.gP, w.gS, start[e], c, 0, 0};
+      gu[1] = EpTcGroup{w.uP, w.uS, start[e], c, a.I, 0};
+      gd[0] = EpTcGroup{w.dP, w.dS, start[e], c, 0, 0};
     }
   }
   for (int it = tid; it < total; it += blockDim.x) {
@@ -336,8 +346,8 @@ AINFER_REGISTER(EpPlan, EpPlanArgs, 1024, 0, 0, nullptr, F(SelIdx), F(Send), F(I
 AINFER_REGISTER(EpPack, EpPackArgs, 128, 1, 0, nullptr, F(Q8), F(SQ), F(ItemDest), F(Send), F(k), F(H), F(cap), F(slot_bytes));
 #undef F
 #define F(f) AINFER_ARG(EpGroupArgs, f)
-AINFER_REGISTER(EpGroup, EpGroupArgs, 1024, 0, 0, nullptr, F(Recv), F(Experts), F(Sorted), F(GroupsGateUp), F(GroupsDown), F(Counts), F(world),
-                F(rank), F(experts_per_rank), F(cap), F(I), F(slot_bytes), F(shared_row0), F(shared_rows), F(shared_expert));
+AINFER_REGISTER(EpGroup, EpGroupArgs, 1024, 0, 0, nullptr, F(Recv), F(Experts), F(Sorted), F(GroupsGateUp), F(GroupsDown), F(GroupsGateUpL), F(GroupsDownL), F(Counts), F(world),
+                F(rank), F(experts_per_rank), F(cap), F(I), F(slot_bytes), F(shared_row0), F(shared_rows), F(shared_expert), F(small_rows));
 #undef F
 #define F(f) AINFER_ARG(EpGatherArgs, f)
 AINFER_REGISTER(EpGather, EpGatherArgs, 128, 1, 0, nullptr, F(Recv), F(Sorted), F(Counts), F(XQ), F(SQ), F(H), F(cap), F(slot_bytes));

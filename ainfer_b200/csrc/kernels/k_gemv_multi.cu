@@ -179,12 +179,199 @@ __global__ void __launch_bounds__(kMvThreads, 2) Int4GemvA8Multi(const Int4GemvA
   }
 }
 
+// ---- grouped form: a list of problems of one shape, each with at most 8 activation rows ----
+// Problem i has its own weights and its own range of activation / output rows (an expert and the
+// tokens routed to it); list and length live in device memory. Tiles of all problems form one
+// sequence (problem-major) that is dealt to the blocks in contiguous ranges; a block restages the
+// activations when its range enters another problem. Problems with more than 8 rows are not for
+// this kernel (the caller gives them to the tensor-core form): they are skipped.
+struct MvGroup {           // = the tensor-core form's problem record
+  const uint8_t *P;
+  const uint16_t *S;
+  int32_t x_row0, M, y_col, pad;
+};
+static_assert(sizeof(MvGroup) == 32, "problem record");
+struct Int4GemvA8MultiGroupedArgs {
+  const MvGroup *Groups;
+  const int32_t *NGroups;
+  const int8_t *XQ;
+  const float *SQ;
+  float *Y;
+  int32_t N, K, ldy;
+};
+
+__global__ void __launch_bounds__(kMvThreads, 2) Int4GemvA8MultiGrouped(const Int4GemvA8MultiGroupedArgs a) {
+  __shared__ unsigned long long full[kMvStages], empty[kMvStages];
+  __shared__ uint32_t s_fail;
+  constexpr int MB = 8;
+  const int tid = threadIdx.x, K = a.K, G = K >> 7, RPI = 256 / G;
+  unsigned char *ring = mv_smem + mv_round128(staged4_bytes(K, MB)) + mv_round128(mv_t_floats(K, MB) * 4u);
+  float *T = reinterpret_cast<float *>(mv_smem + mv_round128(staged4_bytes(K, MB)));
+  if (tid == 0) {
+    for (int s = 0; s < kMvStages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 8); }
+    s_fail = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  const int tpg = (a.N + RPI - 1) / RPI;               // tiles per problem
+  const int ntiles = __ldg(a.NGroups) * tpg;
+  const int t0 = (int)((long)ntiles * blockIdx.x / gridDim.x), t1 = (int)((long)ntiles * (blockIdx.x + 1) / gridDim.x);
+  const bool bulk_scales = G >= 8;
+  const size_t row_bytes = (size_t)(K >> 1);
+  auto load_group = [&](int gi) {
+    union { uint4 q[2]; MvGroup g; } u;
+    const uint4 *p = reinterpret_cast<const uint4 *>(a.Groups + gi);
+    u.q[0] = __ldg(p); u.q[1] = __ldg(p + 1);
+    return u.g;
+  };
+  if (tid >= kMvCons) {
+    if (tid == kMvCons) {
+      uint32_t st = 0, ph = 0, issued = 0;
+      int cur = -1;
+      MvGroup gr{};
+      bool ok = 256 % G == 0;
+      for (int t = t0; t < t1 && ok; ++t) {
+        const int gi = t / tpg, tg = t - gi * tpg;
+        if (gi != cur) {
+          gr = load_group(gi);
+          cur = gi;
+          if ((((uintptr_t)gr.P | (bulk_scales ? (uintptr_t)gr.S : 0)) & 15u) != 0) { ok = false; break; }
+        }
+        if (gr.M > MB) continue;   // not this kernel's problem: no tile is produced, the consumers skip it too
+        if (issued >= (uint32_t)kMvStages && !mv_wait(&empty[st], ph ^ 1u, &s_fail)) break;
+        const int rows = a.N - tg * RPI < RPI ? a.N - tg * RPI : RPI;
+        const uint32_t wb = (uint32_t)(rows * row_bytes), sb = bulk_scales ? (uint32_t)(rows * G * 2) : 0u;
+        unsigned char *dst = ring + st * kMvStride;
+        mbar_arrive_expect(&full[st], wb + sb);
+        bulk_g2s(dst, gr.P + (size_t)tg * RPI * row_bytes, wb, &full[st]);
+        if (sb) bulk_g2s(dst + kMvTile, gr.S + (size_t)tg * RPI * G, sb, &full[st]);
+        ++issued;
+        if (++st == kMvStages) { st = 0; ph ^= 1u; }
+      }
+      if (!ok) {
+        s_fail = 1;
+        if (g_stream_fault_word) *reinterpret_cast<volatile unsigned int *>(g_stream_fault_word) = 2;
+      }
+    }
+    return;
+  }
+  const int g = tid % G, rt = tid / G, lane = tid & 31;
+  const int rot = (tid >> 1) & 3;
+  const uint32_t ring_a = smem_addr(ring), lane_off = (uint32_t)tid * 64u;
+  const int R = 2 * RPI, TS = R + 1;
+  uint32_t *xw = reinterpret_cast<uint32_t *>(mv_smem);
+  uint32_t st = 0, ph = 0;
+  int cur = -1;
+  MvGroup gr{};
+  int M = 0;
+  float *sqs = reinterpret_cast<float *>(mv_smem);
+#pragma unroll 1
+  for (int t = t0; t < t1;) {
+    const int gi = t / tpg, tg = t - gi * tpg;
+    if (gi != cur) {
+      gr = load_group(gi);
+      cur = gi;
+      M = gr.M;
+      if (M <= MB) {
+        // restage this problem's activations (no consumer still reads the previous problem's: the
+        // barrier that ended the previous pair is behind every lane)
+        sqs = reinterpret_cast<float *>(mv_smem + (size_t)M * K);
+        const int8_t *xq = a.XQ + (size_t)gr.x_row0 * K;
+        for (int i = tid; i < M * (K / 8); i += kMvCons) {
+          const int m = i / (K / 8), pc = i % (K / 8);
+          const uint2 v = __ldcg(reinterpret_cast<const uint2 *>(xq + (size_t)m * K + (size_t)pc * 8));
+          xw[staged4_word(K, m, pc, 0)] = __byte_perm(v.x, v.y, 0x6420);
+          xw[staged4_word(K, m, pc, 1)] = __byte_perm(v.x, v.y, 0x7531);
+        }
+        for (int i = tid; i < M * G; i += kMvCons) sqs[i] = __ldcg(a.SQ + (size_t)gr.x_row0 * G + i);
+        mv_cons_sync();
+      }
+    }
+    if (M > MB) { t = (gi + 1) * tpg; continue; }   // skip the whole problem
+    const bool second = tg + 1 < tpg && t + 1 < t1;  // the pair's second tile: same problem, inside this block's range
+    uint32_t w[2][32];
+    float sc[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      sc[u] = 0.0f;
+      if (u == 0 || second) {
+        const bool ok = mv_wait(&full[st], ph, &s_fail);
+        const uint32_t base = ring_a + st * kMvStride;
+#pragma unroll
+        for (int s = 0; s < 4; ++s) {
+          uint4 p = make_uint4(0, 0, 0, 0);
+          if (ok) p = lds128(base + lane_off + (uint32_t)(((s + rot) & 3) << 4));
+          w[u][8 * s + 0] = (p.x * 16u) & 0xF0F0F0F0u; w[u][8 * s + 1] = p.x & 0xF0F0F0F0u;
+          w[u][8 * s + 2] = (p.y * 16u) & 0xF0F0F0F0u; w[u][8 * s + 3] = p.y & 0xF0F0F0F0u;
+          w[u][8 * s + 4] = (p.z * 16u) & 0xF0F0F0F0u; w[u][8 * s + 5] = p.z & 0xF0F0F0F0u;
+          w[u][8 * s + 6] = (p.w * 16u) & 0xF0F0F0F0u; w[u][8 * s + 7] = p.w & 0xF0F0F0F0u;
+        }
+        const int row = (tg + u) * RPI + rt;
+        if (row < a.N) {
+          const uint32_t raw = bulk_scales && ok ? lds_u16(base + kMvTile + tid * 2) : (uint32_t)__ldg(gr.S + (size_t)row * G + g);
+          sc[u] = __uint_as_float(raw << 16);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[st]);
+        if (++st == kMvStages) { st = 0; ph ^= 1u; }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) w[u][i] = 0u;
+      }
+    }
+    const uint4 *xg = reinterpret_cast<const uint4 *>(mv_smem) + g;
+#pragma unroll 1
+    for (int m = 0; m < M; ++m) {
+      const uint4 *xv = xg + (size_t)m * 8 * G;
+      const float sqg = sqs[m * G + g];
+      int d0 = 0, d1 = 0;
+#pragma unroll
+      for (int s = 0; s < 4; ++s) {
+        const int j = (s + rot) & 3;
+        const uint4 xa = xv[(2 * j) * G], xb = xv[(2 * j + 1) * G];
+        d0 = __dp4a((int)w[0][8 * s + 0], (int)xa.x, d0); d0 = __dp4a((int)w[0][8 * s + 1], (int)xa.y, d0);
+        d0 = __dp4a((int)w[0][8 * s + 2], (int)xa.z, d0); d0 = __dp4a((int)w[0][8 * s + 3], (int)xa.w, d0);
+        d0 = __dp4a((int)w[0][8 * s + 4], (int)xb.x, d0); d0 = __dp4a((int)w[0][8 * s + 5], (int)xb.y, d0);
+        d0 = __dp4a((int)w[0][8 * s + 6], (int)xb.z, d0); d0 = __dp4a((int)w[0][8 * s + 7], (int)xb.w, d0);
+        d1 = __dp4a((int)w[1][8 * s + 0], (int)xa.x, d1); d1 = __dp4a((int)w[1][8 * s + 1], (int)xa.y, d1);
+        d1 = __dp4a((int)w[1][8 * s + 2], (int)xa.z, d1); d1 = __dp4a((int)w[1][8 * s + 3], (int)xa.w, d1);
+        d1 = __dp4a((int)w[1][8 * s + 4], (int)xb.x, d1); d1 = __dp4a((int)w[1][8 * s + 5], (int)xb.y, d1);
+        d1 = __dp4a((int)w[1][8 * s + 6], (int)xb.z, d1); d1 = __dp4a((int)w[1][8 * s + 7], (int)xb.w, d1);
+      }
+      float *tm = T + ((size_t)m * G + g) * TS;
+      tm[rt] = ((float)(d0 >> 4) * sc[0]) * sqg;
+      tm[RPI + rt] = ((float)(d1 >> 4) * sc[1]) * sqg;
+    }
+    mv_cons_sync();
+    for (int i = tid; i < M * R; i += kMvCons) {
+      const int m = i / R, r = i % R;
+      const int row = tg * RPI + r;
+      if ((r < RPI || second) && row < a.N) {
+        const float *tr = T + (size_t)m * G * TS + r;
+        float acc = 0.0f;
+        for (int gg = 0; gg < G; ++gg) acc = acc + tr[gg * TS];
+        a.Y[(size_t)(gr.x_row0 + m) * a.ldy + gr.y_col + row] = acc;
+      }
+    }
+    mv_cons_sync();
+    t += second ? 2 : 1;
+  }
+}
+
+static uint32_t mv_grouped_smem_fn(const void *args) {
+  return mv_smem_bytes(((const Int4GemvA8MultiGroupedArgs *)args)->K, 8);
+}
+
 static uint32_t mv_smem_fn(const void *args) {
   const Int4GemvA8MultiArgs *a = (const Int4GemvA8MultiArgs *)args;
   return mv_smem_bytes(a->K, a->M);
 }
 #define F(f) AINFER_ARG(Int4GemvA8MultiArgs, f)
 AINFER_REGISTER(Int4GemvA8Multi, Int4GemvA8MultiArgs, kMvThreads, 0, 0, mv_smem_fn, F(P), F(S), F(XQ), F(SQ), F(Y), F(N), F(K), F(M), F(ldy));
+#undef F
+#define F(f) AINFER_ARG(Int4GemvA8MultiGroupedArgs, f)
+AINFER_REGISTER(Int4GemvA8MultiGrouped, Int4GemvA8MultiGroupedArgs, kMvThreads, 0, 0, mv_grouped_smem_fn, F(Groups), F(NGroups), F(XQ), F(SQ), F(Y),
+                F(N), F(K), F(ldy));
 #undef F
 
 }  // namespace ainfer

@@ -50,6 +50,14 @@ struct Rec {   // appends launches to a list; arguments by index in member order
       return;
     }
     const int N = (int)t.entry->shape[0];
+    const int G = K / 128;
+    if (rows <= 8 && G <= 256 && 256 % G == 0) {
+      // few rows: the dp4a kernel streams the weights once and has a fraction of the tensor-core kernel's latency
+      const uint32_t tiles = (uint32_t)((N + 256 / G - 1) / (256 / G));
+      launch("Int4GemvA8Multi", std::min<uint32_t>(tiles, 2u * (uint32_t)b->sm_count), (const uint8_t *)t.data, (const uint16_t *)t.scales, XQ, SQ,
+             Y, (int32_t)N, (int32_t)K, (int32_t)rows, (int32_t)N);
+      return;
+    }
     const uint32_t tiles = (uint32_t)((N + 127) / 128);
     launch("Int4GemmA8Tc", std::min<uint32_t>(tiles, 2u * (uint32_t)b->sm_count), (const uint8_t *)t.data, (const uint16_t *)t.scales, XQ, SQ, Y,
            (int32_t)N, (int32_t)K, (int32_t)rows, (int32_t)N);

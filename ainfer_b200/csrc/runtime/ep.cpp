@@ -169,8 +169,9 @@ int EpMoe::create(DeviceModel *model, const void *id128, int rank_, int world_, 
   r |= alloc(&ItemDest, (size_t)cap * 4);
   r |= alloc(&Send, (size_t)world * slot_d); r |= alloc(&Recv, (size_t)world * slot_d);
   r |= alloc(&Ret, (size_t)world * slot_r); r |= alloc(&Back, (size_t)world * slot_r);
-  r |= alloc(&Sorted, (size_t)rows * 4); r |= alloc(&Counts, 16);
+  r |= alloc(&Sorted, (size_t)rows * 4); r |= alloc(&Counts, 32);
   r |= alloc(&GroupsGU, (size_t)2 * (epr + 1) * 32); r |= alloc(&GroupsD, (size_t)(epr + 1) * 32);
+  r |= alloc(&GroupsGUL, (size_t)2 * (epr + 1) * 32); r |= alloc(&GroupsDL, (size_t)(epr + 1) * 32);
   r |= alloc(&XQs, (size_t)(rows + n) * H); r |= alloc(&SQs, (size_t)(rows + n) * G * 4);
   r |= alloc(&GU, (size_t)(rows + shn) * 2 * I * 4); r |= alloc(&AQ, (size_t)(rows + shn) * I);
   r |= alloc(&ASQ, (size_t)(rows + shn) * (I / 128) * 4);
@@ -236,15 +237,28 @@ int EpMoe::record_layer(int L) {
     r.copy(Recv, Send, slot_d);
   }
   // ---- B: the experts of this rank on everything received ----
-  r.launch("EpGroup", 1u, (const unsigned char *)Recv, tab, Sorted, GroupsGU, GroupsD, Counts, (int32_t)world, (int32_t)rank, (int32_t)epr,
-           (int32_t)cap, (int32_t)I, slot_d, (int32_t)rows, (int32_t)(shared ? n : 0), (int32_t)E);
+  // experts with few rows: the dp4a kernel (weights once, a fraction of the tensor-core kernel's latency); the rest: tensor cores
+  const bool multi_ok = 256 % (H / 128) == 0 && 256 % (I / 128) == 0;
+  r.launch("EpGroup", 1u, (const unsigned char *)Recv, tab, Sorted, GroupsGU, GroupsD, GroupsGUL, GroupsDL, Counts, (int32_t)world, (int32_t)rank, (int32_t)epr,
+           (int32_t)cap, (int32_t)I, slot_d, (int32_t)rows, (int32_t)(shared ? n : 0), (int32_t)E,
+           (int32_t)(multi_ok ? 8 : (1 << 30)));
   r.launch("EpGather", (uint32_t)rows, (const unsigned char *)Recv, (const int32_t *)Sorted, (const int32_t *)Counts, XQs, SQs, (int32_t)H,
            (int32_t)cap, slot_d);
-  r.launch("Int4GemmA8TcGrouped", tc_blocks, (const void *)GroupsGU, (const int32_t *)(Counts + 1), (const int8_t *)XQs, (const float *)SQs, GU,
-           (int32_t)I, (int32_t)H, (int32_t)std::min(batch, 64), (int32_t)(2 * I));
+  const void *gu_tc = multi_ok ? GroupsGUL : GroupsGU, *d_tc = multi_ok ? GroupsDL : GroupsD;
+  const int32_t *ngu_tc = multi_ok ? Counts + 3 : Counts + 1, *nd_tc = multi_ok ? Counts + 4 : Counts + 2;
+  if (multi_ok)
+    r.launch("Int4GemvA8MultiGrouped", tc_blocks, (const void *)GroupsGU, (const int32_t *)(Counts + 1), (const int8_t *)XQs, (const float *)SQs,
+             GU, (int32_t)I, (int32_t)H, (int32_t)(2 * I));
+  if (batch > 8 || !multi_ok)
+    r.launch("Int4GemmA8TcGrouped", tc_blocks, gu_tc, ngu_tc, (const int8_t *)XQs, (const float *)SQs, GU, (int32_t)I, (int32_t)H,
+             (int32_t)std::min(batch, 64), (int32_t)(2 * I));
   r.launch("SiluQuantRows", (uint32_t)(rows + (shared ? n : 0)), (const float *)GU, (const int32_t *)Counts, AQ, ASQ, (int32_t)I, (int32_t)rows);
-  r.launch("Int4GemmA8TcGrouped", tc_blocks, (const void *)GroupsD, (const int32_t *)(Counts + 2), (const int8_t *)AQ, (const float *)ASQ, Y2,
-           (int32_t)H, (int32_t)I, (int32_t)std::min(batch, 64), (int32_t)H);
+  if (multi_ok)
+    r.launch("Int4GemvA8MultiGrouped", tc_blocks, (const void *)GroupsD, (const int32_t *)(Counts + 2), (const int8_t *)AQ, (const float *)ASQ, Y2,
+             (int32_t)H, (int32_t)I, (int32_t)H);
+  if (batch > 8 || !multi_ok)
+    r.launch("Int4GemmA8TcGrouped", tc_blocks, d_tc, nd_tc, (const int8_t *)AQ, (const float *)ASQ, Y2, (int32_t)H, (int32_t)I,
+             (int32_t)std::min(batch, 64), (int32_t)H);
   r.launch("EpScatter", (uint32_t)rows, (const float *)Y2, (const int32_t *)Sorted, (const int32_t *)Counts, Ret, (int32_t)H, slot_r);
   if (world > 1) {
     if (close(r) || new_list(&la)) return 1;

@@ -38,7 +38,7 @@ struct EpMoe {
   unsigned char *Send = nullptr, *Recv = nullptr, *Ret = nullptr, *Back = nullptr;
   // expert side
   int32_t *Sorted = nullptr, *Counts = nullptr;
-  void *GroupsGU = nullptr, *GroupsD = nullptr;
+  void *GroupsGU = nullptr, *GroupsD = nullptr, *GroupsGUL = nullptr, *GroupsDL = nullptr;   // problem lists: few rows / many rows
   int8_t *XQs = nullptr, *AQ = nullptr;
   float *SQs = nullptr, *GU = nullptr, *ASQ = nullptr, *Y2 = nullptr;
   float *Ysh = nullptr;   // shared expert's outputs of the owned rows (tail of Y2)

@@ -253,7 +253,7 @@ int ainfer_ep_buffer(ainfer_ep_t ep, const char *which, void **dptr, uint64_t *b
   else if (w == "sel_w") { *dptr = e.SelW; *bytes = (uint64_t)e.n * (e.k + 1) * 4; }
   else if (w == "near_gap") { *dptr = e.NearGap; *bytes = (uint64_t)e.n * 4; }
   else if (w == "router_bias") { *dptr = e.Bias; *bytes = (uint64_t)e.E * 4; }
-  else if (w == "counts") { *dptr = e.Counts; *bytes = 16; }
+  else if (w == "counts") { *dptr = e.Counts; *bytes = 32; }
   else return set_err(2, "unknown buffer: " + w);
   return 0;
 }

@@ -137,8 +137,9 @@ int ainfer_ep_unique_id(void *out128);
 int ainfer_ep_create(ainfer_model_t m, const void *id128, int rank, int world, int batch, int flags, ainfer_ep_t *out);
 int ainfer_ep_destroy(ainfer_ep_t ep);
 /* Device buffers: "res" [n][H] f32 input rows of this rank, "x" [n][H] f32 output, "sel_idx"
- * [n][k+1] i32, "sel_w" [n][k+1] f32, "near_gap" [n] f32, "router_bias" [E] f32, "counts" [4] i32
- * (items received, gate/up problems, down problems of the last layer run). */
+ * [n][k+1] i32, "sel_w" [n][k+1] f32, "near_gap" [n] f32, "router_bias" [E] f32, "counts" [8] i32
+ * of the last layer run (items received; gate/up and down problems of experts with at most 8 rows;
+ * gate/up and down problems of experts with more). */
 int ainfer_ep_buffer(ainfer_ep_t ep, const char *which, void **dptr, uint64_t *bytes);
 /* x = res + MoE(post_attention_norm_L(res)) for the owned rows, then res <- x (so that layers
  * chain); asynchronous on the device's queue. */

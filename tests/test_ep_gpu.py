@@ -49,7 +49,9 @@ def test_one_rank_equals_oracle(preset, batch, layer):
     assert np.array_equal(ep.read("sel_idx", np.int32).reshape(batch, k + 1)[:, :k], routed)
     assert np.array_equal(got, want)
     counts = ep.read("counts", np.int32)
-    assert counts[0] == batch * k and counts[1] == 2 * counts[2] and 1 <= counts[2] <= min(model.config["experts"], batch * k) + 1   # + the shared expert
+    n_down = counts[2] + counts[4]                       # experts with few rows + experts with many
+    assert counts[0] == batch * k and counts[1] + counts[3] == 2 * n_down
+    assert 1 <= n_down <= min(model.config["experts"], batch * k) + 1   # + the shared expert
     # a second layer through the same object, chained (res <- x), equals two oracle layers
     if model.config["text_layers"] > layer + 1:
         ep.write("res", res)
