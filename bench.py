@@ -295,6 +295,33 @@ def run_ep(args, dev, model, rank, world, dist):
             "expert_bytes_per_layer_all_ranks_upper": cfg["experts"] * 3 * H * I * (0.5 + 2.0 / 128)}
 
 
+def run_mtp(args, dev, model, ms_plain):
+    """MTP draft / batched-verify rounds (config 3's speculative loop) next to plain greedy decoding:
+    same tokens, the cost of a round (draft_k drafts + one pass of draft_k + 1 rows through the trunk +
+    rollback) against the same number of plain steps, and the acceptance needed to break even. With
+    seeded random weights no draft is ever accepted, so the headline stays the plain loop."""
+    from ainfer_b200 import runtime
+    cfg = model.config
+    if not cfg.get("mtp_layers"):
+        return {"skipped": "the model has no MTP head"}
+    K, P, G = 3, 64, 33
+    prompt = prompt_ids(cfg["vocab"], P, seed=5)
+    s = runtime.Session(model, P + 2 * G + 32, runtime.Session.PERSISTENT)
+    want = s.generate(prompt, G)
+    s.reset()
+    s.generate_mtp(prompt, 2 * K + 4, draft_k=K)          # creates the verifier and records its lists (untimed)
+    s.reset(); dev.sync()
+    t0 = time.time(); s.generate_mtp(prompt, 1, draft_k=K); t_prompt = time.time() - t0
+    s.reset(); dev.sync()
+    t0 = time.time(); got, st = s.generate_mtp(prompt, G, draft_k=K); t_all = time.time() - t0
+    s.close()
+    round_ms = (t_all - t_prompt) * 1000.0 / max(st["rounds"], 1)
+    return {"draft_k": K, "rows_per_verify_pass": K + 1, "generated": G, "tokens_equal_plain_greedy": got.tolist() == want.tolist(),
+            "stats": st, "round_ms": round_ms, "plain_ms_for_the_same_rows": ms_plain * (K + 1),
+            "tokens_per_round_to_break_even": round_ms / ms_plain,
+            "note": "seeded random weights: no draft is accepted, every round yields one token"}
+
+
 def run_batch(args, dev, model, rank, world, dist):
     """Batched decode (the metric's batch-64 half): BATCH sequences, each at a long context with an
     INT8 KV cache, advance one greedy token per step. Sequences are split over the ranks (state and
@@ -440,6 +467,12 @@ def run_ours(args):
         gen_ms, t_e2e = float(t[0]), float(t[1])
     ep_line = None if args.no_ep else run_ep(args, dev, model, rank, world, dist)
     batch_line = None if args.no_batch else run_batch(args, dev, model, rank, world, dist)
+    mtp_line = None
+    if rank == 0 and not args.no_mtp:
+        try:
+            mtp_line = run_mtp(args, dev, model, gen_ms / args.steps)
+        except Exception as e:
+            mtp_line = {"error": str(e)[:200]}
     if rank != 0:
         model.close(); dev.close()
         dist.destroy_process_group()
@@ -517,7 +550,7 @@ def run_ours(args):
         "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "int4xint8->int32, fp32 rescale", "data": "synthetic",
         "config": dict(workload_config(args.model, P, cfg),
-                       mtp="off", step=("one persistent cooperative launch per token (DecodeStep)" if persistent else
+                       mtp="off in the timed steps (measured separately in `mtp`)", step=("one persistent cooperative launch per token (DecodeStep)" if persistent else
                                         "one recorded list of stand-alone launches chained by programmatic dependencies"),
                        parallelism=("batch-1 steps: one independent replica per GPU (the batch-1 path has no exchange); "
                                     "the `ep` object times the sharded MoE layers") if world > 1 else "single GPU",
@@ -529,7 +562,7 @@ def run_ours(args):
         "repeats": {"windows": len(win_ms), "ms_per_step_median": float(np.median(win_ms)), "ms_per_step_min": float(np.min(win_ms)),
                     "ms_per_step_max": float(np.max(win_ms))},
         "clocks": clk, "roofline": roof, "gemv_sweep": sweep,
-        "cpu_baseline": cpu, "parity": parity, "ep": ep_line, "batch_decode": batch_line,
+        "cpu_baseline": cpu, "parity": parity, "ep": ep_line, "batch_decode": batch_line, "mtp": mtp_line,
         "timing": {"model_fill_s": t_load, "prompt_s": t_prompt, "prompt_by": "token-by-token decode" if args.loop_prompt else "chunked prefill (64 rows per pass)", "timed_wall_s": t_wall, "first_tokens": [int(t) for t in toks0[:8]]},
     }
     print(json.dumps(line))
@@ -551,6 +584,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="skip the isolated GEMV probes")
     ap.add_argument("--loop-prompt", action="store_true", help="run the prompt token by token instead of by chunked prefill")
+    ap.add_argument("--no-mtp", action="store_true", help="skip the MTP round measurement")
     ap.add_argument("--no-batch", action="store_true", help="skip the batched decode measurement")
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--batch-ctx", type=int, default=32768)
