@@ -6,8 +6,9 @@
 //   rows' RMSNorm + quantiser -> batched W4A8 GEMM on the tensor cores for every projection
 //   (weights cross HBM once per chunk, not once per token) -> DeltaNet: conv + SiLU over the rows,
 //   beta / decay, the recurrence with the state on the chip for the whole chunk, gated norm ->
-//   attention: per row, in order, the decode kernels (head norm + RoPE + INT8 append, chunked
-//   attention over the cache, merge) -> output projection -> the MoE block of the rows (router,
+//   attention: the decode kernels' bodies for all rows at once (head norm + RoPE + INT8 append of
+//   every row, then every row's chunked attention over the cache up to its own position, then the
+//   merges) -> output projection -> the MoE block of the rows (router,
 //   device permute by expert, grouped tensor-core expert GEMMs, slot-ordered combine; ep.cpp with
 //   one rank), which also performs the residual add.
 // Every row's arithmetic is the decode path's, so a prefilled session is bit-identical to one that
@@ -44,6 +45,7 @@ struct Prefill {
   int8_t *Q8 = nullptr; float *SQ = nullptr;     // [rows][maxK], [rows][maxK/128]
   float *Pq = nullptr, *Mx = nullptr, *Z = nullptr, *Br = nullptr, *Ar = nullptr, *Bt = nullptr, *Gt = nullptr, *O = nullptr;
   float *Q16 = nullptr, *K16 = nullptr, *V16 = nullptr;
+  float *Qn = nullptr, *Pm = nullptr, *Pse = nullptr, *Pacc = nullptr;   // per-row attention scratch
   std::map<std::string, ainfer_kernel_t> kernels;
 };
 
@@ -144,6 +146,8 @@ int prefill_create(Session *s, int rows_cap, bool verify, Prefill **out) {
   r |= palloc(p, (size_t)R * nV, &p->Bt); r |= palloc(p, (size_t)R * nV, &p->Gt);
   r |= palloc(p, (size_t)R * VD, &p->O);
   r |= palloc(p, (size_t)R * QN, &p->Q16); r |= palloc(p, (size_t)R * KN, &p->K16); r |= palloc(p, (size_t)R * KN, &p->V16);
+  r |= palloc(p, (size_t)R * AK, &p->Qn); r |= palloc(p, (size_t)R * c.q_heads * s->max_chunks, &p->Pm);
+  r |= palloc(p, (size_t)R * c.q_heads * s->max_chunks, &p->Pse); r |= palloc(p, (size_t)R * c.q_heads * s->max_chunks * c.head_dim, &p->Pacc);
   if (verify) {
     p->snap_s_stride = (size_t)c.n_lin() * nV * 128 * 128;
     p->snap_c_stride = (size_t)c.n_lin() * C * 3;
@@ -209,21 +213,19 @@ int prefill_run(Prefill *p, const int *tokens, int n, int start_pos, int *predic
         const size_t kv_off = (size_t)slot * s->max_ctx * nKV;
         int8_t *Kc = s->Kc + kv_off * D, *Vc = s->Vc + kv_off * D;
         uint16_t *Ks = s->Ks + kv_off, *Vs = s->Vs + kv_off;
-        const uint32_t g_split = (uint32_t)std::min(s->max_chunks * nKV, s->sm_count * 8);
-        for (int i = 0; i < rows && !l.status; ++i) {   // rows in order: row i attends to the rows before it
-          const int32_t *ci = p->Ctrl + 4 * i;
-          const float *q16 = p->Q16 + (size_t)i * QN;
-          l.launch("AttnPrep", (uint32_t)((nQ + 2 * nKV + 7) / 8), q16, (const float *)(p->K16 + (size_t)i * KN),
-                   (const float *)(p->V16 + (size_t)i * KN), (const float *)(m->q_norm + (size_t)slot * D),
-                   (const float *)(m->k_norm + (size_t)slot * D), (const float *)m->rope_cos, (const float *)m->rope_sin, ci, s->Qn, Kc,
-                   Vc, Ks, Vs, (int32_t)nQ, (int32_t)nKV, (int32_t)c.rotary_dim, (int32_t)s->max_ctx, eps);
-          l.launch("AttnSplit", g_split, (const float *)s->Qn, (const int8_t *)Kc, (const int8_t *)Vc, (const uint16_t *)Ks,
-                   (const uint16_t *)Vs, ci, s->Pm, s->Pse, s->Pacc, (int32_t)nQ, (int32_t)nKV, (int32_t)s->max_ctx,
-                   (int32_t)s->max_chunks);
-          l.launch("AttnCombine", (uint32_t)nQ, (const float *)s->Pm, (const float *)s->Pse, (const float *)s->Pacc, q16, ci,
-                   p->Q8 + (size_t)i * AK, p->SQ + (size_t)i * (AK / 128), (float *)nullptr, (int32_t)nQ, (int32_t)s->max_ctx,
-                   (int32_t)s->max_chunks);
-        }
+        // all rows at once, three launches: every row appends its K / V (its own cache position), then
+        // every row attends to the cache up to its own position (rows before it included: the appends of
+        // the whole pass are complete), then the merges. Per row the arithmetic is the decode kernels'.
+        auto attn = [&](const char *name, int groups) {
+          l.launch(name, (uint32_t)(rows * groups), (const float *)p->Q16, (const float *)p->K16, (const float *)p->V16,
+                   (const float *)(m->q_norm + (size_t)slot * D), (const float *)(m->k_norm + (size_t)slot * D), (const float *)m->rope_cos,
+                   (const float *)m->rope_sin, (const int32_t *)p->Ctrl, p->Qn, Kc, Vc, Ks, Vs, p->Pm, p->Pse, p->Pacc, p->Q8, p->SQ, (int32_t)nQ,
+                   (int32_t)nKV, (int32_t)c.rotary_dim, (int32_t)s->max_ctx, (int32_t)s->max_chunks, (int32_t)rows, (int32_t)groups, eps,
+                   (int64_t)0);
+        };
+        attn("BatchAttnPrep", (nQ + 2 * nKV + 7) / 8);
+        attn("BatchAttnSplit", std::max(1, std::min(s->max_chunks * nKV, (s->sm_count * 8 + rows - 1) / rows)));
+        attn("BatchAttnCombine", nQ);
         l.gemm(m->tensor(pf + "self_attn.o_proj.weight"), p->Q8, p->SQ, ep.Add, AK, rows);
       } else {
         l.gemm(m->tensor(pf + "linear_attn.in_proj_qkv.weight"), p->Q8, p->SQ, p->Pq, H, rows);
