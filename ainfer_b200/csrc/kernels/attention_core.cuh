@@ -123,11 +123,28 @@ struct AttnSplitArgs {
 // instruction cache, so its time follows the amount of distinct code it executes: the rolled
 // loops are several times faster here than the same work unrolled over registers.
 // kvs: 2*C*D bytes (K rows, then V rows), kss/vss: C scales each; shared memory of the caller.
+// The heads' score sums of one token: lane partials -> warp_tree_sum per head -> (sum * k_scale) * scale,
+// stored at dst[head]. With 2, 4 or 8 heads the sums of all heads share one butterfly
+// (warp_tree_sum_multi: the same additions, a fraction of the shuffles).
+template <int GQ>
+__device__ __forceinline__ void attn_store_scores(const float (&part)[GQ], int lane, float *dst, float ks, float scale) {
+  if constexpr (GQ == 2 || GQ == 4 || GQ == 8) {
+    const float r = warp_tree_sum_multi<GQ>(part, lane);
+    if ((lane & (32 / GQ - 1)) == 0) dst[warp_tree_owner<GQ>(lane)] = (r * ks) * scale;
+  } else {
+#pragma unroll
+    for (int g = 0; g < GQ; ++g) {
+      const float r = warp_tree_sum(part[g]);
+      if (lane == 0) dst[g] = (r * ks) * scale;
+    }
+  }
+}
+
 template <int GQ, bool kStage>  // query heads per KV head
 __device__ __forceinline__ void attn_split_body(const AttnSplitArgs &a, int blk, int nblk, unsigned char *kvs,
                                                 uint16_t *kss, uint16_t *vss) {
   constexpr int D = kHeadDim, C = kAttnChunk;
-  __shared__ float sc[GQ][C];   // scores, then p = w * v_scale
+  __shared__ __align__(16) float sc[C][GQ];   // per token the heads' scores, then p = w * v_scale
   __shared__ float hmax[GQ], hse[GQ];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
   int T = __ldcg(a.Ctrl + CTRL_LEN);
@@ -187,14 +204,15 @@ __device__ __forceinline__ void attn_split_body(const AttnSplitArgs &a, int blk,
           kf[j] = (float)(int)(int8_t)((kw.x >> (8 * j)) & 0xFF);
           kf[4 + j] = (float)(int)(int8_t)((kw.y >> (8 * j)) & 0xFF);
         }
+        float part[GQ];
 #pragma unroll
         for (int g = 0; g < GQ; ++g) {
           float acc = 0.0f;
 #pragma unroll
           for (int j = 0; j < 8; ++j) acc = fmaf(q[g][j], kf[j], acc);
-          acc = warp_tree_sum(acc);
-          if (lane == 0) sc[g][tt] = (acc * ks) * scale;
+          part[g] = acc;
         }
+        attn_store_scores<GQ>(part, lane, &sc[tt][0], ks, scale);
       }
     } else {
     // phase 1: scores. warp w takes tokens t0+w, t0+w+8, ...; all its K rows (C/8 of them) are
@@ -225,14 +243,15 @@ __device__ __forceinline__ void attn_split_body(const AttnSplitArgs &a, int blk,
             kf[j] = (float)(int)(int8_t)((kw.x >> (8 * j)) & 0xFF);
             kf[4 + j] = (float)(int)(int8_t)((kw.y >> (8 * j)) & 0xFF);
           }
+          float part[GQ];
 #pragma unroll
           for (int g = 0; g < GQ; ++g) {
             float acc = 0.0f;
 #pragma unroll
             for (int j = 0; j < 8; ++j) acc = fmaf(q[g][j], kf[j], acc);
-            acc = warp_tree_sum(acc);
-            if (lane == 0) sc[g][tt] = (acc * ks) * scale;
+            part[g] = acc;
           }
+          attn_store_scores<GQ>(part, lane, &sc[tt][0], ks, scale);
         }
       }
     }
@@ -241,28 +260,61 @@ __device__ __forceinline__ void attn_split_body(const AttnSplitArgs &a, int blk,
     // phase 2: per head max, weights, sum of exp (ascending t)
     if (tid < GQ) {
       float mx = -INFINITY;
-      for (int tt = 0; tt < nt; ++tt) mx = fmaxf(mx, sc[tid][tt]);
+      for (int tt = 0; tt < nt; ++tt) mx = fmaxf(mx, sc[tt][tid]);
       hmax[tid] = mx;
     }
     __syncthreads();
     for (int i = tid; i < GQ * nt; i += 256) {
-      int g = i / nt, tt = i % nt;
-      sc[g][tt] = det_expf(sc[g][tt] - hmax[g]);
+      int tt = i / GQ, g = i % GQ;
+      sc[tt][g] = det_expf(sc[tt][g] - hmax[g]);
     }
     __syncthreads();
     if (tid < GQ) {
       float se = 0.0f;
-      for (int tt = 0; tt < nt; ++tt) se = se + sc[tid][tt];
+      for (int tt = 0; tt < nt; ++tt) se = se + sc[tt][tid];
       hse[tid] = se;
     }
     __syncthreads();
     for (int i = tid; i < GQ * nt; i += 256) {
-      int g = i / nt, tt = i % nt;
-      sc[g][tt] = sc[g][tt] * f16_to_f32(kStage ? vss[tt] : __ldcg(a.Vs + (size_t)(t0 + tt) * a.nKV + kv));
+      int tt = i / GQ, g = i % GQ;
+      sc[tt][g] = sc[tt][g] * f16_to_f32(kStage ? vss[tt] : __ldcg(a.Vs + (size_t)(t0 + tt) * a.nKV + kv));
     }
     __syncthreads();
     AINFER_MARK(2);
-    // phase 3: thread d accumulates dim d for all heads of the group, ascending t
+    // phase 3: every (head, dim) sum runs over the tokens in ascending order. With the heads in
+    // fours (one 16-byte read gives a token's weights for four heads) a thread owns four heads
+    // of one or two dims; otherwise thread d owns dim d of every head.
+    if constexpr (kStage && GQ % 4 == 0) {
+      constexpr int HQ = GQ / 4 > 0 ? GQ / 4 : 1, DPT = D * HQ / 256 > 0 ? D * HQ / 256 : 1;
+      const int hq = tid / (256 / HQ), d0 = (tid % (256 / HQ)) * DPT;
+      float a4[DPT][4];
+#pragma unroll
+      for (int j = 0; j < DPT; ++j) a4[j][0] = a4[j][1] = a4[j][2] = a4[j][3] = 0.0f;
+      const int8_t *vs = reinterpret_cast<const int8_t *>(kvs + C * D) + d0;
+#pragma unroll 2
+      for (int tt = 0; tt < nt; ++tt) {
+        const float4 pw = *reinterpret_cast<const float4 *>(&sc[tt][(4 * hq) % GQ]);
+#pragma unroll
+        for (int j = 0; j < DPT; ++j) {
+          const float v = (float)(int)vs[tt * D + j];
+          a4[j][0] = fmaf(pw.x, v, a4[j][0]);
+          a4[j][1] = fmaf(pw.y, v, a4[j][1]);
+          a4[j][2] = fmaf(pw.z, v, a4[j][2]);
+          a4[j][3] = fmaf(pw.w, v, a4[j][3]);
+        }
+      }
+#pragma unroll
+      for (int hh = 0; hh < 4; ++hh) {
+        const size_t slot = (size_t)(kv * GQ + 4 * hq + hh) * a.max_chunks + c;
+#pragma unroll
+        for (int j = 0; j < DPT; ++j) a.Pacc[slot * D + d0 + j] = a4[j][hh];
+      }
+      if (tid < GQ) {
+        const size_t slot = (size_t)(kv * GQ + tid) * a.max_chunks + c;
+        a.Pm[slot] = hmax[tid];
+        a.Pse[slot] = hse[tid];
+      }
+    } else {
     float acc[GQ];
 #pragma unroll
     for (int g = 0; g < GQ; ++g) acc[g] = 0.0f;
@@ -272,7 +324,7 @@ __device__ __forceinline__ void attn_split_body(const AttnSplitArgs &a, int blk,
       for (int tt = 0; tt < nt; ++tt) {
         const float v = (float)(int)vs[tt * D];
 #pragma unroll
-        for (int g = 0; g < GQ; ++g) acc[g] = fmaf(sc[g][tt], v, acc[g]);
+        for (int g = 0; g < GQ; ++g) acc[g] = fmaf(sc[tt][g], v, acc[g]);
       }
     } else {
       const int8_t *vp = a.Vc + ((size_t)t0 * a.nKV + kv) * D + tid;
@@ -280,7 +332,7 @@ __device__ __forceinline__ void attn_split_body(const AttnSplitArgs &a, int blk,
       for (int tt = 0; tt < nt; ++tt) {
         float v = (float)(int)__ldcg(vp + (size_t)tt * a.nKV * D);
 #pragma unroll
-        for (int g = 0; g < GQ; ++g) acc[g] = fmaf(sc[g][tt], v, acc[g]);
+        for (int g = 0; g < GQ; ++g) acc[g] = fmaf(sc[tt][g], v, acc[g]);
       }
     }
 #pragma unroll
@@ -291,6 +343,7 @@ __device__ __forceinline__ void attn_split_body(const AttnSplitArgs &a, int blk,
         a.Pm[slot] = hmax[g];
         a.Pse[slot] = hse[g];
       }
+    }
     }
     AINFER_MARK(3);
     __syncthreads();

@@ -83,6 +83,46 @@ __device__ __forceinline__ float warp_tree_sum(float v) {
   for (int off = 16; off > 0; off >>= 1) v = v + __shfl_xor_sync(kFull, v, off);
   return v;
 }
+// warp_tree_sum of N values at once (N = 2, 4 or 8; other N: one by one). The butterfly's first
+// log2(N) levels exchange HALF of the values a lane still holds instead of all of them: at the
+// level with offset `off` a lane keeps the values whose index bit matches its own lane bit and
+// adds its partner's copy of them (the same two operands the plain butterfly adds at that level,
+// and a + b == b + a), so after those levels it holds ONE value, summed over the same lanes in the
+// same association as the plain butterfly; the remaining levels are plain. Shuffles: N - 1 +
+// (5 - log2 N) instead of 5 N. On return the sum of value g is in `out` on every lane whose bits
+// (16, 8, 4 for N = 8) spell g; warp_tree_owner<N>(lane) is that g.
+template <int N>
+__device__ __forceinline__ int warp_tree_owner(int lane) {
+  return N == 8 ? ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1)
+       : N == 4 ? ((lane >> 4) & 1) * 2 + ((lane >> 3) & 1)
+       : N == 2 ? ((lane >> 4) & 1) : 0;
+}
+template <int N>
+__device__ __forceinline__ float warp_tree_sum_multi(const float (&v)[N], int lane) {
+  static_assert(N == 2 || N == 4 || N == 8, "2, 4 or 8 values");
+  float a[N];
+#pragma unroll
+  for (int i = 0; i < N; ++i) a[i] = v[i];
+  int n = N, off = 16;
+#pragma unroll
+  for (int lvl = 0; lvl < (N == 8 ? 3 : N == 4 ? 2 : 1); ++lvl) {
+    const bool hi = (lane & off) != 0;
+    const int half = n >> 1;
+#pragma unroll
+    for (int i = 0; i < N / 2; ++i) {
+      if (i < half) {
+        const float send = hi ? a[i] : a[i + half], keep = hi ? a[i + half] : a[i];
+        a[i] = keep + __shfl_xor_sync(kFull, send, off);
+      }
+    }
+    n = half;
+    off >>= 1;
+  }
+  float r = a[0];
+#pragma unroll
+  for (int o = (N == 8 ? 2 : N == 4 ? 4 : 8); o > 0; o >>= 1) r = r + __shfl_xor_sync(kFull, r, o);
+  return r;
+}
 __device__ __forceinline__ double warp_tree_sum(double v) {
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) v = v + __shfl_xor_sync(kFull, v, off);

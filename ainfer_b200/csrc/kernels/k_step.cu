@@ -838,7 +838,7 @@ static __device__ __noinline__ void attn_stage_t(unsigned epoch, const StepLayer
   const int nch = (T + C - 1) / C, nitems = nch * nKV;
   unsigned char *kvs = step_smem + kFbufOff;  // K rows [C][D], then V rows [C][D]
   float *qs = reinterpret_cast<float *>(step_smem + kTOff);  // [GQ][D]
-  float *sc = qs + GQ * D;                                // [GQ][C]
+  float *sc = qs + GQ * D;                                // [C][GQ]: per token the heads' scores, then weights
   uint16_t *kss = reinterpret_cast<uint16_t *>(sc + GQ * C), *vss = kss + C;
   StepShared *sh = SH;
   const int p = pos < P.max_ctx ? pos : P.max_ctx - 1;  // clamp, kernels.cpp:456
@@ -877,6 +877,7 @@ static __device__ __noinline__ void attn_stage_t(unsigned epoch, const StepLayer
     if (tid < C) kss[tid] = scr;
     else if (tid < 2 * C) vss[tid - C] = scr;
     csync();
+    stamp(20);
     // query heads of the group: warp g. New key row: warp GQ, new value row: warp GQ+1.
     if (warp < GQ || ((warp == GQ || warp == GQ + 1) && p >= t0 && p < t0 + nt)) {
       float x[8];
@@ -921,6 +922,7 @@ static __device__ __noinline__ void attn_stage_t(unsigned epoch, const StepLayer
       }
     }
     csync();
+    stamp(21);
     // scores: warp w takes tokens w, w+16, ...
 #pragma unroll 1
     for (int tt = warp; tt < nt; tt += 16) {
@@ -932,6 +934,7 @@ static __device__ __noinline__ void attn_stage_t(unsigned epoch, const StepLayer
         kf[j] = (float)(int)(int8_t)((kw.x >> (8 * j)) & 0xFF);
         kf[4 + j] = (float)(int)(int8_t)((kw.y >> (8 * j)) & 0xFF);
       }
+      float part[GQ];
 #pragma unroll
       for (int g = 0; g < GQ; ++g) {
         const float4 q0 = *reinterpret_cast<const float4 *>(qs + g * D + lane * 8),
@@ -945,33 +948,29 @@ static __device__ __noinline__ void attn_stage_t(unsigned epoch, const StepLayer
         acc = fmaf(q1.y, kf[5], acc);
         acc = fmaf(q1.z, kf[6], acc);
         acc = fmaf(q1.w, kf[7], acc);
-        acc = warp_tree_sum(acc);
-        if (lane == 0) sc[g * C + tt] = (acc * ksf) * scale;
+        part[g] = acc;
       }
+      attn_store_scores<GQ>(part, lane, sc + tt * GQ, ksf, scale);   // one butterfly for all heads
     }
     csync();
+    stamp(22);
     if (tid < GQ) {
       float mx = -INFINITY;
-      for (int tt = 0; tt < nt; ++tt) mx = fmaxf(mx, sc[tid * C + tt]);
+      for (int tt = 0; tt < nt; ++tt) mx = fmaxf(mx, sc[tt * GQ + tid]);
       sh->hmax[tid] = mx;
     }
     csync();
-    for (int i = tid; i < GQ * nt; i += kCons) {
-      const int g = i / nt, tt = i % nt;
-      sc[g * C + tt] = det_expf(sc[g * C + tt] - sh->hmax[g]);
-    }
+    for (int i = tid; i < GQ * nt; i += kCons) sc[i] = det_expf(sc[i] - sh->hmax[i % GQ]);
     csync();
     if (tid < GQ) {
       float se = 0.0f;
-      for (int tt = 0; tt < nt; ++tt) se = se + sc[tid * C + tt];
+      for (int tt = 0; tt < nt; ++tt) se = se + sc[tt * GQ + tid];
       sh->hse[tid] = se;
     }
     csync();
-    for (int i = tid; i < GQ * nt; i += kCons) {
-      const int g = i / nt, tt = i % nt;
-      sc[g * C + tt] = sc[g * C + tt] * f16_to_f32(vss[tt]);
-    }
+    for (int i = tid; i < GQ * nt; i += kCons) sc[i] = sc[i] * f16_to_f32(vss[i / GQ]);
     csync();
+    stamp(23);
     // weighted values: thread (dim, half) accumulates its dim for the heads of its half
     {
       const int dim = tid & 255, g0 = (tid >> 8) * GH;
@@ -979,12 +978,24 @@ static __device__ __noinline__ void attn_stage_t(unsigned epoch, const StepLayer
 #pragma unroll
       for (int g = 0; g < GH; ++g) acc[g] = 0.0f;
       const int8_t *vs = reinterpret_cast<const int8_t *>(kvs + C * D) + dim;
+      if constexpr (GQ == 8) {   // four heads per half: one 16-byte read gives a token's four weights
 #pragma unroll 2
-      for (int tt = 0; tt < nt; ++tt) {
-        const float v = (float)(int)vs[tt * D];
+        for (int tt = 0; tt < nt; ++tt) {
+          const float v = (float)(int)vs[tt * D];
+          const float4 pw = *reinterpret_cast<const float4 *>(sc + tt * GQ + g0);
+          acc[0] = fmaf(pw.x, v, acc[0]);
+          acc[1] = fmaf(pw.y, v, acc[1]);
+          acc[2] = fmaf(pw.z, v, acc[2]);
+          acc[3] = fmaf(pw.w, v, acc[3]);
+        }
+      } else {
+#pragma unroll 2
+        for (int tt = 0; tt < nt; ++tt) {
+          const float v = (float)(int)vs[tt * D];
 #pragma unroll
-        for (int g = 0; g < GH; ++g)
-          if (g0 + g < GQ) acc[g] = fmaf(sc[(g0 + g) * C + tt], v, acc[g]);
+          for (int g = 0; g < GH; ++g)
+            if (g0 + g < GQ) acc[g] = fmaf(sc[tt * GQ + g0 + g], v, acc[g]);
+        }
       }
 #pragma unroll
       for (int g = 0; g < GH; ++g) {
@@ -998,6 +1009,7 @@ static __device__ __noinline__ void attn_stage_t(unsigned epoch, const StepLayer
         }
       }
     }
+    stamp(24);
     csync();
   }
 }
