@@ -350,10 +350,193 @@ __device__ __forceinline__ void attn_split_body(const AttnSplitArgs &a, int blk,
   }
 }
 
+// Eight INT8 values (a row's bytes 8*lane .. 8*lane+7) as floats, exactly: a byte b with its
+// sign bit flipped is b + 128 in 0..255; placed in the low mantissa byte of 2^23 it reads as the
+// float 8388608 + 128 + b, and subtracting 8388736 leaves b. One byte permute and one addition
+// per value on the full-rate pipes, where the integer-to-float conversion has a quarter-rate unit.
+__device__ __forceinline__ void s8x8_to_f32(uint2 w, float (&f)[8]) {
+  const uint32_t lo = w.x ^ 0x80808080u, hi = w.y ^ 0x80808080u;
+  f[0] = __uint_as_float(__byte_perm(lo, 0x4B000000u, 0x7650)) - 8388736.0f;
+  f[1] = __uint_as_float(__byte_perm(lo, 0x4B000000u, 0x7651)) - 8388736.0f;
+  f[2] = __uint_as_float(__byte_perm(lo, 0x4B000000u, 0x7652)) - 8388736.0f;
+  f[3] = __uint_as_float(__byte_perm(lo, 0x4B000000u, 0x7653)) - 8388736.0f;
+  f[4] = __uint_as_float(__byte_perm(hi, 0x4B000000u, 0x7650)) - 8388736.0f;
+  f[5] = __uint_as_float(__byte_perm(hi, 0x4B000000u, 0x7651)) - 8388736.0f;
+  f[6] = __uint_as_float(__byte_perm(hi, 0x4B000000u, 0x7652)) - 8388736.0f;
+  f[7] = __uint_as_float(__byte_perm(hi, 0x4B000000u, 0x7653)) - 8388736.0f;
+}
+
+// The same chunk arithmetic as attn_split_body with ONE WARP per (chunk, KV head) item, for
+// launches with thousands of items (batched decode at long contexts, prefill passes). A chunk's
+// result depends on nothing outside the chunk, so who computes it is free; a warp on its own
+// needs no block barrier between the phases, never idles while eight threads run the softmax
+// sums, and reads every K and V row straight into registers (lane l: bytes 8l..8l+7 of a row,
+// eight rows in flight) without a pass through shared memory. The row loads are unconditional
+// (past the chunk's end the last row is fetched again): a load under a condition into a register
+// that lives across iterations was measured to be waited for at once. In the value pass a lane owns its
+// eight dims of every head: 64 sums fed by one 8-byte row piece and the token's weights.
+template <int GQ>
+__device__ __forceinline__ void attn_split_warp_body(const AttnSplitArgs &a, int blk, int nblk, unsigned char *scratch) {
+  constexpr int D = kHeadDim, C = kAttnChunk, W = 8, PF = 8;
+  static_assert(GQ % 4 == 0 && 32 % GQ == 0 && C == 64, "lane partition of the warp form");
+  static_assert(W * C * (GQ + 2) * 4 <= 2 * C * D, "fits the block form's K/V staging area");
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // per warp: [C][GQ] scores (then p = w * v_scale) and the C key and C value scales as floats
+  float(*sc)[GQ] = reinterpret_cast<float(*)[GQ]>(scratch) + (size_t)warp * C;
+  float *scf = &sc[0][0], *vsf = reinterpret_cast<float *>(scratch) + W * C * GQ + warp * 2 * C,
+        *ksf = vsf + C;
+  int T = __ldcg(a.Ctrl + CTRL_LEN);
+  if (T > a.max_ctx) T = a.max_ctx;  // clamp, kernels.cpp:227-228
+  const int nch = (T + C - 1) / C;
+  const float scale = 1.0f / sqrtf((float)D);
+  const size_t rs = (size_t)a.nKV * D;   // bytes between consecutive tokens' rows
+#pragma unroll 1
+  for (int item = blk * W + warp; item < nch * a.nKV; item += nblk * W) {
+    const int c = item / a.nKV, kv = item % a.nKV;
+    const int t0 = c * C, nt = min(T, t0 + C) - t0;
+    const int8_t *kb = a.Kc + ((size_t)t0 * a.nKV + kv) * D + lane * 8;
+    const int8_t *vb = a.Vc + ((size_t)t0 * a.nKV + kv) * D + lane * 8;
+    uint2 ring[PF];
+#pragma unroll
+    for (int i = 0; i < PF; ++i) {
+      ring[i] = __ldcg(reinterpret_cast<const uint2 *>(kb + (size_t)min(i, nt - 1) * rs));
+    }
+    {  // scales: lane l fetches those of tokens l and l + 32
+      uint16_t ks0 = 0, ks1 = 0, vs0 = 0, vs1 = 0;
+      if (lane < nt) {
+        ks0 = __ldcg(a.Ks + (size_t)(t0 + lane) * a.nKV + kv);
+        vs0 = __ldcg(a.Vs + (size_t)(t0 + lane) * a.nKV + kv);
+      }
+      if (lane + 32 < nt) {
+        ks1 = __ldcg(a.Ks + (size_t)(t0 + lane + 32) * a.nKV + kv);
+        vs1 = __ldcg(a.Vs + (size_t)(t0 + lane + 32) * a.nKV + kv);
+      }
+      ksf[lane] = f16_to_f32(ks0);
+      ksf[lane + 32] = f16_to_f32(ks1);
+      vsf[lane] = f16_to_f32(vs0);
+      vsf[lane + 32] = f16_to_f32(vs1);
+    }
+    {
+      // ---- phase 1: scores; lane holds dims 8*lane .. 8*lane+7 of each query head of the group
+      float q[GQ][8];
+#pragma unroll
+      for (int g = 0; g < GQ; ++g) {
+        const float4 *qp = reinterpret_cast<const float4 *>(a.Qn + (size_t)(kv * GQ + g) * D + lane * 8);
+        const float4 v0 = __ldcg(qp), v1 = __ldcg(qp + 1);
+        q[g][0] = v0.x; q[g][1] = v0.y; q[g][2] = v0.z; q[g][3] = v0.w;
+        q[g][4] = v1.x; q[g][5] = v1.y; q[g][6] = v1.z; q[g][7] = v1.w;
+      }
+      __syncwarp();
+#pragma unroll 1
+      for (int b0 = 0; b0 < nt; b0 += PF) {
+#pragma unroll
+        for (int i = 0; i < PF; ++i) {
+          const int tt = b0 + i;
+          const uint2 cur = ring[i];
+          ring[i] = __ldcg(reinterpret_cast<const uint2 *>(kb + (size_t)min(tt + PF, nt - 1) * rs));
+          if (tt < nt) {
+            float kf[8];
+            s8x8_to_f32(cur, kf);
+            const float ks = ksf[tt];
+            float part[GQ];
+#pragma unroll
+            for (int g = 0; g < GQ; ++g) {
+              float acc = 0.0f;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) acc = fmaf(q[g][j], kf[j], acc);
+              part[g] = acc;
+            }
+            attn_store_scores<GQ>(part, lane, &sc[tt][0], ks, scale);
+          }
+        }
+      }
+    }
+    // the first V rows travel during the softmax
+#pragma unroll
+    for (int i = 0; i < PF; ++i) {
+      ring[i] = __ldcg(reinterpret_cast<const uint2 *>(vb + (size_t)min(i, nt - 1) * rs));
+    }
+    __syncwarp();
+    // ---- phase 2: per head max, weights, sum of exp (ascending t), p = w * v_scale.
+    // Element i = lane + 32 k of the [token][head] array belongs to head lane % GQ for every k.
+    float mx = -INFINITY;
+    for (int i = lane; i < GQ * nt; i += 32) mx = fmaxf(mx, scf[i]);
+#pragma unroll
+    for (int off = GQ; off < 32; off <<= 1) mx = fmaxf(mx, __shfl_xor_sync(kFull, mx, off));
+    for (int i = lane; i < GQ * nt; i += 32) scf[i] = det_expf(scf[i] - mx);
+    __syncwarp();
+    float se = 0.0f;
+    if (lane < GQ)
+      for (int tt = 0; tt < nt; ++tt) se = se + sc[tt][lane];
+    __syncwarp();
+    for (int i = lane; i < GQ * nt; i += 32) scf[i] = scf[i] * vsf[i / GQ];
+    __syncwarp();
+    // ---- phase 3: every (head, dim) sum runs over the tokens in ascending order
+    float acc[GQ][8];
+#pragma unroll
+    for (int g = 0; g < GQ; ++g)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[g][j] = 0.0f;
+#pragma unroll 1
+    for (int b0 = 0; b0 < nt; b0 += PF) {
+#pragma unroll
+      for (int i = 0; i < PF; ++i) {
+        const int tt = b0 + i;
+        const uint2 cur = ring[i];
+        ring[i] = __ldcg(reinterpret_cast<const uint2 *>(vb + (size_t)min(tt + PF, nt - 1) * rs));
+        if (tt < nt) {
+          float vf[8];
+          s8x8_to_f32(cur, vf);
+#pragma unroll
+          for (int g4 = 0; g4 < GQ / 4; ++g4) {
+            const float4 pw = *reinterpret_cast<const float4 *>(&sc[tt][4 * g4]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              acc[4 * g4 + 0][j] = fmaf(pw.x, vf[j], acc[4 * g4 + 0][j]);
+              acc[4 * g4 + 1][j] = fmaf(pw.y, vf[j], acc[4 * g4 + 1][j]);
+              acc[4 * g4 + 2][j] = fmaf(pw.z, vf[j], acc[4 * g4 + 2][j]);
+              acc[4 * g4 + 3][j] = fmaf(pw.w, vf[j], acc[4 * g4 + 3][j]);
+            }
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < GQ; ++g) {
+      const size_t slot = (size_t)(kv * GQ + g) * a.max_chunks + c;
+      float4 *dst = reinterpret_cast<float4 *>(a.Pacc + slot * D + lane * 8);
+      dst[0] = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+      dst[1] = make_float4(acc[g][4], acc[g][5], acc[g][6], acc[g][7]);
+    }
+    if (lane < GQ) {
+      const size_t slot = (size_t)(kv * GQ + lane) * a.max_chunks + c;
+      a.Pm[slot] = mx;
+      a.Pse[slot] = se;
+    }
+    __syncwarp();   // the next item overwrites sc and vsf
+  }
+}
+
+// warp_form_items > 0: launches of the batched kernels, whose rows take the one-warp-per-item
+// form when the launch holds at least that many (chunk, KV head) items (rows x chunks x KV heads;
+// the same bits either way, so rows of one launch may differ in the form they take).
 template <bool kStage>
-__device__ __forceinline__ void attn_split_dispatch(const AttnSplitArgs &a, int blk, int nblk) {
+__device__ __forceinline__ void attn_split_dispatch(const AttnSplitArgs &a, int blk, int nblk, long rows = 0,
+                                                    long warp_form_items = 0) {
   __shared__ __align__(16) unsigned char kvs[kStage ? 2 * kAttnChunk * kHeadDim : 16];
   __shared__ uint16_t kss[kStage ? kAttnChunk : 1], vss[kStage ? kAttnChunk : 1];
+  if constexpr (kStage) {
+    const int gq = a.nQ / a.nKV;
+    if (warp_form_items > 0 && (gq == 8 || gq == 4)) {
+      int T = __ldcg(a.Ctrl + CTRL_LEN);
+      if (T > a.max_ctx) T = a.max_ctx;
+      if (rows * ((T + kAttnChunk - 1) / kAttnChunk) * a.nKV >= warp_form_items) {
+        if (gq == 8) attn_split_warp_body<8>(a, blk, nblk, kvs);
+        else attn_split_warp_body<4>(a, blk, nblk, kvs);
+        return;
+      }
+    }
+  }
   switch (a.nQ / a.nKV) {
     case 1: attn_split_body<1, kStage>(a, blk, nblk, kvs, kss, vss); break;
     case 2: attn_split_body<2, kStage>(a, blk, nblk, kvs, kss, vss); break;

@@ -87,7 +87,9 @@ __global__ void __launch_bounds__(256) BatchAttnPrep(const BatchAttnArgs a) {
   p.nQ = a.nQ; p.nKV = a.nKV; p.rot = a.rot; p.max_ctx = a.max_ctx; p.eps = a.eps;
   attn_prep_body(p, blockIdx.x % a.groups, a.groups);
 }
-__global__ void __launch_bounds__(256) BatchAttnSplit(const BatchAttnArgs a) {
+// From this many items in a launch the one-warp-per-item form of the split is used.
+constexpr long kWarpFormItems = 2048;
+__global__ void __launch_bounds__(256, 2) BatchAttnSplit(const BatchAttnArgs a) {
   const int b = blockIdx.x / a.groups;
   if (b >= a.B) return;
   AttnSplitArgs p;
@@ -98,7 +100,7 @@ __global__ void __launch_bounds__(256) BatchAttnSplit(const BatchAttnArgs a) {
   p.Pm = a.Pm + (size_t)b * a.nQ * a.max_chunks; p.Pse = a.Pse + (size_t)b * a.nQ * a.max_chunks;
   p.Pacc = a.Pacc + (size_t)b * a.nQ * a.max_chunks * kHeadDim;
   p.nQ = a.nQ; p.nKV = a.nKV; p.max_ctx = a.max_ctx; p.max_chunks = a.max_chunks;
-  attn_split_dispatch<true>(p, blockIdx.x % a.groups, a.groups);
+  attn_split_dispatch<true>(p, blockIdx.x % a.groups, a.groups, a.B, kWarpFormItems);
 }
 __global__ void __launch_bounds__(256) BatchAttnCombine(const BatchAttnArgs a) {
   const int b = blockIdx.x / a.groups;

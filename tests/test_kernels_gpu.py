@@ -285,6 +285,51 @@ def test_attention_decode_int8kv(dev, nQ, nKV, T):
     assert np.array_equal(dev.download(dSQ, nQ * 2, np.float32), sq)
 
 
+@pytest.mark.parametrize("nQ,nKV", [(16, 2), (8, 2)])
+def test_batch_attention_both_forms(dev, nQ, nKV):
+    """BatchAttnSplit over rows that share one INT8 cache and end at their own lengths (the prefill
+    layout). The long rows make the launch hold more than 2048 (chunk, KV head) items, so they take
+    the one-warp-per-item form; the short rows take the one-block-per-item form. Every row, merged by
+    AttnCombine, must equal the oracle's attention bit for bit."""
+    L = O.lib()
+    rng = np.random.default_rng(nQ)
+    D, max_ctx = 256, 2200
+    Ts = [2049 + 4 * b for b in range(32)] + [1, 64, 65, 700]
+    B = len(Ts)
+    nch = (max_ctx + 63) // 64
+    assert B * ((2049 + 63) // 64) * nKV >= 2048 and B * ((700 + 63) // 64) * nKV < 2048
+    Kc = np.zeros((max_ctx, nKV, D), np.int8); Vc = np.zeros((max_ctx, nKV, D), np.int8)
+    Ks = np.zeros((max_ctx, nKV), np.uint16); Vs = np.zeros((max_ctx, nKV), np.uint16)
+    prior = rng.standard_normal((2, max_ctx, nKV, D)).astype(np.float32)
+    prior[1] *= rng.uniform(0.2, 3.0, (max_ctx, nKV, 1)).astype(np.float32)   # value scales that differ by token
+    for t in range(max_ctx):
+        for h in range(nKV):
+            L.orc_kv_quant_row(prior[0, t, h], D, Kc[t, h], Ks[t, h:h + 1])
+            L.orc_kv_quant_row(prior[1, t, h], D, Vc[t, h], Vs[t, h:h + 1])
+    qn = rng.standard_normal((B, nQ, D)).astype(np.float32)
+    q16 = np.zeros((B, nQ, 2 * D), np.float32)
+    q16[:, :, D:] = rng.standard_normal((B, nQ, D)).astype(np.float32)   # the gates
+    ctrl = np.array([[0, T - 1, T, -1] for T in Ts], np.int32)
+    dCtrl, dQ16, dQn = dev.upload(ctrl), dev.upload(q16), dev.upload(qn)
+    dKc, dVc, dKs, dVs = dev.upload(Kc), dev.upload(Vc), dev.upload(Ks), dev.upload(Vs)
+    dPm, dPse, dPacc = dev.zeros(B * nQ * nch * 4), dev.zeros(B * nQ * nch * 4), dev.zeros(B * nQ * nch * D * 4)
+    dQ8, dSQ = dev.zeros(B * nQ * D), dev.zeros(B * nQ * 2 * 4)
+    groups = (dev.info().sm_count * 8 + B - 1) // B
+    dev.kernel("BatchAttnSplit")(B * groups, 0, 0, 0, 0, 0, 0, 0, dCtrl, dQn, dKc, dVc, dKs, dVs, dPm, dPse, dPacc, dQ8, dSQ,
+                                 nQ, nKV, 64, max_ctx, nch, B, groups, 1e-6, 0)
+    dAtt = dev.zeros(nQ * D * 4)
+    d8, dS = dev.zeros(nQ * D), dev.zeros(nQ * 2 * 4)
+    comb = dev.kernel("AttnCombine")
+    for b, T in enumerate(Ts):
+        comb(nQ, dPm + b * nQ * nch * 4, dPse + b * nQ * nch * 4, dPacc + b * nQ * nch * D * 4, dQ16 + b * nQ * 2 * D * 4,
+             dCtrl + 16 * b, d8, dS, dAtt, nQ, max_ctx, nch)
+        dev.sync()
+        want = np.zeros((nQ, D), np.float32)
+        L.orc_attn_int8kv(qn[b], Kc.reshape(-1), Ks.reshape(-1), Vc.reshape(-1), Vs.reshape(-1),
+                          np.ascontiguousarray(q16[b, :, D:]), nQ, nKV, D, T, want)
+        assert np.array_equal(dev.download(dAtt, (nQ, D), np.float32), want), (b, T)
+
+
 @pytest.mark.parametrize("E,k,H,I", [(32, 2, 256, 128), (64, 4, 1024, 256), (512, 10, 2048, 512)])
 def test_moe_block(dev, E, k, H, I):
     """RouterTopK + ExpertGateUp + ExpertDownCombine vs the oracle's MoE arithmetic."""
