@@ -32,9 +32,11 @@ struct RouterLogitsRowsArgs {
   int32_t E, H, rows;
   int32_t tokens_per_block;   // launched with ceil((E + 1) / 8) x ceil(rows / tokens_per_block) blocks
 };
-// One warp per router row and block of tokens (the row's weights stay in L1 across the block's
-// tokens); per token the sums of RouterTopK (router_row_fma order, then the lane tree).
-__global__ void __launch_bounds__(256) RouterLogitsRows(const RouterLogitsRowsArgs a) {
+// One warp per router row and block of tokens; per token the sums of RouterTopK (router_row_fma
+// order, then the lane tree). The row's first chunk of weights is fetched once, and four tokens
+// are summed side by side: a token's sum is one chain of dependent additions per lane, so four
+// chains in flight is what keeps the lanes busy.
+__global__ void __launch_bounds__(256, 2) RouterLogitsRows(const RouterLogitsRowsArgs a) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int nrows = a.E + (a.Wsg ? 1 : 0), n = a.H / 256;
   const int nrb = (a.E + 1 + 7) / 8, rb = blockIdx.x % nrb, tb = blockIdx.x / nrb;
@@ -44,15 +46,52 @@ __global__ void __launch_bounds__(256) RouterLogitsRows(const RouterLogitsRowsAr
     if (e >= nrows) return;
     const uint16_t *w = e < a.E ? a.Wr + (size_t)e * a.H : a.Wsg;
     const float bias = a.Bias && e < a.E ? __ldg(a.Bias + e) : 0.0f;
-    for (int t = tb * a.tokens_per_block; t < t_end; ++t) {
-      float acc = 0.0f;
-      for (int i0 = 0; i0 < n; i0 += kRouterChunk) {
-        RouterRowRegs r;
+    RouterRowRegs r0;
+    router_row_load(r0, w, 0, n, lane);
+    for (int t = tb * a.tokens_per_block; t < t_end; t += 4) {
+      float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      RouterRowRegs r = r0;
+      const float *hn[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) hn[u] = a.Hn + (size_t)(t + u < t_end ? t + u : t_end - 1) * a.H;   // past the end: the last token again, not stored
+      for (int i0 = 0;;) {
+#pragma unroll
+        for (int c = 0; c < kRouterChunk; ++c) {
+          const int ic = i0 + c < n ? i0 + c : n - 1, k0 = (ic * 32 + lane) * 8;
+          float4 x0[4], x1[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            x0[u] = __ldcg(reinterpret_cast<const float4 *>(hn[u] + k0));
+            x1[u] = __ldcg(reinterpret_cast<const float4 *>(hn[u] + k0 + 4));
+          }
+          if (i0 + c < n) {
+            const uint4 wv = r.w[c];
+            const float w0 = u2f(wv.x << 16), w1 = u2f(wv.x & 0xFFFF0000u), w2 = u2f(wv.y << 16), w3 = u2f(wv.y & 0xFFFF0000u),
+                        w4 = u2f(wv.z << 16), w5 = u2f(wv.z & 0xFFFF0000u), w6 = u2f(wv.w << 16), w7 = u2f(wv.w & 0xFFFF0000u);
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {   // router_row_fma's order for each token
+              float s = acc[u];
+              s = fmaf(w0, x0[u].x, s);
+              s = fmaf(w1, x0[u].y, s);
+              s = fmaf(w2, x0[u].z, s);
+              s = fmaf(w3, x0[u].w, s);
+              s = fmaf(w4, x1[u].x, s);
+              s = fmaf(w5, x1[u].y, s);
+              s = fmaf(w6, x1[u].z, s);
+              s = fmaf(w7, x1[u].w, s);
+              acc[u] = s;
+            }
+          }
+        }
+        i0 += kRouterChunk;
+        if (i0 >= n) break;
         router_row_load(r, w, i0, n, lane);
-        acc = router_row_fma(r, a.Hn + (size_t)t * a.H, i0, n, lane, acc);
       }
-      acc = warp_tree_sum(acc);
-      if (lane == 0) a.Logits[(size_t)t * (a.E + 1) + e] = a.Bias ? acc + bias : acc;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float sum = warp_tree_sum(acc[u]);
+        if (lane == 0 && t + u < t_end) a.Logits[(size_t)(t + u) * (a.E + 1) + e] = a.Bias ? sum + bias : sum;
+      }
     }
   }
 }

@@ -65,21 +65,26 @@ struct RouterRowRegs { uint4 w[kRouterChunk]; };
 __device__ __forceinline__ const uint16_t *router_row_ptr(const RouterTopKArgs &a, int e) {
   return e < a.E ? a.Wr + (size_t)e * a.H : a.Wsg;
 }
+// The loads are unconditional (past the row's end the last piece is fetched again and not used):
+// a load under a condition into a register that stays live was measured to be waited for where
+// it is issued, which serialises the chunk's round trips.
 __device__ __forceinline__ void router_row_load(RouterRowRegs &r, const uint16_t *w, int i0, int n, int lane) {
 #pragma unroll
-  for (int c = 0; c < kRouterChunk; ++c)
-    if (i0 + c < n) r.w[c] = __ldg(reinterpret_cast<const uint4 *>(w + ((i0 + c) * 32 + lane) * 8));
+  for (int c = 0; c < kRouterChunk; ++c) {
+    const int ic = i0 + c < n ? i0 + c : n - 1;
+    r.w[c] = __ldg(reinterpret_cast<const uint4 *>(w + (ic * 32 + lane) * 8));
+  }
 }
 __device__ __forceinline__ float router_row_fma(const RouterRowRegs &r, const float *Hn, int i0, int n, int lane,
                                                 float acc) {
   float4 x0[kRouterChunk], x1[kRouterChunk];
 #pragma unroll
-  for (int c = 0; c < kRouterChunk; ++c)
-    if (i0 + c < n) {
-      const int k0 = ((i0 + c) * 32 + lane) * 8;
-      x0[c] = __ldcg(reinterpret_cast<const float4 *>(Hn + k0));
-      x1[c] = __ldcg(reinterpret_cast<const float4 *>(Hn + k0 + 4));
-    }
+  for (int c = 0; c < kRouterChunk; ++c) {
+    const int ic = i0 + c < n ? i0 + c : n - 1;
+    const int k0 = (ic * 32 + lane) * 8;
+    x0[c] = __ldcg(reinterpret_cast<const float4 *>(Hn + k0));
+    x1[c] = __ldcg(reinterpret_cast<const float4 *>(Hn + k0 + 4));
+  }
 #pragma unroll
   for (int c = 0; c < kRouterChunk; ++c)
     if (i0 + c < n) {
