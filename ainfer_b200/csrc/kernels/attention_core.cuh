@@ -418,14 +418,18 @@ __device__ __forceinline__ void attn_split_warp_body(const AttnSplitArgs &a, int
     }
     {
       // ---- phase 1: scores; lane holds dims 8*lane .. 8*lane+7 of each query head of the group
+      // slot g of this lane holds head g ^ own, where `own` is the head whose score sum the lane ends
+      // up with: the shared butterfly then needs no selection by lane (warp_tree_sum_multi_permuted)
+      const int own = warp_tree_owner<GQ>(lane);
       float q[GQ][8];
 #pragma unroll
       for (int g = 0; g < GQ; ++g) {
-        const float4 *qp = reinterpret_cast<const float4 *>(a.Qn + (size_t)(kv * GQ + g) * D + lane * 8);
+        const float4 *qp = reinterpret_cast<const float4 *>(a.Qn + (size_t)(kv * GQ + (g ^ own)) * D + lane * 8);
         const float4 v0 = __ldcg(qp), v1 = __ldcg(qp + 1);
         q[g][0] = v0.x; q[g][1] = v0.y; q[g][2] = v0.z; q[g][3] = v0.w;
         q[g][4] = v1.x; q[g][5] = v1.y; q[g][6] = v1.z; q[g][7] = v1.w;
       }
+      const bool writer = (lane & (32 / GQ - 1)) == 0;
       __syncwarp();
 #pragma unroll 1
       for (int b0 = 0; b0 < nt; b0 += PF) {
@@ -446,7 +450,8 @@ __device__ __forceinline__ void attn_split_warp_body(const AttnSplitArgs &a, int
               for (int j = 0; j < 8; ++j) acc = fmaf(q[g][j], kf[j], acc);
               part[g] = acc;
             }
-            attn_store_scores<GQ>(part, lane, &sc[tt][0], ks, scale);
+            const float r = warp_tree_sum_multi_permuted<GQ>(part, lane);
+            if (writer) sc[tt][own] = (r * ks) * scale;
           }
         }
       }

@@ -123,6 +123,30 @@ __device__ __forceinline__ float warp_tree_sum_multi(const float (&v)[N], int la
   for (int o = (N == 8 ? 2 : N == 4 ? 4 : 8); o > 0; o >>= 1) r = r + __shfl_xor_sync(kFull, r, o);
   return r;
 }
+// warp_tree_sum_multi for a caller that can choose which value sits in which slot: lane l passes
+// value (i ^ warp_tree_owner<N>(l)) in slot i. The values a lane keeps at each level are then
+// always the lower half of its slots and the ones it sends the upper half, so no selection by
+// lane bit is needed; the additions are the same pairs as in warp_tree_sum_multi. Returns the
+// sum of value warp_tree_owner<N>(lane).
+template <int N>
+__device__ __forceinline__ float warp_tree_sum_multi_permuted(const float (&v)[N], int lane) {
+  static_assert(N == 2 || N == 4 || N == 8, "2, 4 or 8 values");
+  float a[N];
+#pragma unroll
+  for (int i = 0; i < N; ++i) a[i] = v[i];
+  int off = 16;
+#pragma unroll
+  for (int half = N / 2; half > 0; half >>= 1) {
+#pragma unroll
+    for (int i = 0; i < N / 2; ++i)
+      if (i < half) a[i] = a[i] + __shfl_xor_sync(kFull, a[i + half], off);
+    off >>= 1;
+  }
+  float r = a[0];
+#pragma unroll
+  for (int o = (N == 8 ? 2 : N == 4 ? 4 : 8); o > 0; o >>= 1) r = r + __shfl_xor_sync(kFull, r, o);
+  return r;
+}
 __device__ __forceinline__ double warp_tree_sum(double v) {
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) v = v + __shfl_xor_sync(kFull, v, off);
