@@ -366,6 +366,140 @@ __device__ __forceinline__ void s8x8_to_f32(uint2 w, float (&f)[8]) {
   f[7] = __uint_as_float(__byte_perm(hi, 0x4B000000u, 0x7653)) - 8388736.0f;
 }
 
+// One (chunk c, KV head kv) item by one warp. kFull: the chunk holds all 64 tokens (every chunk of
+// a sequence but its last), so the token bounds are compile-time constants.
+template <int GQ, bool kFull>
+__device__ __forceinline__ void attn_warp_item(const AttnSplitArgs &a, int c, int kv, int nt_rt, float (*sc)[GQ], float *vsf,
+                                               float *ksf, float scale, size_t rs, int lane) {
+  constexpr int D = kHeadDim, C = kAttnChunk, PF = 8;
+  const int t0 = c * C, nt = kFull ? C : nt_rt;
+  float *scf = &sc[0][0];
+  const int8_t *kb = a.Kc + ((size_t)t0 * a.nKV + kv) * D + lane * 8;
+  const int8_t *vb = a.Vc + ((size_t)t0 * a.nKV + kv) * D + lane * 8;
+  uint2 ring[PF];
+#pragma unroll
+  for (int i = 0; i < PF; ++i) {
+    ring[i] = __ldcg(reinterpret_cast<const uint2 *>(kb + (size_t)min(i, nt - 1) * rs));
+  }
+  {  // scales: lane l fetches those of tokens l and l + 32
+    uint16_t ks0 = 0, ks1 = 0, vs0 = 0, vs1 = 0;
+    if (lane < nt) {
+      ks0 = __ldcg(a.Ks + (size_t)(t0 + lane) * a.nKV + kv);
+      vs0 = __ldcg(a.Vs + (size_t)(t0 + lane) * a.nKV + kv);
+    }
+    if (lane + 32 < nt) {
+      ks1 = __ldcg(a.Ks + (size_t)(t0 + lane + 32) * a.nKV + kv);
+      vs1 = __ldcg(a.Vs + (size_t)(t0 + lane + 32) * a.nKV + kv);
+    }
+    ksf[lane] = f16_to_f32(ks0);
+    ksf[lane + 32] = f16_to_f32(ks1);
+    vsf[lane] = f16_to_f32(vs0);
+    vsf[lane + 32] = f16_to_f32(vs1);
+  }
+  {
+    // ---- phase 1: scores; lane holds dims 8*lane .. 8*lane+7 of each query head of the group
+    // slot g of this lane holds head g ^ own, where `own` is the head whose score sum the lane ends
+    // up with: the shared butterfly then needs no selection by lane (warp_tree_sum_multi_permuted)
+    const int own = warp_tree_owner<GQ>(lane);
+    float q[GQ][8];
+#pragma unroll
+    for (int g = 0; g < GQ; ++g) {
+      const float4 *qp = reinterpret_cast<const float4 *>(a.Qn + (size_t)(kv * GQ + (g ^ own)) * D + lane * 8);
+      const float4 v0 = __ldcg(qp), v1 = __ldcg(qp + 1);
+      q[g][0] = v0.x; q[g][1] = v0.y; q[g][2] = v0.z; q[g][3] = v0.w;
+      q[g][4] = v1.x; q[g][5] = v1.y; q[g][6] = v1.z; q[g][7] = v1.w;
+    }
+    const bool writer = (lane & (32 / GQ - 1)) == 0;
+    __syncwarp();
+#pragma unroll 1
+    for (int b0 = 0; b0 < nt; b0 += PF) {
+#pragma unroll
+      for (int i = 0; i < PF; ++i) {
+        const int tt = b0 + i;
+        const uint2 cur = ring[i];
+        ring[i] = __ldcg(reinterpret_cast<const uint2 *>(kb + (size_t)min(tt + PF, nt - 1) * rs));
+        if (tt < nt) {
+          float kf[8];
+          s8x8_to_f32(cur, kf);
+          const float ks = ksf[tt];
+          float part[GQ];
+#pragma unroll
+          for (int g = 0; g < GQ; ++g) {
+            float acc = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc = fmaf(q[g][j], kf[j], acc);
+            part[g] = acc;
+          }
+          const float r = warp_tree_sum_multi_permuted<GQ>(part, lane);
+          if (writer) sc[tt][own] = (r * ks) * scale;
+        }
+      }
+    }
+  }
+  // the first V rows travel during the softmax
+#pragma unroll
+  for (int i = 0; i < PF; ++i) {
+    ring[i] = __ldcg(reinterpret_cast<const uint2 *>(vb + (size_t)min(i, nt - 1) * rs));
+  }
+  __syncwarp();
+  // ---- phase 2: per head max, weights, sum of exp (ascending t), p = w * v_scale.
+  // Element i = lane + 32 k of the [token][head] array belongs to head lane % GQ for every k.
+  float mx = -INFINITY;
+  for (int i = lane; i < GQ * nt; i += 32) mx = fmaxf(mx, scf[i]);
+#pragma unroll
+  for (int off = GQ; off < 32; off <<= 1) mx = fmaxf(mx, __shfl_xor_sync(kFull, mx, off));
+  for (int i = lane; i < GQ * nt; i += 32) scf[i] = det_expf(scf[i] - mx);
+  __syncwarp();
+  float se = 0.0f;
+  if (lane < GQ)
+    for (int tt = 0; tt < nt; ++tt) se = se + sc[tt][lane];
+  __syncwarp();
+  for (int i = lane; i < GQ * nt; i += 32) scf[i] = scf[i] * vsf[i / GQ];
+  __syncwarp();
+  // ---- phase 3: every (head, dim) sum runs over the tokens in ascending order
+  float acc[GQ][8];
+#pragma unroll
+  for (int g = 0; g < GQ; ++g)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[g][j] = 0.0f;
+#pragma unroll 1
+  for (int b0 = 0; b0 < nt; b0 += PF) {
+#pragma unroll
+    for (int i = 0; i < PF; ++i) {
+      const int tt = b0 + i;
+      const uint2 cur = ring[i];
+      ring[i] = __ldcg(reinterpret_cast<const uint2 *>(vb + (size_t)min(tt + PF, nt - 1) * rs));
+      if (tt < nt) {
+        float vf[8];
+        s8x8_to_f32(cur, vf);
+#pragma unroll
+        for (int g4 = 0; g4 < GQ / 4; ++g4) {
+          const float4 pw = *reinterpret_cast<const float4 *>(&sc[tt][4 * g4]);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            acc[4 * g4 + 0][j] = fmaf(pw.x, vf[j], acc[4 * g4 + 0][j]);
+            acc[4 * g4 + 1][j] = fmaf(pw.y, vf[j], acc[4 * g4 + 1][j]);
+            acc[4 * g4 + 2][j] = fmaf(pw.z, vf[j], acc[4 * g4 + 2][j]);
+            acc[4 * g4 + 3][j] = fmaf(pw.w, vf[j], acc[4 * g4 + 3][j]);
+          }
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int g = 0; g < GQ; ++g) {
+    const size_t slot = (size_t)(kv * GQ + g) * a.max_chunks + c;
+    float4 *dst = reinterpret_cast<float4 *>(a.Pacc + slot * D + lane * 8);
+    dst[0] = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+    dst[1] = make_float4(acc[g][4], acc[g][5], acc[g][6], acc[g][7]);
+  }
+  if (lane < GQ) {
+    const size_t slot = (size_t)(kv * GQ + lane) * a.max_chunks + c;
+    a.Pm[slot] = mx;
+    a.Pse[slot] = se;
+  }
+}
+
 // The same chunk arithmetic as attn_split_body with ONE WARP per (chunk, KV head) item, for
 // launches with thousands of items (batched decode at long contexts, prefill passes). A chunk's
 // result depends on nothing outside the chunk, so who computes it is free; a warp on its own
@@ -377,14 +511,13 @@ __device__ __forceinline__ void s8x8_to_f32(uint2 w, float (&f)[8]) {
 // eight dims of every head: 64 sums fed by one 8-byte row piece and the token's weights.
 template <int GQ>
 __device__ __forceinline__ void attn_split_warp_body(const AttnSplitArgs &a, int blk, int nblk, unsigned char *scratch) {
-  constexpr int D = kHeadDim, C = kAttnChunk, W = 8, PF = 8;
+  constexpr int D = kHeadDim, C = kAttnChunk, W = 8;
   static_assert(GQ % 4 == 0 && 32 % GQ == 0 && C == 64, "lane partition of the warp form");
   static_assert(W * C * (GQ + 2) * 4 <= 2 * C * D, "fits the block form's K/V staging area");
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // per warp: [C][GQ] scores (then p = w * v_scale) and the C key and C value scales as floats
   float(*sc)[GQ] = reinterpret_cast<float(*)[GQ]>(scratch) + (size_t)warp * C;
-  float *scf = &sc[0][0], *vsf = reinterpret_cast<float *>(scratch) + W * C * GQ + warp * 2 * C,
-        *ksf = vsf + C;
+  float *vsf = reinterpret_cast<float *>(scratch) + W * C * GQ + warp * 2 * C, *ksf = vsf + C;
   int T = __ldcg(a.Ctrl + CTRL_LEN);
   if (T > a.max_ctx) T = a.max_ctx;  // clamp, kernels.cpp:227-228
   const int nch = (T + C - 1) / C;
@@ -394,130 +527,8 @@ __device__ __forceinline__ void attn_split_warp_body(const AttnSplitArgs &a, int
   for (int item = blk * W + warp; item < nch * a.nKV; item += nblk * W) {
     const int c = item / a.nKV, kv = item % a.nKV;
     const int t0 = c * C, nt = min(T, t0 + C) - t0;
-    const int8_t *kb = a.Kc + ((size_t)t0 * a.nKV + kv) * D + lane * 8;
-    const int8_t *vb = a.Vc + ((size_t)t0 * a.nKV + kv) * D + lane * 8;
-    uint2 ring[PF];
-#pragma unroll
-    for (int i = 0; i < PF; ++i) {
-      ring[i] = __ldcg(reinterpret_cast<const uint2 *>(kb + (size_t)min(i, nt - 1) * rs));
-    }
-    {  // scales: lane l fetches those of tokens l and l + 32
-      uint16_t ks0 = 0, ks1 = 0, vs0 = 0, vs1 = 0;
-      if (lane < nt) {
-        ks0 = __ldcg(a.Ks + (size_t)(t0 + lane) * a.nKV + kv);
-        vs0 = __ldcg(a.Vs + (size_t)(t0 + lane) * a.nKV + kv);
-      }
-      if (lane + 32 < nt) {
-        ks1 = __ldcg(a.Ks + (size_t)(t0 + lane + 32) * a.nKV + kv);
-        vs1 = __ldcg(a.Vs + (size_t)(t0 + lane + 32) * a.nKV + kv);
-      }
-      ksf[lane] = f16_to_f32(ks0);
-      ksf[lane + 32] = f16_to_f32(ks1);
-      vsf[lane] = f16_to_f32(vs0);
-      vsf[lane + 32] = f16_to_f32(vs1);
-    }
-    {
-      // ---- phase 1: scores; lane holds dims 8*lane .. 8*lane+7 of each query head of the group
-      // slot g of this lane holds head g ^ own, where `own` is the head whose score sum the lane ends
-      // up with: the shared butterfly then needs no selection by lane (warp_tree_sum_multi_permuted)
-      const int own = warp_tree_owner<GQ>(lane);
-      float q[GQ][8];
-#pragma unroll
-      for (int g = 0; g < GQ; ++g) {
-        const float4 *qp = reinterpret_cast<const float4 *>(a.Qn + (size_t)(kv * GQ + (g ^ own)) * D + lane * 8);
-        const float4 v0 = __ldcg(qp), v1 = __ldcg(qp + 1);
-        q[g][0] = v0.x; q[g][1] = v0.y; q[g][2] = v0.z; q[g][3] = v0.w;
-        q[g][4] = v1.x; q[g][5] = v1.y; q[g][6] = v1.z; q[g][7] = v1.w;
-      }
-      const bool writer = (lane & (32 / GQ - 1)) == 0;
-      __syncwarp();
-#pragma unroll 1
-      for (int b0 = 0; b0 < nt; b0 += PF) {
-#pragma unroll
-        for (int i = 0; i < PF; ++i) {
-          const int tt = b0 + i;
-          const uint2 cur = ring[i];
-          ring[i] = __ldcg(reinterpret_cast<const uint2 *>(kb + (size_t)min(tt + PF, nt - 1) * rs));
-          if (tt < nt) {
-            float kf[8];
-            s8x8_to_f32(cur, kf);
-            const float ks = ksf[tt];
-            float part[GQ];
-#pragma unroll
-            for (int g = 0; g < GQ; ++g) {
-              float acc = 0.0f;
-#pragma unroll
-              for (int j = 0; j < 8; ++j) acc = fmaf(q[g][j], kf[j], acc);
-              part[g] = acc;
-            }
-            const float r = warp_tree_sum_multi_permuted<GQ>(part, lane);
-            if (writer) sc[tt][own] = (r * ks) * scale;
-          }
-        }
-      }
-    }
-    // the first V rows travel during the softmax
-#pragma unroll
-    for (int i = 0; i < PF; ++i) {
-      ring[i] = __ldcg(reinterpret_cast<const uint2 *>(vb + (size_t)min(i, nt - 1) * rs));
-    }
-    __syncwarp();
-    // ---- phase 2: per head max, weights, sum of exp (ascending t), p = w * v_scale.
-    // Element i = lane + 32 k of the [token][head] array belongs to head lane % GQ for every k.
-    float mx = -INFINITY;
-    for (int i = lane; i < GQ * nt; i += 32) mx = fmaxf(mx, scf[i]);
-#pragma unroll
-    for (int off = GQ; off < 32; off <<= 1) mx = fmaxf(mx, __shfl_xor_sync(kFull, mx, off));
-    for (int i = lane; i < GQ * nt; i += 32) scf[i] = det_expf(scf[i] - mx);
-    __syncwarp();
-    float se = 0.0f;
-    if (lane < GQ)
-      for (int tt = 0; tt < nt; ++tt) se = se + sc[tt][lane];
-    __syncwarp();
-    for (int i = lane; i < GQ * nt; i += 32) scf[i] = scf[i] * vsf[i / GQ];
-    __syncwarp();
-    // ---- phase 3: every (head, dim) sum runs over the tokens in ascending order
-    float acc[GQ][8];
-#pragma unroll
-    for (int g = 0; g < GQ; ++g)
-#pragma unroll
-      for (int j = 0; j < 8; ++j) acc[g][j] = 0.0f;
-#pragma unroll 1
-    for (int b0 = 0; b0 < nt; b0 += PF) {
-#pragma unroll
-      for (int i = 0; i < PF; ++i) {
-        const int tt = b0 + i;
-        const uint2 cur = ring[i];
-        ring[i] = __ldcg(reinterpret_cast<const uint2 *>(vb + (size_t)min(tt + PF, nt - 1) * rs));
-        if (tt < nt) {
-          float vf[8];
-          s8x8_to_f32(cur, vf);
-#pragma unroll
-          for (int g4 = 0; g4 < GQ / 4; ++g4) {
-            const float4 pw = *reinterpret_cast<const float4 *>(&sc[tt][4 * g4]);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              acc[4 * g4 + 0][j] = fmaf(pw.x, vf[j], acc[4 * g4 + 0][j]);
-              acc[4 * g4 + 1][j] = fmaf(pw.y, vf[j], acc[4 * g4 + 1][j]);
-              acc[4 * g4 + 2][j] = fmaf(pw.z, vf[j], acc[4 * g4 + 2][j]);
-              acc[4 * g4 + 3][j] = fmaf(pw.w, vf[j], acc[4 * g4 + 3][j]);
-            }
-          }
-        }
-      }
-    }
-#pragma unroll
-    for (int g = 0; g < GQ; ++g) {
-      const size_t slot = (size_t)(kv * GQ + g) * a.max_chunks + c;
-      float4 *dst = reinterpret_cast<float4 *>(a.Pacc + slot * D + lane * 8);
-      dst[0] = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
-      dst[1] = make_float4(acc[g][4], acc[g][5], acc[g][6], acc[g][7]);
-    }
-    if (lane < GQ) {
-      const size_t slot = (size_t)(kv * GQ + lane) * a.max_chunks + c;
-      a.Pm[slot] = mx;
-      a.Pse[slot] = se;
-    }
+    if (nt == C) attn_warp_item<GQ, true>(a, c, kv, nt, sc, vsf, ksf, scale, rs, lane);
+    else attn_warp_item<GQ, false>(a, c, kv, nt, sc, vsf, ksf, scale, rs, lane);
     __syncwarp();   // the next item overwrites sc and vsf
   }
 }
