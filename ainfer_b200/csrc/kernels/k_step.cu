@@ -979,7 +979,7 @@ static __device__ __noinline__ void attn_stage_t(unsigned epoch, const StepLayer
       for (int g = 0; g < GH; ++g) acc[g] = 0.0f;
       const int8_t *vs = reinterpret_cast<const int8_t *>(kvs + C * D) + dim;
       if constexpr (GQ == 8) {   // four heads per half: one 16-byte read gives a token's four weights
-#pragma unroll 2
+#pragma unroll 8
         for (int tt = 0; tt < nt; ++tt) {
           const float v = (float)(int)vs[tt * D];
           const float4 pw = *reinterpret_cast<const float4 *>(sc + tt * GQ + g0);
@@ -1053,7 +1053,7 @@ static __device__ __noinline__ void attn_combine_stage(int T) {
       for (int ch = tid; ch < nch; ch += 256) s_pm[ch] = det_expf(s_pm[ch] - M);
       hsync();
       for (int ch = 0; ch < nch; ++ch) se = fmaf(s_pf[ch], s_pm[ch], se);
-#pragma unroll 8
+#pragma unroll 16
       for (int ch = 0; ch < nch; ++ch) acc = fmaf(__ldcg(pacc + (size_t)ch * D + tid), s_pm[ch], acc);
     } else {
       for (int ch = 0; ch < nch; ++ch) M = fmaxf(M, __ldcg(pm + ch));
