@@ -90,6 +90,9 @@ struct Session {
   int max_chunks = 0;
   int argmax_parts = 0;
   Prefill *prefill = nullptr;   // created on the first ainfer_session_prefill
+  // expert parallelism of the prefill's MoE block (ainfer_session_prefill_ep): world 1 = none
+  int pf_rank = 0, pf_world = 1;
+  unsigned char pf_id[128] = {0};
   // device sampler scratch (created on first use): probabilities, marks, seen ids, {rng state, token}
   double *samp_work = nullptr; unsigned char *samp_mark = nullptr; int32_t *samp_seen = nullptr; uint64_t *samp_io = nullptr;
   Prefill *verifier = nullptr;  // rows of the MTP loop's batched verification (created on first use)
@@ -100,7 +103,10 @@ int session_create(DeviceModel *m, int max_ctx, int flags, Session **out, std::s
 // without producing logits; bit-identical to n decode steps. The object holds the row buffers.
 struct Prefill;
 // rows_cap: rows per pass (1..64); verify: also allocate what per-row predictions and rollback need.
-int prefill_create(Session *s, int rows_cap, bool verify, Prefill **out);
+// ep_world > 1: the MoE block of every pass runs expert-parallel over that many ranks (id128: the NCCL
+// id shared by the ranks); every rank then has to run the same passes (prompts of one length).
+int prefill_create(Session *s, int rows_cap, bool verify, Prefill **out, int ep_rank = 0, int ep_world = 1,
+                   const void *id128 = nullptr);
 void prefill_destroy(Prefill *p);
 int prefill_run(Prefill *p, const int *tokens, int n, int start_pos, int *predictions);
 int prefill_rollback(Prefill *p, int keep);

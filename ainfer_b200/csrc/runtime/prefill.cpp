@@ -130,7 +130,7 @@ struct Launcher {   // immediate launches, or appended to recorded lists; argume
 
 }  // namespace
 
-int prefill_create(Session *s, int rows_cap, bool verify, Prefill **out) {
+int prefill_create(Session *s, int rows_cap, bool verify, Prefill **out, int ep_rank, int ep_world, const void *id128) {
   const ModelConfig &c = s->m->cfg;
   Prefill *p = new Prefill;
   p->s = s;
@@ -155,7 +155,8 @@ int prefill_create(Session *s, int rows_cap, bool verify, Prefill **out) {
     r |= palloc(p, (size_t)R * p->snap_s_stride, &p->SnapS); r |= palloc(p, (size_t)R * p->snap_c_stride, &p->SnapC);
   }
   if (!r) {
-    int e = p->ep.create(s->m, nullptr, 0, 1, R, EP_RES_ADD);
+    // the expert-parallel block counts rows over all ranks: every rank brings R of them
+    int e = p->ep.create(s->m, ep_world > 1 ? id128 : nullptr, ep_rank, ep_world, R * ep_world, EP_RES_ADD);
     if (e) { s->err = "prefill: " + p->ep.err; r = e; }
     else p->ep_ready = true;
   }

@@ -162,11 +162,22 @@ int ainfer_session_prefill(ainfer_session_t h, const int *tokens, int n, int sta
   if (!h || (!tokens && n > 0)) return set_err(2, "usage: null argument");
   Session *s = h->s;
   if (!s->prefill) {
-    int r = prefill_create(s, 64, false, &s->prefill);
+    // the expert-parallel block takes at most 64 rows over all ranks
+    int r = prefill_create(s, 64 / s->pf_world, false, &s->prefill, s->pf_rank, s->pf_world, s->pf_id);
     if (r) return set_err(r, s->err);
   }
   int r = prefill_run(s->prefill, tokens, n, start_pos, nullptr);
   return set_err(r, s->err);
+}
+int ainfer_session_prefill_ep(ainfer_session_t h, const void *id128, int rank, int world) {
+  if (!h) return set_err(2, "usage: null argument");
+  Session *s = h->s;
+  if (world < 1 || world > 64 || 64 % world || rank < 0 || rank >= world || (world > 1 && !id128))
+    return set_err(2, "usage: 0 <= rank < world, world divides 64, and an id for more than one rank");
+  if (s->prefill) { prefill_destroy(s->prefill); s->prefill = nullptr; }
+  s->pf_rank = rank; s->pf_world = world;
+  if (id128) std::memcpy(s->pf_id, id128, 128);
+  return 0;
 }
 int ainfer_session_step(ainfer_session_t s, int token, int pos, int *out_token) {
   if (!s) return 2;

@@ -43,6 +43,7 @@ SIGNATURES = {
     "ainfer_session_buffer": (_i, [_vp, C.c_char_p, _pp, C.POINTER(_u64)]),
     "ainfer_session_step": (_i, [_vp, _i, _i, C.POINTER(_i)]),
     "ainfer_session_prefill": (_i, [_vp, C.POINTER(_i), _i, _i]),
+    "ainfer_session_prefill_ep": (_i, [_vp, C.c_char_p, _i, _i]),
     "ainfer_session_generate": (_i, [_vp, C.POINTER(_i), _i, _i, _i, C.POINTER(_i), C.POINTER(C.c_float)]),
     "ainfer_session_logits": (_i, [_vp, _vp]),
     "ainfer_session_sample": (_i, [_vp, C.POINTER(SampleParams), _vp, _i, C.POINTER(_u64), C.POINTER(_i)]),
@@ -214,6 +215,11 @@ class Session:
         """Advances the state over the tokens in chunks of up to 64 rows (no logits)."""
         t = np.ascontiguousarray(tokens, np.int32)
         _check(load().ainfer_session_prefill(self.h, t.ctypes.data_as(C.POINTER(C.c_int)), len(t), int(start_pos)))
+
+    def prefill_ep(self, rank, world, nccl_id=None):
+        """Expert parallelism for this session's prefill: every rank prefills its own sequence of the
+        same length, passes of 64 / world rows; nccl_id = ep_unique_id() of one rank."""
+        _check(load().ainfer_session_prefill_ep(self.h, nccl_id, int(rank), int(world)))
 
     def mtp_draft(self, next_token, pos, from_trunk=True):
         """One draft of the MTP head (hidden input: the trunk's last residual, or chained)."""

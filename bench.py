@@ -398,6 +398,43 @@ def run_batch(args, dev, model, rank, world, dist):
             "cache_fill": "seeded INT8 pattern and fp16 scales (not decoded prompts)"}
 
 
+def run_prefill_ep(args, dev, model, rank, world, dist):
+    """Prefill with expert parallelism (N > 1): every rank prefills its own seeded prompt of the same
+    length, passes of 64 / N rows, the MoE block of each pass exchanged between the ranks (NCCL
+    all-to-all inside the timed region). Wall clock around the call after a device sync, max over ranks."""
+    from ainfer_b200 import runtime
+    if world == 1 or 64 % world or model.config["experts"] % world:
+        return None
+    import torch
+    t = torch.zeros(128, dtype=torch.uint8, device="cuda")
+    if rank == 0:
+        t = torch.frombuffer(bytearray(runtime.ep_unique_id()), dtype=torch.uint8).cuda()
+    dist.broadcast(t, 0)
+    nid = bytes(t.cpu().numpy().tobytes())
+    n_tok = args.prefill_ep_tokens
+    try:
+        sess = runtime.Session(model, n_tok + 16)
+        sess.prefill_ep(rank, world, nid)
+        prompt = prompt_ids(model.config["vocab"], n_tok, seed=100 + rank)
+        sess.prefill(prompt[:2 * (64 // world)])     # creates the row buffers and the communicator, records the MoE lists
+        sess.reset()
+        dev.sync()
+        dist.barrier()
+        t0 = time.time()
+        sess.prefill(prompt)
+        dev.sync()
+        sec = time.time() - t0
+    except Exception as e:
+        return {"skipped": f"expert-parallel prefill failed: {str(e)[:200]}"}
+    tt = torch.tensor([sec], device="cuda", dtype=torch.float64)
+    dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    sec = float(tt[0])
+    sess.close()
+    return {"workload": f"prefill of {n_tok} seeded tokens on each of {world} ranks (one sequence per rank), passes of {64 // world} rows, experts split over the ranks",
+            "tokens_per_s": world * n_tok / sec, "seconds": sec, "prompt_tokens_per_rank": n_tok, "world": world,
+            "rows_per_pass": 64 // world, "scaling": "weak"}
+
+
 def run_ours(args):
     rank, local_rank, world = dist_env()
     dist = None
@@ -473,6 +510,7 @@ def run_ours(args):
         gen_ms, t_e2e = float(t[0]), float(t[1])
     ep_line = None if args.no_ep else run_ep(args, dev, model, rank, world, dist)
     batch_line = None if args.no_batch else run_batch(args, dev, model, rank, world, dist)
+    prefill_ep_line = None if (args.no_batch or world == 1) else run_prefill_ep(args, dev, model, rank, world, dist)
     mtp_line = None
     if rank == 0 and not args.no_mtp:
         try:
@@ -569,6 +607,7 @@ def run_ours(args):
                     "ms_per_step_max": float(np.max(win_ms))},
         "clocks": clk, "roofline": roof, "gemv_sweep": sweep,
         "cpu_baseline": cpu, "parity": parity, "ep": ep_line, "batch_decode": batch_line, "mtp": mtp_line,
+        "prefill_ep": prefill_ep_line,
         "prefill": None if args.loop_prompt else {"prompt_tokens": P - 1, "seconds": t_prompt_only, "tokens_per_s": (P - 1) / max(t_prompt_only, 1e-9),
                                                   "how": "chunked prefill, 64 rows per pass, one sequence (wall clock around the call, this rank)"},
         "timing": {"model_fill_s": t_load, "prompt_s": t_prompt, "prompt_by": "token-by-token decode" if args.loop_prompt else "chunked prefill (64 rows per pass)", "timed_wall_s": t_wall, "first_tokens": [int(t) for t in toks0[:8]]},
@@ -598,6 +637,7 @@ def main():
     ap.add_argument("--batch-ctx", type=int, default=32768)
     ap.add_argument("--batch-steps", type=int, default=8)
     ap.add_argument("--batch-warmup", type=int, default=2)
+    ap.add_argument("--prefill-ep-tokens", type=int, default=1024, help="prompt length per rank of the expert-parallel prefill (N > 1)")
     ap.add_argument("--no-ep", action="store_true", help="skip the expert-parallel MoE stack")
     ap.add_argument("--ep-batch", type=int, default=64)
     ap.add_argument("--ep-steps", type=int, default=5)

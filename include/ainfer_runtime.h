@@ -99,6 +99,15 @@ int ainfer_session_generate(ainfer_session_t s, const int *prompt, int P, int G,
  * of tools/cmdlist/chunklayer_replay.cpp:366-443). The state afterwards is bit-identical to n calls
  * of ainfer_session_step; follow with ainfer_session_generate(s, &last_prompt_id, 1, G, start_pos + n, ...). */
 int ainfer_session_prefill(ainfer_session_t s, const int *tokens, int n, int start_pos);
+/* Expert parallelism for this session's prefill (config "prefill ... at 8 GPUs with expert
+ * parallelism"): every rank prefills its OWN sequence, the MoE block of each pass exchanges rows
+ * with the ranks that hold the routed experts (512 / world experts per rank, the all-to-all of
+ * ainfer_ep_*), everything else stays on the rank. id128: ainfer_ep_unique_id of one rank, handed
+ * to all. Passes hold 64 / world rows, and the exchanges are collective: every rank must prefill
+ * the same number of tokens in the same calls. Call before the first ainfer_session_prefill (a
+ * later call drops the prefill object); world == 1 switches back. The state a rank ends with is
+ * bit-identical to the one-GPU prefill of the same tokens. */
+int ainfer_session_prefill_ep(ainfer_session_t s, const void *id128, int rank, int world);
 /* ---- MTP head (multi-token prediction; dataflow of tools/t72/mtp_accept.py:11-16,142-151) ----
  * x = fc . quant([rms1w(embed(next_token)) ; rms1w(h)]) -> one full-attention decoder layer with
  * its own KV cache and MoE -> mtp.norm -> shared lm_head -> argmax. h is the trunk's final
