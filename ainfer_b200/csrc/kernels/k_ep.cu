@@ -36,63 +36,88 @@ struct RouterLogitsRowsArgs {
 // order, then the lane tree). The row's first chunk of weights is fetched once, and four tokens
 // are summed side by side: a token's sum is one chain of dependent additions per lane, so four
 // chains in flight is what keeps the lanes busy.
-__global__ void __launch_bounds__(256, 2) RouterLogitsRows(const RouterLogitsRowsArgs a) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int nrows = a.E + (a.Wsg ? 1 : 0), n = a.H / 256;
-  const int nrb = (a.E + 1 + 7) / 8, rb = blockIdx.x % nrb, tb = blockIdx.x / nrb;
-  const int t_end = (tb + 1) * a.tokens_per_block < a.rows ? (tb + 1) * a.tokens_per_block : a.rows;
-  {
-    const int e = rb * 8 + warp;
-    if (e >= nrows) return;
-    const uint16_t *w = e < a.E ? a.Wr + (size_t)e * a.H : a.Wsg;
-    const float bias = a.Bias && e < a.E ? __ldg(a.Bias + e) : 0.0f;
-    RouterRowRegs r0;
-    router_row_load(r0, w, 0, n, lane);
-    for (int t = tb * a.tokens_per_block; t < t_end; t += 4) {
-      float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-      RouterRowRegs r = r0;
-      const float *hn[4];
+// kSmem: the block's tokens' activations were staged in shared memory (hn points there, token stride H)
+template <bool kSmem>
+__device__ __forceinline__ void router_rows_compute(const RouterLogitsRowsArgs &a, const uint16_t *w, const RouterRowRegs &r0,
+                                                    const float *hn_base, int t_begin, int t_end, int e, bool store, float bias,
+                                                    int lane) {
+  const int n = a.H / 256;
+  for (int t = t_begin; t < t_end; t += 4) {
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    RouterRowRegs r = r0;
+    const float *hn[4];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) hn[u] = a.Hn + (size_t)(t + u < t_end ? t + u : t_end - 1) * a.H;   // past the end: the last token again, not stored
-      for (int i0 = 0;;) {
+    for (int u = 0; u < 4; ++u) hn[u] = hn_base + (size_t)((t + u < t_end ? t + u : t_end - 1) - (kSmem ? t_begin : 0)) * a.H;   // past the end: the last token again, not stored
+    for (int i0 = 0;;) {
 #pragma unroll
-        for (int c = 0; c < kRouterChunk; ++c) {
-          const int ic = i0 + c < n ? i0 + c : n - 1, k0 = (ic * 32 + lane) * 8;
-          float4 x0[4], x1[4];
+      for (int c = 0; c < kRouterChunk; ++c) {
+        const int ic = i0 + c < n ? i0 + c : n - 1, k0 = (ic * 32 + lane) * 8;
+        float4 x0[4], x1[4];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < 4; ++u) {
+          if (kSmem) {
+            x0[u] = *reinterpret_cast<const float4 *>(hn[u] + k0);
+            x1[u] = *reinterpret_cast<const float4 *>(hn[u] + k0 + 4);
+          } else {
             x0[u] = __ldcg(reinterpret_cast<const float4 *>(hn[u] + k0));
             x1[u] = __ldcg(reinterpret_cast<const float4 *>(hn[u] + k0 + 4));
           }
-          if (i0 + c < n) {
-            const uint4 wv = r.w[c];
-            const float w0 = u2f(wv.x << 16), w1 = u2f(wv.x & 0xFFFF0000u), w2 = u2f(wv.y << 16), w3 = u2f(wv.y & 0xFFFF0000u),
-                        w4 = u2f(wv.z << 16), w5 = u2f(wv.z & 0xFFFF0000u), w6 = u2f(wv.w << 16), w7 = u2f(wv.w & 0xFFFF0000u);
+        }
+        if (i0 + c < n) {
+          const uint4 wv = r.w[c];
+          const float w0 = u2f(wv.x << 16), w1 = u2f(wv.x & 0xFFFF0000u), w2 = u2f(wv.y << 16), w3 = u2f(wv.y & 0xFFFF0000u),
+                      w4 = u2f(wv.z << 16), w5 = u2f(wv.z & 0xFFFF0000u), w6 = u2f(wv.w << 16), w7 = u2f(wv.w & 0xFFFF0000u);
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {   // router_row_fma's order for each token
-              float s = acc[u];
-              s = fmaf(w0, x0[u].x, s);
-              s = fmaf(w1, x0[u].y, s);
-              s = fmaf(w2, x0[u].z, s);
-              s = fmaf(w3, x0[u].w, s);
-              s = fmaf(w4, x1[u].x, s);
-              s = fmaf(w5, x1[u].y, s);
-              s = fmaf(w6, x1[u].z, s);
-              s = fmaf(w7, x1[u].w, s);
-              acc[u] = s;
-            }
+          for (int u = 0; u < 4; ++u) {   // router_row_fma's order for each token
+            float s = acc[u];
+            s = fmaf(w0, x0[u].x, s);
+            s = fmaf(w1, x0[u].y, s);
+            s = fmaf(w2, x0[u].z, s);
+            s = fmaf(w3, x0[u].w, s);
+            s = fmaf(w4, x1[u].x, s);
+            s = fmaf(w5, x1[u].y, s);
+            s = fmaf(w6, x1[u].z, s);
+            s = fmaf(w7, x1[u].w, s);
+            acc[u] = s;
           }
         }
-        i0 += kRouterChunk;
-        if (i0 >= n) break;
-        router_row_load(r, w, i0, n, lane);
       }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const float sum = warp_tree_sum(acc[u]);
-        if (lane == 0 && t + u < t_end) a.Logits[(size_t)(t + u) * (a.E + 1) + e] = a.Bias ? sum + bias : sum;
-      }
+      i0 += kRouterChunk;
+      if (i0 >= n) break;
+      router_row_load(r, w, i0, n, lane);
     }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const float sum = warp_tree_sum(acc[u]);
+      if (lane == 0 && store && t + u < t_end) a.Logits[(size_t)(t + u) * (a.E + 1) + e] = a.Bias ? sum + bias : sum;
+    }
+  }
+}
+constexpr int kRouterStageFloats = 8192;   // 32 KB: four tokens of 2048
+__global__ void __launch_bounds__(256, 2) RouterLogitsRows(const RouterLogitsRowsArgs a) {
+  // The block's tokens are read by all eight warps: staged once in shared memory they cross from
+  // L2 once per block instead of once per warp (at 64 tokens and 513 rows the per-warp reads were
+  // 266 MB a launch, and the launch took as long as that takes).
+  __shared__ __align__(16) float hs[kRouterStageFloats];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nrows = a.E + (a.Wsg ? 1 : 0), n = a.H / 256;
+  const int nrb = (a.E + 1 + 7) / 8, rb = blockIdx.x % nrb, tb = blockIdx.x / nrb;
+  const int t_begin = tb * a.tokens_per_block;
+  const int t_end = t_begin + a.tokens_per_block < a.rows ? t_begin + a.tokens_per_block : a.rows;
+  const int e_raw = rb * 8 + warp, e = e_raw < nrows ? e_raw : nrows - 1;   // a warp past the last row repeats it and stores nothing
+  const uint16_t *w = e < a.E ? a.Wr + (size_t)e * a.H : a.Wsg;
+  const float bias = a.Bias && e < a.E ? __ldg(a.Bias + e) : 0.0f;
+  RouterRowRegs r0;
+  router_row_load(r0, w, 0, n, lane);
+  const bool staged = (t_end - t_begin) * a.H <= kRouterStageFloats;   // the same for every thread of the block
+  if (staged) {
+    const float4 *src = reinterpret_cast<const float4 *>(a.Hn + (size_t)t_begin * a.H);
+    const int n4 = (t_end - t_begin) * a.H / 4;
+    for (int i = threadIdx.x; i < n4; i += 256) reinterpret_cast<float4 *>(hs)[i] = __ldcg(src + i);
+    __syncthreads();
+    router_rows_compute<true>(a, w, r0, hs, t_begin, t_end, e, e_raw < nrows, bias, lane);
+  } else {
+    router_rows_compute<false>(a, w, r0, a.Hn, t_begin, t_end, e, e_raw < nrows, bias, lane);
   }
 }
 struct RouterSelectRowsArgs {
