@@ -58,6 +58,14 @@ struct Rec {   // appends launches to a list; arguments by index in member order
              Y, (int32_t)N, (int32_t)K, (int32_t)rows, (int32_t)N);
       return;
     }
+    if (row_slabs_pay(N, K, rows)) {
+      // few output rows: slabs of eight rows through the dp4a kernel beat the tensor-core kernel's latency (row_slabs.h)
+      RowSlabs sl;
+      if (row_slabs_get(b->dev, b->slabs, b->owned, t, rows, &sl, b->err)) { status = 1; return; }
+      launch("Int4GemvA8MultiGrouped", 2u * (uint32_t)b->sm_count, (const void *)sl.groups, (const int32_t *)sl.count, XQ, SQ, Y, (int32_t)N,
+             (int32_t)K, (int32_t)N);
+      return;
+    }
     const uint32_t tiles = (uint32_t)((N + 127) / 128);
     launch("Int4GemmA8Tc", std::min<uint32_t>(tiles, 2u * (uint32_t)b->sm_count), (const uint8_t *)t.data, (const uint16_t *)t.scales, XQ, SQ, Y,
            (int32_t)N, (int32_t)K, (int32_t)rows, (int32_t)N);

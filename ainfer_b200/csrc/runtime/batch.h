@@ -6,6 +6,7 @@
 
 #include "ep.h"
 #include "model.h"
+#include "row_slabs.h"
 
 namespace ainfer {
 
@@ -31,6 +32,7 @@ struct BatchDecode {
   ainfer_list_t embed_list = nullptr, tail_list = nullptr;
   std::map<std::string, ainfer_kernel_t> kernels;
   std::vector<void *> owned;
+  RowSlabCache slabs;   // problem lists of the GEMMs with few output rows (row_slabs.h)
 
   // Returns 0, 1 (device / NCCL error) or 2 (usage); err holds the message.
   int create(DeviceModel *model, const void *id128, int rank, int world, int batch, int max_ctx, int flags);

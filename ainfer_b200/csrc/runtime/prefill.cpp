@@ -24,6 +24,7 @@
 
 #include "ep.h"
 #include "executor.h"
+#include "row_slabs.h"
 
 namespace ainfer {
 
@@ -47,6 +48,7 @@ struct Prefill {
   float *Q16 = nullptr, *K16 = nullptr, *V16 = nullptr;
   float *Qn = nullptr, *Pm = nullptr, *Pse = nullptr, *Pacc = nullptr;   // per-row attention scratch
   std::map<std::string, ainfer_kernel_t> kernels;
+  RowSlabCache slabs;   // problem lists of the GEMMs with few output rows (row_slabs.h)
 };
 
 namespace {
@@ -120,6 +122,14 @@ struct Launcher {   // immediate launches, or appended to recorded lists; argume
       const uint32_t tiles = (uint32_t)((N + 256 / G - 1) / (256 / G));
       launch("Int4GemvA8Multi", std::min<uint32_t>(tiles, 2u * (uint32_t)s->sm_count), (const uint8_t *)t.data, (const uint16_t *)t.scales, XQ, SQ,
              Y, (int32_t)N, (int32_t)K, (int32_t)rows, (int32_t)N);
+      return;
+    }
+    if (row_slabs_pay(N, K, rows)) {
+      // few output rows: slabs of eight rows through the dp4a kernel beat the tensor-core kernel's latency (row_slabs.h)
+      RowSlabs sl;
+      if (row_slabs_get(s->dev, p->slabs, p->owned, t, rows, &sl, s->err)) { status = 1; return; }
+      launch("Int4GemvA8MultiGrouped", 2u * (uint32_t)s->sm_count, (const void *)sl.groups, (const int32_t *)sl.count, XQ, SQ, Y, (int32_t)N,
+             (int32_t)K, (int32_t)N);
       return;
     }
     const uint32_t tiles = (uint32_t)((N + 127) / 128);
