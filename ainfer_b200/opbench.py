@@ -417,6 +417,8 @@ def main(argv=None):
             st = sess.read("stage_stamps", np.uint64)
             half = len(st) // 2
             mask = (1 << 48) - 1
+            nz = st[st != 0]
+            origin = int(min(int(t) & mask for t in nz)) if len(nz) else 0   # both lists on one time axis
             for name, part in (("consumer", st[:half]), ("producer", st[half:])):
                 part = part[part != 0]
                 ev = [(int(t) >> 48, int(t) & mask) for t in part]
@@ -424,7 +426,8 @@ def main(argv=None):
                 for (i, t) in ev:
                     out.append([i, round((t - prev) / 1000.0, 2)])
                     prev = t
-                print(json.dumps({"op": "stage_clock", "who": name, "unit": "us", "events": out}), flush=True)
+                print(json.dumps({"op": "stage_clock", "who": name, "unit": "us", "events": out,
+                                  "at_us": [round((t - origin) / 1000.0, 2) for (_, t) in ev]}), flush=True)
         sess.close(); model.close()
     dev.close()
     return 0
