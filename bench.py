@@ -282,6 +282,27 @@ def run_ep(args, dev, model, rank, world, dist):
     else:
         items_max = items_sum = float(items)
     ep.close()
+    # The exchange an all-reduce form of the block would need instead of the two all-to-alls: one
+    # fp32 sum of the batch's partial outputs [B][H] over the ranks per layer (the library's
+    # collective on the framework's communicator; device events, max over ranks). Not the product
+    # path: its sum order is the collective's, not the slot order the parity contract fixes.
+    allreduce_us = None
+    if dist is not None:
+        import torch
+        buf = torch.zeros(B * H, device="cuda", dtype=torch.float32)
+        for _ in range(10):
+            dist.all_reduce(buf)
+        torch.cuda.synchronize()
+        dist.barrier()
+        a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a0.record()
+        for _ in range(100):
+            dist.all_reduce(buf)
+        a1.record()
+        torch.cuda.synchronize()
+        tt = torch.tensor([a0.elapsed_time(a1) * 10.0], device="cuda", dtype=torch.float64)   # us per call
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        allreduce_us = float(tt[0])
     med = float(np.median(passes))
     I, k = cfg["expert_intermediate"], cfg["top_k"]
     return {"workload": f"batch {B} through the MoE block of {L} layers, experts sharded over {world} rank(s), Zipf(1.1) router bias",
@@ -291,6 +312,7 @@ def run_ep(args, dev, model, rank, world, dist):
             "exchange": "NCCL send/recv all-to-all, fixed-size slots" if world > 1 else "none (one rank)",
             "segments_us_per_layer_rank0": dict(zip(("route_pack", "dispatch", "experts", "return", "shared_combine"),
                                                     [round(x * 1000.0 / L, 2) for x in seg])),
+            "allreduce_variant_exchange_us_per_layer": allreduce_us,
             "last_layer_items": {"max_rank": items_max, "mean_rank": items_sum / world, "total": B * k},
             "expert_bytes_per_layer_all_ranks_upper": cfg["experts"] * 3 * H * I * (0.5 + 2.0 / 128)}
 
