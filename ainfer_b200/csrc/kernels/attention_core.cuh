@@ -603,7 +603,7 @@ __device__ __forceinline__ void attn_combine_body(const AttnCombineArgs &a, int 
       for (int c = tid; c < nch; c += 256) s_pm[c] = det_expf(s_pm[c] - M);
       __syncthreads();
       for (int c = 0; c < nch; ++c) se = fmaf(s_pf[c], s_pm[c], se);
-#pragma unroll 16
+#pragma unroll 32
       for (int c = 0; c < nch; ++c) acc = fmaf(__ldcg(pacc + (size_t)c * D + tid), s_pm[c], acc);
     } else {
 #pragma unroll 8
