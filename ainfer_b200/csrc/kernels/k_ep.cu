@@ -211,6 +211,7 @@ struct EpGroupArgs {
   // (the owner's quantiser writes them there). shared_rows == 0: none.
   int32_t shared_row0, shared_rows, shared_expert;
   int32_t small_rows;   // problems up to this many rows go to the first pair of lists (a large value: all of them)
+  int32_t max_rows;     // an expert with more rows is cut into problems of at most this many (same weights, consecutive rows)
 };
 // One block. Items are numbered (source rank, index) in ascending order; an item's row in the
 // grouped layout is the start of its expert's range plus the number of earlier items of the same
@@ -244,7 +245,8 @@ __global__ void __launch_bounds__(1024) EpGroup(const EpGroupArgs a) {
     int run = 0, nact = 0, nactl = 0;
     for (int e0 = 0; e0 < a.experts_per_rank; e0 += 32) {
       const int e = e0 + tid;
-      const int c = e < a.experts_per_rank ? hist[e] : 0, f = c > 0 && c <= a.small_rows, fl = c > a.small_rows;
+      const int c = e < a.experts_per_rank ? hist[e] : 0, f = c > 0 && c <= a.small_rows;
+      const int fl = c > a.small_rows ? (c + a.max_rows - 1) / a.max_rows : 0;   // problems in the many-row lists
       int sc = c, sf = f, sl = fl;
 #pragma unroll
       for (int off = 1; off < 32; off <<= 1) {
@@ -257,13 +259,18 @@ __global__ void __launch_bounds__(1024) EpGroup(const EpGroupArgs a) {
       nactl += __shfl_sync(kFull, sl, 31);
     }
     if (tid == 0) {
-      const int sh = a.shared_rows > 0 && a.shared_rows <= a.small_rows ? 1 : 0, shl = a.shared_rows > a.small_rows ? 1 : 0;
+      const int sh = a.shared_rows > 0 && a.shared_rows <= a.small_rows ? 1 : 0;
+      const int shl = a.shared_rows > a.small_rows ? (a.shared_rows + a.max_rows - 1) / a.max_rows : 0;
       if (sh || shl) {
         const ExpertW w = a.Experts[a.shared_expert];
-        EpTcGroup *gu = sh ? a.GroupsGateUp + 2 * nact : a.GroupsGateUpL + 2 * nactl, *gd = sh ? a.GroupsDown + nact : a.GroupsDownL + nactl;
-        gu[0] = EpTcGroup{w.gP, w.gS, a.shared_row0, a.shared_rows, 0, 0};
-        gu[1] = EpTcGroup{w.uP, w.uS, a.shared_row0, a.shared_rows, a.I, 0};
-        gd[0] = EpTcGroup{w.dP, w.dS, a.shared_row0, a.shared_rows, 0, 0};
+        const int cut = sh ? a.shared_rows : a.max_rows;
+        for (int j = 0; j < sh + shl; ++j) {
+          const int r0 = a.shared_row0 + j * cut, mr = min(cut, a.shared_rows - j * cut);
+          EpTcGroup *gu = sh ? a.GroupsGateUp + 2 * nact : a.GroupsGateUpL + 2 * (nactl + j), *gd = sh ? a.GroupsDown + nact : a.GroupsDownL + nactl + j;
+          gu[0] = EpTcGroup{w.gP, w.gS, r0, mr, 0, 0};
+          gu[1] = EpTcGroup{w.uP, w.uS, r0, mr, a.I, 0};
+          gd[0] = EpTcGroup{w.dP, w.dS, r0, mr, 0, 0};
+        }
       }
       *reinterpret_cast<int4 *>(a.Counts) = make_int4(total, 2 * (nact + sh), nact + sh, 2 * (nactl + shl));
       *reinterpret_cast<int4 *>(a.Counts + 4) = make_int4(nactl + shl, 0, 0, 0);
@@ -276,10 +283,14 @@ __global__ void __launch_bounds__(1024) EpGroup(const EpGroupArgs a) {
       const ExpertW w = a.Experts[a.rank * a.experts_per_rank + e];
       const bool large = active[e] >= (1 << 20);
       const int g = active[e] & ((1 << 20) - 1);
-      EpTcGroup *gu = (large ? a.GroupsGateUpL : a.GroupsGateUp) + 2 * g, *gd = (large ? a.GroupsDownL : a.GroupsDown) + g;
-      gu[0] = EpTcGroup{w.gP, w.gS, start[e], c, 0, 0};
-      gu[1] = EpTcGroup{w.uP, w.uS, start[e], c, a.I, 0};
-      gd[0] = EpTcGroup{w.dP, w.dS, start[e], c, 0, 0};
+      const int cut = large ? a.max_rows : c, np = (c + cut - 1) / cut;
+      for (int j = 0; j < np; ++j) {
+        const int r0 = start[e] + j * cut, mr = min(cut, c - j * cut);
+        EpTcGroup *gu = (large ? a.GroupsGateUpL : a.GroupsGateUp) + 2 * (g + j), *gd = (large ? a.GroupsDownL : a.GroupsDown) + g + j;
+        gu[0] = EpTcGroup{w.gP, w.gS, r0, mr, 0, 0};
+        gu[1] = EpTcGroup{w.uP, w.uS, r0, mr, a.I, 0};
+        gd[0] = EpTcGroup{w.dP, w.dS, r0, mr, 0, 0};
+      }
     }
   }
   for (int it = tid; it < total; it += blockDim.x) {
@@ -411,7 +422,7 @@ AINFER_REGISTER(EpPack, EpPackArgs, 128, 1, 0, nullptr, F(Q8), F(SQ), F(ItemDest
 #undef F
 #define F(f) AINFER_ARG(EpGroupArgs, f)
 AINFER_REGISTER(EpGroup, EpGroupArgs, 1024, 0, 0, nullptr, F(Recv), F(Experts), F(Sorted), F(GroupsGateUp), F(GroupsDown), F(GroupsGateUpL), F(GroupsDownL), F(Counts), F(world),
-                F(rank), F(experts_per_rank), F(cap), F(I), F(slot_bytes), F(shared_row0), F(shared_rows), F(shared_expert), F(small_rows));
+                F(rank), F(experts_per_rank), F(cap), F(I), F(slot_bytes), F(shared_row0), F(shared_rows), F(shared_expert), F(small_rows), F(max_rows));
 #undef F
 #define F(f) AINFER_ARG(EpGatherArgs, f)
 AINFER_REGISTER(EpGather, EpGatherArgs, 128, 1, 0, nullptr, F(Recv), F(Sorted), F(Counts), F(XQ), F(SQ), F(H), F(cap), F(slot_bytes));

@@ -147,13 +147,15 @@ int EpMoe::create(DeviceModel *model, const void *id128, int rank_, int world_, 
   const ModelConfig &c = m->cfg;
   H = c.hidden; E = c.experts; k = c.top_k; I = c.expert_inter; shared = c.shared_experts != 0;
   if (world < 1 || world > 64 || rank < 0 || rank >= world) { err = "usage: 0 <= rank < world <= 64"; return 2; }
-  if (batch < world || batch % world || batch / world > 64) { err = "usage: the batch must divide over the ranks, at most 64 rows per rank"; return 2; }
+  if (batch < world || batch % world) { err = "usage: the batch must divide over the ranks"; return 2; }
   if (E % world) { err = "usage: the experts must divide evenly over the ranks"; return 2; }
   if (E > 1024 || H % 256 || I % 128) { err = "usage: unsupported shape (experts <= 1024, hidden % 256 == 0, intermediate % 128 == 0)"; return 2; }
   n = batch / world;
   epr = E / world;
   cap = n * k;
-  if (cap > 2048 || batch * k > 2048 || batch > 64) { err = "usage: batch x top-k above the planner's limit (2048 items, 64 rows)"; return 2; }
+  if (cap > 2048 || batch * k > 2048) { err = "usage: batch x top-k above the planner's limit (2048 items)"; return 2; }
+  // shapes the dp4a kernel does not take run every expert as one tensor-core problem, which holds at most 64 rows
+  if (batch > 64 && !(256 % (H / 128) == 0 && 256 % (I / 128) == 0)) { err = "usage: more than 64 rows need hidden and intermediate sizes whose group counts divide 256"; return 2; }
   slot_d = (uint32_t)((16 + (size_t)cap * 16 + (size_t)cap * item_bytes(H) + 15) & ~(size_t)15);
   slot_r = (uint32_t)((size_t)cap * H * 4);
   ainfer_device_info info;
@@ -171,7 +173,8 @@ int EpMoe::create(DeviceModel *model, const void *id128, int rank_, int world_, 
   r |= alloc(&Ret, (size_t)world * slot_r); r |= alloc(&Back, (size_t)world * slot_r);
   r |= alloc(&Sorted, (size_t)rows * 4); r |= alloc(&Counts, 32);
   r |= alloc(&GroupsGU, (size_t)2 * (epr + 1) * 32); r |= alloc(&GroupsD, (size_t)(epr + 1) * 32);
-  r |= alloc(&GroupsGUL, (size_t)2 * (epr + 1) * 32); r |= alloc(&GroupsDL, (size_t)(epr + 1) * 32);
+  const size_t nlarge = (size_t)epr + 1 + (size_t)rows / 64 + (size_t)n / 64 + 2;   // an expert with more than 64 rows is cut into 64-row problems
+  r |= alloc(&GroupsGUL, 2 * nlarge * 32); r |= alloc(&GroupsDL, nlarge * 32);
   r |= alloc(&XQs, (size_t)(rows + n) * H); r |= alloc(&SQs, (size_t)(rows + n) * G * 4);
   r |= alloc(&GU, (size_t)(rows + shn) * 2 * I * 4); r |= alloc(&AQ, (size_t)(rows + shn) * I);
   r |= alloc(&ASQ, (size_t)(rows + shn) * (I / 128) * 4);
@@ -241,7 +244,7 @@ int EpMoe::record_layer(int L) {
   const bool multi_ok = 256 % (H / 128) == 0 && 256 % (I / 128) == 0;
   r.launch("EpGroup", 1u, (const unsigned char *)Recv, tab, Sorted, GroupsGU, GroupsD, GroupsGUL, GroupsDL, Counts, (int32_t)world, (int32_t)rank, (int32_t)epr,
            (int32_t)cap, (int32_t)I, slot_d, (int32_t)rows, (int32_t)(shared ? n : 0), (int32_t)E,
-           (int32_t)(multi_ok ? 8 : (1 << 30)));
+           (int32_t)(multi_ok ? 8 : (1 << 30)), (int32_t)64);
   r.launch("EpGather", (uint32_t)rows, (const unsigned char *)Recv, (const int32_t *)Sorted, (const int32_t *)Counts, XQs, SQs, (int32_t)H,
            (int32_t)cap, slot_d);
   const void *gu_tc = multi_ok ? GroupsGUL : GroupsGU, *d_tc = multi_ok ? GroupsDL : GroupsD;

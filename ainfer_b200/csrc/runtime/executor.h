@@ -91,7 +91,7 @@ struct Session {
   int argmax_parts = 0;
   Prefill *prefill = nullptr;   // created on the first ainfer_session_prefill
   // expert parallelism of the prefill's MoE block (ainfer_session_prefill_ep): world 1 = none
-  int pf_rank = 0, pf_world = 1;
+  int pf_rank = 0, pf_world = 1, pf_rows = 0;   // pf_rows: rows per pass (0: the default)
   unsigned char pf_id[128] = {0};
   // device sampler scratch (created on first use): probabilities, marks, seen ids, {rng state, token}
   double *samp_work = nullptr; unsigned char *samp_mark = nullptr; int32_t *samp_seen = nullptr; uint64_t *samp_io = nullptr;

@@ -133,8 +133,9 @@ struct Launcher {   // immediate launches, or appended to recorded lists; argume
       return;
     }
     const uint32_t tiles = (uint32_t)((N + 127) / 128);
-    launch("Int4GemmA8Tc", std::min<uint32_t>(tiles, 2u * (uint32_t)s->sm_count), (const uint8_t *)t.data, (const uint16_t *)t.scales, XQ, SQ, Y,
-           (int32_t)N, (int32_t)K, (int32_t)rows, (int32_t)N);
+    for (int r0 = 0; r0 < rows; r0 += 64)   // the tensor-core kernel takes 64 rows a launch
+      launch("Int4GemmA8Tc", std::min<uint32_t>(tiles, 2u * (uint32_t)s->sm_count), (const uint8_t *)t.data, (const uint16_t *)t.scales,
+             XQ + (size_t)r0 * K, SQ + (size_t)r0 * G, Y + (size_t)r0 * N, (int32_t)N, (int32_t)K, (int32_t)std::min(64, rows - r0), (int32_t)N);
   }
 };
 

@@ -1,6 +1,6 @@
 // Problem lists that cover the rows of one row-batched GEMM in slabs of eight rows, for
 // Int4GemvA8MultiGrouped (the dp4a kernel that streams a tile of weights once for up to eight
-// rows). With 9..64 rows the tensor-core GEMM (Int4GemmA8Tc) spends about 2 us per group of 128
+// rows). With 9 rows or more the tensor-core GEMM (Int4GemmA8Tc, at most 64 rows a launch) spends about 2 us per group of 128
 // input columns whatever the number of its output rows, so a matrix of few output rows is one or a
 // few tiles of pure latency (35 us at K = 2048); the slabs re-read such a matrix from L2 once per
 // eight rows and finish in a fraction of that (measured at 64 rows: 14 us against 35 us for 32 or
@@ -29,7 +29,7 @@ struct RowSlabCache {
 // True when a GEMM of `rows` rows over this matrix should take the slabs.
 inline bool row_slabs_pay(int N, int K, int rows) {
   const int G = K / 128;
-  return rows > 8 && rows <= 64 && N <= 4096 && G <= 256 && 256 % G == 0;
+  return rows > 8 && N <= 4096 && G <= 256 && 256 % G == 0;
 }
 
 // The list for (matrix, rows), built on first use (two small synchronous uploads); the device

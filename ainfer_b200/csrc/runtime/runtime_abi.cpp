@@ -162,12 +162,22 @@ int ainfer_session_prefill(ainfer_session_t h, const int *tokens, int n, int sta
   if (!h || (!tokens && n > 0)) return set_err(2, "usage: null argument");
   Session *s = h->s;
   if (!s->prefill) {
-    // the expert-parallel block takes at most 64 rows over all ranks
-    int r = prefill_create(s, 64 / s->pf_world, false, &s->prefill, s->pf_rank, s->pf_world, s->pf_id);
+    // rows per pass: the planner of the expert-parallel block takes 2048 (row, expert) items over all ranks
+    const int topk = s->m->cfg.top_k > 0 ? s->m->cfg.top_k : 1;
+    int rows = s->pf_rows > 0 ? s->pf_rows : (s->pf_world == 1 ? 192 : 64 / s->pf_world);
+    rows = std::max(1, std::min(rows, 2048 / (topk * s->pf_world)));
+    int r = prefill_create(s, rows, false, &s->prefill, s->pf_rank, s->pf_world, s->pf_id);
     if (r) return set_err(r, s->err);
   }
   int r = prefill_run(s->prefill, tokens, n, start_pos, nullptr);
   return set_err(r, s->err);
+}
+int ainfer_session_prefill_rows(ainfer_session_t h, int rows) {
+  if (!h || rows < 1) return set_err(2, "usage: a session and at least one row");
+  Session *s = h->s;
+  if (s->prefill) { prefill_destroy(s->prefill); s->prefill = nullptr; }
+  s->pf_rows = rows;
+  return 0;
 }
 int ainfer_session_prefill_ep(ainfer_session_t h, const void *id128, int rank, int world) {
   if (!h) return set_err(2, "usage: null argument");

@@ -44,6 +44,7 @@ SIGNATURES = {
     "ainfer_session_step": (_i, [_vp, _i, _i, C.POINTER(_i)]),
     "ainfer_session_prefill": (_i, [_vp, C.POINTER(_i), _i, _i]),
     "ainfer_session_prefill_ep": (_i, [_vp, C.c_char_p, _i, _i]),
+    "ainfer_session_prefill_rows": (_i, [_vp, _i]),
     "ainfer_session_generate": (_i, [_vp, C.POINTER(_i), _i, _i, _i, C.POINTER(_i), C.POINTER(C.c_float)]),
     "ainfer_session_logits": (_i, [_vp, _vp]),
     "ainfer_session_sample": (_i, [_vp, C.POINTER(SampleParams), _vp, _i, C.POINTER(_u64), C.POINTER(_i)]),
@@ -212,9 +213,13 @@ class Session:
         return tok.value, state.value
 
     def prefill(self, tokens, start_pos=0):
-        """Advances the state over the tokens in chunks of up to 64 rows (no logits)."""
+        """Advances the state over the tokens in passes of up to 192 rows (no logits)."""
         t = np.ascontiguousarray(tokens, np.int32)
         _check(load().ainfer_session_prefill(self.h, t.ctypes.data_as(C.POINTER(C.c_int)), len(t), int(start_pos)))
+
+    def prefill_rows(self, rows):
+        """Rows per pass of the next prefill (default 192 on one rank, 64 / world with expert parallelism)."""
+        _check(load().ainfer_session_prefill_rows(self.h, int(rows)))
 
     def prefill_ep(self, rank, world, nccl_id=None):
         """Expert parallelism for this session's prefill: every rank prefills its own sequence of the

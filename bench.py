@@ -631,8 +631,8 @@ def run_ours(args):
         "cpu_baseline": cpu, "parity": parity, "ep": ep_line, "batch_decode": batch_line, "mtp": mtp_line,
         "prefill_ep": prefill_ep_line,
         "prefill": None if args.loop_prompt else {"prompt_tokens": P - 1, "seconds": t_prompt_only, "tokens_per_s": (P - 1) / max(t_prompt_only, 1e-9),
-                                                  "how": "chunked prefill, 64 rows per pass, one sequence (wall clock around the call, this rank)"},
-        "timing": {"model_fill_s": t_load, "prompt_s": t_prompt, "prompt_by": "token-by-token decode" if args.loop_prompt else "chunked prefill (64 rows per pass)", "timed_wall_s": t_wall, "first_tokens": [int(t) for t in toks0[:8]]},
+                                                  "how": "chunked prefill, up to 192 rows per pass, one sequence (wall clock around the call, this rank)"},
+        "timing": {"model_fill_s": t_load, "prompt_s": t_prompt, "prompt_by": "token-by-token decode" if args.loop_prompt else "chunked prefill (up to 192 rows per pass)", "timed_wall_s": t_wall, "first_tokens": [int(t) for t in toks0[:8]]},
     }
     print(json.dumps(line))
     sess.close(); model.close(); dev.close()

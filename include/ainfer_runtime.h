@@ -95,10 +95,13 @@ int ainfer_session_step(ainfer_session_t s, int token, int pos, int *out_token);
 int ainfer_session_generate(ainfer_session_t s, const int *prompt, int P, int G, int start_pos,
                             int *out_tokens, float *gen_ms);
 /* Chunked prefill: advances the session's state (DeltaNet state, conv history, INT8 KV cache) over
- * n tokens at positions start_pos.. in chunks of up to 64 rows, without logits (chunk orchestration
+ * n tokens at positions start_pos.. in passes of up to 192 rows, without logits (chunk orchestration
  * of tools/cmdlist/chunklayer_replay.cpp:366-443). The state afterwards is bit-identical to n calls
  * of ainfer_session_step; follow with ainfer_session_generate(s, &last_prompt_id, 1, G, start_pos + n, ...). */
 int ainfer_session_prefill(ainfer_session_t s, const int *tokens, int n, int start_pos);
+/* Rows per pass of the next prefill object (default 192 on one rank, 64 / world with expert
+ * parallelism; 1 <= rows, rows x world x top-k <= 2048). Drops the current prefill object. */
+int ainfer_session_prefill_rows(ainfer_session_t s, int rows);
 /* Expert parallelism for this session's prefill (config "prefill ... at 8 GPUs with expert
  * parallelism"): every rank prefills its OWN sequence, the MoE block of each pass exchanges rows
  * with the ranks that hold the routed experts (512 / world experts per rank, the all-to-all of
@@ -142,7 +145,8 @@ typedef struct ainfer_ep_s *ainfer_ep_t;
 enum { AINFER_EP_ROUTER_BIAS = 1 /* add the "router_bias" buffer to the routed logits (load generators) */ };
 /* 128 bytes of a fresh NCCL id: one rank calls it, the caller distributes the bytes. */
 int ainfer_ep_unique_id(void *out128);
-/* id128 may be NULL when world == 1 (no NCCL is loaded then). batch <= 64, batch % world == 0. */
+/* id128 may be NULL when world == 1 (no NCCL is loaded then). batch % world == 0, batch x top-k <= 2048
+ * (an expert that receives more than 64 rows is computed as several 64-row problems). */
 int ainfer_ep_create(ainfer_model_t m, const void *id128, int rank, int world, int batch, int flags, ainfer_ep_t *out);
 int ainfer_ep_destroy(ainfer_ep_t ep);
 /* Device buffers: "res" [n][H] f32 input rows of this rank, "x" [n][H] f32 output, "sel_idx"

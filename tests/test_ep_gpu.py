@@ -66,7 +66,7 @@ def test_usage_errors():
     from ainfer_b200 import cuda_abi, runtime
     dev = cuda_abi.Device(0)
     model = runtime.Model(dev, "synth:tiny:seed=0")
-    for kw in (dict(batch=3, world=2), dict(batch=130), dict(batch=4, world=2, rank=0)):   # ragged split, too many rows, no id
+    for kw in (dict(batch=3, world=2), dict(batch=4096), dict(batch=4, world=2, rank=0)):   # ragged split, too many (row, expert) items, no id
         with pytest.raises(Exception) as e:
             runtime.EpMoe(model, **kw)
         assert "usage" in str(e.value)

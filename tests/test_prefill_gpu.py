@@ -1,4 +1,4 @@
-"""Chunked prefill (ainfer_session_prefill: up to 64 prompt rows per pass through row-batched
+"""Chunked prefill (ainfer_session_prefill: up to 192 prompt rows per pass through row-batched
 kernels: tensor-core GEMMs, DeltaNet chunk kernels, per-row attention, the batched MoE block)
 against token-by-token decoding of the same prompt: the tokens generated afterwards and the whole
 session state (DeltaNet state, conv history, INT8 KV cache and its scales) must be bit-identical."""
@@ -19,7 +19,8 @@ def dev():
 
 
 @pytest.mark.parametrize("preset,P,splits,flags", [("tiny", 150, [149], 0), ("mini", 131, [64, 1, 65], 0),
-                                                   ("mini", 70, [69], 16), ("small", 100, [99], 16)])
+                                                   ("mini", 70, [69], 16), ("small", 100, [99], 16),
+                                                   ("mini", 461, [460], 0), ("small", 300, [299], 16)])   # passes of 192 rows and a ragged last one
 def test_prefill_equals_token_by_token_decode(dev, preset, P, splits, flags):
     from ainfer_b200 import runtime
     model = runtime.Model(dev, f"synth:{preset}:seed=4")
