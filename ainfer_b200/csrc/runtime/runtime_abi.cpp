@@ -164,8 +164,9 @@ int ainfer_session_prefill(ainfer_session_t h, const int *tokens, int n, int sta
   if (!s->prefill) {
     // rows per pass: the planner of the expert-parallel block takes 2048 (row, expert) items over all ranks
     const int topk = s->m->cfg.top_k > 0 ? s->m->cfg.top_k : 1;
-    int rows = s->pf_rows > 0 ? s->pf_rows : (s->pf_world == 1 ? 192 : 64 / s->pf_world);
-    rows = std::max(1, std::min(rows, 2048 / (topk * s->pf_world)));
+    const int most = std::max(1, 2048 / (topk * s->pf_world));   // rows a rank may bring to a pass
+    int rows = s->pf_rows > 0 ? s->pf_rows : std::min(192, most >= 8 ? most / 8 * 8 : most);
+    rows = std::max(1, std::min(rows, most));
     int r = prefill_create(s, rows, false, &s->prefill, s->pf_rank, s->pf_world, s->pf_id);
     if (r) return set_err(r, s->err);
   }

@@ -218,12 +218,12 @@ class Session:
         _check(load().ainfer_session_prefill(self.h, t.ctypes.data_as(C.POINTER(C.c_int)), len(t), int(start_pos)))
 
     def prefill_rows(self, rows):
-        """Rows per pass of the next prefill (default 192 on one rank, 64 / world with expert parallelism)."""
+        """Rows per pass of the next prefill (rows x world x top-k <= 2048; default the largest multiple of 8 within that, at most 192)."""
         _check(load().ainfer_session_prefill_rows(self.h, int(rows)))
 
     def prefill_ep(self, rank, world, nccl_id=None):
         """Expert parallelism for this session's prefill: every rank prefills its own sequence of the
-        same length, passes of 64 / world rows; nccl_id = ep_unique_id() of one rank."""
+        same length, passes of up to 2048 / (top-k x world) rows; nccl_id = ep_unique_id() of one rank."""
         _check(load().ainfer_session_prefill_ep(self.h, nccl_id, int(rank), int(world)))
 
     def mtp_draft(self, next_token, pos, from_trunk=True):

@@ -438,7 +438,7 @@ def run_prefill_ep(args, dev, model, rank, world, dist):
         sess = runtime.Session(model, n_tok + 16)
         sess.prefill_ep(rank, world, nid)
         prompt = prompt_ids(model.config["vocab"], n_tok, seed=100 + rank)
-        sess.prefill(prompt[:2 * (64 // world)])     # creates the row buffers and the communicator, records the MoE lists
+        sess.prefill(prompt[:64])     # creates the row buffers and the communicator, records the MoE lists
         sess.reset()
         dev.sync()
         dist.barrier()
@@ -452,9 +452,11 @@ def run_prefill_ep(args, dev, model, rank, world, dist):
     dist.all_reduce(tt, op=dist.ReduceOp.MAX)
     sec = float(tt[0])
     sess.close()
-    return {"workload": f"prefill of {n_tok} seeded tokens on each of {world} ranks (one sequence per rank), passes of {64 // world} rows, experts split over the ranks",
+    most = max(1, 2048 // (model.config["top_k"] * world))
+    rows_pp = min(192, most // 8 * 8 if most >= 8 else most)     # the runtime's default
+    return {"workload": f"prefill of {n_tok} seeded tokens on each of {world} ranks (one sequence per rank), passes of {rows_pp} rows, experts split over the ranks",
             "tokens_per_s": world * n_tok / sec, "seconds": sec, "prompt_tokens_per_rank": n_tok, "world": world,
-            "rows_per_pass": 64 // world, "scaling": "weak"}
+            "rows_per_pass": rows_pp, "scaling": "weak"}
 
 
 def run_ours(args):

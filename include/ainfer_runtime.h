@@ -99,14 +99,14 @@ int ainfer_session_generate(ainfer_session_t s, const int *prompt, int P, int G,
  * of tools/cmdlist/chunklayer_replay.cpp:366-443). The state afterwards is bit-identical to n calls
  * of ainfer_session_step; follow with ainfer_session_generate(s, &last_prompt_id, 1, G, start_pos + n, ...). */
 int ainfer_session_prefill(ainfer_session_t s, const int *tokens, int n, int start_pos);
-/* Rows per pass of the next prefill object (default 192 on one rank, 64 / world with expert
- * parallelism; 1 <= rows, rows x world x top-k <= 2048). Drops the current prefill object. */
+/* Rows per pass of the next prefill object (1 <= rows, rows x world x top-k <= 2048; default: the
+ * largest multiple of 8 within that bound, at most 192). Drops the current prefill object. */
 int ainfer_session_prefill_rows(ainfer_session_t s, int rows);
 /* Expert parallelism for this session's prefill (config "prefill ... at 8 GPUs with expert
  * parallelism"): every rank prefills its OWN sequence, the MoE block of each pass exchanges rows
  * with the ranks that hold the routed experts (512 / world experts per rank, the all-to-all of
  * ainfer_ep_*), everything else stays on the rank. id128: ainfer_ep_unique_id of one rank, handed
- * to all. Passes hold 64 / world rows, and the exchanges are collective: every rank must prefill
+ * to all. Passes hold up to 2048 / (top-k x world) rows of every rank, and the exchanges are collective: every rank must prefill
  * the same number of tokens in the same calls. Call before the first ainfer_session_prefill (a
  * later call drops the prefill object); world == 1 switches back. The state a rank ends with is
  * bit-identical to the one-GPU prefill of the same tokens. */
