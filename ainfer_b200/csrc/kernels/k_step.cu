@@ -145,6 +145,13 @@ __device__ __forceinline__ bool mbar_wait_b(uint32_t addr, uint32_t parity, int 
 
 // Optional stage clock (plan->stage_stamps non-null): block 0 appends (id << 48 | %globaltimer)
 // records, consumer thread 0 to the first half of the buffer, the producer thread to the second.
+// Consumer ids: 1 a grid barrier was passed, 2 a stage's prologue (norm / quantiser) is done, 3 its
+// GEMV and epilogues are done, 4 the recurrence's barrier was passed, 5 the experts are selected,
+// 6 their pointer records are fetched, 20-24 inside the attention stage (chunk staged, heads
+// prepared, scores, softmax, values). Producer ids: 10-12 the tiles of the first projections, the
+// output projection and the router are issued, 13 the selection arrived, 14 / 15 the gate/up and
+// the down tiles are issued. A record costs a few hundred nanoseconds, so a stamped step is a few
+// per cent slower than the product's.
 static __device__ __noinline__ void stamp(int id) {
   if (PL.stage_stamps && blockIdx.x == 0 && (threadIdx.x == 0 || threadIdx.x == kCons)) {
     const int who = threadIdx.x == 0 ? 0 : 1, half = PL.stage_stamp_cap / 2;
